@@ -1,0 +1,126 @@
+// C ABI of the sm_100a kernel library (liboa_kernels.so).
+//
+// Every entry point takes raw device pointers and a CUDA stream (as void*), launches
+// asynchronously on that stream and returns an OA_* code (0 = launched).  Nothing in
+// this library allocates device memory: callers hand in outputs and scratch buffers.
+// dtype codes follow the reference's OaScalarType values that appear in checkpoint
+// files (Source/Public/Oa/Core/Type.gen.h:17-65): 0 = fp32, 1 = bf16.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { OA_OK = 0, OA_ERR_ARG = 1, OA_ERR_ALIGN = 2, OA_ERR_DRIVER = 3, OA_ERR_LAUNCH = 4, OA_ERR_UNSUPPORTED = 5,
+       OA_ERR_TOO_LARGE = 6 };
+enum { OA_F32 = 0, OA_BF16 = 1 };
+enum { OA_ACT_NONE = 0, OA_ACT_GELU = 1, OA_ACT_RELU = 2, OA_ACT_SILU = 3, OA_ACT_GELU_BWD = 4, OA_ACT_RELU_BWD = 5 };
+
+// unary ops: y = f(x; s0, s1)
+enum { OA_U_COPY = 0, OA_U_NEG, OA_U_ABS, OA_U_LOG, OA_U_EXP, OA_U_SQRT, OA_U_SIN, OA_U_COS, OA_U_RECIP, OA_U_SCALE,
+       OA_U_ADD_SCALAR, OA_U_POW, OA_U_CLAMP_MAX, OA_U_CLAMP_MIN, OA_U_RELU, OA_U_GELU, OA_U_SILU, OA_U_TANH,
+       OA_U_SIGMOID, OA_U_SOFTPLUS, OA_U_LEAKY_RELU, OA_U_ELU, OA_U_MISH, OA_U_SQUARE, OA_U_RSUB_SCALAR,
+       OA_U_SIGN, OA_U_COUNT };
+// binary ops: y = f(a, b).  The *_BWD ops take a = saved forward input (or output, see elementwise.cu), b = upstream grad.
+enum { OA_B_ADD = 0, OA_B_SUB, OA_B_MUL, OA_B_DIV, OA_B_MAX, OA_B_MIN, OA_B_EQ, OA_B_GE, OA_B_RELU_BWD, OA_B_GELU_BWD,
+       OA_B_SILU_BWD, OA_B_TANH_BWD, OA_B_SIGMOID_BWD, OA_B_SOFTPLUS_BWD, OA_B_LEAKY_RELU_BWD, OA_B_ELU_BWD,
+       OA_B_MISH_BWD, OA_B_ABS_BWD, OA_B_LOG_BWD, OA_B_SQRT_BWD, OA_B_RECIP_BWD, OA_B_SILU_MUL, OA_B_COUNT };
+// broadcast modes of the second operand of a binary op
+enum { OA_BC_NONE = 0, OA_BC_ROW = 1 /* b is [inner] repeated over rows */, OA_BC_COL = 2 /* b is [rows], one per row of `inner` */,
+       OA_BC_SCALAR = 3 };
+// row reductions
+enum { OA_R_SUM = 0, OA_R_MEAN = 1, OA_R_MAX = 2, OA_R_ARGMAX = 3 };
+
+// ---- GEMM (gemm_tcgen05.cu, gemm_f32.cu)
+int oa_gemm_plan_splits(int M, int N, int K, int bn, int sms);
+size_t oa_gemm_workspace_bytes(int M, int N, int K);
+int oa_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
+                 int b_mn, const void* bias, const void* residual, int ldr, void* aux_out, const void* aux_in,
+                 int ldaux, int act, int out_f32, int accumulate, float alpha, void* workspace,
+                 size_t workspace_bytes, int force_bn, int* status, void* stream);
+// fp32 SIMT GEMM with arbitrary element strides and a batch dimension:
+//   C[b][m,n] = act(alpha * sum_k A[b][m*sam + k*sak] * B[b][n*sbn + k*sbk] + bias[n]) (+ C if accumulate)
+int oa_gemm_f32(const float* A, const float* B, float* C, int M, int N, int K, long long sam, long long sak,
+                long long sbn, long long sbk, int ldc, int batch, long long batch_a, long long batch_b,
+                long long batch_c, const float* bias, int act, int accumulate, float alpha, void* stream);
+
+// ---- elementwise (elementwise.cu)
+int oa_unary(int op, int dtype, const void* x, void* y, long long n, float s0, float s1, void* stream);
+int oa_binary(int op, int dtype, const void* a, const void* b, void* y, long long n, long long inner_b, int bcast_mode,
+              void* stream);
+int oa_cast(int src_dtype, int dst_dtype, const void* x, void* y, long long n, void* stream);
+int oa_fill(int dtype, void* y, long long n, float value, void* stream);
+int oa_swiglu_fwd(int dtype, const void* gate_up, void* out, long long rows, int F, void* stream);
+int oa_swiglu_bwd(int dtype, const void* gate_up, const void* dout, void* dgate_up, long long rows, int F, void* stream);
+int oa_rope(int dtype, void* x, long long rows, int row_stride, int n_heads, int head_dim, int seq_len, int pos_offset,
+            float theta, int backward, void* stream);
+int oa_embedding_fwd(int dtype, const void* table, const int* ids, void* out, long long n_ids, int dim, int vocab,
+                     const void* pos_table, int seq_len, void* stream);
+int oa_embedding_bwd(int dtype, const void* dout, const int* ids, float* dtable_f32, long long n_ids, int dim,
+                     int vocab, void* stream);
+int oa_col_sum(int dtype, const void* x, void* out, int out_dtype, long long rows, int cols, float* scratch,
+               int accumulate, void* stream);
+int oa_bias_add(int dtype, void* x, const void* bias, long long rows, int cols, void* stream);
+int oa_row_reduce(int op, int dtype, const void* x, void* y, long long rows, int cols, void* stream);
+int oa_softmax(int dtype, const void* x, void* y, long long rows, int cols, int log_mode, float scale,
+               const void* mask, void* stream);
+int oa_softmax_bwd(int dtype, const void* y, const void* dy, void* dx, long long rows, int cols, int log_mode,
+                   float scale, void* stream);
+int oa_philox(int dtype, void* y, long long n, unsigned long long seed, unsigned long long offset, int normal,
+              float a, float b, void* stream);
+int oa_dropout(int dtype, const void* x, void* y, long long n, float p, unsigned long long seed,
+               unsigned long long offset, void* stream);
+int oa_copy_strided(int dtype, const void* x, void* y, int rank, const long long* shape, const long long* src_strides,
+                    void* stream);
+
+// ---- norms (norm.cu)
+size_t oa_norm_bwd_scratch_bytes(long long rows, int cols);
+int oa_rmsnorm_fwd(int dtype, const void* x, const void* w, void* y, float* rstd, long long rows, int cols, float eps,
+                   const void* residual_in, void* residual_out, void* stream);
+int oa_rmsnorm_bwd(int dtype, const void* x, const void* w, const void* dy, const float* rstd, void* dx, void* dw,
+                   int dw_dtype, long long rows, int cols, const void* dres, float* scratch, int accumulate_dw,
+                   void* stream);
+int oa_layernorm_fwd(int dtype, const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                     long long rows, int cols, float eps, void* stream);
+int oa_layernorm_bwd(int dtype, const void* x, const void* w, const void* dy, const float* mean, const float* rstd,
+                     void* dx, void* dw, void* db, int dw_dtype, long long rows, int cols, float* scratch,
+                     int accumulate_dw, void* stream);
+
+// ---- loss (xent.cu)
+int oa_xent_fwd_bwd(int dtype, const void* logits, const int* targets, float* row_loss, void* dlogits, long long rows,
+                    int vocab, int ld, float grad_scale, int ignore_index, void* stream);
+int oa_mean_f32(const float* x, float* out, long long n, float scale, void* stream);
+
+// ---- optimizers (optim.cu)
+// state = device float[8] {step, lr, beta1, beta2, eps, weight_decay, grad_scale, unused}; the step lives on the
+// device so that a captured graph can be replayed (same idea as Source/Public/Oa/Ml/FnOptim.h:25-53).
+int oa_optim_advance(float* state, void* stream);
+int oa_adamw(int param_dtype, int grad_dtype, void* param, const void* grad, float* master, float* m, float* v,
+             long long n, const float* state, int decoupled, const float* inv_clip, void* stream);
+int oa_sgd(int param_dtype, int grad_dtype, void* param, const void* grad, float* master, float* mom, long long n,
+           float lr, float momentum, float weight_decay, void* stream);
+int oa_sumsq(int dtype, const void* x, long long n, float* partial, float* out, int accumulate, void* stream);
+int oa_clip_coef(const float* sumsq, float max_norm, float* coef, void* stream);
+int oa_scale_inplace(int dtype, void* x, long long n, const float* coef, void* stream);
+
+// ---- attention (flash_attn.cu)
+size_t oa_flash_bwd_scratch_bytes(int batch, int heads, int seq, int head_dim);
+int oa_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int batch, int heads, int seq,
+                 int head_dim, long long q_row_stride, long long kv_row_stride, long long o_row_stride, float scale,
+                 int causal, int* status, void* stream);
+int oa_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout, const float* lse,
+                 void* dq, void* dk, void* dv, int batch, int heads, int seq, int head_dim, long long q_row_stride,
+                 long long kv_row_stride, long long o_row_stride, long long dq_row_stride, long long dkv_row_stride,
+                 float scale, int causal, float* scratch, int* status, void* stream);
+int oa_attn_f32(const float* q, const float* k, const float* v, float* o, float* lse, int batch, int heads, int seq,
+                int head_dim, long long row_stride, long long o_row_stride, float scale, int causal, void* stream);
+int oa_attn_f32_bwd(const float* q, const float* k, const float* v, const float* o, const float* dout,
+                    const float* lse, float* dq, float* dk, float* dv, int batch, int heads, int seq, int head_dim,
+                    long long row_stride, long long o_row_stride, long long d_row_stride, float scale, int causal,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif

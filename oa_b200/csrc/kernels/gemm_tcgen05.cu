@@ -1,0 +1,549 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   D[M,N] = epilogue( alpha * sum_k A(m,k) * B(n,k) )
+//
+// Operands are bf16, accumulation is fp32 in TMEM.  Each operand may be stored
+// "K-major" (the reduction index is the contiguous one: A is [M,K], B is [N,K],
+// which is the reference's MatMulNt / Linear convention, Core/FnMatrix/Blas/FnMatrixBlas.gen.h:7)
+// or "MN-major" (stored as [K,M] / [K,N]), which is what the data-gradient
+// (dX = dY * W) and weight-gradient (dW = dY^T * X) products need, so no
+// transposed copies are ever made.
+//
+// Structure: persistent kernel, one CTA per SM, 192 threads.
+//   warp 0 (one lane)  TMA producer: cp.async.bulk.tensor tiles into a 4/6 stage smem ring (128B swizzle)
+//   warp 1 (one lane)  tcgen05.mma issuer: 128 x BN x 16 MMAs into one of two TMEM accumulators
+//   warps 2..5         epilogue: tcgen05.ld the finished accumulator, fuse bias / GELU / residual /
+//                      GELU-backward / accumulate, store bf16 or fp32
+// The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
+// Split-K (for weight gradients whose output has too few tiles to fill 148 SMs) writes fp32
+// partials to a workspace that a small second kernel reduces in a fixed order (deterministic).
+//
+// Replaces the reference's GemmTiled / GemmCmSgBf16 / GemmCmWgBf16 family
+// (Source/Private/Oa/Core/Shader/Compute/Blas/Gemm/*.slang) with one kernel family.
+#include "common.cuh"
+#include "api.h"
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+#include <cstdio>
+
+namespace oa {
+
+struct GemmParams {
+  int M, N, K;
+  void* out;
+  int ldc;
+  int out_f32;
+  const __nv_bfloat16* bias;       // [N] or null
+  const __nv_bfloat16* residual;   // [M, ldr] or null
+  int ldr;
+  __nv_bfloat16* aux_out;          // pre-activation copy [M, ldaux] or null
+  const __nv_bfloat16* aux_in;     // pre-activation input for GELU backward [M, ldaux] or null
+  int ldaux;
+  int act;                         // OA_ACT_*
+  int accumulate;                  // out += result
+  float alpha;
+  int splits;                      // split-K factor; >1 => write fp32 partials to workspace
+  float* workspace;                // [splits, M, N] fp32
+  int group_m;
+  int* status;
+};
+
+constexpr int BM = 128;
+constexpr int BK = 64;       // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
+  int per_group = group_m * n_tiles;
+  int g = t / per_group;
+  int first_m = g * group_m;
+  int gsz = min(m_tiles - first_m, group_m);
+  int r = t - g * per_group;
+  mi = first_m + (r % gsz);
+  ni = r / gsz;
+}
+
+template <int BN>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int split) {
+  if (row >= p.M || col0 >= p.N) return;
+  // N is a multiple of 8, so every 8-column group is either fully inside or fully outside.
+  int ncols = min(32, p.N - col0);
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+
+  if (p.splits > 1) {
+    float* w = p.workspace + ((size_t)split * p.M + row) * p.N + col0;
+#pragma unroll
+    for (int g = 0; g < 8; ++g)
+      if (g * 4 < ncols) *reinterpret_cast<float4*>(w + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+    return;
+  }
+  if (p.bias) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+        v[g * 8 + 0] += f0.x; v[g * 8 + 1] += f0.y; v[g * 8 + 2] += f1.x; v[g * 8 + 3] += f1.y;
+        v[g * 8 + 4] += f2.x; v[g * 8 + 5] += f2.y; v[g * 8 + 6] += f3.x; v[g * 8 + 7] += f3.y;
+      }
+    }
+  }
+  if (p.aux_out) {
+    __nv_bfloat16* a = p.aux_out + (size_t)row * p.ldaux + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (g * 8 < ncols)
+        *reinterpret_cast<uint4*>(a + g * 8) =
+            make_uint4(pack_bf16x2(v[g * 8], v[g * 8 + 1]), pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
+                       pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]));
+  }
+  if (p.act == OA_ACT_GELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+  } else if (p.act == OA_ACT_RELU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+  } else if (p.act == OA_ACT_SILU) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+  }
+  if (p.aux_in) {  // multiply by d(act)/dz of the saved pre-activation (backward of a fused Linear+act)
+    const __nv_bfloat16* a = p.aux_in + (size_t)row * p.ldaux + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        uint4 b = *reinterpret_cast<const uint4*>(a + g * 8);
+        uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 z = unpack_bf16x2(w[j]);
+          if (p.act == OA_ACT_GELU_BWD) {
+            v[g * 8 + 2 * j] *= gelu_tanh_grad(z.x);
+            v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(z.y);
+          } else {  // OA_ACT_RELU_BWD
+            v[g * 8 + 2 * j] = z.x > 0.f ? v[g * 8 + 2 * j] : 0.f;
+            v[g * 8 + 2 * j + 1] = z.y > 0.f ? v[g * 8 + 2 * j + 1] : 0.f;
+          }
+        }
+      }
+    }
+  }
+  if (p.residual) {
+    const __nv_bfloat16* a = p.residual + (size_t)row * p.ldr + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        uint4 b = *reinterpret_cast<const uint4*>(a + g * 8);
+        float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+        v[g * 8 + 0] += f0.x; v[g * 8 + 1] += f0.y; v[g * 8 + 2] += f1.x; v[g * 8 + 3] += f1.y;
+        v[g * 8 + 4] += f2.x; v[g * 8 + 5] += f2.y; v[g * 8 + 6] += f3.x; v[g * 8 + 7] += f3.y;
+      }
+    }
+  }
+  if (p.out_f32) {
+    float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldc + col0;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (g * 4 < ncols) {
+        float4 x = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+        if (p.accumulate) {
+          float4 c = *reinterpret_cast<float4*>(o + g * 4);
+          x.x += c.x; x.y += c.y; x.z += c.z; x.w += c.w;
+        }
+        *reinterpret_cast<float4*>(o + g * 4) = x;
+      }
+    }
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldc + col0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      if (g * 8 < ncols) {
+        if (p.accumulate) {
+          uint4 b = *reinterpret_cast<uint4*>(o + g * 8);
+          float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+          v[g * 8 + 0] += f0.x; v[g * 8 + 1] += f0.y; v[g * 8 + 2] += f1.x; v[g * 8 + 3] += f1.y;
+          v[g * 8 + 4] += f2.x; v[g * 8 + 5] += f2.y; v[g * 8 + 6] += f3.x; v[g * 8 + 7] += f3.y;
+        }
+        *reinterpret_cast<uint4*>(o + g * 8) =
+            make_uint4(pack_bf16x2(v[g * 8], v[g * 8 + 1]), pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
+                       pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]));
+      }
+    }
+  }
+}
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * Cfg::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int m_tiles = (p.M + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int mn_tiles = m_tiles * n_tiles;
+  const int total_tiles = mn_tiles * p.splits;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_per_split = (kb_total + p.splits - 1) / p.splits;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);  // one arrive per epilogue warp
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<Cfg::TMEM_COLS>(tmem_slot);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int split = t / mn_tiles;
+        int mi, ni;
+        tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.group_m, mi, ni);
+        int kb0 = split * kb_per_split;
+        int kb1 = min(kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) {
+            report_error(p.status, OA_KERR_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          uint8_t* a = sA + stage * Cfg::A_BYTES;
+          uint8_t* b = sB + stage * Cfg::B_BYTES;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a + j * (64 * BK * 2), &tmA, &full[stage], mi * BM + j * 64, kb * BK);
+          } else {
+            tma_load_2d(a, &tmA, &full[stage], kb * BK, mi * BM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b + j * (64 * BK * 2), &tmB, &full[stage], ni * BN + j * 64, kb * BK);
+          } else {
+            tma_load_2d(b, &tmB, &full[stage], kb * BK, ni * BN);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      // K-major: 8-row groups are 1024 B apart; one UMMA_K step is 32 B inside the swizzled row.
+      // MN-major: 64-element column groups are one [64 x BK] box (BK*128 B) apart, 8-k groups 1024 B apart;
+      //           one UMMA_K step is 16 k-rows of 128 B.
+      constexpr uint32_t a_lbo = A_MN ? BK * 128 : 16, a_sbo = 1024, a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      constexpr uint32_t b_lbo = B_MN ? BK * 128 : 16, b_sbo = 1024, b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int split = t / mn_tiles;
+        int kb0 = split * kb_per_split;
+        int kb1 = min(kb_total, kb0 + kb_per_split);
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) {
+          report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) {
+            report_error(p.status, OA_KERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * Cfg::A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * Cfg::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t da = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, a_sbo);
+            uint64_t db = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, b_sbo);
+            umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue warps (2..5); TMEM lane quadrant = warp % 4
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      int split = t / mn_tiles;
+      int mi, ni;
+      tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.group_m, mi, ni);
+      int kb0 = split * kb_per_split;
+      int kb1 = min(kb_total, kb0 + kb_per_split);
+      bool ok = mbar_wait(&tfull[acc], acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL);
+        break;
+      }
+      tc_fence_after();
+      const int row = mi * BM + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
+      const bool empty_split = (kb1 <= kb0);  // nothing accumulated: treat as zeros
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (c == BN / 32 - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+        if (empty_split) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0;
+        }
+        epilogue_chunk<BN>(p, r, row, ni * BN + c * 32, split);
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<Cfg::TMEM_COLS>(tmem_base);
+  }
+}
+
+// Fixed-order reduction of split-K partials (deterministic), then the plain store / accumulate epilogue.
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, void* out, int ldc,
+                                     int out_f32, int accumulate) {
+  size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t total4 = (size_t)M * N / 4;
+  if (i4 >= total4) return;
+  size_t e = i4 * 4;
+  int row = (int)(e / N), col = (int)(e % N);
+  float4 s = *reinterpret_cast<const float4*>(ws + e);
+  for (int k = 1; k < splits; ++k) {
+    float4 x = *reinterpret_cast<const float4*>(ws + (size_t)k * M * N + e);
+    s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+  }
+  if (out_f32) {
+    float* o = reinterpret_cast<float*>(out) + (size_t)row * ldc + col;
+    if (accumulate) {
+      float4 c = *reinterpret_cast<float4*>(o);
+      s.x += c.x; s.y += c.y; s.z += c.z; s.w += c.w;
+    }
+    *reinterpret_cast<float4*>(o) = s;
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldc + col;
+    if (accumulate) {
+      uint2 c = *reinterpret_cast<uint2*>(o);
+      float2 a = unpack_bf16x2(c.x), b = unpack_bf16x2(c.y);
+      s.x += a.x; s.y += a.y; s.z += b.x; s.w += b.y;
+    }
+    *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16x2(s.x, s.y), pack_bf16x2(s.z, s.w));
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static PFN_encodeTiled get_encode() {
+  static PFN_encodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_encodeTiled>(f);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: inner (contiguous) extent `inner`, outer extent `outer`, row pitch `ld` elements.
+int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return OA_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15)) return OA_ERR_ALIGN;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OA_OK : OA_ERR_DRIVER;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int A_MN, int B_MN>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::SMEM_BYTES) != cudaSuccess)
+      return OA_ERR_LAUNCH;
+    attr_set = true;
+  }
+  kfn<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+}
+
+}  // namespace oa
+
+using namespace oa;
+
+extern "C" int oa_gemm_plan_splits(int M, int N, int K, int bn, int sms) {
+  // Choose a split-K factor so that the tile count fills the machine; only worth it for long K.
+  int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+  int kb = (K + BK - 1) / BK;
+  if (tiles >= sms || kb < 16) return 1;
+  int best = 1;
+  double best_eff = 0;
+  for (int s = 1; s <= 16 && kb / s >= 8; ++s) {
+    int t = tiles * s;
+    int waves = (t + sms - 1) / sms;
+    double eff = (double)t / (waves * sms);
+    if (eff > best_eff + 0.04) { best_eff = eff; best = s; }
+  }
+  return best;
+}
+
+extern "C" size_t oa_gemm_workspace_bytes(int M, int N, int K) {
+  int bn = (N >= 256) ? 256 : 128;
+  int s = oa_gemm_plan_splits(M, N, K, bn, 148);
+  int s2 = oa_gemm_plan_splits(M, N, K, 128, 148);
+  if (s2 > s) s = s2;
+  return s > 1 ? (size_t)s * M * N * sizeof(float) : 0;
+}
+
+extern "C" int oa_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc,
+                            int a_mn, int b_mn, const void* bias, const void* residual, int ldr, void* aux_out,
+                            const void* aux_in, int ldaux, int act, int out_f32, int accumulate, float alpha,
+                            void* workspace, size_t workspace_bytes, int force_bn, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return OA_ERR_ARG;
+  if ((N & 7) || (K & 7) || (a_mn && (M & 7))) return OA_ERR_ALIGN;
+  if ((ldc & (out_f32 ? 3 : 7)) || (residual && (ldr & 7)) || ((aux_out || aux_in) && (ldaux & 7))) return OA_ERR_ALIGN;
+  int bn = force_bn ? force_bn : ((N >= 256) ? 256 : 128);
+  int sms = num_sms();
+  if (!force_bn && bn == 256) {
+    // Prefer the 128-wide tile when it fills the machine noticeably better.
+    int t256 = ((M + BM - 1) / BM) * ((N + 255) / 256), t128 = ((M + BM - 1) / BM) * ((N + 127) / 128);
+    double e256 = (double)t256 / (((t256 + sms - 1) / sms) * sms), e128 = (double)t128 / (((t128 + sms - 1) / sms) * sms);
+    if (t256 < sms && e128 > e256 + 0.15) bn = 128;
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual; p.ldr = ldr;
+  p.aux_out = (__nv_bfloat16*)aux_out; p.aux_in = (const __nv_bfloat16*)aux_in; p.ldaux = ldaux;
+  p.act = act; p.accumulate = accumulate; p.alpha = alpha;
+  p.status = status;
+  p.group_m = 16;
+  p.splits = 1;
+  p.workspace = (float*)workspace;
+  bool plain = !bias && !residual && !aux_out && !aux_in && act == OA_ACT_NONE;
+  if (workspace && plain && (N % 4 == 0)) {
+    int s = oa_gemm_plan_splits(M, N, K, bn, sms);
+    if (s > 1 && (size_t)s * M * N * sizeof(float) <= workspace_bytes) p.splits = s;
+  }
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn) rc = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
+  else      rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (rc) return rc;
+  if (b_mn) rc = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
+  else      rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bn);
+  if (rc) return rc;
+  int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * p.splits;
+  int grid = tiles < sms ? tiles : sms;
+  cudaStream_t st = (cudaStream_t)stream;
+  int sel = (bn == 256 ? 4 : 0) | (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  switch (sel) {
+    case 0: rc = launch_gemm<128, 0, 0>(ta, tb, p, grid, st); break;
+    case 1: rc = launch_gemm<128, 0, 1>(ta, tb, p, grid, st); break;
+    case 2: rc = launch_gemm<128, 1, 0>(ta, tb, p, grid, st); break;
+    case 3: rc = launch_gemm<128, 1, 1>(ta, tb, p, grid, st); break;
+    case 4: rc = launch_gemm<256, 0, 0>(ta, tb, p, grid, st); break;
+    case 5: rc = launch_gemm<256, 0, 1>(ta, tb, p, grid, st); break;
+    case 6: rc = launch_gemm<256, 1, 0>(ta, tb, p, grid, st); break;
+    default: rc = launch_gemm<256, 1, 1>(ta, tb, p, grid, st); break;
+  }
+  if (rc) return rc;
+  if (p.splits > 1) {
+    size_t total4 = (size_t)M * N / 4;
+    int threads = 256;
+    unsigned blocks = (unsigned)((total4 + threads - 1) / threads);
+    splitk_reduce_kernel<<<blocks, threads, 0, st>>>(p.workspace, p.splits, M, N, out, ldc, out_f32, accumulate);
+    if (cudaGetLastError() != cudaSuccess) return OA_ERR_LAUNCH;
+  }
+  return OA_OK;
+}
