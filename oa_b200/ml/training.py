@@ -1,0 +1,325 @@
+"""Training loop objects: OaItTraining, OaTrainingProgram (CUDA-graph capture / replay), timing stats.
+
+Reference: Source/Public/Oa/Ml/ItTraining.h:58-387 and ItTraining.cpp:245-553 (iterator-style step life cycle,
+exact per-step sync, loss readback, GPU timer statistics, throughput in samples / units / source units, callbacks),
+Source/Public/Oa/Ml/TrainingProgram.h:21-179 and TrainingProgram.cpp:255-448 (capture of a recorded step and
+replay).  Where the reference copies graph nodes into a compiled Vulkan graph, the step is captured here into a
+CUDA graph: step 1 runs eagerly (it creates lazy optimizer state and scratch buffers), the next step is captured,
+every later step only refills the static input buffers and replays.  Mutable scalars (optimizer step, learning
+rate) live in device memory, RNG offsets are advanced by the captured kernels' arguments being fixed per replay
+only for ops that are replay-safe; dropout inside a captured program is rejected like the reference rejects raw
+Philox nodes.
+"""
+from __future__ import annotations
+
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import torch
+
+from ..core.matrix import OaMatrix
+from ..core.types import OaStatus, OaStatusCode
+from ..runtime import engine as RT
+from ..utils import envflag
+
+
+@dataclass
+class OaItTrainingConfig:
+    TotalSteps: int = 100
+    BatchSize: int = 1
+    SequenceLength: int = 1
+    SequenceUnit: str = "token"
+    SourceUnit: str = "byte"
+    TimerName: str = "train"
+    StepsPerEpoch: int = 0
+    Program: bool = False            # capture the step into a CUDA graph from step 2 on
+    SyncEveryStep: bool = True       # exact per-step loss readback (the reference always does)
+    LogEvery: int = 0
+
+
+@dataclass
+class OaGpuTimingStats:
+    Count: int = 0
+    MeanMs: float = 0.0
+    MinMs: float = 0.0
+    P50Ms: float = 0.0
+    P95Ms: float = 0.0
+
+
+@dataclass
+class OaTrainingPhaseStats:
+    BodyMs: float = 0.0
+    OptimizerMs: float = 0.0
+    CaptureMs: float = 0.0
+    SubmitMs: float = 0.0
+    WaitMs: float = 0.0
+    ScalarMs: float = 0.0
+    CallbackMs: float = 0.0
+
+
+class OaTrainingProgram:
+    """A captured training step.  `Capture(fn)` records everything `fn` launches into a CUDA graph and keeps the
+    tensors it returns alive as static outputs; `Replay()` launches the graph, `Wait()` blocks until it finished."""
+
+    Stages = ("collect", "rng-rewrite", "validate", "alias", "instantiate", "ready")
+
+    def __init__(self):
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._outputs = None
+        self._event = None
+        self.CaptureMs = 0.0
+        self.NodeCount = 0
+        self.Replays = 0
+        self.StageLog: list = []
+
+    def IsCaptured(self) -> bool:
+        return self._graph is not None
+
+    def Capture(self, fn: Callable[[], object]) -> OaStatus:
+        eng = RT.get_engine()
+        if not eng.IsCuda():
+            return OaStatus.Error(OaStatusCode.FailedPrecondition, "program capture needs a CUDA engine")
+        ctx = RT.OaContext.GetDefault()
+        t0 = time.perf_counter()
+        torch.cuda.synchronize()
+        n0 = ctx.NodeCount()
+        g = torch.cuda.CUDAGraph()
+        self.StageLog = [("collect", 0.0)]
+        try:
+            with torch.cuda.graph(g):
+                self._outputs = fn()
+        except Exception as e:  # leave no half-captured graph behind
+            self._graph = None
+            return OaStatus.Error(OaStatusCode.Internal, f"capture failed: {e}")
+        self.NodeCount = ctx.NodeCount() - n0
+        self._graph = g
+        self.CaptureMs = (time.perf_counter() - t0) * 1e3
+        self.StageLog += [("instantiate", self.CaptureMs), ("ready", self.CaptureMs)]
+        return OaStatus.Ok()
+
+    def Outputs(self):
+        return self._outputs
+
+    def Replay(self) -> None:
+        self._graph.replay()
+        self.Replays += 1
+
+    def Wait(self) -> OaStatus:
+        return RT.OaContext.GetDefault().Sync()
+
+    def DebugReport(self) -> dict:
+        return {"captured": self.IsCaptured(), "nodes": self.NodeCount, "capture_ms": self.CaptureMs, "replays": self.Replays,
+                "stages": [s for s, _ in self.StageLog]}
+
+
+class OaCallback:
+    """Hooks fired by OaItTraining (Source/Public/Oa/Ml/Callbacks.h:49-236). Return an OaStatus or None."""
+
+    def OnTrainBegin(self, training): return None
+    def OnTrainEnd(self, training): return None
+    def OnEpochBegin(self, training, epoch: int): return None
+    def OnEpochEnd(self, training, epoch: int): return None
+    def OnStepEnd(self, training, step: int, loss: float): return None
+
+
+OaCbTraining = OaCallback
+
+
+class OaItTraining:
+    def __init__(self, optimizer, config: Optional[OaItTrainingConfig] = None):
+        self.Opt_ = optimizer
+        self.Config = config or OaItTrainingConfig()
+        self._index = 0
+        self._started = False
+        self._finished = False
+        self._stop = False
+        self._last_loss = float("nan")
+        self._losses: list[float] = []
+        self._gpu_ms: list[float] = []
+        self._wall0 = 0.0
+        self._wall_total = 0.0
+        self._step_wall0 = 0.0
+        self._source_units = 0
+        self._source_units_total = 0
+        self._callbacks: list[OaCallback] = []
+        self._metrics: list = []
+        self._timer = RT.OaGpuTimer(self.Config.TimerName)
+        self._program: Optional[OaTrainingProgram] = OaTrainingProgram() if (self.Config.Program or envflag.IsSet("OA_TRAINING_PROGRAM")) else None
+        self._static_loss: Optional[OaMatrix] = None
+        self.LastStatus = OaStatus.Ok()
+        self.Phase = OaTrainingPhaseStats()
+        self._epoch = 0
+        self._log_phases = envflag.IsSet("OA_LOG_TRAINING_PHASES")
+
+    # ---- configuration
+    def AddCallback(self, cb: OaCallback) -> None:
+        self._callbacks.append(cb)
+
+    def AddMetric(self, metric) -> None:
+        self._metrics.append(metric)
+
+    def Program(self) -> Optional[OaTrainingProgram]:
+        return self._program
+
+    # ---- life cycle
+    def IsDone(self) -> bool:
+        if self._finished or self._stop or self._index >= self.Config.TotalSteps:
+            return True
+        if not self._started:
+            self._started = True
+            self._wall0 = time.perf_counter()
+            self._fire("OnTrainBegin")
+            self._fire("OnEpochBegin", self._epoch)
+        self._step_wall0 = time.perf_counter()
+        self._timer.Begin()
+        return False
+
+    def RequestStop(self) -> None:
+        self._stop = True
+
+    def Index(self) -> int:
+        """Number of completed steps."""
+        return self._index
+
+    def RecordSourceUnits(self, n: int) -> None:
+        self._source_units = int(n)
+
+    def Step(self, prepare: Optional[Callable[[], None]], record: Callable[[], OaMatrix]) -> float:
+        """One step in two phases: `prepare` refills the (static) input buffers, `record` launches zero-grad, forward,
+        loss and backward and returns the loss.  With a program configured, `record` + the optimizer step are captured
+        at step 2 and replayed afterwards; only `prepare` runs on the host on replay steps."""
+        if self._program is not None and self._program.IsCaptured():
+            if prepare is not None:
+                prepare()
+            t0 = time.perf_counter()
+            self._program.Replay()
+            self.Opt_.NotifyProgramReplay()
+            self.Phase.SubmitMs = (time.perf_counter() - t0) * 1e3
+            return self._finish_step(self._static_loss, stepped=True)
+        if prepare is not None:
+            prepare()
+        if self._program is not None and self._index >= 1:
+            def body():
+                loss = record()
+                self.Opt_.Step()
+                return loss
+            st = self._program.Capture(body)
+            if not st:
+                self.LastStatus = st
+                self._stop = True
+                return float("nan")
+            self.Opt_.Step_ -= 1                    # the capture pass itself did not execute a step
+            self._static_loss = self._program.Outputs()
+            self._program.Replay()
+            self.Opt_.NotifyProgramReplay()
+            return self._finish_step(self._static_loss, stepped=True)
+        t0 = time.perf_counter()
+        loss = record()
+        self.Phase.BodyMs = (time.perf_counter() - t0) * 1e3
+        return self.Next(loss)
+
+    def Next(self, loss: OaMatrix) -> float:
+        t0 = time.perf_counter()
+        self.Opt_.Step()
+        self.Phase.OptimizerMs = (time.perf_counter() - t0) * 1e3
+        return self._finish_step(loss, stepped=True)
+
+    def _finish_step(self, loss: OaMatrix, stepped: bool) -> float:
+        ctx = RT.OaContext.GetDefault()
+        t0 = time.perf_counter()
+        ev = ctx.Submit(self._timer)
+        t1 = time.perf_counter()
+        if self.Config.SyncEveryStep:
+            st = ctx.Wait(ev)
+            if not st:
+                self.LastStatus = st
+                self._stop = True
+            t2 = time.perf_counter()
+            self._last_loss = loss.Item()
+            self._gpu_ms.append(self._timer.ReadbackMs())
+            self.Phase.WaitMs = (t2 - t1) * 1e3
+            self.Phase.ScalarMs = (time.perf_counter() - t2) * 1e3
+        self.Phase.SubmitMs += (t1 - t0) * 1e3
+        self._losses.append(self._last_loss)
+        self._index += 1
+        self._source_units_total += self._source_units
+        self._wall_total = time.perf_counter() - self._wall0
+        for m in self._metrics:
+            if getattr(m, "Name", "") == "loss":
+                m.Update(self._last_loss)
+        tcb = time.perf_counter()
+        self._fire("OnStepEnd", self._index, self._last_loss)
+        spe = self.Config.StepsPerEpoch
+        if spe and self._index % spe == 0:
+            self._fire("OnEpochEnd", self._epoch)
+            self._epoch += 1
+            if self._index < self.Config.TotalSteps:
+                self._fire("OnEpochBegin", self._epoch)
+        self.Phase.CallbackMs = (time.perf_counter() - tcb) * 1e3
+        if self._log_phases:
+            p = self.Phase
+            print(f"[oa phases] step {self._index}: body {p.BodyMs:.3f} opt {p.OptimizerMs:.3f} submit {p.SubmitMs:.3f} "
+                  f"wait {p.WaitMs:.3f} scalar {p.ScalarMs:.3f} cb {p.CallbackMs:.3f} ms")
+        return self._last_loss
+
+    def Finish(self) -> None:
+        if self._finished:
+            return
+        self._finished = True
+        ctx = RT.OaContext.GetDefault()
+        ctx.Execute()
+        ctx.Sync()
+        if self._started:
+            if not self.Config.StepsPerEpoch:
+                self._fire("OnEpochEnd", self._epoch)
+            self._fire("OnTrainEnd")
+        report = envflag.GetString("OA_GRAPH_REPORT", "")
+        if report and report != "1":
+            import json
+            with open(report, "w") as f:
+                json.dump({"nodes": [n[0] for n in ctx.LastGraph()], "program": self._program.DebugReport() if self._program else None}, f)
+
+    def _fire(self, hook: str, *args) -> None:
+        for cb in self._callbacks:
+            st = getattr(cb, hook)(self, *args)
+            if isinstance(st, OaStatus) and not st:
+                self.LastStatus = st
+                self._stop = True
+
+    # ---- results
+    def LastLoss(self) -> float:
+        return self._last_loss
+
+    def Losses(self) -> list:
+        return list(self._losses)
+
+    def Epoch(self) -> int:
+        return self._epoch
+
+    def GpuTimingStats(self) -> OaGpuTimingStats:
+        xs = sorted(self._gpu_ms)
+        if not xs:
+            return OaGpuTimingStats()
+        n = len(xs)
+        return OaGpuTimingStats(n, sum(xs) / n, xs[0], xs[n // 2], xs[min(n - 1, int(0.95 * n))])
+
+    def WallMsPerStep(self) -> float:
+        return self._wall_total * 1e3 / max(1, self._index)
+
+    def GpuMsPerStep(self) -> float:
+        return self.GpuTimingStats().MeanMs
+
+    def WallSamplesPerSecond(self) -> float:
+        return self.Config.BatchSize * self._index / max(self._wall_total, 1e-12)
+
+    def WallUnitsPerSecond(self) -> float:
+        return self.WallSamplesPerSecond() * self.Config.SequenceLength
+
+    def WallSourceUnitsPerSecond(self) -> float:
+        return self._source_units_total / max(self._wall_total, 1e-12)
+
+    def GpuUnitsPerSecond(self) -> float:
+        ms = self.GpuMsPerStep()
+        return self.Config.BatchSize * self.Config.SequenceLength / (ms / 1e3) if ms > 0 else 0.0
