@@ -121,6 +121,24 @@ int oa_attn_f32_bwd(const float* q, const float* k, const float* v, const float*
                     long long row_stride, long long o_row_stride, long long d_row_stride, float scale, int causal,
                     void* stream);
 
+
+// ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
+int oa_ipc_alloc(size_t bytes, void** out);
+int oa_ipc_free(void* p);
+int oa_ipc_get_handle(void* p, void* handle64);
+int oa_ipc_open(const void* handle64, void** out);
+int oa_ipc_close(void* p);
+int oa_peer_signal(const void* const* flags_peers, void* epoch_local, int rank, int world, void* stream);
+int oa_peer_wait(const void* my_flags, const void* epoch_local, int world, int* status, void* stream);
+int oa_dp_reduce_adam_gather(const void* const* grad_peers, const void* const* param_peers, float* master, float* m, float* v,
+                             long long shard_lo, long long shard_n, const float* state, const float* inv_clip,
+                             int decoupled, int rank, int world, const void* my_flags, const void* epoch_local,
+                             int* status, int max_blocks, void* stream);
+int oa_peer_reduce(int dtype, const void* const* in_peers, void* out, long long lo, long long n, int world, int op,
+                   void* stream);
+int oa_peer_push(const void* const* dst_peers, long long dst_off_bytes, const void* src, long long nbytes, int world,
+                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif

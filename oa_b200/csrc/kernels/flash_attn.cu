@@ -13,8 +13,10 @@
 // one CTA per query block accumulates dQ in TMEM over the key blocks.  Probabilities are recomputed from the
 // saved log-sum-exp.
 //
-// CTA = 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2..5 = softmax /
-// epilogue (TMEM lane quadrant = warp % 4).  Every wait is bounded and reports to a status word.
+// CTA = 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2..9 = softmax /
+// epilogue.  Two threads share a query row: warp w works on TMEM lane quadrant w % 4 and on key columns
+// [64*half, 64*half+64) with half = (w-2)/4, which doubles the warps available to hide TMEM-load and
+// exp latency.  Every wait is bounded and reports to a status word.
 #include "common.cuh"
 #include "api.h"
 
@@ -23,6 +25,12 @@ namespace oa {
 constexpr int FA_BM = 128;   // queries per tile
 constexpr int FA_BN = 128;   // keys per tile
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr int FA_THREADS = 320;   // 2 service warps + 8 softmax warps
+
+// 64-thread named barrier shared by the two warps that own the same 32 query rows.
+__device__ __forceinline__ void pair_sync(int quad) {
+  asm volatile("bar.sync %0, 64;" ::"r"(quad + 1) : "memory");
+}
 
 struct FlashParams {
   int batch, heads, seq, head_dim;
@@ -59,7 +67,7 @@ struct FwdCfg {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(192, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(FA_THREADS, HD == 64 ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   using Cfg = FwdCfg<HD>;
@@ -90,7 +98,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(o_full, 1);
     mbar_fence_init();
   }
@@ -163,16 +171,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else {
-    // ------------- softmax + output: thread = one query row
+    // ------------- softmax + output: two threads per query row (key columns split in halves)
+    constexpr int OC = HD / 2;                   // output columns owned by this thread
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const int qi = qb * FA_BM + r;               // query index inside the sequence
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
     float m_run = -INFINITY, l_run = 0.f;
-    float acc[HD];
+    float acc[OC];
 #pragma unroll
-    for (int d = 0; d < HD; ++d) acc[d] = 0.f;
+    for (int d = 0; d < OC; ++d) acc[d] = 0.f;
     uint8_t* sP = smem + Cfg::OFF_P;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
@@ -180,14 +190,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
-      const int k0 = j * FA_BN;
-      const bool need_mask = (p.causal && j == qb) || (k0 + FA_BN > p.seq);
-      // pass 1: row maximum
+      const int k0 = j * FA_BN + half * 64;
+      const bool need_mask = (p.causal && j == qb) || (j * FA_BN + FA_BN > p.seq);
+      const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + half * 64;
+      // pass 1: maximum over this thread's 64 key columns, then exchange with the partner thread.
+      // The exchange slot is the first word of the PARTNER's own row of the P tile: the P tile is idle here
+      // (the previous P*V has completed before s_full fires) and only the slot's reader overwrites it later.
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t s[32];
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + c * 32, s);
+        tmem_ld32(s_addr + c * 32, s);
         tmem_ld_wait();
         if (need_mask) {
 #pragma unroll
@@ -201,15 +214,20 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
         }
       }
+      float* slot_mine = reinterpret_cast<float*>(sP + half * (FA_BM * 128) + r * 128);
+      float* slot_partner = reinterpret_cast<float*>(sP + (half ^ 1) * (FA_BM * 128) + r * 128);
+      *slot_partner = mx;
+      pair_sync(quad);
+      mx = fmaxf(mx, *slot_mine);
       const float m_new = fmaxf(m_run, mx * sl2);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // fully masked row so far
-      const float alpha = fast_exp2(m_run - m_use);                 // m_run = -inf -> 0
+      const float alpha = fast_exp2(m_run - m_use);             // m_run = -inf -> 0
       float l_add = 0.f;
-      // pass 2: probabilities -> bf16 -> swizzled smem tile (A operand of P*V)
+      // pass 2: probabilities -> bf16 -> swizzled smem tile (A operand of P*V); this thread owns box `half`
 #pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t s[32];
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + c * 32, s);
+        tmem_ld32(s_addr + c * 32, s);
         tmem_ld_wait();
         float pr[32];
 #pragma unroll
@@ -226,7 +244,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int g = 0; g < 4; ++g) {
           uint4 pk = make_uint4(pack_bf16x2(pr[g * 8], pr[g * 8 + 1]), pack_bf16x2(pr[g * 8 + 2], pr[g * 8 + 3]),
                                 pack_bf16x2(pr[g * 8 + 4], pr[g * 8 + 5]), pack_bf16x2(pr[g * 8 + 6], pr[g * 8 + 7]));
-          *reinterpret_cast<uint4*>(sP + sw128_offset(r, c * 32 + g * 8, FA_BM * 128)) = pk;
+          *reinterpret_cast<uint4*>(sP + sw128_offset(r, half * 64 + c * 32 + g * 8, FA_BM * 128)) = pk;
         }
       }
       l_run = l_run * alpha + l_add;
@@ -235,37 +253,44 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      // accumulate the partial output of this key block
+      // accumulate the partial output of this key block (this thread's half of the head dimension)
       ok = mbar_wait(o_full, j & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < OC / 32; ++c) {
         uint32_t o[32];
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_O + c * 32, o);
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_O + half * OC + c * 32, o);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(o[i]);
       }
       tc_fence_before();
     }
+    // combine the two partial row sums (same exchange slots; the last P*V has completed)
+    {
+      float* slot_mine = reinterpret_cast<float*>(sP + half * (FA_BM * 128) + r * 128);
+      float* slot_partner = reinterpret_cast<float*>(sP + (half ^ 1) * (FA_BM * 128) + r * 128);
+      *slot_partner = l_run;
+      pair_sync(quad);
+      l_run += *slot_mine;
+    }
     if (ok && qi < p.seq) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* op = p.o + (long long)(row0 + qi) * p.o_stride + h * HD;
+      __nv_bfloat16* op = p.o + (long long)(row0 + qi) * p.o_stride + h * HD + half * OC;
 #pragma unroll
-      for (int g = 0; g < HD / 8; ++g)
+      for (int g = 0; g < OC / 8; ++g)
         *reinterpret_cast<uint4*>(op + g * 8) =
             make_uint4(pack_bf16x2(acc[g * 8] * inv, acc[g * 8 + 1] * inv), pack_bf16x2(acc[g * 8 + 2] * inv, acc[g * 8 + 3] * inv),
                        pack_bf16x2(acc[g * 8 + 4] * inv, acc[g * 8 + 5] * inv), pack_bf16x2(acc[g * 8 + 6] * inv, acc[g * 8 + 7] * inv));
-      if (p.lse) p.lse[((long long)b * p.heads + h) * p.seq + qi] = (m_run + log2f(l_run)) / LOG2E;
+      if (p.lse && half == 0) p.lse[((long long)b * p.heads + h) * p.seq + qi] = (m_run + log2f(l_run)) / LOG2E;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
 }
-
 
 // ===================================================================================== backward
 struct FlashBwdParams {
@@ -323,7 +348,7 @@ struct BwdKvCfg {
 
 // One CTA per (key block, head, batch): dK, dV accumulate in TMEM over the query blocks.
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(FA_THREADS, 1)
 flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const FlashBwdParams p) {
@@ -356,7 +381,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(fin_full, 1);
     mbar_fence_init();
   }
@@ -432,6 +457,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;            // this thread owns key columns [64*half, 64*half+64)
     const int r = quad * 32 + lane;
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
@@ -452,7 +478,8 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int k0 = jb * FA_BN;
       const bool need_mask = (p.causal && ib == jb) || (k0 + FA_BN > p.seq) || !q_ok;
 #pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t s[32], dp[32];
         tmem_ld32(tmem_base + t_lane + Cfg::TM_S + c * 32, s);
         tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + c * 32, dp);
@@ -497,7 +524,8 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         __nv_bfloat16* base = (which == 0 ? p.dv : p.dk) + (long long)(row0 + kj) * p.dkv_stride + h * HD;
         const uint32_t tcol = which == 0 ? Cfg::TM_DV : Cfg::TM_DK;
 #pragma unroll 1
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int cc = 0; cc < HD / 64; ++cc) {
+          const int c = half * (HD / 64) + cc;
           uint32_t a[32];
           tmem_ld32(tmem_base + t_lane + tcol + c * 32, a);
           tmem_ld_wait();
@@ -537,7 +565,7 @@ struct BwdQCfg {
 
 // One CTA per (query block, head, batch): dQ accumulates in TMEM over the key blocks.
 template <int HD>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(FA_THREADS, 1)
 flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const FlashBwdParams p) {
@@ -569,7 +597,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(ds_full, 4);
+    mbar_init(ds_full, 8);
     mbar_init(fin_full, 1);
     mbar_fence_init();
   }
@@ -640,6 +668,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
@@ -658,7 +687,8 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int k0 = j * FA_BN;
       const bool need_mask = (p.causal && j == ib) || (k0 + FA_BN > p.seq) || !q_ok;
 #pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
         uint32_t s[32], dp[32];
         tmem_ld32(tmem_base + t_lane + Cfg::TM_S + c * 32, s);
         tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + c * 32, dp);
@@ -695,7 +725,8 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       __nv_bfloat16* base = p.dq + (long long)(row0 + qi) * p.dq_stride + h * HD;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int cc = 0; cc < HD / 64; ++cc) {
+        const int c = half * (HD / 64) + cc;
         uint32_t a[32];
         tmem_ld32(tmem_base + t_lane + Cfg::TM_DQ + c * 32, a);
         tmem_ld_wait();
@@ -743,11 +774,11 @@ extern "C" int oa_flash_fwd(const void* q, const void* k, const void* v, void* o
   if (head_dim == 64) {
     static bool set = false;
     if (!set) { if (cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
-    flash_fwd_kernel<64><<<grid, 192, FwdCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    flash_fwd_kernel<64><<<grid, FA_THREADS, FwdCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, p);
   } else {
     static bool set = false;
     if (!set) { if (cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
-    flash_fwd_kernel<128><<<grid, 192, FwdCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    flash_fwd_kernel<128><<<grid, FA_THREADS, FwdCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, p);
   }
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
@@ -801,8 +832,8 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
       if ((rc = set_max_smem(flash_bwd_q_kernel<64>, BwdQCfg<64>::SMEM_BYTES))) return rc;
       set = true;
     }
-    flash_bwd_kv_kernel<64><<<grid, 192, BwdKvCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    flash_bwd_q_kernel<64><<<grid, 192, BwdQCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_kv_kernel<64><<<grid, FA_THREADS, BwdKvCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_q_kernel<64><<<grid, FA_THREADS, BwdQCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
   } else {
     static bool set = false;
     if (!set) {
@@ -810,8 +841,8 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
       if ((rc = set_max_smem(flash_bwd_q_kernel<128>, BwdQCfg<128>::SMEM_BYTES))) return rc;
       set = true;
     }
-    flash_bwd_kv_kernel<128><<<grid, 192, BwdKvCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    flash_bwd_q_kernel<128><<<grid, 192, BwdQCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_kv_kernel<128><<<grid, FA_THREADS, BwdKvCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_q_kernel<128><<<grid, FA_THREADS, BwdQCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
   }
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
