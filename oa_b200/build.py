@@ -52,7 +52,7 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
         obj = OBJ_DIR / (src.stem + ".o")
         objs.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr):
-            jobs.append(([_nvcc(), *NVCC_FLAGS, "-I", str(KERNEL_DIR), "-c", str(src), "-o", str(obj)],
+            jobs.append(([_nvcc(), *NVCC_FLAGS, *os.environ.get("OA_NVCC_EXTRA", "").split(), "-I", str(KERNEL_DIR), "-c", str(src), "-o", str(obj)],
                          OBJ_DIR / (src.stem + ".log")))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:

@@ -40,6 +40,19 @@ int oa_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, i
                  int b_mn, const void* bias, const void* residual, int ldr, void* aux_out, const void* aux_in,
                  int ldaux, int act, int out_f32, int accumulate, float alpha, void* workspace,
                  size_t workspace_bytes, int force_bn, int* status, void* stream);
+// `batch` independent problems of one shape; s*_batch are element strides between problems (sbias_batch may be 0).
+int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc, int a_mn,
+                         int b_mn, const void* bias, const void* residual, int ldr, void* aux_out, const void* aux_in,
+                         int ldaux, int act, int out_f32, int accumulate, float alpha, void* workspace,
+                         size_t workspace_bytes, int force_bn, int batch, long long sa_batch, long long sb_batch,
+                         long long sc_batch, long long sr_batch, long long saux_batch, long long sbias_batch, int* status,
+                         void* stream);
+// Grouped (mixture-of-experts) GEMMs; group segments are padded to multiples of 128 rows, `offsets` (int[groups+1]) is on the device.
+//   mode 1: out[r,:] = act(A[r,:] * B[g(r)]^T + bias[g(r)]);   mode 2: out[g] = A_g^T * B_g (+ out[g])
+int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc,
+                         int b_mn, const void* bias, int act, void* aux_out, const void* aux_in, int ldaux, int out_f32,
+                         int accumulate, int groups, const int* offsets, long long max_rows, long long sb_batch,
+                         long long sc_batch, long long sbias_batch, int* status, void* stream);
 // fp32 SIMT GEMM with arbitrary element strides and a batch dimension:
 //   C[b][m,n] = act(alpha * sum_k A[b][m*sam + k*sak] * B[b][n*sbn + k*sbk] + bias[n]) (+ C if accumulate)
 int oa_gemm_f32(const float* A, const float* B, float* C, int M, int N, int K, long long sam, long long sak,
@@ -121,6 +134,23 @@ int oa_attn_f32_bwd(const float* q, const float* k, const float* v, const float*
                     long long row_stride, long long o_row_stride, long long d_row_stride, float scale, int causal,
                     void* stream);
 
+
+// ---- mixture of experts (moe.cu)
+int oa_moe_router(int dtype, const void* logits, const float* sel_bias, float* probs, int* topk_idx, float* topk_w,
+                  long long tokens, int E, int K, void* stream);
+int oa_moe_router_bwd(int dtype, const float* probs, const int* topk_idx, const float* topk_w, const float* dw,
+                      const float* dprobs_col, float dprobs_scale, void* dlogits, long long tokens, int E, int K, void* stream);
+size_t oa_moe_plan_scratch_bytes(long long routes, int E);
+int oa_moe_plan(const int* topk_idx, long long tokens, int K, int E, int* counts, int* offsets, int* packed_token, int* inverse,
+                long long max_rows, int* scratch, void* stream);
+int oa_moe_gather(const void* x, const int* packed_token, void* packed, const int* offsets, int E, int dim, long long max_rows,
+                  void* stream);
+int oa_moe_combine(const void* packed, const float* gate, const int* inverse, const void* base, void* out, long long tokens,
+                   int K, int dim, void* stream);
+int oa_moe_combine_bwd(const void* packed, const float* gate, const int* inverse, const int* packed_token, const void* dout,
+                       void* dpacked, float* dgate, const int* offsets, int E, int K, int dim, long long max_rows, void* stream);
+int oa_moe_gather_bwd(const void* dpacked, const int* inverse, const void* base, void* dx, long long tokens, int K, int dim,
+                      void* stream);
 
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);

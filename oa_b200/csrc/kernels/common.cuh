@@ -60,7 +60,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   asm volatile(
       "{\n\t"
       ".reg .pred P;\n\t"
+#ifdef OA_MBAR_TEST_WAIT
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+#else
       "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+#endif
       "selp.b32 %0, 1, 0, P;\n\t"
       "}\n"
       : "=r"(ok)
@@ -69,16 +73,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: ~2^22 polls with back-off (a second or two at most), then false.
-#ifndef OA_WAIT_LIMIT
-#define OA_WAIT_LIMIT (1u << 22)
+// Bounded wait.  mbarrier.try_wait suspends the thread in hardware until the phase completes (or a short
+// system time limit passes), so the loop itself does not back off with __nanosleep: a sleep of even a few
+// nanoseconds is rounded up to about a microsecond, which would be added to every producer/consumer hand-off.
+// The bound is wall time: after OA_WAIT_LIMIT_NS (2 s) without completion the wait gives up and returns false.
+#ifndef OA_WAIT_LIMIT_NS
+#define OA_WAIT_LIMIT_NS 2000000000ull
 #endif
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t it = 0; it < OA_WAIT_LIMIT; ++it) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 64) __nanosleep(it > 4096 ? 256 : 20);
+    if ((it & 0x3ff) == 0) {
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > OA_WAIT_LIMIT_NS) return false;
+    }
   }
-  return false;
+}
+
+// Whole-warp wait: every lane waits (so the warp stays converged) and the outcome is made uniform.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
+#ifdef OA_WARP_WAIT_ONE_LANE
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity);
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (ok && (threadIdx.x & 31) != 0) ok = mbar_try_wait(bar, parity);   // completes at once; gives each lane the acquire
+  return __all_sync(0xffffffffu, ok);
+#else
+  bool ok = mbar_wait(bar, parity);
+  return __all_sync(0xffffffffu, ok);
+#endif
 }
 
 __device__ __forceinline__ void report_error(int* status, int code) {

@@ -76,7 +76,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* q_full = bars + 0;
   uint64_t* k_full = bars + 1;   // [2]
   uint64_t* v_full = bars + 3;   // [2]
-  uint64_t* kv_empty = bars + 5; // [2]
+  uint64_t* kv_empty = bars + 5; // [2]  V stage free (P*V done)
+  uint64_t* k_empty = bars + 11; // [2]  K stage free (Q*K^T done): lets the next K load start one iteration earlier
   uint64_t* s_full = bars + 7;
   uint64_t* p_full = bars + 8;
   uint64_t* o_full = bars + 9;
@@ -96,7 +97,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&k_empty[s], 1); }
     mbar_init(s_full, 1);
     mbar_init(p_full, 8);
     mbar_init(o_full, 1);
@@ -109,39 +110,46 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ------------- producer.  The whole warp walks the loop and waits together; one lane issues the copies.
+    // (A warp split between a spinning lane and 31 lanes parked at the final barrier hands off very slowly.)
     if (lane == 0) {
-      // ------------- producer
       mbar_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
       for (int x = 0; x < HD / 64; ++x)
         tma_load_2d(smem + Cfg::OFF_Q + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + qb * FA_BM);
-      for (int j = 0; j < n_kv; ++j) {
-        int st = j & 1;
-        uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1)) { report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+    }
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!warp_wait(&k_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+      if (lane == 0) {
         mbar_expect_tx(&k_full[st], Cfg::KV_BYTES);
 #pragma unroll
         for (int x = 0; x < HD / 64; ++x)
           tma_load_2d(smem + Cfg::OFF_K + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmK, &k_full[st], h * HD + x * 64, row0 + j * FA_BN);
+      }
+      if (!warp_wait(&kv_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+      if (lane == 0) {
         mbar_expect_tx(&v_full[st], Cfg::KV_BYTES);
 #pragma unroll
         for (int x = 0; x < HD / 64; ++x)
           tma_load_2d(smem + Cfg::OFF_V + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmV, &v_full[st], h * HD + x * 64, row0 + j * FA_BN);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------- MMA issuer
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_BM, HD, 0, 1);
-      const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q);
-      const uint32_t p_addr = smem_u32(smem + Cfg::OFF_P);
-      bool ok = mbar_wait(q_full, 0);
-      if (!ok) report_error(p.status, OA_KERR_WAIT_FULL);
-      auto issue_qk = [&](int j) -> bool {
-        int st = j & 1;
-        if (!mbar_wait(&k_full[st], (j >> 1) & 1)) { report_error(p.status, OA_KERR_WAIT_FULL); return false; }
-        tc_fence_after();
+    // ------------- MMA issuer (warp-uniform waits, lane 0 issues)
+    constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_BM, HD, 0, 1);
+    const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q);
+    const uint32_t p_addr = smem_u32(smem + Cfg::OFF_P);
+    bool ok = warp_wait(q_full, 0);
+    if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
+    auto issue_qk = [&](int j) -> bool {
+      const int st = j & 1;
+      if (!warp_wait(&k_full[st], (j >> 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); return false; }
+      tc_fence_after();
+      if (lane == 0) {
         const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
@@ -149,15 +157,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(q_addr + off, 16, 1024),
                    umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
         }
+        umma_commit(&k_empty[st]);
         umma_commit(s_full);
-        return true;
-      };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        int st = j & 1;
-        if (!mbar_wait(p_full, j & 1)) { report_error(p.status, OA_KERR_WAIT_SOFTMAX); break; }
-        if (!mbar_wait(&v_full[st], (j >> 1) & 1)) { report_error(p.status, OA_KERR_WAIT_FULL); break; }
-        tc_fence_after();
+      }
+      __syncwarp();
+      return true;
+    };
+    if (ok) ok = issue_qk(0);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int st = j & 1;
+      if (!warp_wait(p_full, j & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); break; }
+      if (!warp_wait(&v_full[st], (j >> 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      tc_fence_after();
+      if (lane == 0) {
         const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < FA_BN / 16; ++ks) {
@@ -167,8 +179,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         umma_commit(&kv_empty[st]);
         umma_commit(o_full);
-        if (j + 1 < n_kv) ok = issue_qk(j + 1);
       }
+      __syncwarp();
+      if (j + 1 < n_kv) ok = issue_qk(j + 1);
     }
   } else {
     // ------------- softmax + output: two threads per query row (key columns split in halves)
@@ -186,34 +199,43 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     uint8_t* sP = smem + Cfg::OFF_P;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      ok = mbar_wait(s_full, j & 1);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = warp_wait(s_full, j & 1);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
       const int k0 = j * FA_BN + half * 64;
       const bool need_mask = (p.causal && j == qb) || (j * FA_BN + FA_BN > p.seq);
       const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + half * 64;
-      // pass 1: maximum over this thread's 64 key columns, then exchange with the partner thread.
-      // The exchange slot is the first word of the PARTNER's own row of the P tile: the P tile is idle here
-      // (the previous P*V has completed before s_full fires) and only the slot's reader overwrites it later.
+      // pass 1: maximum over this thread's 64 key columns.  Masked tiles (the diagonal one and the sequence tail)
+      // take a separate loop so that the common loop carries no per-element predicate.
       float mx = -INFINITY;
+      if (need_mask) {
+        const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - k0;   // columns i <= lim are alive
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t s[32];
-        tmem_ld32(s_addr + c * 32, s);
-        tmem_ld_wait();
-        if (need_mask) {
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sv[32];
+          tmem_ld32(s_addr + c * 32, sv);
+          tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            int kj = k0 + c * 32 + i;
-            bool dead = (p.causal && kj > qi) || kj >= p.seq;
-            mx = fmaxf(mx, dead ? -INFINITY : __uint_as_float(s[i]));
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c * 32 + i <= lim) ? __uint_as_float(sv[i]) : -INFINITY);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sv[32];
+          tmem_ld32(s_addr + c * 32, sv);
+          tmem_ld_wait();
+          float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]), m3 = __uint_as_float(sv[3]);
+#pragma unroll
+          for (int i = 4; i < 32; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(sv[i])); m1 = fmaxf(m1, __uint_as_float(sv[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(sv[i + 2])); m3 = fmaxf(m3, __uint_as_float(sv[i + 3]));
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+          mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
         }
       }
+      // Exchange with the partner thread.  The slot is the first word of the PARTNER's own row of the P tile: the
+      // P tile is idle here (the previous P*V has completed before s_full fires) and only the slot's reader
+      // overwrites it later.
       float* slot_mine = reinterpret_cast<float*>(sP + half * (FA_BM * 128) + r * 128);
       float* slot_partner = reinterpret_cast<float*>(sP + (half ^ 1) * (FA_BM * 128) + r * 128);
       *slot_partner = mx;
@@ -222,40 +244,47 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float m_new = fmaxf(m_run, mx * sl2);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // fully masked row so far
       const float alpha = fast_exp2(m_run - m_use);             // m_run = -inf -> 0
-      float l_add = 0.f;
-      // pass 2: probabilities -> bf16 -> swizzled smem tile (A operand of P*V); this thread owns box `half`
+      const float neg_m = -m_use;
+      float l0 = 0.f, l1 = 0.f;
+      uint8_t* prow = sP + half * (FA_BM * 128) + r * 128;       // this thread's 128-byte row of box `half`
+      const int rx = r & 7;
+      // pass 2: probabilities -> bf16 -> swizzled smem tile (A operand of P*V)
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
-        uint32_t s[32];
-        tmem_ld32(s_addr + c * 32, s);
+        uint32_t sv[32];
+        tmem_ld32(s_addr + c * 32, sv);
         tmem_ld_wait();
-        float pr[32];
+        uint32_t pk[16];
+        if (need_mask) {
+          const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - k0 - c * 32;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(s[i]) * sl2 - m_use);
-          if (need_mask) {
-            int kj = k0 + c * 32 + i;
-            if ((p.causal && kj > qi) || kj >= p.seq) e = 0.f;
+          for (int i = 0; i < 32; i += 2) {
+            float e0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, neg_m)) : 0.f;
+            float e1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_m)) : 0.f;
+            l0 += e0; l1 += e1;
+            pk[i >> 1] = pack_bf16x2(e0, e1);
           }
-          pr[i] = e;
-          l_add += e;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, neg_m));
+            float e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_m));
+            l0 += e0; l1 += e1;
+            pk[i >> 1] = pack_bf16x2(e0, e1);
+          }
         }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint4 pk = make_uint4(pack_bf16x2(pr[g * 8], pr[g * 8 + 1]), pack_bf16x2(pr[g * 8 + 2], pr[g * 8 + 3]),
-                                pack_bf16x2(pr[g * 8 + 4], pr[g * 8 + 5]), pack_bf16x2(pr[g * 8 + 6], pr[g * 8 + 7]));
-          *reinterpret_cast<uint4*>(sP + sw128_offset(r, half * 64 + c * 32 + g * 8, FA_BM * 128)) = pk;
-        }
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4*>(prow + (((c * 4 + g) ^ rx) << 4)) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
       }
-      l_run = l_run * alpha + l_add;
+      l_run = l_run * alpha + (l0 + l1);
       m_run = m_new;
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
       // accumulate the partial output of this key block (this thread's half of the head dimension)
-      ok = mbar_wait(o_full, j & 1);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = warp_wait(o_full, j & 1);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
 #pragma unroll
@@ -264,7 +293,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld32(tmem_base + t_lane + Cfg::TM_O + half * OC + c * 32, o);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha + __uint_as_float(o[i]);
+        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(o[i]));
       }
       tc_fence_before();
     }
@@ -477,7 +506,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_after();
       const int k0 = jb * FA_BN;
       const bool need_mask = (p.causal && ib == jb) || (k0 + FA_BN > p.seq) || !q_ok;
-#pragma unroll 1
+#pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
         uint32_t s[32], dp[32];
@@ -485,23 +514,28 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + c * 32, dp);
         tmem_ld_wait();
         uint32_t pw[16], dw[16];
+        const float nlse = -lse2, ndlt = -dlt * p.scale;
+        if (need_mask) {
+          const int lim = q_ok ? (min(p.causal ? qi : 0x7fffffff, p.seq - 1) - (k0 + c * 32)) : -1;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = fast_exp2(__uint_as_float(s[i]) * sl2 - lse2);
-          float p1 = fast_exp2(__uint_as_float(s[i + 1]) * sl2 - lse2);
-          if (need_mask) {
-            int kj = k0 + c * 32 + i;
-            if (!q_ok || (p.causal && kj > qi) || kj >= p.seq) p0 = 0.f;
-            if (!q_ok || (p.causal && kj + 1 > qi) || kj + 1 >= p.seq) p1 = 0.f;
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse)) : 0.f;
+            float p1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse)) : 0.f;
+            pw[i >> 1] = pack_bf16x2(p0, p1);
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
           }
-          float d0 = p0 * (__uint_as_float(dp[i]) - dlt) * p.scale;
-          float d1 = p1 * (__uint_as_float(dp[i + 1]) - dlt) * p.scale;
-          pw[i >> 1] = pack_bf16x2(p0, p1);
-          dw[i >> 1] = pack_bf16x2(d0, d1);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse));
+            float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse));
+            pw[i >> 1] = pack_bf16x2(p0, p1);
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          uint32_t off = sw128_offset(r, c * 32 + g * 8, FA_BM * 128);
+          const uint32_t off = half * (FA_BM * 128) + r * 128 + ((((cc * 4 + g) ^ (r & 7))) << 4);
           *reinterpret_cast<uint4*>(sP + off) = make_uint4(pw[g * 4], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
           *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dw[g * 4], dw[g * 4 + 1], dw[g * 4 + 2], dw[g * 4 + 3]);
         }
@@ -686,7 +720,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       const int k0 = j * FA_BN;
       const bool need_mask = (p.causal && j == ib) || (k0 + FA_BN > p.seq) || !q_ok;
-#pragma unroll 1
+#pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
         const int c = half * 2 + cc;
         uint32_t s[32], dp[32];
@@ -694,21 +728,26 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + c * 32, dp);
         tmem_ld_wait();
         uint32_t dw[16];
+        const float nlse = -lse2, ndlt = -dlt * p.scale;
+        if (need_mask) {
+          const int lim = q_ok ? (min(p.causal ? qi : 0x7fffffff, p.seq - 1) - (k0 + c * 32)) : -1;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = fast_exp2(__uint_as_float(s[i]) * sl2 - lse2);
-          float p1 = fast_exp2(__uint_as_float(s[i + 1]) * sl2 - lse2);
-          if (need_mask) {
-            int kj = k0 + c * 32 + i;
-            if (!q_ok || (p.causal && kj > qi) || kj >= p.seq) p0 = 0.f;
-            if (!q_ok || (p.causal && kj + 1 > qi) || kj + 1 >= p.seq) p1 = 0.f;
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse)) : 0.f;
+            float p1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse)) : 0.f;
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
           }
-          dw[i >> 1] = pack_bf16x2(p0 * (__uint_as_float(dp[i]) - dlt) * p.scale,
-                                   p1 * (__uint_as_float(dp[i + 1]) - dlt) * p.scale);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse));
+            float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse));
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(sDS + sw128_offset(r, c * 32 + g * 8, FA_BM * 128)) =
+          *reinterpret_cast<uint4*>(sDS + half * (FA_BM * 128) + r * 128 + ((((cc * 4 + g) ^ (r & 7))) << 4)) =
               make_uint4(dw[g * 4], dw[g * 4 + 1], dw[g * 4 + 2], dw[g * 4 + 3]);
       }
       tc_fence_before();
@@ -846,3 +885,4 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
   }
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
+

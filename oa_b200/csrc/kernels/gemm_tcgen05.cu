@@ -48,6 +48,14 @@ struct GemmParams {
   float* workspace;                // [splits, M, N] fp32
   int group_m;
   int* status;
+  int batch;                       // independent problems of the same shape (tensor maps are rank 3)
+  long long sc_batch, sr_batch, saux_batch, sbias_batch;   // element strides between problems
+  // Grouped (mixture-of-experts) modes; `batch` is then the number of groups and offsets[batch+1] are row offsets,
+  // every group padded to a multiple of 128 rows.
+  //   1: the ROWS of A / out are grouped (Y[r,:] = X[r,:] * W[g(r)]^T): A and out are flat [rows, .], B is batched.
+  //   2: the REDUCTION is grouped (dW[g] = dY_g^T * X_g): A and B are flat [rows, .] MN-major, out is batched.
+  int group_mode;
+  const int* group_offsets;
 };
 
 constexpr int BM = 128;
@@ -61,7 +69,7 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1280 /*group tile prefix*/;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
@@ -74,8 +82,48 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
   ni = r / gsz;
 }
 
+struct TileInfo {
+  int bi;        // batch / group index (selects the B problem, bias row, output problem)
+  int row0;      // first output row of the tile (global row for grouped-rows mode)
+  int ni;        // n tile index
+  int kb0, kb1;  // k-block range
+  int split;
+  int a_batch, b_batch;  // z coordinates for the A / B tensor maps
+};
+
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t, const int* s_prefix, int m_tiles, int n_tiles,
+                                                int mn_tiles, int tiles_per_batch, int kb_total, int kb_per_split) {
+  TileInfo ti;
+  if (p.group_mode == 1) {
+    int lo = 0, hi = p.batch;            // largest g with s_prefix[g] <= t
+    while (hi - lo > 1) {
+      int mid = (lo + hi) >> 1;
+      if (s_prefix[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int g = lo;
+    const int off = p.group_offsets[g];
+    const int mt = (p.group_offsets[g + 1] - off) >> 7;
+    const int local = t - s_prefix[g];
+    ti.bi = g; ti.row0 = off + (local % mt) * BM; ti.ni = local / mt;
+    ti.kb0 = 0; ti.kb1 = kb_total; ti.split = 0; ti.a_batch = 0; ti.b_batch = g;
+    return ti;
+  }
+  int bi = t / tiles_per_batch;
+  int tb = t - bi * tiles_per_batch;
+  int split = tb / mn_tiles;
+  int mi, ni;
+  tile_coords(tb - split * mn_tiles, m_tiles, n_tiles, p.group_m, mi, ni);
+  ti.bi = bi; ti.row0 = mi * BM; ti.ni = ni; ti.split = split;
+  if (p.group_mode == 2) {
+    ti.kb0 = p.group_offsets[bi] >> 6; ti.kb1 = p.group_offsets[bi + 1] >> 6; ti.a_batch = 0; ti.b_batch = 0;
+  } else {
+    ti.kb0 = split * kb_per_split; ti.kb1 = min(kb_total, ti.kb0 + kb_per_split); ti.a_batch = bi; ti.b_batch = bi;
+  }
+  return ti;
+}
+
 template <int BN>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int split) {
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int split, int bi) {
   if (row >= p.M || col0 >= p.N) return;
   // N is a multiple of 8, so every 8-column group is either fully inside or fully outside.
   int ncols = min(32, p.N - col0);
@@ -84,7 +132,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
 
   if (p.splits > 1) {
-    float* w = p.workspace + ((size_t)split * p.M + row) * p.N + col0;
+    float* w = p.workspace + (((size_t)split * p.batch + bi) * p.M + row) * p.N + col0;
 #pragma unroll
     for (int g = 0; g < 8; ++g)
       if (g * 4 < ncols) *reinterpret_cast<float4*>(w + g * 4) = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
@@ -94,7 +142,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       if (g * 8 < ncols) {
-        uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0 + g * 8));
+        uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + bi * p.sbias_batch + col0 + g * 8));
         float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
         v[g * 8 + 0] += f0.x; v[g * 8 + 1] += f0.y; v[g * 8 + 2] += f1.x; v[g * 8 + 3] += f1.y;
         v[g * 8 + 4] += f2.x; v[g * 8 + 5] += f2.y; v[g * 8 + 6] += f3.x; v[g * 8 + 7] += f3.y;
@@ -102,7 +150,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     }
   }
   if (p.aux_out) {
-    __nv_bfloat16* a = p.aux_out + (size_t)row * p.ldaux + col0;
+    __nv_bfloat16* a = p.aux_out + bi * p.saux_batch + (size_t)row * p.ldaux + col0;
 #pragma unroll
     for (int g = 0; g < 4; ++g)
       if (g * 8 < ncols)
@@ -121,7 +169,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
   }
   if (p.aux_in) {  // multiply by d(act)/dz of the saved pre-activation (backward of a fused Linear+act)
-    const __nv_bfloat16* a = p.aux_in + (size_t)row * p.ldaux + col0;
+    const __nv_bfloat16* a = p.aux_in + bi * p.saux_batch + (size_t)row * p.ldaux + col0;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       if (g * 8 < ncols) {
@@ -142,7 +190,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     }
   }
   if (p.residual) {
-    const __nv_bfloat16* a = p.residual + (size_t)row * p.ldr + col0;
+    const __nv_bfloat16* a = p.residual + bi * p.sr_batch + (size_t)row * p.ldr + col0;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       if (g * 8 < ncols) {
@@ -154,7 +202,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
     }
   }
   if (p.out_f32) {
-    float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldc + col0;
+    float* o = reinterpret_cast<float*>(p.out) + bi * p.sc_batch + (size_t)row * p.ldc + col0;
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
       if (g * 4 < ncols) {
@@ -167,7 +215,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       }
     }
   } else {
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldc + col0;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + bi * p.sc_batch + (size_t)row * p.ldc + col0;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       if (g * 8 < ncols) {
@@ -207,7 +255,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
   const int mn_tiles = m_tiles * n_tiles;
-  const int total_tiles = mn_tiles * p.splits;
+  const int tiles_per_batch = mn_tiles * p.splits;
+  int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
+  if (p.group_mode == 1 && threadIdx.x == 32) {
+    int run = 0;
+    for (int g = 0; g < p.batch; ++g) {
+      s_prefix[g] = run;
+      run += ((p.group_offsets[g + 1] - p.group_offsets[g]) >> 7) * n_tiles;
+    }
+    s_prefix[p.batch] = run;
+  }
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb_per_split = (kb_total + p.splits - 1) / p.splits;
 
@@ -232,6 +289,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = p.group_mode == 1 ? s_prefix[p.batch] : tiles_per_batch * p.batch;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -240,12 +298,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int split = t / mn_tiles;
-        int mi, ni;
-        tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.group_m, mi, ni);
-        int kb0 = split * kb_per_split;
-        int kb1 = min(kb_total, kb0 + kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
+        for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             report_error(p.status, OA_KERR_WAIT_EMPTY);
             ok = false;
@@ -256,15 +310,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* b = sB + stage * Cfg::B_BYTES;
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(a + j * (64 * BK * 2), &tmA, &full[stage], mi * BM + j * 64, kb * BK);
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(a + j * (64 * BK * 2), &tmA, &full[stage], ti.row0 + j * 64, kb * BK, ti.a_batch);
           } else {
-            tma_load_2d(a, &tmA, &full[stage], kb * BK, mi * BM);
+            tma_load_3d(a, &tmA, &full[stage], kb * BK, ti.row0, ti.a_batch);
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(b + j * (64 * BK * 2), &tmB, &full[stage], ni * BN + j * 64, kb * BK);
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(b + j * (64 * BK * 2), &tmB, &full[stage], ti.ni * BN + j * 64, kb * BK, ti.b_batch);
           } else {
-            tma_load_2d(b, &tmB, &full[stage], kb * BK, ni * BN);
+            tma_load_3d(b, &tmB, &full[stage], kb * BK, ti.ni * BN, ti.b_batch);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -285,9 +339,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int split = t / mn_tiles;
-        int kb0 = split * kb_per_split;
-        int kb1 = min(kb_total, kb0 + kb_per_split);
+        const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
+        const int kb0 = ti.kb0, kb1 = ti.kb1;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) {
           report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY);
           break;
@@ -324,11 +377,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      int split = t / mn_tiles;
-      int mi, ni;
-      tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.group_m, mi, ni);
-      int kb0 = split * kb_per_split;
-      int kb1 = min(kb_total, kb0 + kb_per_split);
+      const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
+      const int bi = ti.bi, ni = ti.ni, split = ti.split, kb0 = ti.kb0, kb1 = ti.kb1;
       bool ok = mbar_wait(&tfull[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -336,7 +386,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         break;
       }
       tc_fence_after();
-      const int row = mi * BM + quad * 32 + lane;
+      const int row = ti.row0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
       const bool empty_split = (kb1 <= kb0);  // nothing accumulated: treat as zeros
 #pragma unroll 1
@@ -353,7 +403,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0;
         }
-        epilogue_chunk<BN>(p, r, row, ni * BN + c * 32, split);
+        epilogue_chunk<BN>(p, r, row, ni * BN + c * 32, split, bi);
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
@@ -369,26 +419,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 // Fixed-order reduction of split-K partials (deterministic), then the plain store / accumulate epilogue.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, void* out, int ldc,
-                                     int out_f32, int accumulate) {
+                                     int out_f32, int accumulate, int batch, long long sc_batch) {
   size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  size_t total4 = (size_t)M * N / 4;
+  size_t total4 = (size_t)batch * M * N / 4;
   if (i4 >= total4) return;
   size_t e = i4 * 4;
-  int row = (int)(e / N), col = (int)(e % N);
+  size_t per = (size_t)M * N;
+  int bi = (int)(e / per);
+  size_t eb = e - (size_t)bi * per;
+  int row = (int)(eb / N), col = (int)(eb % N);
   float4 s = *reinterpret_cast<const float4*>(ws + e);
   for (int k = 1; k < splits; ++k) {
-    float4 x = *reinterpret_cast<const float4*>(ws + (size_t)k * M * N + e);
+    float4 x = *reinterpret_cast<const float4*>(ws + (size_t)k * batch * per + e);
     s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
   }
   if (out_f32) {
-    float* o = reinterpret_cast<float*>(out) + (size_t)row * ldc + col;
+    float* o = reinterpret_cast<float*>(out) + bi * sc_batch + (size_t)row * ldc + col;
     if (accumulate) {
       float4 c = *reinterpret_cast<float4*>(o);
       s.x += c.x; s.y += c.y; s.z += c.z; s.w += c.w;
     }
     *reinterpret_cast<float4*>(o) = s;
   } else {
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldc + col;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + bi * sc_batch + (size_t)row * ldc + col;
     if (accumulate) {
       uint2 c = *reinterpret_cast<uint2*>(o);
       float2 a = unpack_bf16x2(c.x), b = unpack_bf16x2(c.y);
@@ -427,6 +480,23 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? OA_OK : OA_ERR_DRIVER;
+}
+
+// 3-D bf16 tensor map: [batch][outer][inner], box = one [box_outer x box_inner] tile of one problem.
+int make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t ld,
+                      uint64_t batch_stride, uint32_t box_inner, uint32_t box_outer) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return OA_ERR_DRIVER;
+  if (batch <= 1) batch_stride = ld * outer;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15) || ((batch_stride * 2) & 15)) return OA_ERR_ALIGN;
+  cuuint64_t dims[3] = {inner, outer, batch < 1 ? 1 : batch};
+  cuuint64_t strides[2] = {ld * 2, batch_stride * 2};
+  cuuint32_t box[3] = {box_inner, box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OA_OK : OA_ERR_DRIVER;
@@ -484,18 +554,21 @@ extern "C" size_t oa_gemm_workspace_bytes(int M, int N, int K) {
   return s > 1 ? (size_t)s * M * N * sizeof(float) : 0;
 }
 
-extern "C" int oa_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc,
-                            int a_mn, int b_mn, const void* bias, const void* residual, int ldr, void* aux_out,
-                            const void* aux_in, int ldaux, int act, int out_f32, int accumulate, float alpha,
-                            void* workspace, size_t workspace_bytes, int force_bn, int* status, void* stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return OA_ERR_ARG;
+extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc,
+                                    int a_mn, int b_mn, const void* bias, const void* residual, int ldr, void* aux_out,
+                                    const void* aux_in, int ldaux, int act, int out_f32, int accumulate, float alpha,
+                                    void* workspace, size_t workspace_bytes, int force_bn, int batch, long long sa_batch,
+                                    long long sb_batch, long long sc_batch, long long sr_batch, long long saux_batch,
+                                    long long sbias_batch, int* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return OA_ERR_ARG;
   if ((N & 7) || (K & 7) || (a_mn && (M & 7))) return OA_ERR_ALIGN;
   if ((ldc & (out_f32 ? 3 : 7)) || (residual && (ldr & 7)) || ((aux_out || aux_in) && (ldaux & 7))) return OA_ERR_ALIGN;
+  if (batch > 1 && ((sc_batch & 7) || (sr_batch & 7) || (saux_batch & 7) || (sbias_batch & 7))) return OA_ERR_ALIGN;
   int bn = force_bn ? force_bn : ((N >= 256) ? 256 : 128);
   int sms = num_sms();
   if (!force_bn && bn == 256) {
     // Prefer the 128-wide tile when it fills the machine noticeably better.
-    int t256 = ((M + BM - 1) / BM) * ((N + 255) / 256), t128 = ((M + BM - 1) / BM) * ((N + 127) / 128);
+    long long t256 = (long long)batch * ((M + BM - 1) / BM) * ((N + 255) / 256), t128 = (long long)batch * ((M + BM - 1) / BM) * ((N + 127) / 128);
     double e256 = (double)t256 / (((t256 + sms - 1) / sms) * sms), e128 = (double)t128 / (((t128 + sms - 1) / sms) * sms);
     if (t256 < sms && e128 > e256 + 0.15) bn = 128;
   }
@@ -510,21 +583,23 @@ extern "C" int oa_gemm_bf16(const void* A, const void* B, void* out, int M, int 
   p.group_m = 16;
   p.splits = 1;
   p.workspace = (float*)workspace;
+  p.batch = batch; p.sc_batch = sc_batch; p.sr_batch = sr_batch; p.saux_batch = saux_batch; p.sbias_batch = sbias_batch;
+  p.group_mode = 0; p.group_offsets = nullptr;
   bool plain = !bias && !residual && !aux_out && !aux_in && act == OA_ACT_NONE;
   if (workspace && plain && (N % 4 == 0)) {
-    int s = oa_gemm_plan_splits(M, N, K, bn, sms);
-    if (s > 1 && (size_t)s * M * N * sizeof(float) <= workspace_bytes) p.splits = s;
+    int s = oa_gemm_plan_splits(M * batch, N, K, bn, sms);
+    if (s > 1 && (size_t)s * batch * M * N * sizeof(float) <= workspace_bytes) p.splits = s;
   }
   CUtensorMap ta, tb;
   int rc;
-  if (a_mn) rc = make_tmap_2d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, 64, BK);
-  else      rc = make_tmap_2d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BK, BM);
+  if (a_mn) rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, batch, (uint64_t)lda, sa_batch, 64, BK);
+  else      rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, batch, (uint64_t)lda, sa_batch, BK, BM);
   if (rc) return rc;
-  if (b_mn) rc = make_tmap_2d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 64, BK);
-  else      rc = make_tmap_2d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BK, (uint32_t)bn);
+  if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, batch, (uint64_t)ldb, sb_batch, 64, BK);
+  else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, batch, (uint64_t)ldb, sb_batch, BK, (uint32_t)bn);
   if (rc) return rc;
-  int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * p.splits;
-  int grid = tiles < sms ? tiles : sms;
+  long long tiles = (long long)batch * ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * p.splits;
+  int grid = tiles < sms ? (int)tiles : sms;
   cudaStream_t st = (cudaStream_t)stream;
   int sel = (bn == 256 ? 4 : 0) | (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   switch (sel) {
@@ -539,11 +614,67 @@ extern "C" int oa_gemm_bf16(const void* A, const void* B, void* out, int M, int 
   }
   if (rc) return rc;
   if (p.splits > 1) {
-    size_t total4 = (size_t)M * N / 4;
+    size_t total4 = (size_t)batch * M * N / 4;
     int threads = 256;
     unsigned blocks = (unsigned)((total4 + threads - 1) / threads);
-    splitk_reduce_kernel<<<blocks, threads, 0, st>>>(p.workspace, p.splits, M, N, out, ldc, out_f32, accumulate);
+    splitk_reduce_kernel<<<blocks, threads, 0, st>>>(p.workspace, p.splits, M, N, out, ldc, out_f32, accumulate, batch, sc_batch);
     if (cudaGetLastError() != cudaSuccess) return OA_ERR_LAUNCH;
   }
   return OA_OK;
+}
+
+extern "C" int oa_gemm_bf16(const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc,
+                            int a_mn, int b_mn, const void* bias, const void* residual, int ldr, void* aux_out,
+                            const void* aux_in, int ldaux, int act, int out_f32, int accumulate, float alpha,
+                            void* workspace, size_t workspace_bytes, int force_bn, int* status, void* stream) {
+  return oa_gemm_bf16_batched(A, B, out, M, N, K, lda, ldb, ldc, a_mn, b_mn, bias, residual, ldr, aux_out, aux_in, ldaux, act,
+                              out_f32, accumulate, alpha, workspace, workspace_bytes, force_bn, 1, 0, 0, 0, 0, 0, 0, status, stream);
+}
+
+// Grouped GEMMs for mixture-of-experts layers (group segments padded to multiples of 128 rows, offsets on the device).
+//   mode 1: out[r, :] = act(A[r, :] * B[g(r)]^T + bias[g(r)])   A [max_rows, K], B [groups, N, K] (or [groups, K, N] when b_mn)
+//   mode 2: out[g]    = A_g^T * B_g (+ out[g])                  A [max_rows, M], B [max_rows, N], out [groups, M, N]
+extern "C" int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb,
+                                    int ldc, int b_mn, const void* bias, int act, void* aux_out, const void* aux_in, int ldaux,
+                                    int out_f32, int accumulate, int groups, const int* offsets, long long max_rows,
+                                    long long sb_batch, long long sc_batch, long long sbias_batch, int* status, void* stream) {
+  if (mode != 1 && mode != 2) return OA_ERR_ARG;
+  if (groups < 1 || groups > 256 || max_rows <= 0 || (max_rows & 127)) return OA_ERR_ARG;
+  if ((N & 7) || (ldc & (out_f32 ? 3 : 7))) return OA_ERR_ALIGN;
+  int sms = num_sms();
+  GemmParams p;
+  p.N = N; p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
+  p.bias = (const __nv_bfloat16*)bias; p.residual = nullptr; p.ldr = 0;
+  p.aux_out = (__nv_bfloat16*)aux_out; p.aux_in = (const __nv_bfloat16*)aux_in; p.ldaux = ldaux;
+  p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.splits = 1; p.workspace = nullptr;
+  p.batch = groups; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = sbias_batch;
+  p.group_mode = mode; p.group_offsets = offsets;
+  CUtensorMap ta, tb;
+  int rc, bn, grid;
+  if (mode == 1) {
+    if (K & 7) return OA_ERR_ALIGN;
+    p.M = (int)max_rows; p.K = K; p.sc_batch = 0;
+    bn = (N >= 256) ? 256 : 128;
+    if ((rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)max_rows, 1, (uint64_t)lda, 0, BK, BM))) return rc;
+    if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, groups, (uint64_t)ldb, sb_batch, 64, BK);
+    else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, groups, (uint64_t)ldb, sb_batch, BK, (uint32_t)bn);
+    if (rc) return rc;
+    grid = sms;   // the tile count lives on the device; surplus CTAs exit immediately
+  } else {
+    if ((M & 7)) return OA_ERR_ALIGN;
+    p.M = M; p.K = (int)max_rows; p.sc_batch = sc_batch;
+    bn = (N >= 256) ? 256 : 128;
+    if ((rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)max_rows, 1, (uint64_t)lda, 0, 64, BK))) return rc;
+    if ((rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)max_rows, 1, (uint64_t)ldb, 0, 64, BK))) return rc;
+    long long tiles = (long long)groups * ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
+    grid = tiles < sms ? (int)tiles : sms;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (mode == 1) {
+    if (bn == 256) rc = b_mn ? launch_gemm<256, 0, 1>(ta, tb, p, grid, st) : launch_gemm<256, 0, 0>(ta, tb, p, grid, st);
+    else           rc = b_mn ? launch_gemm<128, 0, 1>(ta, tb, p, grid, st) : launch_gemm<128, 0, 0>(ta, tb, p, grid, st);
+  } else {
+    rc = bn == 256 ? launch_gemm<256, 1, 1>(ta, tb, p, grid, st) : launch_gemm<128, 1, 1>(ta, tb, p, grid, st);
+  }
+  return rc;
 }

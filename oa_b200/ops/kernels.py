@@ -178,6 +178,44 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     raise N.OaKernelError(f"gemm: unsupported dtype {a.dtype}")
 
 
+def bgemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
+          out_dtype: Optional[torch.dtype] = None, accumulate: bool = False, alpha: float = 1.0,
+          residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Batched bf16 GEMM on the tensor cores: out[n] = alpha * A[n] @ B[n]^T (+ residual[n]) (+ out[n]).
+    a is [n, M, K] (or [n, K, M] when a_mn), b is [n, N, K] (or [n, K, N] when b_mn); the last dimension of every
+    operand must be contiguous, the batch and row strides are free."""
+    nb = a.shape[0]
+    M, Kd = (a.shape[2], a.shape[1]) if a_mn else (a.shape[1], a.shape[2])
+    Nn, Kb = (b.shape[2], b.shape[1]) if b_mn else (b.shape[1], b.shape[2])
+    assert Kd == Kb and b.shape[0] == nb
+    odt = out_dtype or (out.dtype if out is not None else a.dtype)
+    if out is None:
+        out = torch.empty((nb, M, Nn), dtype=odt, device=a.device)
+    if not a.is_cuda:
+        A = (a.transpose(1, 2) if a_mn else a).float()
+        B = (b.transpose(1, 2) if b_mn else b).float()
+        v = alpha * torch.bmm(A, B.transpose(1, 2))
+        if residual is not None:
+            v = v + residual.float()
+        if accumulate:
+            v = v + out.float()
+        out.copy_(v)
+        return out
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.stride(2) == 1 and b.stride(2) == 1 and out.stride(2) == 1
+    lib = N.require()
+    ws = workspace(a.device)
+    plain = residual is None
+    rc = lib.oa_gemm_bf16_batched(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, Nn, Kd, a.stride(1), b.stride(1), out.stride(1),
+                                  int(a_mn), int(b_mn), None, N.ptr(residual), residual.stride(1) if residual is not None else 0,
+                                  None, None, 0, ACT_NONE, int(out.dtype == torch.float32), int(accumulate), float(alpha),
+                                  ws.data_ptr() if plain else None, ws.numel() if plain else 0, 0, nb, a.stride(0), b.stride(0),
+                                  out.stride(0), residual.stride(0) if residual is not None else 0, 0, 0,
+                                  status_word(a.device).data_ptr(), N.stream())
+    _launch(rc, f"oa_gemm_bf16_batched n={nb} M={M} N={Nn} K={Kd}")
+    return out
+
+
 def bmm_f32(a: torch.Tensor, b: torch.Tensor, *, b_mn: bool = False, alpha: float = 1.0) -> torch.Tensor:
     """Batched fp32 product out[n] = a[n] @ (b[n] if b_mn else b[n]^T); a [B,M,K], b [B,N,K] or [B,K,N]."""
     Bn, M, K = a.shape

@@ -80,6 +80,25 @@ def test_gemm_bf16_split_k():
     assert torch.equal(out, out2), "split-K reduction must be deterministic"
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_bf16_batched(a_mn, b_mn):
+    torch.manual_seed(12)
+    nb, M, N, K_ = 5, 200, 136, 96
+    a = _rand(nb, K_, M) if a_mn else _rand(nb, M, K_)
+    b = _rand(nb, K_, N) if b_mn else _rand(nb, N, K_)
+    out = K.bgemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = K.bgemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn)
+    _close(out, ref, 1e-2, what="batched gemm")
+    # strided batch view (e.g. heads inside a packed activation) and fp32 accumulate
+    big = _rand(nb, 256, 2 * K_)
+    a2 = big[:, :M, K_:]
+    if not a_mn and not b_mn:
+        acc = torch.randn(nb, M, N, device=DEV)
+        ref2 = acc.cpu() + torch.bmm(a2.cpu().float(), b.cpu().float().transpose(1, 2))
+        K.bgemm(a2, b, out=acc, accumulate=True)
+        _close(acc, ref2, 1e-2, what="batched strided accumulate")
+
+
 def test_gemm_f32():
     torch.manual_seed(3)
     a, b = torch.randn(70, 50, device=DEV), torch.randn(33, 50, device=DEV)
