@@ -135,6 +135,12 @@ int oa_attn_f32_bwd(const float* q, const float* k, const float* v, const float*
                     void* stream);
 
 
+// ---- recurrent scans (rnn.cu): gates = 3 (GRU: reset | update | candidate) or 1 (tanh RNN)
+int oa_rnn_scan_fwd(int dtype, int gates, const void* gates_i, const void* w_hh, const void* b_hh, const void* h0, void* out,
+                    void* hprev, int batch, int seq, int H, void* stream);
+int oa_rnn_scan_bwd(int dtype, int gates, const void* gates_i, const void* w_hh, const void* b_hh, const void* hprev,
+                    const void* dout, void* dgi, void* dgh, void* dh0, int batch, int seq, int H, void* stream);
+
 // ---- mixture of experts (moe.cu)
 int oa_moe_router(int dtype, const void* logits, const float* sel_bias, float* probs, int* topk_idx, float* topk_w,
                   long long tokens, int E, int K, void* stream);

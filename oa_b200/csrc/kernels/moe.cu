@@ -207,7 +207,8 @@ __global__ void moe_plan_place_kernel(const int* __restrict__ topk_idx, long lon
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ packed_token, T* __restrict__ packed,
                                   const int* __restrict__ offsets, int E, int dim, long long max_rows) {
-  const long long rows = min((long long)offsets[E], max_rows);
+  const long long rows = max_rows;   // rows past the last segment are padding too (packed_token = -1): keep them zero
+  (void)offsets; (void)E;
   const int vec = dim / 8;
   long long total = rows * vec;
   long long stride = (long long)gridDim.x * blockDim.x;
@@ -258,7 +259,8 @@ __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ packed,
                                        const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dpacked,
                                        float* __restrict__ dgate, const int* __restrict__ offsets, int E, int Kk, int dim,
                                        long long max_rows) {
-  const long long rows = min((long long)offsets[E], max_rows);
+  const long long rows = max_rows;
+  (void)offsets; (void)E;
   long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (r >= rows) return;

@@ -88,7 +88,8 @@ class OaTrainingProgram:
         g = torch.cuda.CUDAGraph()
         self.StageLog = [("collect", 0.0)]
         try:
-            with torch.cuda.graph(g):
+            # thread-local capture mode: a communication watchdog thread may query events while we capture
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self._outputs = fn()
         except Exception as e:  # leave no half-captured graph behind
             self._graph = None

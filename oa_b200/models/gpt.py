@@ -16,6 +16,7 @@ from ..core.matrix import OaMatrix
 from ..ml import fn_loss as L
 from ..ml.module import OaModule
 from ..ml.nn.layers import OaEmbedding, OaLayerNorm, OaLinear, OaRmsNorm, OaTransformerBlock
+from ..ml.nn.moe import OaMoE
 
 
 @dataclass
@@ -32,6 +33,12 @@ class OaGptConfig:
     Bias: bool = True
     Eps: float = 1e-5
     InitStd: Optional[float] = 0.02
+    NumExperts: int = 0          # > 0: every block's FFN is a sparse MoE layer
+    TopK: int = 2
+    ExpertFf: int = 0
+    SharedExperts: int = 0
+    AuxAlpha: float = 0.0
+    ExpertBias: bool = True
 
     @staticmethod
     def CharLm() -> "OaGptConfig":
@@ -42,6 +49,13 @@ class OaGptConfig:
     def Gpt350M() -> "OaGptConfig":
         """vocab 32000, d 1024, 24 layers, 16 heads (head_dim 64), FFN 4096 GELU, RMSNorm, RoPE, seq 2048."""
         return OaGptConfig(32000, 1024, 24, 16, 4096, 2048, "rms", "gelu", 10000.0, False, 1e-5, 0.02)
+
+    @staticmethod
+    def Moe16x2048() -> "OaGptConfig":
+        """vocab 32000, d 2048, 16 layers, 16 heads, 64 experts top-2 (softmax router), SwiGLU expert FFN 1408, one shared
+        expert, load-balance loss 0.01, RMSNorm, RoPE, seq 2048."""
+        return OaGptConfig(32000, 2048, 16, 16, 1408, 2048, "rms", "swiglu", 10000.0, False, 1e-5, 0.02, NumExperts=64, TopK=2,
+                           ExpertFf=1408, SharedExperts=1, AuxAlpha=0.01, ExpertBias=False)
 
     @staticmethod
     def Llama7B() -> "OaGptConfig":
@@ -60,8 +74,13 @@ class OaGptModel(OaModule):
         self.Blocks = []
         blocks = OaModule()
         for i in range(cfg.NLayers):
+            moe = None
+            if cfg.NumExperts > 0:
+                moe = OaMoE(cfg.DModel, cfg.ExpertFf or cfg.DFf, cfg.NumExperts, cfg.TopK, cfg.Eps, cfg.SharedExperts, cfg.InitStd,
+                            expert_bias=cfg.ExpertBias)
+                moe.SetAuxLossAlpha(cfg.AuxAlpha)
             b = OaTransformerBlock(cfg.DModel, cfg.DFf, cfg.SeqLen, cfg.NHeads, cfg.Eps, norm=cfg.Norm, ffn=cfg.Ffn, bias=cfg.Bias,
-                                   rope_theta=cfg.RopeTheta, init_std=cfg.InitStd)
+                                   rope_theta=cfg.RopeTheta, init_std=cfg.InitStd, moe=moe)
             blocks.RegisterModule(str(i), b)
             self.Blocks.append(b)
         self.RegisterModule("blocks", blocks)
@@ -82,7 +101,11 @@ class OaGptModel(OaModule):
     def Loss(self, ids: OaMatrix, targets: OaMatrix) -> OaMatrix:
         """Mean next-token cross-entropy; the logits buffer is reused for its own gradient."""
         logits = self.Forward(ids)
-        return L.CrossEntropy(logits, targets.Reshape([targets.NumElements()]), in_place_grad=True)
+        loss = L.CrossEntropy(logits, targets.Reshape([targets.NumElements()]), in_place_grad=True)
+        if self.Cfg.NumExperts > 0 and self.Cfg.AuxAlpha > 0:
+            for b in self.Blocks:
+                loss = F.Add(loss, b.Moe.AuxLoss())
+        return loss
 
     def OamConfig(self) -> dict:
         c = self.Cfg
@@ -93,5 +116,8 @@ class OaGptModel(OaModule):
         """Training FLOPs per token (forward + backward = 3x forward), attention counted causal."""
         c = self.Cfg
         ffn_mats = 3 if c.Ffn == "swiglu" else 2
-        per_layer = 2 * (4 * c.DModel * c.DModel + ffn_mats * c.DModel * c.DFf) + 2 * 2 * c.SeqLen * c.DModel / 2
+        ffn = ffn_mats * c.DModel * c.DFf
+        if c.NumExperts > 0:
+            ffn = 3 * c.DModel * (c.ExpertFf or c.DFf) * (c.TopK + c.SharedExperts) + c.DModel * c.NumExperts
+        per_layer = 2 * (4 * c.DModel * c.DModel + ffn) + 2 * 2 * c.SeqLen * c.DModel / 2
         return 3.0 * (c.NLayers * per_layer + 2 * c.DModel * c.Vocab)

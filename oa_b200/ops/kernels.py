@@ -811,3 +811,76 @@ def flash_bwd(q, k, v, o, dout, lse, batch: int, seq: int, heads: int, head_dim:
                                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), batch, heads, seq, head_dim, q.stride(0),
                                 o.stride(0), dq.stride(0), float(scale), int(causal), N.stream()), "oa_attn_f32_bwd", 2)
     return dq, dk, dv
+
+
+# ---------------------------------------------------------------- recurrent scans
+def rnn_scan_fwd(gates_i: torch.Tensor, w_hh: torch.Tensor, b_hh: Optional[torch.Tensor], gates: int, h0: Optional[torch.Tensor] = None,
+                 save: bool = True):
+    """gates_i [B, S, gates*H] (input projection of all steps) -> (out [B,S,H], hprev [B,S,H] or None)."""
+    B, S, GH = gates_i.shape
+    H = GH // gates
+    out = torch.empty((B, S, H), dtype=gates_i.dtype, device=gates_i.device)
+    hprev = torch.empty_like(out) if save else None
+    if not gates_i.is_cuda:
+        h = h0.float().clone() if h0 is not None else torch.zeros(B, H)
+        W = w_hh.float()
+        bb = b_hh.float() if b_hh is not None else 0.0
+        gi_all = gates_i.float()
+        for t in range(S):
+            gh = h @ W.t() + bb
+            gi = gi_all[:, t]
+            if hprev is not None:
+                hprev[:, t] = h
+            if gates == 3:
+                r = torch.sigmoid(gi[:, :H] + gh[:, :H])
+                z = torch.sigmoid(gi[:, H:2 * H] + gh[:, H:2 * H])
+                n = torch.tanh(gi[:, 2 * H:] + r * gh[:, 2 * H:])
+                h = (1 - z) * n + z * h
+            else:
+                h = torch.tanh(gi + gh)
+            out[:, t] = h
+        return out, hprev
+    _launch(N.require().oa_rnn_scan_fwd(dt(gates_i), gates, gates_i.contiguous().data_ptr(), w_hh.contiguous().data_ptr(), N.ptr(b_hh),
+                                        N.ptr(h0), out.data_ptr(), N.ptr(hprev), B, S, H, N.stream()), "oa_rnn_scan_fwd")
+    return out, hprev
+
+
+def rnn_scan_bwd(gates_i, w_hh, b_hh, hprev, dout, gates: int):
+    """Returns (dgates_i [B,S,gates*H], dgates_h [B,S,gates*H], dh0 [B,H])."""
+    B, S, GH = gates_i.shape
+    H = GH // gates
+    dgi = torch.empty_like(gates_i)
+    dgh = torch.empty_like(gates_i)
+    dh0 = torch.empty((B, H), dtype=gates_i.dtype, device=gates_i.device)
+    if not gates_i.is_cuda:
+        W = w_hh.float()
+        bb = b_hh.float() if b_hh is not None else 0.0
+        carry = torch.zeros(B, H)
+        gi_all, hp_all, do_all = gates_i.float(), hprev.float(), dout.float()
+        for t in range(S - 1, -1, -1):
+            hp = hp_all[:, t]
+            gh = hp @ W.t() + bb
+            gi = gi_all[:, t]
+            d = do_all[:, t] + carry
+            if gates == 3:
+                r = torch.sigmoid(gi[:, :H] + gh[:, :H])
+                z = torch.sigmoid(gi[:, H:2 * H] + gh[:, H:2 * H])
+                n = torch.tanh(gi[:, 2 * H:] + r * gh[:, 2 * H:])
+                dn_pre = d * (1 - z) * (1 - n * n)
+                dz_pre = d * (hp - n) * z * (1 - z)
+                dr_pre = dn_pre * gh[:, 2 * H:] * r * (1 - r)
+                gi_g = torch.cat([dr_pre, dz_pre, dn_pre], 1)
+                gh_g = torch.cat([dr_pre, dz_pre, dn_pre * r], 1)
+                carry = d * z + gh_g @ W
+            else:
+                hn = torch.tanh(gi + gh)
+                gi_g = gh_g = d * (1 - hn * hn)
+                carry = gh_g @ W
+            dgi[:, t] = gi_g
+            dgh[:, t] = gh_g
+        dh0.copy_(carry)
+        return dgi, dgh, dh0
+    _launch(N.require().oa_rnn_scan_bwd(dt(gates_i), gates, gates_i.contiguous().data_ptr(), w_hh.contiguous().data_ptr(), N.ptr(b_hh),
+                                        hprev.data_ptr(), dout.contiguous().data_ptr(), dgi.data_ptr(), dgh.data_ptr(), dh0.data_ptr(),
+                                        B, S, H, N.stream()), "oa_rnn_scan_bwd")
+    return dgi, dgh, dh0
