@@ -158,6 +158,46 @@ int oa_moe_combine_bwd(const void* packed, const float* gate, const int* inverse
 int oa_moe_gather_bwd(const void* dpacked, const int* inverse, const void* base, void* dx, long long tokens, int K, int dim,
                       void* stream);
 
+// expert parallelism over peer memory (moe.cu): layout from the exchanged counts, dispatch (push), combine (pull)
+int oa_ep_layout(const int* counts_all, const int* topk_idx, const int* inverse, const int* offsets_local, int* route_rank,
+                 int* route_row, int* loc_offsets, int* loc_counts, int* counts_global, long long routes, int E, int world,
+                 int rank, void* stream);
+int oa_ep_push_rows(const void* x, const void* const* dst_peers, const int* route_rank, const int* route_row, const float* gate,
+                    long long routes, int K, int dim, int world, int cap_rows, int* status, void* stream);
+int oa_ep_pull_rows(const void* const* src_peers, const int* route_rank, const int* route_row, const float* gate, const void* base,
+                    void* out, long long tokens, int K, int dim, int world, void* stream);
+int oa_ep_pull_dot(const void* const* src_peers, const int* route_rank, const int* route_row, const void* dout, float* dgate,
+                   long long routes, int K, int dim, int world, void* stream);
+int oa_ep_zero_pad(void* buf, const int* loc_offsets, const int* loc_counts, int E_loc, int dim, void* stream);
+
+// ---- Mamba-3 SISO selective scan (mamba3.cu): preprocess, chunk-checkpointed scan forward/backward, decode step
+int oa_mamba3_pre_fwd(int dtype, const void* proj, long long stride, const float* dt_bias, int rows, int H, int N, int A,
+                      int d_inner, float eps, float dt_min, float dt_max, float afloor, float* Bn, float* Cn, float* rstd,
+                      float* dt, float* adt, float* trap, float* angle, void* stream);
+int oa_mamba3_pre_bwd(int dtype, const void* proj, void* dproj, long long stride, const float* dt_bias, int rows, int H, int N,
+                      int A, int d_inner, float eps, float dt_min, float dt_max, float afloor, const float* Bn,
+                      const float* Cn, const float* rstd, const float* dBn, const float* dCn, const float* ddt,
+                      const float* dadt, const float* dtrap, const float* dangle, float* ddt_bias, void* stream);
+int oa_mamba3_scan_fwd(int dtype, const void* x, const void* z, long long xs, const float* Cn, const float* Bn, const float* dt,
+                       const float* adt, const float* trap, const float* angle, const float* Cb, const float* Bb,
+                       const float* D, void* y, long long ys, float* Hck, float* Tck, float* Hfinal, float* Tfinal,
+                       float* Kfinal, float* Vfinal, int B, int L, int H, int P, int N, int A, int chunk, void* stream);
+size_t oa_mamba3_scratch_floats(int B, int H, int P, int N, int chunk);
+int oa_mamba3_scan_bwd(int dtype, const void* x, const void* z, long long xs, const float* Cn, const float* Bn, const float* dt,
+                       const float* adt, const float* trap, const float* angle, const float* Cb, const float* Bb,
+                       const float* D, const void* dy, long long dys, void* dx, void* dz, long long dxs, float* dCn,
+                       float* dBn, float* ddt, float* dadt, float* dtrap, float* dangle, float* dCb, float* dBb, float* dD,
+                       const float* Hck, const float* Tck, float* scratch, int B, int L, int H, int P, int N, int A,
+                       int chunk, void* stream);
+int oa_mamba3_step(int dtype, const void* x, const void* z, long long xs, const float* Cn, const float* Bn, const float* dt,
+                   const float* adt, const float* trap, const float* angle, const float* Cb, const float* Bb, const float* D,
+                   void* y, long long ys, float* Hst, float* Vst, const float* Tin, const float* Kin, float* Tout,
+                   float* Kout, int B, int H, int P, int N, int A, int first, void* stream);
+int oa_gated_norm_fwd(int dtype, const void* y, const void* z, long long zs, const float* w, void* out, float* rstd,
+                      long long rows, int H, int P, float eps, void* stream);
+int oa_gated_norm_bwd(int dtype, const void* y, const void* z, long long zs, const float* w, const float* rstd, const void* dout,
+                      void* dy, void* dz, long long dzs, float* dw, long long rows, int H, int P, void* stream);
+
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);
 int oa_ipc_free(void* p);

@@ -401,3 +401,191 @@ extern "C" int oa_moe_gather_bwd(const void* dpacked, const int* inverse, const 
   moe_gather_bwd_kernel<<<mgrid(tokens * (dim / 8)), 256, 0, ST>>>((const __nv_bfloat16*)dpacked, inverse, (const __nv_bfloat16*)base, (__nv_bfloat16*)dx, tokens, K, dim);
   return CHECK_LAUNCH();
 }
+
+// =====================================================================================================
+// Expert parallelism: the all-to-all dispatch / combine as peer-memory kernels (one process per GPU).
+// Rank s owns experts [s*E_loc, (s+1)*E_loc).  Every rank knows counts_all[src][e] (exchanged with oa_peer_push), so
+// every sender can compute the row that each of its routes occupies in the owner's expert-major buffer:
+//   row = seg_off[e] + sum_{s' < s} counts_all[s'][e] + (rank of the route among this sender's routes to e)
+// with seg_off the owner's 128-padded segment starts.  Dispatch = gather fused with the remote store (rows are
+// written straight into the owner's buffer over NVLink), combine = weighted pull of the result rows from the owners.
+namespace oa {
+
+struct PeerPtrs { void* ptr[8]; };
+
+// Per-route destination: route_rank[r], route_row[r]; owner-side plan: loc_offsets[E_loc+1], loc_counts[E_loc],
+// loc_valid[max_rows] (1 = real row, 0 = padding).
+__global__ void ep_layout_kernel(const int* __restrict__ counts_all, const int* __restrict__ topk_idx, const int* __restrict__ inverse,
+                                 const int* __restrict__ offsets_local, int* __restrict__ route_rank, int* __restrict__ route_row,
+                                 int* __restrict__ loc_offsets, int* __restrict__ loc_counts, int* __restrict__ counts_global,
+                                 long long routes, int E, int world, int rank) {
+  __shared__ int seg_off[MOE_MAX_E];     // owner-local padded segment start of every global expert
+  __shared__ int src_off[MOE_MAX_E];     // rows of earlier sources inside the segment
+  const int E_loc = E / world;
+  if (threadIdx.x == 0) {
+    for (int d = 0; d < world; ++d) {
+      int off = 0;
+      for (int le = 0; le < E_loc; ++le) {
+        int e = d * E_loc + le, tot = 0, before = 0;
+        for (int s = 0; s < world; ++s) {
+          int c = counts_all[s * E + e];
+          if (s < rank) before += c;
+          tot += c;
+        }
+        seg_off[e] = off;
+        src_off[e] = before;
+        if (blockIdx.x == 0) {
+          counts_global[e] = tot;
+          if (d == rank) { loc_offsets[le] = off; loc_counts[le] = tot; }
+        }
+        off += (tot + MOE_SEG_ALIGN - 1) / MOE_SEG_ALIGN * MOE_SEG_ALIGN;
+      }
+      if (blockIdx.x == 0 && d == rank) loc_offsets[E_loc] = off;
+    }
+  }
+  __syncthreads();
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < routes; r += stride) {
+    int e = topk_idx[r];
+    int within = inverse[r] - offsets_local[e];
+    route_rank[r] = e / E_loc;
+    route_row[r] = seg_off[e] + src_off[e] + within;
+  }
+}
+
+// dst_peer[route_rank[r]][route_row[r], :] = scale_r * x[token(r), :]   (scale = gate[r] when given)
+__global__ void ep_push_rows_kernel(const __nv_bfloat16* __restrict__ x, PeerPtrs dst, const int* __restrict__ route_rank,
+                                    const int* __restrict__ route_row, const float* __restrict__ gate, long long routes, int Kk,
+                                    int dim, int cap_rows, int* status) {
+  const int vec = dim / 8;
+  long long total = routes * vec;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    long long r = i / vec;
+    int c = (int)(i % vec) * 8;
+    uint4 v = *reinterpret_cast<const uint4*>(x + (r / Kk) * dim + c);
+    if (gate) {
+      const float g = gate[r];
+      float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+      v = make_uint4(pack_bf16x2(g * f0.x, g * f0.y), pack_bf16x2(g * f1.x, g * f1.y), pack_bf16x2(g * f2.x, g * f2.y),
+                     pack_bf16x2(g * f3.x, g * f3.y));
+    }
+    const int row = route_row[r];
+    if (row < 0 || row >= cap_rows) {          // more rows than the owner's buffer holds: drop and report
+      if (c == 0) report_error(status, OA_KERR_BAD_ARG);
+      continue;
+    }
+    __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(dst.ptr[route_rank[r]]) + (long long)row * dim + c;
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(d), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+}
+
+// out[t,:] = base[t,:] + sum_k gate[t,k] * src_peer[rank(t,k)][row(t,k), :]; when dgate != null also
+// dgate[t,k] = <dout[t,:], src_peer[..][row,:]> (backward of combine) and nothing is written to out.
+__global__ void ep_pull_rows_kernel(PeerPtrs src, const int* __restrict__ route_rank, const int* __restrict__ route_row,
+                                    const float* __restrict__ gate, const __nv_bfloat16* __restrict__ base,
+                                    __nv_bfloat16* __restrict__ out, long long tokens, int Kk, int dim) {
+  const int vec = dim / 8;
+  long long total = tokens * vec;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    long long t = i / vec;
+    int c = (int)(i % vec) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (base) {
+      uint4 b = *reinterpret_cast<const uint4*>(base + t * dim + c);
+      float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+      acc[0] = f0.x; acc[1] = f0.y; acc[2] = f1.x; acc[3] = f1.y; acc[4] = f2.x; acc[5] = f2.y; acc[6] = f3.x; acc[7] = f3.y;
+    }
+    for (int k = 0; k < Kk; ++k) {
+      const long long r = t * Kk + k;
+      const float g = gate ? gate[r] : 1.f;
+      const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.ptr[route_rank[r]]) + (long long)route_row[r] * dim + c;
+      uint4 b;
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(s) : "memory");
+      float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
+      acc[0] += g * f0.x; acc[1] += g * f0.y; acc[2] += g * f1.x; acc[3] += g * f1.y;
+      acc[4] += g * f2.x; acc[5] += g * f2.y; acc[6] += g * f3.x; acc[7] += g * f3.y;
+    }
+    *reinterpret_cast<uint4*>(out + t * dim + c) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                              pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+// dgate[r] = <dout[token(r), :], src_peer[rank(r)][row(r), :]>, one warp per route.
+__global__ void ep_pull_dot_kernel(PeerPtrs src, const int* __restrict__ route_rank, const int* __restrict__ route_row,
+                                   const __nv_bfloat16* __restrict__ dout, float* __restrict__ dgate, long long routes, int Kk, int dim) {
+  long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (r >= routes) return;
+  const __nv_bfloat16* s = reinterpret_cast<const __nv_bfloat16*>(src.ptr[route_rank[r]]) + (long long)route_row[r] * dim;
+  const __nv_bfloat16* d = dout + (r / Kk) * dim;
+  float dot = 0.f;
+  for (int c = lane * 8; c < dim; c += 256) {
+    uint4 y;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(y.x), "=r"(y.y), "=r"(y.z), "=r"(y.w) : "l"(s + c) : "memory");
+    uint4 g = *reinterpret_cast<const uint4*>(d + c);
+    float2 d0 = unpack_bf16x2(g.x), d1 = unpack_bf16x2(g.y), d2 = unpack_bf16x2(g.z), d3 = unpack_bf16x2(g.w);
+    float2 y0 = unpack_bf16x2(y.x), y1 = unpack_bf16x2(y.y), y2 = unpack_bf16x2(y.z), y3 = unpack_bf16x2(y.w);
+    dot += d0.x * y0.x + d0.y * y0.y + d1.x * y1.x + d1.y * y1.y + d2.x * y2.x + d2.y * y2.y + d3.x * y3.x + d3.y * y3.y;
+  }
+  dot = warp_sum(dot);
+  if (lane == 0) dgate[r] = dot;
+}
+
+// Zeroes the padding rows of an owner-side buffer: rows [loc_offsets[le] + loc_counts[le], loc_offsets[le+1]).
+__global__ void ep_zero_pad_kernel(__nv_bfloat16* buf, const int* __restrict__ loc_offsets, const int* __restrict__ loc_counts,
+                                   int E_loc, int dim) {
+  const int le = blockIdx.y;
+  const int r0 = loc_offsets[le] + loc_counts[le], r1 = loc_offsets[le + 1];
+  const int vec = dim / 8;
+  long long total = (long long)(r1 - r0) * vec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+    *reinterpret_cast<uint4*>(buf + (long long)(r0 + i / vec) * dim + (i % vec) * 8) = make_uint4(0, 0, 0, 0);
+}
+
+}  // namespace oa
+
+static PeerPtrs make_peers(const void* const* ptrs, int world) {
+  PeerPtrs t;
+  for (int i = 0; i < 8; ++i) t.ptr[i] = i < world ? const_cast<void*>(ptrs[i]) : nullptr;
+  return t;
+}
+
+extern "C" int oa_ep_layout(const int* counts_all, const int* topk_idx, const int* inverse, const int* offsets_local,
+                            int* route_rank, int* route_row, int* loc_offsets, int* loc_counts, int* counts_global,
+                            long long routes, int E, int world, int rank, void* stream) {
+  if (E > MOE_MAX_E || world < 1 || world > 8 || E % world) return OA_ERR_ARG;
+  ep_layout_kernel<<<mgrid(routes), 256, 0, ST>>>(counts_all, topk_idx, inverse, offsets_local, route_rank, route_row, loc_offsets,
+                                                  loc_counts, counts_global, routes, E, world, rank);
+  return CHECK_LAUNCH();
+}
+extern "C" int oa_ep_push_rows(const void* x, const void* const* dst_peers, const int* route_rank, const int* route_row,
+                               const float* gate, long long routes, int K, int dim, int world, int cap_rows, int* status,
+                               void* stream) {
+  if (dim % 8) return OA_ERR_ALIGN;
+  ep_push_rows_kernel<<<mgrid(routes * (dim / 8)), 256, 0, ST>>>((const __nv_bfloat16*)x, make_peers(dst_peers, world), route_rank,
+                                                                route_row, gate, routes, K, dim, cap_rows, status);
+  return CHECK_LAUNCH();
+}
+extern "C" int oa_ep_pull_rows(const void* const* src_peers, const int* route_rank, const int* route_row, const float* gate,
+                               const void* base, void* out, long long tokens, int K, int dim, int world, void* stream) {
+  if (dim % 8) return OA_ERR_ALIGN;
+  ep_pull_rows_kernel<<<mgrid(tokens * (dim / 8)), 256, 0, ST>>>(make_peers(src_peers, world), route_rank, route_row, gate,
+                                                                (const __nv_bfloat16*)base, (__nv_bfloat16*)out, tokens, K, dim);
+  return CHECK_LAUNCH();
+}
+extern "C" int oa_ep_pull_dot(const void* const* src_peers, const int* route_rank, const int* route_row, const void* dout,
+                              float* dgate, long long routes, int K, int dim, int world, void* stream) {
+  if (dim % 8) return OA_ERR_ALIGN;
+  unsigned blocks = (unsigned)((routes + 7) / 8);
+  ep_pull_dot_kernel<<<blocks, 256, 0, ST>>>(make_peers(src_peers, world), route_rank, route_row, (const __nv_bfloat16*)dout, dgate,
+                                             routes, K, dim);
+  return CHECK_LAUNCH();
+}
+extern "C" int oa_ep_zero_pad(void* buf, const int* loc_offsets, const int* loc_counts, int E_loc, int dim, void* stream) {
+  if (dim % 8) return OA_ERR_ALIGN;
+  dim3 grid(8, E_loc);
+  ep_zero_pad_kernel<<<grid, 256, 0, ST>>>((__nv_bfloat16*)buf, loc_offsets, loc_counts, E_loc, dim);
+  return CHECK_LAUNCH();
+}

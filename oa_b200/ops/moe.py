@@ -177,10 +177,11 @@ def _segments(P: Plan):
 
 
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], P: Plan, *, b_mn: bool = False,
-                   act: int = K.ACT_NONE) -> torch.Tensor:
+                   act: int = K.ACT_NONE, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[r,:] = x[r,:] @ W[e(r)]^T (+ bias[e(r)]).  w is [E, N, K] (or [E, K, N] with b_mn: the data-gradient form)."""
     Nn = w.shape[2] if b_mn else w.shape[1]
-    out = torch.empty((P.max_rows, Nn), dtype=x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty((P.max_rows, Nn), dtype=x.dtype, device=x.device)
     if not x.is_cuda:
         out.zero_()
         for e, lo, hi in _segments(P):

@@ -1,0 +1,220 @@
+"""Mamba-3 SISO: the PyTorch statement against a naive scalar recurrence, decode step against the full forward,
+module gradients against torch.autograd (CPU), and the CUDA kernels against the PyTorch statement (GPU)."""
+import math
+
+import pytest
+import torch
+
+from oa_b200.ops import mamba3 as M3
+
+
+def _dims(H=2, P=4, N=8, A=2, has_z=True, chunk=16):
+    return M3.Mamba3Dims(d_inner=H * P, heads=H, headdim=P, d_state=N, angles=A, has_z=has_z, chunk=chunk)
+
+
+def _inputs(d, B, L, device="cpu", dtype=torch.float32, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    proj = torch.randn(B * L, d.d_in_proj, generator=g)
+    o = d.offsets()
+    proj[:, o[4]:o[4] + d.heads] -= 3.0                 # dt around softplus(-3 + bias): inside the clamp for most entries
+    proj[:, o[7]:] *= 3.0                               # visible rotation
+    dt_bias = torch.rand(1, d.heads, generator=g)
+    Bb = 1.0 + 0.1 * torch.randn(d.heads, d.d_state, generator=g)
+    Cb = 1.0 + 0.1 * torch.randn(d.heads, d.d_state, generator=g)
+    D = 0.5 * torch.randn(d.heads, generator=g)
+    mv = lambda t, dt_=torch.float32: t.to(device=device, dtype=dt_)
+    return mv(proj, dtype), mv(dt_bias), mv(Bb), mv(Cb), mv(D)
+
+
+def _naive(proj, dt_bias, Bb, Cb, D, d, B, L):
+    """Scalar loops, look-ahead form: scale_t = gamma_t + dt_{t+1} (1 - sigmoid(trap_{t+1}))."""
+    z, x, Bn, Cn, dt, adt, trap, angle = [t.double() for t in M3.reference_preprocess(proj, dt_bias, d, B, L)]
+    H, P, N, A = d.heads, d.headdim, d.d_state, d.angles
+    y = torch.zeros(B, L, H, P, dtype=torch.float64)
+    for b in range(B):
+        for h in range(H):
+            Hs = torch.zeros(P, N, dtype=torch.float64)
+            th = torch.zeros(A, dtype=torch.float64)
+            for t in range(L):
+                th = th + angle[b, t] * dt[b, t, h]
+                C = Cn[b, t] + Cb[h].double()
+                Bv = Bn[b, t] + Bb[h].double()
+                Cr, Br = C.clone(), Bv.clone()
+                for k in range(A):
+                    c, s = math.cos(th[k]), math.sin(th[k])
+                    Cr[2 * k], Cr[2 * k + 1] = C[2 * k] * c - C[2 * k + 1] * s, C[2 * k] * s + C[2 * k + 1] * c
+                    Br[2 * k], Br[2 * k + 1] = Bv[2 * k] * c - Bv[2 * k + 1] * s, Bv[2 * k] * s + Bv[2 * k + 1] * c
+                a = math.exp(adt[b, t, h])
+                gamma = dt[b, t, h] * torch.sigmoid(trap[b, t, h])
+                sg = dt[b, t + 1, h] * (1 - torch.sigmoid(trap[b, t + 1, h])) if t + 1 < L else 0.0
+                qk = (Cr * Br).sum()
+                xt = x[b, t, h * P:(h + 1) * P]
+                yt = (a * Hs) @ Cr + (D[h].double() + gamma * qk) * xt
+                if d.has_z:
+                    zt = z[b, t, h * P:(h + 1) * P]
+                    yt = yt * zt * torch.sigmoid(zt)
+                y[b, t, h] = yt
+                Hs = a * Hs + (gamma + sg) * xt[:, None] * Br[None, :]
+    return y.reshape(B * L, H * P)
+
+
+@pytest.mark.parametrize("has_z", [True, False])
+def test_reference_matches_naive_recurrence(has_z):
+    d = _dims(has_z=has_z)
+    B, L = 2, 9
+    args = _inputs(d, B, L)
+    got = M3.reference_core(*args, d, B, L)
+    want = _naive(*args, d, B, L)
+    assert (got.double() - want).abs().max().item() < 1e-5
+
+
+def test_step_matches_forward_cpu():
+    d = _dims()
+    B, L = 2, 7
+    proj, dtb, Bb, Cb, D = _inputs(d, B, L)
+    full = M3.reference_core(proj, dtb, Bb, Cb, D, d, B, L).reshape(B, L, -1)
+    state = {}
+    p3 = proj.reshape(B, L, -1)
+    for t in range(L):
+        y = M3.step(p3[:, t].contiguous(), dtb, Bb, Cb, D, d, state)
+        assert (y - full[:, t]).abs().max().item() < 1e-5
+    # prefill 4 tokens, then step the rest
+    st = {}
+    M3.core_fwd(p3[:, :4].reshape(B * 4, -1).contiguous(), dtb, Bb, Cb, D, d, B, 4, save=False, final=st)
+    for t in range(4, L):
+        y = M3.step(p3[:, t].contiguous(), dtb, Bb, Cb, D, d, st)
+        assert (y - full[:, t]).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("norm", [False, True])
+def test_module_gradients_cpu(norm):
+    from oa_b200.core.matrix import OaMatrix
+    from oa_b200.ml import autograd as AG
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.ml.nn.mamba3 import OaMamba3Module
+
+    torch.manual_seed(0)
+    m = OaMamba3Module(16, d_state=16, expand=2, headdim=8, is_outproj_norm=norm, chunk=8)
+    B, L = 2, 6
+    x = torch.randn(B, L, 16)
+    for p in m.Parameters():
+        p.Data.Tensor().copy_(p.Data.Tensor() + 0.05 * torch.randn_like(p.Data.Tensor()))
+    tape = AG.OaGradientTape()
+    xm = OaMatrix(x.clone())
+    xm.SetRequiresGrad(True)
+    out = m.Forward(xm)
+    w = torch.randn(B, L, 16)
+    loss = F.Sum(F.Mul(out, OaMatrix(w)))
+    tape.Backward(loss)
+    tape.Close()
+    # the same composite in plain torch
+    leaves = {p.Name: p.Data.Tensor().detach().clone().requires_grad_(True) for p in m.Parameters()}
+    xt = x.clone().requires_grad_(True)
+    proj = xt.reshape(B * L, 16) @ leaves["in_proj"].t()
+    y = M3.reference_core(proj, leaves["dt_bias"], leaves["B_bias"], leaves["C_bias"], leaves["D"], m.Dims, B, L)
+    if norm:
+        H, P = m.NHeads, m.HeadDim
+        yf = y.reshape(B * L, H, P)
+        zf = proj[:, :m.DInner].reshape(B * L, H, P)
+        y = (yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + 1e-5) * leaves["norm_weight"].reshape(1, H, P)
+             * torch.nn.functional.silu(zf)).reshape(B * L, H * P)
+    ref_out = (y @ leaves["out_proj"].t()).reshape(B, L, 16)
+    assert (out.Tensor() - ref_out).abs().max().item() < 1e-4
+    (ref_out * w).sum().backward()
+    assert (xm.GradTensor() - xt.grad).abs().max().item() < 1e-4
+    for p in m.Parameters():
+        g, r = p.Grad().Tensor().float(), leaves[p.Name].grad
+        assert (g.reshape(r.shape) - r).abs().max().item() <= 1e-4 * max(1.0, r.abs().max().item()), p.Name
+
+
+# --------------------------------------------------------------------------------------------------------------- GPU
+CASES = [
+    dict(H=4, P=16, N=32, A=8, B=2, L=41, chunk=16),       # several chunks, ragged last chunk and sub-chunk
+    dict(H=2, P=64, N=128, A=32, B=2, L=70, chunk=32),     # the large-model head shape
+    dict(H=3, P=8, N=16, A=0, B=1, L=9, chunk=8),          # no rotary angles, small head
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("has_z", [True, False])
+def test_scan_kernels_match_reference(case, has_z):
+    from oa_b200.ops import kernels as K
+    c = dict(case)
+    B, L = c.pop("B"), c.pop("L")
+    d = _dims(has_z=has_z, **c)
+    cpu = _inputs(d, B, L)
+    gpu = tuple(t.cuda() for t in cpu)
+    y, saved = M3.core_fwd(gpu[0], *gpu[1:], d, B, L, save=True)
+    want = M3.reference_core(*cpu, d, B, L)
+    assert (y.cpu() - want).abs().max().item() <= 2e-4 * max(1.0, want.abs().max().item())
+    dy = torch.randn(B * L, d.d_inner, generator=torch.Generator().manual_seed(1))
+    got = M3.core_bwd(saved, dy.cuda())
+    _, scpu = M3.core_fwd(cpu[0], *cpu[1:], d, B, L)
+    ref = M3.core_bwd(scpu, dy)
+    for g, r, nm in zip(got, ref, ("dproj", "ddt_bias", "dB_bias", "dC_bias", "dD")):
+        scale = max(1.0, r.abs().max().item())
+        err = (g.cpu().float().reshape(r.shape) - r.float()).abs().max().item()
+        assert err <= 5e-4 * scale, (nm, err, scale)
+    torch.cuda.synchronize()
+    K.check_status()
+
+
+@pytest.mark.gpu
+def test_step_kernel_matches_forward():
+    d = _dims(H=4, P=16, N=32, A=8, chunk=16)
+    B, L = 3, 12
+    cpu = _inputs(d, B, L)
+    gpu = tuple(t.cuda() for t in cpu)
+    full = M3.reference_core(*cpu, d, B, L).reshape(B, L, -1)
+    p3 = gpu[0].reshape(B, L, -1)
+    st = {}
+    for t in range(L):
+        y = M3.step(p3[:, t].contiguous(), *gpu[1:], d, st)
+        assert (y.cpu() - full[:, t]).abs().max().item() < 2e-4, t
+    st = {}
+    M3.core_fwd(p3[:, :5].reshape(B * 5, -1).contiguous(), *gpu[1:], d, B, 5, save=False, final=st)
+    for t in range(5, L):
+        y = M3.step(p3[:, t].contiguous(), *gpu[1:], d, st)
+        assert (y.cpu() - full[:, t]).abs().max().item() < 2e-4, t
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("P", [16, 64])
+def test_gated_norm_kernels(P):
+    H, rows = 4, 37
+    d = M3.Mamba3Dims(d_inner=H * P, heads=H, headdim=P, d_state=16, angles=2, has_z=False)
+    g = torch.Generator().manual_seed(0)
+    y = torch.randn(rows, H * P, generator=g)
+    proj = torch.randn(rows, d.d_in_proj, generator=g)
+    w = 1 + 0.1 * torch.randn(H, P, generator=g)
+    do = torch.randn(rows, H * P, generator=g)
+    out_r, rstd_r = M3.gated_norm_fwd(y, proj, w, d)
+    dproj_r = torch.zeros_like(proj)
+    dy_r, dw_r = M3.gated_norm_bwd(y, proj, w, rstd_r, do, d, dproj_r)
+    out, rstd = M3.gated_norm_fwd(y.cuda(), proj.cuda(), w.cuda(), d)
+    dproj = torch.zeros_like(proj).cuda()
+    dy, dw = M3.gated_norm_bwd(y.cuda(), proj.cuda(), w.cuda(), rstd, do.cuda(), d, dproj)
+    for a, b in ((out, out_r), (dy, dy_r), (dw, dw_r), (dproj, dproj_r)):
+        assert (a.cpu() - b).abs().max().item() <= 1e-4 * max(1.0, b.abs().max().item())
+
+
+@pytest.mark.gpu
+def test_module_bf16_runs_and_tracks_fp32():
+    from oa_b200.core.matrix import OaMatrix
+    from oa_b200.ml.nn.mamba3 import OaMamba3Module
+    from oa_b200.ops import kernels as K
+
+    d = _dims(H=4, P=16, N=32, A=8, chunk=16)
+    B, L = 2, 33
+    cpu = _inputs(d, B, L)
+    y, saved = M3.core_fwd(cpu[0].cuda().bfloat16(), *[t.cuda() for t in cpu[1:]], d, B, L)
+    want = M3.reference_core(cpu[0].bfloat16().float(), *cpu[1:], d, B, L)
+    assert (y.float().cpu() - want).abs().max().item() <= 3e-2 * max(1.0, want.abs().max().item())
+    dy = torch.randn(B * L, d.d_inner).bfloat16()
+    got = M3.core_bwd(saved, dy.cuda())
+    _, scpu = M3.core_fwd(cpu[0].bfloat16().float(), *cpu[1:], d, B, L)
+    ref = M3.core_bwd(scpu, dy.float())
+    for g, r in zip(got, ref):
+        assert (g.cpu().float().reshape(r.shape) - r).abs().max().item() <= 4e-2 * max(1.0, r.abs().max().item())
+    K.check_status()
