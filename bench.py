@@ -94,7 +94,7 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="oa_b200")
-    ap.add_argument("--model", default="gpt350m", choices=["gpt350m", "tiny"])
+    ap.add_argument("--model", default="gpt350m", choices=["gpt350m", "tiny", "mamba3", "mamba3-tiny", "moe"])
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
@@ -131,12 +131,21 @@ def main() -> int:
 
     cfg_e = OaEngineConfig(Precision=OaPrecision.BF16, DeviceIndex=local_rank)
     assert OaInitComputeEngine(cfg_e)
-    mcfg = OaGptConfig.Gpt350M() if args.model == "gpt350m" else OaGptConfig(1024, 256, 2, 4, 1024, 256, "rms", "gelu", 10000.0, False, 1e-5, 0.02)
+    from oa_b200.models import OaMamba3Config, OaMamba3LmModel
+    names = {"gpt350m": "dense GPT 24x1024, 16 heads, FFN 4096 GELU, RMSNorm, RoPE, vocab 32000", "tiny": "tiny",
+             "mamba3": "Mamba-3 32x1536, state 128, expand 2, head dim 64, chunk 256, vocab 32000", "mamba3-tiny": "mamba3-tiny",
+             "moe": "sparse MoE 16x2048, 64 experts top-2, SwiGLU 1408, 1 shared expert, vocab 32000 (single-GPU experts)"}
+    if args.model in ("mamba3", "mamba3-tiny"):
+        mcfg = OaMamba3Config.Mamba3_32x1536() if args.model == "mamba3" else OaMamba3Config(1024, 256, 2, 32, 2, 16, 256, 64)
+    elif args.model == "moe":
+        mcfg = OaGptConfig.Moe16x2048()
+    else:
+        mcfg = OaGptConfig.Gpt350M() if args.model == "gpt350m" else OaGptConfig(1024, 256, 2, 4, 1024, 256, "rms", "gelu", 10000.0, False, 1e-5, 0.02)
     if args.seq:
         mcfg.SeqLen = args.seq
     B, S = args.micro_batch, mcfg.SeqLen
     F.SetRngSeed(20260714)                      # same weights on every rank
-    model = OaGptModel(mcfg)
+    model = OaMamba3LmModel(mcfg) if args.model.startswith("mamba3") else OaGptModel(mcfg)
     params = model.AllParameterPtrs()
     opt = OaAdamW(params, 3e-4, weight_decay=0.1)
     dp = None
@@ -237,7 +246,7 @@ def main() -> int:
         "metric": "train tokens/s (device-timed, max over ranks)", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform token ids, random-init N(0,0.02) weights)",
-        "config": {"model": "dense GPT 24x1024, 16 heads, FFN 4096 GELU, RMSNorm, RoPE, vocab 32000" if args.model == "gpt350m" else "tiny",
+        "config": {"model": names[args.model],
                    "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}", "optimizer": "AdamW fp32 master",
                    "l2": "inputs larger than L2 (activations and weights >> 126 MB per step)",
                    "executor": "cuda graph replay" if (prog is not None and prog.IsCaptured()) else "eager stream",
