@@ -250,8 +250,15 @@ def Silu(m): return _unary("Silu", "silu", m, 0.0, lambda x, y, g: K.binary("sil
 def Tanh(m): return _unary("Tanh", "tanh", m, 0.0, lambda x, y, g: K.binary("tanh_bwd", y, g))
 def Sigmoid(m): return _unary("Sigmoid", "sigmoid", m, 0.0, lambda x, y, g: K.binary("sigmoid_bwd", y, g))
 def Softplus(m): return _unary("Softplus", "softplus", m, 0.0, lambda x, y, g: K.binary("softplus_bwd", x, g))
-def LeakyRelu(m, slope: float = 0.01): return _unary("LeakyRelu", "leaky_relu", m, slope, lambda x, y, g: K.binary("leaky_relu_bwd", x, g))
-def Elu(m, alpha: float = 1.0): return _unary("Elu", "elu", m, alpha, lambda x, y, g: K.binary("elu_bwd", x, g))
+def LeakyRelu(m, slope: float = 0.01):
+    # d/dx = slope + (1 - slope) * [x > 0]
+    return _unary("LeakyRelu", "leaky_relu", m, slope,
+                  lambda x, y, g: K.binary("add", K.unary("scale", K.binary("relu_bwd", x, g), 1.0 - slope), K.unary("scale", g, slope)))
+def Elu(m, alpha: float = 1.0):
+    def bwd(x, y, g):           # d/dx = 1 for x > 0, y + alpha otherwise
+        r = K.binary("relu_bwd", x, g)
+        return K.binary("add", r, K.binary("mul", K.binary("sub", g, r), K.unary("add_scalar", y, alpha)))
+    return _unary("Elu", "elu", m, alpha, bwd)
 def Mish(m): return _unary("Mish", "mish", m, 0.0, lambda x, y, g: K.binary("mish_bwd", x, g))
 
 
@@ -273,14 +280,59 @@ def _reduce_to(g: torch.Tensor, shape) -> torch.Tensor:
         return K.row_reduce("sum", g.reshape(1, -1)).reshape(shape)
     if n == g.shape[-1] and shape[-1] == g.shape[-1]:
         return K.col_sum(g.reshape(-1, g.shape[-1])).reshape(shape)
-    if g.dim() >= 1 and n == g.numel() // g.shape[-1]:
+    if g.dim() >= 1 and n == g.numel() // g.shape[-1] and shape[-1] == 1 and len(shape) == g.dim():
         return K.row_reduce("sum", g.reshape(-1, g.shape[-1])).reshape(shape)
-    raise ValueError(f"cannot reduce gradient {tuple(g.shape)} to {shape}")
+    # general case: one dimension at a time, [outer, d, inner] -> [outer, inner]
+    padded = (1,) * (g.dim() - len(shape)) + shape
+    cur = g
+    for i in range(g.dim()):
+        if padded[i] == cur.shape[i]:
+            continue
+        if padded[i] != 1:
+            raise ValueError(f"cannot reduce gradient {tuple(g.shape)} to {shape}")
+        outer = 1
+        for d in cur.shape[:i]:
+            outer *= d
+        dsz = cur.shape[i]
+        inner = cur.numel() // (outer * dsz)
+        v = _c(cur).reshape(outer, dsz, inner)
+        if inner == 1:
+            r = K.row_reduce("sum", v.reshape(outer, dsz))
+        elif outer == 1:
+            r = K.col_sum(v.reshape(dsz, inner))
+        else:
+            r = K.row_reduce("sum", K.contiguous(v.permute(0, 2, 1)).reshape(outer * inner, dsz))
+        cur = r.reshape(*cur.shape[:i], 1, *cur.shape[i + 1:])
+    return cur.reshape(shape)
+
+
+def _fast_broadcast(big: torch.Tensor, small: torch.Tensor) -> bool:
+    """True when ops.kernels.binary handles (big, small) without materialising the broadcast."""
+    if big.shape == small.shape or small.numel() == 1:
+        return True
+    if small.numel() == big.shape[-1] and (small.dim() == 1 or all(d == 1 for d in small.shape[:-1])):
+        return True
+    return small.dim() == big.dim() and small.shape[-1] == 1 and small.numel() == big.numel() // big.shape[-1]
 
 
 def _binary(name: str, op: str, a: OaMatrix, b: OaMatrix, bwd) -> OaMatrix:
     _ctx_add(name)
     ta, tb = _c(a.Tensor()), _c(b.Tensor())
+    if ta.shape != tb.shape:
+        full = torch.broadcast_shapes(ta.shape, tb.shape)
+        big, small = (ta, tb) if ta.numel() >= tb.numel() else (tb, ta)
+        if tuple(big.shape) != tuple(full) or not _fast_broadcast(big, small):
+            xa, xb = K.contiguous(ta.expand(full)), K.contiguous(tb.expand(full))
+            y = K.binary(op, xa, xb)
+            out = _w(y)
+            if bwd is None:
+                return out
+
+            def back_full(g):
+                ga, gb = bwd(xa, xb, y, _c(g))
+                return (_reduce_to(ga, ta.shape) if ga is not None else None, _reduce_to(gb, tb.shape) if gb is not None else None)
+
+            return AG.attach(name, out, [a, b], back_full)
     swap = ta.numel() < tb.numel()
     if swap and op in ("add", "mul"):
         y = K.binary(op, tb, ta)
@@ -525,7 +577,8 @@ def SoftmaxBwd(y: OaMatrix, dy: OaMatrix) -> OaMatrix:
 
 
 def SoftmaxScaledMasked(scores: OaMatrix, scale: float, mask: Optional[OaMatrix] = None) -> OaMatrix:
-    """softmax(scores * scale + mask) over the last dimension; mask is additive, same shape as scores."""
+    """softmax(scores * scale + mask) over the last dimension; the additive mask has the scores' shape or is one
+    [rows, cols] block that repeats over the leading dimensions (a [S, S] causal mask for [B*H, S, S] scores)."""
     _ctx_add("SoftmaxScaledMasked")
     t = scores.Tensor()
     mk = _rows(mask.Tensor()) if mask is not None else None
@@ -743,10 +796,17 @@ def ResidualRmsNorm(x: OaMatrix, residual: OaMatrix, w: OaMatrix, eps: float = 1
     return RmsNorm(s, w, eps), s
 
 
-def RmsNormGated(x: OaMatrix, gate: OaMatrix, w: OaMatrix, eps: float = 1e-6) -> OaMatrix:
-    """RmsNorm(x * silu(gate)) * w."""
-    return RmsNorm(_binary("SiluMul", "silu_mul", gate, x, lambda tg, tx, y, g: (
-        K.binary("mul", K.binary("silu_bwd", tg, g), tx), K.binary("silu_mul", tg, g))), w, eps)
+def RmsNormGated(x: OaMatrix, w: OaMatrix, bias: Optional[OaMatrix], z: OaMatrix, eps: float = 1e-5,
+                 norm_before_gate: bool = True) -> OaMatrix:
+    """norm_before_gate: (RmsNorm(x) * w + bias) * silu(z); otherwise RmsNorm(x * silu(z)) * w + bias
+    (Source/Public/Oa/Ml/FnMatrix.h:503-506)."""
+    if norm_before_gate:
+        n = RmsNorm(x, w, eps)
+        if bias is not None:
+            n = Add(n, bias)
+        return SiluMul(z, n)
+    n = RmsNorm(SiluMul(z, x), w, eps)
+    return Add(n, bias) if bias is not None else n
 
 
 def LayerNorm(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], eps: float = 1e-5) -> OaMatrix:
@@ -866,6 +926,11 @@ def Embedding(table: OaMatrix, ids: OaMatrix, pos_table: Optional[OaMatrix] = No
         if pos_table is not None and pos_table.RequiresGrad():
             n = g.shape[0]
             gp = K.col_sum(K.contiguous(g.reshape(n // seq_len, seq_len * dim))).reshape(seq_len, dim)
+            if tp.shape[0] != seq_len:           # rows of the position table beyond the sequence get a zero gradient
+                full = torch.empty_like(tp, dtype=gp.dtype)
+                K.fill_(full, 0.0)
+                K.unary("copy", gp, out=full[:seq_len])
+                gp = full
         return (gt if tt.dtype == torch.float32 else K.cast(gt, tt.dtype), None, gp)
 
     return AG.attach("Embedding", out, [table, ids, pos_table], back)

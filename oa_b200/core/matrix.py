@@ -222,6 +222,14 @@ class OaMatrix:
         self.AccumulateGradTensor(d._t)
 
     def ZeroGrad(self) -> None:
+        from ..ops import kernels as K
+        m = self._meta
+        if m is not None and m.grad is not None:
+            K.fill_(m.grad, 0.0)
+            m.grad_fresh = True
+
+    def _mark_grad_fresh(self) -> None:
+        """The owner of the gradient buffer zeroed it already (flat arena): the next accumulation overwrites."""
         m = self._meta
         if m is not None and m.grad is not None:
             m.grad_fresh = True

@@ -78,7 +78,7 @@ int oa_col_sum(int dtype, const void* x, void* out, int out_dtype, long long row
 int oa_bias_add(int dtype, void* x, const void* bias, long long rows, int cols, void* stream);
 int oa_row_reduce(int op, int dtype, const void* x, void* y, long long rows, int cols, void* stream);
 int oa_softmax(int dtype, const void* x, void* y, long long rows, int cols, int log_mode, float scale,
-               const void* mask, void* stream);
+               const void* mask, long long mask_rows, void* stream);
 int oa_softmax_bwd(int dtype, const void* y, const void* dy, void* dx, long long rows, int cols, int log_mode,
                    float scale, void* stream);
 int oa_philox(int dtype, void* y, long long n, unsigned long long seed, unsigned long long offset, int normal,

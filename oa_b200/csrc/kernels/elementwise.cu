@@ -342,11 +342,11 @@ __global__ void row_reduce_kernel(int op, const T* __restrict__ x, void* __restr
 // Row softmax / log-softmax of (x * scale + mask), one CTA per row.
 template <typename T>
 __global__ void softmax_kernel(const T* __restrict__ x, T* __restrict__ y, int cols, int log_mode, float scale,
-                               const T* __restrict__ mask) {
+                               const T* __restrict__ mask, long long mask_rows) {
   __shared__ float red[32];
   long long row = blockIdx.x;
   const T* p = x + row * cols;
-  const T* mk = mask ? mask + row * cols : nullptr;
+  const T* mk = mask ? mask + (row % mask_rows) * cols : nullptr;   // the mask repeats every mask_rows rows
   float m = -INFINITY;
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
     float v = IO<T>::ld1(p + c) * scale + (mk ? IO<T>::ld1(mk + c) : 0.f);
@@ -576,10 +576,12 @@ extern "C" int oa_row_reduce(int op, int dtype, const void* x, void* y, long lon
   return CHECK_LAUNCH();
 }
 extern "C" int oa_softmax(int dtype, const void* x, void* y, long long rows, int cols, int log_mode, float scale,
-                          const void* mask, void* stream) {
+                          const void* mask, long long mask_rows, void* stream) {
   if (rows <= 0) return OA_OK;
+  if (mask && mask_rows <= 0) return OA_ERR_ARG;
   int threads = cols >= 1024 ? 256 : (cols >= 128 ? 128 : 32);
-  DISPATCH_T(dtype, softmax_kernel<T><<<(unsigned)rows, threads, 0, ST>>>((const T*)x, (T*)y, cols, log_mode, scale, (const T*)mask));
+  DISPATCH_T(dtype, softmax_kernel<T><<<(unsigned)rows, threads, 0, ST>>>((const T*)x, (T*)y, cols, log_mode, scale, (const T*)mask,
+                                                                             mask_rows));
   return CHECK_LAUNCH();
 }
 extern "C" int oa_softmax_bwd(int dtype, const void* y, const void* dy, void* dx, long long rows, int cols,

@@ -29,7 +29,9 @@ def _set(name: str) -> None:
 
 
 def CrossEntropy(logits: OaMatrix, targets: OaMatrix, ignore_index: int = -100, in_place_grad: bool = False) -> OaMatrix:
-    """Mean cross-entropy of [rows, vocab] logits against integer targets [rows].
+    """Mean cross-entropy of [rows, vocab] logits against integer targets [rows].  The mean is over ALL rows (the
+    reference's contract, Source/Private/Oa/Ml/FnLoss/FnLoss.cpp:177-260); a row whose target is `ignore_index` adds zero
+    loss and zero gradient but still counts in the denominator - use MaskedCrossEntropy for a mean over the kept rows.
 
     With `in_place_grad` the logits buffer is overwritten by the gradient when autograd is recording
     (saves a [rows, vocab] allocation for large vocabularies); the caller must not read logits afterwards.

@@ -190,8 +190,7 @@ class OaMultiHeadAttention(OaModule):
         scores = F.Bmm(qh, F.Transpose(kh, 1, 2))
         mask = None
         if self.Causal:
-            m = F.CausalMask(seq, scores.Dtype())
-            mask = OaMatrix(m.Tensor().unsqueeze(0).expand(batch * H, seq, seq).contiguous())
+            mask = F.CausalMask(seq, scores.Dtype())       # [S, S], repeated over batch and heads by the kernel
         probs = F.SoftmaxScaledMasked(scores, 1.0 / math.sqrt(self.HeadDim), mask)
         return F.MergeHeads(F.Bmm(probs, vh), batch, seq, H)
 

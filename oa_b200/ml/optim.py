@@ -126,7 +126,7 @@ class OaOptimizer:
             RT.OaContext.GetDefault().Add("MultiFill")
             K.fill_(a.grad, 0.0)
             for p in a.params:
-                p.Data.ZeroGrad()
+                p.Data._mark_grad_fresh()
 
     def SetLr(self, lr: float) -> None:
         self.Lr_ = float(lr)

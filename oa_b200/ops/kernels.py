@@ -466,14 +466,22 @@ def row_reduce(op: str, x: torch.Tensor) -> torch.Tensor:
 
 
 def softmax(x: torch.Tensor, *, log: bool = False, scale: float = 1.0, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row softmax of x * scale + mask; the [mask_rows, cols] mask repeats every mask_rows rows of x."""
     rows, cols = x.shape
     out = torch.empty_like(x)
+    mrows = mask.shape[0] if mask is not None else 0
+    if mask is not None and (mask.shape[1] != cols or rows % mrows != 0):
+        raise ValueError(f"softmax: mask {tuple(mask.shape)} does not tile scores {tuple(x.shape)}")
     if not x.is_cuda:
-        v = x.float() * scale + (mask.float() if mask is not None else 0)
+        v = x.float() * scale
+        if mask is not None:
+            v = (v.reshape(rows // mrows, mrows, cols) + mask.float()).reshape(rows, cols)
         out.copy_(torch.log_softmax(v, -1) if log else torch.softmax(v, -1))
         return out
+    if mask is not None:
+        mask = mask.contiguous() if mask.dtype == x.dtype else cast(mask.contiguous(), x.dtype)
     _launch(N.require().oa_softmax(dt(x), x.contiguous().data_ptr(), out.data_ptr(), rows, cols, int(log), float(scale),
-                                   N.ptr(mask), N.stream()), "oa_softmax")
+                                   N.ptr(mask), mrows, N.stream()), "oa_softmax")
     return out
 
 

@@ -85,7 +85,8 @@ class OaGpuTimer:
 
     def __init__(self, name: str = "timer"):
         self.Name = name
-        self._cuda = torch.cuda.is_available()
+        eng = OaEngine.GetGlobal()
+        self._cuda = torch.cuda.is_available() and (eng is None or eng.IsCuda())
         self._e0 = self._e1 = None
         self._t0 = self._t1 = 0.0
 
@@ -224,6 +225,8 @@ class OaContext:
 
     def _check_device(self) -> OaStatus:
         from ..ops import kernels as K
+        if not self._engine.IsCuda():
+            return OaStatus.Ok()
         try:
             if not torch.cuda.is_current_stream_capturing():
                 K.check_status(self._engine.Device())
