@@ -55,6 +55,12 @@ int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void* out, int 
                          long long sc_batch, long long sbias_batch, int* status, void* stream);
 // fp32 SIMT GEMM with arbitrary element strides and a batch dimension:
 //   C[b][m,n] = act(alpha * sum_k A[b][m*sam + k*sak] * B[b][n*sbn + k*sbk] + bias[n]) (+ C if accumulate)
+// Tensor-parallel GEMM fused with its collective over peer memory: mode 1 all-gather(rows of A) -> GEMM, mode 2 GEMM ->
+// reduce-scatter(rows of out).  bufs / flags: host arrays of `world` device pointers; sync2: device u64[2] of the call site.
+int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc,
+                    int b_mn, const void* residual, int ldr, int out_f32, float alpha, const void* src, int ld_src,
+                    const void* const* bufs, const void* const* flags, void* sync2, int world, int rank,
+                    int comm_ctas, int* status, void* stream);
 int oa_gemm_f32(const float* A, const float* B, float* C, int M, int N, int K, long long sam, long long sak,
                 long long sbn, long long sbk, int ldc, int batch, long long batch_a, long long batch_b,
                 long long batch_c, const float* bias, int act, int accumulate, float alpha, void* stream);
@@ -104,6 +110,10 @@ int oa_layernorm_bwd(int dtype, const void* x, const void* w, const void* dy, co
 // ---- loss (xent.cu)
 int oa_xent_fwd_bwd(int dtype, const void* logits, const int* targets, float* row_loss, void* dlogits, long long rows,
                     int vocab, int ld, float grad_scale, int ignore_index, void* stream);
+int oa_vp_xent_stats(int dtype, const void* logits, const int* targets, float* stats, long long rows, int vocab, int v0,
+                     void* stream);
+int oa_vp_xent_finish(int dtype, void* logits, const int* targets, const float* all_stats, float* row_loss, long long rows,
+                      int vocab, int v0, int world, float scale, int want_grad, void* stream);
 int oa_mean_f32(const float* x, float* out, long long n, float scale, void* stream);
 
 // ---- optimizers (optim.cu)

@@ -98,6 +98,50 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// ---- peer memory (NVLink): system-scope loads / stores / flags.  L1 is not coherent with writes of other GPUs, so data
+// that a peer may have written is read with ld.relaxed.sys (served by L2) after an acquire of its flag.
+constexpr int MAX_RANKS = 8;
+
+struct PeerTable {
+  void* ptr[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_peer_v4(void* p, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ void red_release_sys_add(unsigned long long* p, unsigned long long v) {
+  asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+// Waits (wall-time bounded) until *p >= target; false when the limit ran out.
+__device__ __forceinline__ bool wait_ge_sys(const unsigned long long* p, unsigned long long target) {
+  if (ld_acquire_sys(p) >= target) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (ld_acquire_sys(p) >= target) return true;
+    if ((it & 0x3f) == 0) {
+      uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > OA_WAIT_LIMIT_NS) return false;
+      __nanosleep(64);
+    }
+  }
+}
+
 // Whole-warp wait: every lane waits (so the warp stays converged) and the outcome is made uniform.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
 #ifdef OA_WARP_WAIT_ONE_LANE

@@ -56,6 +56,19 @@ struct GemmParams {
   //   2: the REDUCTION is grouped (dW[g] = dY_g^T * X_g): A and B are flat [rows, .] MN-major, out is batched.
   int group_mode;
   const int* group_offsets;
+  // Tensor-parallel modes (the GEMM and its collective are one kernel; peers are reached with plain loads / stores).
+  //   1  all-gather -> GEMM: A is the local staging copy [M, K] of the row-sharded activation.  The last tp_comm CTAs push
+  //      this rank's shard (tp_src) into every rank's staging buffer 128 rows at a time and publish a flag per block; the
+  //      TMA producer of a compute CTA waits for the flag of the block it is about to load.  M tiles are visited own
+  //      shard first, then in the order the peers' blocks arrive.
+  //   2  GEMM -> reduce-scatter: every output tile belongs to the rank that owns its rows; the epilogue stores the bf16
+  //      partial into slot `rank` of the owner's staging buffer and bumps the owner's per-block counter; after its tiles a
+  //      CTA reduces blocks of this rank's own rows over the `world` slots (+ residual) into `out` [M / world, N].
+  int tp_mode, tp_world, tp_rank, tp_comm;
+  const __nv_bfloat16* tp_src; int tp_ld_src;
+  PeerTable tp_bufs;                  // mode 1: staging [M, K] of every rank; mode 2: staging [world, M / world, N] of every rank
+  PeerTable tp_flags;                 // u64 per 128-row block (mode 1: [world * blocks]; mode 2: [blocks]) on every rank
+  unsigned long long* tp_sync;        // [0] epoch of this call site, [1] CTAs finished (device resident: graph replay safe)
 };
 
 constexpr int BM = 128;
@@ -69,7 +82,9 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1280 /*group tile prefix*/;
+  static constexpr int EPI_ROW_BYTES = 144;      // 64 bf16 columns + 16 B pad
+  static constexpr int EPI_BYTES = 4 * 32 * EPI_ROW_BYTES;   // per epilogue warp: 32 rows (reduce-scatter mode only)
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1280 /*group tile prefix*/ + EPI_BYTES;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
@@ -113,6 +128,13 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t, cons
   int split = tb / mn_tiles;
   int mi, ni;
   tile_coords(tb - split * mn_tiles, m_tiles, n_tiles, p.group_m, mi, ni);
+  if (p.tp_mode) {
+    const int per_rank = m_tiles / p.tp_world;
+    const int step = mi / per_rank;
+    const int who = p.tp_mode == 1 ? (p.tp_rank - step + p.tp_world) % p.tp_world      // own shard, then rank-1, rank-2, ...
+                                   : (p.tp_rank + 1 + step) % p.tp_world;              // owners rank+1, ..., own rows last
+    mi = who * per_rank + (mi - step * per_rank);
+  }
   ti.bi = bi; ti.row0 = mi * BM; ti.ni = ni; ti.split = split;
   if (p.group_mode == 2) {
     ti.kb0 = p.group_offsets[bi] >> 6; ti.kb1 = p.group_offsets[bi + 1] >> 6; ti.a_batch = 0; ti.b_batch = 0;
@@ -233,6 +255,92 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
+// Tensor-parallel mode 1, communication CTAs: push this rank's shard into every rank's staging buffer (own buffer last in
+// each round), one 128-row block at a time, and publish the block's flag with release semantics at system scope.
+__device__ __forceinline__ void tp_push_shard(const GemmParams& p, int comm_idx, unsigned long long epoch) {
+  const int W = p.tp_world, r = p.tp_rank;
+  const int blocks = (p.M / W) / BM;
+  const int vec_per_row = p.K >> 3;
+  const int total_vec = BM * vec_per_row;
+  constexpr int UNROLL = 8;
+  for (int item = comm_idx; item < blocks * W; item += p.tp_comm) {
+    const int c = item / W, j = item - c * W;
+    const int peer = (r + 1 + j) % W;                    // j == W - 1 is this rank itself
+    const __nv_bfloat16* src = p.tp_src + (size_t)c * BM * p.tp_ld_src;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.tp_bufs.ptr[peer]) + ((size_t)r * blocks + c) * BM * p.K;
+    if (src != dst) {
+      for (int v0 = threadIdx.x; v0 < total_vec; v0 += 192 * UNROLL) {
+        uint4 buf[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int v = v0 + u * 192;
+          if (v < total_vec) {
+            const int row = v / vec_per_row, cv = v - row * vec_per_row;
+            buf[u] = *reinterpret_cast<const uint4*>(src + (size_t)row * p.tp_ld_src + cv * 8);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+          const int v = v0 + u * 192;
+          if (v < total_vec) st_peer_v4(dst + (size_t)v * 8, buf[u]);
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0)
+      st_release_sys(reinterpret_cast<unsigned long long*>(p.tp_flags.ptr[peer]) + (size_t)r * blocks + c, epoch);
+  }
+}
+
+// Tensor-parallel mode 2, after the tiles: sum the `world` partial slots of this rank's own rows (+ residual) into `out`.
+__device__ __forceinline__ void tp_reduce_rows(const GemmParams& p, int n_tiles, unsigned long long epoch, int* s_ok) {
+  const int W = p.tp_world;
+  const int Ms = p.M / W, blocks = Ms / BM;
+  const int slabs = (p.N + 127) >> 7;
+  const unsigned long long expect = epoch * (unsigned long long)(W * n_tiles * 4);
+  const unsigned long long* cnt = reinterpret_cast<const unsigned long long*>(p.tp_flags.ptr[p.tp_rank]);
+  const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(p.tp_bufs.ptr[p.tp_rank]);
+  for (int u = blockIdx.x; u < blocks * slabs; u += gridDim.x) {
+    const int rb = u / slabs, sl = u - rb * slabs;
+    if (threadIdx.x == 0) {
+      const bool ok = wait_ge_sys(cnt + rb, expect);
+      if (!ok) report_error(p.status, OA_KERR_WAIT_PEER);
+      *s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    const bool ok = *s_ok != 0;
+    __syncthreads();
+    if (!ok) break;
+    for (int e = threadIdx.x; e < BM * 16; e += 192) {
+      const int row = rb * BM + (e >> 4), col = sl * 128 + (e & 15) * 8;
+      if (col >= p.N) continue;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int src = 0; src < W; ++src) {
+        const uint4 v = ld_peer_v4(stage + ((size_t)src * Ms + row) * p.N + col);
+        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      if (p.residual) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col);
+        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      if (p.out_f32) {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldc + col;
+        *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      } else {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldc + col;
+        *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                                                  pack_bf16x2(acc[6], acc[7]));
+      }
+    }
+  }
+}
+
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
@@ -257,6 +365,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int mn_tiles = m_tiles * n_tiles;
   const int tiles_per_batch = mn_tiles * p.splits;
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
+  uint8_t* s_epi = smem + STAGES * Cfg::STAGE_BYTES + 256 + 1280;     // reduce-scatter epilogue staging (4 warps)
+  __shared__ int s_tp_ok;
   if (p.group_mode == 1 && threadIdx.x == 32) {
     int run = 0;
     for (int g = 0; g < p.batch; ++g) {
@@ -290,15 +400,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = p.group_mode == 1 ? s_prefix[p.batch] : tiles_per_batch * p.batch;
+  const int n_compute = (int)gridDim.x - (p.tp_mode == 1 ? p.tp_comm : 0);   // the last tp_comm CTAs only move data
+  const bool is_comm = p.tp_mode == 1 && (int)blockIdx.x >= n_compute;
+  unsigned long long tp_epoch = 0;
+  if (p.tp_mode) tp_epoch = *reinterpret_cast<volatile unsigned long long*>(p.tp_sync) + 1;
 
-  if (warp == 0) {
+  if (is_comm) {
+    tp_push_shard(p, (int)blockIdx.x - n_compute, tp_epoch);
+  } else if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += n_compute) {
         const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
+        if (p.tp_mode == 1) {
+          // the rows of this tile were written into the local staging buffer by a communication CTA of their owner
+          const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(p.tp_flags.ptr[p.tp_rank]);
+          if (!wait_ge_sys(flags + ti.row0 / BM, tp_epoch)) {
+            report_error(p.status, OA_KERR_WAIT_PEER);
+            ok = false;
+            break;
+          }
+          fence_proxy_async_global();     // generic-proxy writes (peer stores) before the async-proxy (TMA) reads below
+        }
         for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
             report_error(p.status, OA_KERR_WAIT_EMPTY);
@@ -338,7 +464,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += n_compute) {
         const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
         const int kb0 = ti.kb0, kb1 = ti.kb1;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) {
@@ -376,7 +502,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quad = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles; t += n_compute) {
       const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
       const int bi = ti.bi, ni = ti.ni, split = ti.split, kb0 = ti.kb0, kb1 = ti.kb1;
       bool ok = mbar_wait(&tfull[acc], acc_phase);
@@ -403,17 +529,67 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0;
         }
-        epilogue_chunk<BN>(p, r, row, ni * BN + c * 32, split, bi);
+        if (p.tp_mode == 2) {
+          // bf16 partial -> per-warp shared tile (64 columns wide) -> 128-byte row segments stored into the owner's slot
+          uint8_t* se = s_epi + quad * (32 * Cfg::EPI_ROW_BYTES);
+          uint8_t* my = se + lane * Cfg::EPI_ROW_BYTES + (c & 1) * 64;
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(my + g * 16) = make_uint4(
+                pack_bf16x2(__uint_as_float(r[g * 8]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha),
+                pack_bf16x2(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha),
+                pack_bf16x2(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha),
+                pack_bf16x2(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha));
+          if (c & 1) {
+            __syncwarp();
+            const int Ms = p.M / p.tp_world;
+            const int owner = ti.row0 / Ms;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.tp_bufs.ptr[owner]) +
+                                 ((size_t)p.tp_rank * Ms + (ti.row0 - owner * Ms) + quad * 32) * p.N;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int idx = it * 32 + lane, rr = idx >> 3, piece = idx & 7;
+              const int col = ni * BN + (c - 1) * 32 + piece * 8;
+              if (col < p.N) st_peer_v4(dst + (size_t)rr * p.N + col, *reinterpret_cast<const uint4*>(se + rr * Cfg::EPI_ROW_BYTES + piece * 16));
+            }
+            __syncwarp();
+          }
+          if (c == BN / 32 - 1) {
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+              const int Ms = p.M / p.tp_world;
+              const int owner = ti.row0 / Ms;
+              red_release_sys_add(reinterpret_cast<unsigned long long*>(p.tp_flags.ptr[owner]) + (ti.row0 - owner * Ms) / BM, 1ull);
+            }
+          }
+        } else {
+          epilogue_chunk<BN>(p, r, row, ni * BN + c * 32, split, bi);
+        }
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+  }
+  if (p.tp_mode == 2) {
+    __syncthreads();
+    tp_reduce_rows(p, n_tiles, tp_epoch, &s_tp_ok);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc<Cfg::TMEM_COLS>(tmem_base);
+  }
+  if (p.tp_mode && threadIdx.x == 0) {
+    // the call site's epoch advances once every CTA (each read it at its start) has finished
+    __threadfence();
+    const unsigned long long old = atomicAdd(p.tp_sync + 1, 1ull);
+    if (old == gridDim.x - 1) {
+      p.tp_sync[1] = 0;
+      __threadfence();
+      p.tp_sync[0] = tp_epoch;
+    }
   }
 }
 
@@ -584,7 +760,7 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
   p.splits = 1;
   p.workspace = (float*)workspace;
   p.batch = batch; p.sc_batch = sc_batch; p.sr_batch = sr_batch; p.saux_batch = saux_batch; p.sbias_batch = sbias_batch;
-  p.group_mode = 0; p.group_offsets = nullptr;
+  p.group_mode = 0; p.group_offsets = nullptr; p.tp_mode = 0; p.tp_comm = 0;
   bool plain = !bias && !residual && !aux_out && !aux_in && act == OA_ACT_NONE;
   if (workspace && plain && (N % 4 == 0)) {
     int s = oa_gemm_plan_splits(M * batch, N, K, bn, sms);
@@ -648,7 +824,7 @@ extern "C" int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void
   p.aux_out = (__nv_bfloat16*)aux_out; p.aux_in = (const __nv_bfloat16*)aux_in; p.ldaux = ldaux;
   p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.splits = 1; p.workspace = nullptr;
   p.batch = groups; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = sbias_batch;
-  p.group_mode = mode; p.group_offsets = offsets;
+  p.group_mode = mode; p.group_offsets = offsets; p.tp_mode = 0; p.tp_comm = 0;
   CUtensorMap ta, tb;
   int rc, bn, grid;
   if (mode == 1) {
@@ -676,5 +852,56 @@ extern "C" int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void
   } else {
     rc = bn == 256 ? launch_gemm<256, 1, 1>(ta, tb, p, grid, st) : launch_gemm<128, 1, 1>(ta, tb, p, grid, st);
   }
+  return rc;
+}
+
+// Tensor-parallel GEMMs fused with their collective (modes described at GemmParams::tp_mode).
+//   mode 1: out[M, N] = allgather_rows(src)[M, K] * B^T.  `stage_local` is this rank's staging buffer [M, K] (= bufs[rank]).
+//   mode 2: out[M / world, N] = reduce_scatter_rows(A[M, K] * B^T) (+ residual [M / world, N]).
+// bufs / flags are host arrays of `world` device pointers (every rank's staging buffer and flag array, peer mapped);
+// sync2 is a device u64[2] that belongs to the call site.  M must be a multiple of 128 * world.
+extern "C" int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out, int M, int N, int K, int lda, int ldb, int ldc,
+                               int b_mn, const void* residual, int ldr, int out_f32, float alpha, const void* src, int ld_src,
+                               const void* const* bufs, const void* const* flags, void* sync2, int world, int rank,
+                               int comm_ctas, int* status, void* stream) {
+  if (mode != 1 && mode != 2) return OA_ERR_ARG;
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return OA_ERR_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || (M % (BM * world))) return OA_ERR_ARG;
+  if ((N & 7) || (K & 7) || (ldc & (out_f32 ? 3 : 7)) || (residual && (ldr & 7))) return OA_ERR_ALIGN;
+  if (mode == 1 && ((ld_src & 7) || lda != K)) return OA_ERR_ALIGN;
+  const int sms = num_sms();
+  if (mode == 1) {
+    if (comm_ctas <= 0) comm_ctas = 20;
+    if (comm_ctas > sms / 2) comm_ctas = sms / 2;
+  } else {
+    comm_ctas = 0;
+  }
+  const int bn = (N >= 256) ? 256 : 128;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
+  p.bias = nullptr; p.residual = (const __nv_bfloat16*)residual; p.ldr = ldr;
+  p.aux_out = nullptr; p.aux_in = nullptr; p.ldaux = 0;
+  p.act = OA_ACT_NONE; p.accumulate = 0; p.alpha = alpha; p.status = status; p.group_m = 16; p.splits = 1; p.workspace = nullptr;
+  p.batch = 1; p.sc_batch = 0; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = 0;
+  p.group_mode = 0; p.group_offsets = nullptr;
+  p.tp_mode = mode; p.tp_world = world; p.tp_rank = rank; p.tp_comm = comm_ctas;
+  p.tp_src = (const __nv_bfloat16*)src; p.tp_ld_src = ld_src;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.tp_bufs.ptr[i] = i < world ? const_cast<void*>(bufs[i]) : nullptr;
+    p.tp_flags.ptr[i] = i < world ? const_cast<void*>(flags[i]) : nullptr;
+  }
+  p.tp_sync = (unsigned long long*)sync2;
+  if (mode == 2) p.residual = (const __nv_bfloat16*)residual;
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, 1, (uint64_t)lda, 0, BK, BM))) return rc;
+  if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb, 0, 64, BK);
+  else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, (uint32_t)bn);
+  if (rc) return rc;
+  // every CTA takes part in the protocol (communication CTAs, the row reduction, the epoch hand-over): a full grid always
+  cudaStream_t st = (cudaStream_t)stream;
+  if (bn == 256) rc = b_mn ? launch_gemm<256, 0, 1>(ta, tb, p, sms, st) : launch_gemm<256, 0, 0>(ta, tb, p, sms, st);
+  else           rc = b_mn ? launch_gemm<128, 0, 1>(ta, tb, p, sms, st) : launch_gemm<128, 0, 0>(ta, tb, p, sms, st);
   return rc;
 }

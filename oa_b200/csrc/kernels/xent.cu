@@ -140,6 +140,109 @@ extern "C" int oa_xent_fwd_bwd(int dtype, const void* logits, const int* targets
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
+// ---- vocabulary-parallel cross-entropy (tensor parallel head): every rank holds [rows, vocab / W] logits.
+// stats: (max, sum exp(l - max), target logit if the target falls into this shard else 0) per row;
+// finish: global lse from all ranks' stats, row loss, and dlogits = (exp(l - lse) - onehot) * scale written in place.
+namespace oa {
+
+template <typename T>
+__global__ void __launch_bounds__(XENT_THREADS)
+vp_xent_stats_kernel(const T* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ stats, int vocab, int v0) {
+  constexpr int V = XIO<T>::VEC;
+  __shared__ float red_m[XENT_THREADS / 32], red_s[XENT_THREADS / 32];
+  const long long row = blockIdx.x;
+  const T* p = logits + row * vocab;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < vocab / V; i += XENT_THREADS) {
+    float v[V];
+    XIO<T>::load(p + i * V, v);
+    float mx = v[0];
+#pragma unroll
+    for (int j = 1; j < V; ++j) mx = fmaxf(mx, v[j]);
+    if (mx > m) { s *= __expf(m - mx); m = mx; }
+#pragma unroll
+    for (int j = 0; j < V; ++j) s += __expf(v[j] - m);
+  }
+  // combine (m, s) pairs: warp, then block
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+    const float mm = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+    m = mm;
+  }
+  if ((threadIdx.x & 31) == 0) { red_m[threadIdx.x >> 5] = m; red_s[threadIdx.x >> 5] = s; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float M = red_m[0], S = red_s[0];
+    for (int w = 1; w < XENT_THREADS / 32; ++w) {
+      const float mm = fmaxf(M, red_m[w]);
+      S = (M == -INFINITY ? 0.f : S * __expf(M - mm)) + (red_m[w] == -INFINITY ? 0.f : red_s[w] * __expf(red_m[w] - mm));
+      M = mm;
+    }
+    const int t = targets[row] - v0;
+    stats[row * 3 + 0] = M;
+    stats[row * 3 + 1] = S;
+    stats[row * 3 + 2] = (t >= 0 && t < vocab) ? XIO<T>::ld1(p + t) : 0.f;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(XENT_THREADS)
+vp_xent_finish_kernel(T* __restrict__ logits, const int* __restrict__ targets, const float* all_stats, float* __restrict__ row_loss,
+                      long long rows, int vocab, int v0, int world, float scale, int want_grad) {
+  constexpr int V = XIO<T>::VEC;
+  const long long row = blockIdx.x;
+  float M = -INFINITY;
+  // peers wrote these: read through L2 (L1 may hold the previous step's values)
+  for (int r = 0; r < world; ++r) M = fmaxf(M, __ldcg(all_stats + ((long long)r * rows + row) * 3));
+  float S = 0.f, tl = 0.f;
+  for (int r = 0; r < world; ++r) {
+    const float* st = all_stats + ((long long)r * rows + row) * 3;
+    S += __ldcg(st + 1) * __expf(__ldcg(st) - M);
+    tl += __ldcg(st + 2);
+  }
+  const float lse = M + __logf(S);
+  if (threadIdx.x == 0) row_loss[row] = lse - tl;
+  if (!want_grad) return;
+  T* p = logits + row * vocab;
+  const int t = targets[row] - v0;
+  for (int i = threadIdx.x; i < vocab / V; i += XENT_THREADS) {
+    float v[V];
+    XIO<T>::load(p + i * V, v);
+#pragma unroll
+    for (int j = 0; j < V; ++j) v[j] = (__expf(v[j] - lse) - ((i * V + j) == t ? 1.f : 0.f)) * scale;
+    XIO<T>::store(p + i * V, v);
+  }
+}
+
+}  // namespace oa
+
+extern "C" int oa_vp_xent_stats(int dtype, const void* logits, const int* targets, float* stats, long long rows, int vocab, int v0,
+                                void* stream) {
+  if (rows <= 0) return OA_OK;
+  if (vocab % 8 || (reinterpret_cast<uintptr_t>(logits) & 15)) return OA_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == OA_F32) oa::vp_xent_stats_kernel<float><<<(unsigned)rows, oa::XENT_THREADS, 0, st>>>((const float*)logits, targets, stats, vocab, v0);
+  else if (dtype == OA_BF16)
+    oa::vp_xent_stats_kernel<__nv_bfloat16><<<(unsigned)rows, oa::XENT_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets, stats, vocab, v0);
+  else return OA_ERR_UNSUPPORTED;
+  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+}
+
+extern "C" int oa_vp_xent_finish(int dtype, void* logits, const int* targets, const float* all_stats, float* row_loss, long long rows,
+                                 int vocab, int v0, int world, float scale, int want_grad, void* stream) {
+  if (rows <= 0) return OA_OK;
+  if (vocab % 8 || (reinterpret_cast<uintptr_t>(logits) & 15)) return OA_ERR_ALIGN;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == OA_F32)
+    oa::vp_xent_finish_kernel<float><<<(unsigned)rows, oa::XENT_THREADS, 0, st>>>((float*)logits, targets, all_stats, row_loss, rows, vocab, v0, world, scale, want_grad);
+  else if (dtype == OA_BF16)
+    oa::vp_xent_finish_kernel<__nv_bfloat16><<<(unsigned)rows, oa::XENT_THREADS, 0, st>>>((__nv_bfloat16*)logits, targets, all_stats, row_loss, rows, vocab, v0, world, scale, want_grad);
+  else return OA_ERR_UNSUPPORTED;
+  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+}
+
 extern "C" int oa_mean_f32(const float* x, float* out, long long n, float scale, void* stream) {
   mean_f32_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(x, out, n, scale);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;

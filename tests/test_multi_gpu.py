@@ -23,3 +23,7 @@ def _run(script: str, nproc: int = 2, timeout: int = 240) -> str:
 
 def test_expert_parallel_matches_single_device():
     assert "EP_CHECK_OK" in _run("ep_check.py")
+
+
+def test_tensor_parallel_kernels_and_model():
+    assert "TP_CHECK_OK" in _run("tp_check.py")
