@@ -1,0 +1,215 @@
+#!/usr/bin/env python
+"""Operator-level benchmarks of the hand-written kernels against the library baselines on the same box.
+
+  python bench_ops.py --only gemm,flash,bw,mamba            (one GPU)
+  torchrun --nproc-per-node N ... bench_ops.py --only tp    (fused tensor-parallel kernels against NCCL + GEMM)
+
+Timing: CUDA events on the launching stream after warm-up, an L2 flush (256 MB write) between timed iterations, median
+of the iterations; multi-GPU numbers are the max over ranks.  Prints one JSON line per measurement and writes them to
+--out when given.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+from oa_b200.ops import kernels as K  # noqa: E402
+
+RESULTS = []
+
+
+def emit(**kw):
+    RESULTS.append(kw)
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps(kw), flush=True)
+
+
+def timeit(fn, iters=15, warm=4, flush=True):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    ts = []
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm():
+    shapes = [(16384, 4096, 1024, 0, 0), (16384, 1024, 4096, 0, 0), (16384, 3072, 1024, 0, 0), (16384, 1024, 1024, 0, 0),
+              (8192, 8192, 8192, 0, 0), (16384, 1024, 4096, 0, 1), (4096, 1024, 16384, 1, 1), (16384, 32000, 1024, 0, 0)]
+    for (M, N, Kk, amn, bmn) in shapes:
+        a = torch.randn((Kk, M) if amn else (M, Kk), device="cuda").bfloat16()
+        b = torch.randn((Kk, N) if bmn else (N, Kk), device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t = timeit(lambda: K.gemm(a, b, a_mn=bool(amn), b_mn=bool(bmn), out=out))
+        A, B = (a.t() if amn else a), (b if bmn else b.t())
+        t2 = timeit(lambda: torch.matmul(A, B, out=out))
+        fl = 2 * M * N * Kk
+        emit(op="gemm_bf16", M=M, N=N, K=Kk, a_mn=amn, b_mn=bmn, ms=t, tflops=fl / t / 1e9, cublas_ms=t2, cublas_tflops=fl / t2 / 1e9)
+    K.check_status()
+
+
+def bench_flash():
+    import torch.nn.functional as Fn
+    for (B, H, S, hd) in [(8, 16, 2048, 64), (1, 32, 4096, 128)]:
+        D = H * hd
+        qkv = torch.randn(B * S, 3 * D, device="cuda").bfloat16()
+        q, k, v = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
+        t = timeit(lambda: K.flash_fwd(q, k, v, B, S, H, hd, causal=True))
+        o, lse = K.flash_fwd(q, k, v, B, S, H, hd, causal=True)
+        do = torch.randn_like(o)
+        dqkv = torch.empty_like(qkv)
+        tb = timeit(lambda: K.flash_bwd(q, k, v, o, do, lse, B, S, H, hd, causal=True, dqkv=dqkv))
+        mk = lambda t_: t_.reshape(B, S, H, hd).transpose(1, 2).contiguous().requires_grad_(True)
+        q4, k4, v4 = mk(q), mk(k), mk(v)
+        ts = timeit(lambda: Fn.scaled_dot_product_attention(q4, k4, v4, is_causal=True))
+        oo = Fn.scaled_dot_product_attention(q4, k4, v4, is_causal=True)
+        g = torch.randn_like(oo)
+        tsb = timeit(lambda: torch.autograd.grad(oo, (q4, k4, v4), g, retain_graph=True))
+        fl = 4 * B * H * S * S * hd / 2
+        emit(op="flash_attention_causal", B=B, H=H, S=S, hd=hd, fwd_ms=t, fwd_tflops=fl / t / 1e9, bwd_ms=tb, bwd_tflops=2.5 * fl / tb / 1e9,
+             sdpa_fwd_ms=ts, sdpa_bwd_ms=tsb)
+    K.check_status()
+
+
+def bench_bw():
+    x = torch.randn(16384, 1024, device="cuda").bfloat16()
+    w = torch.randn(1024, device="cuda").bfloat16()
+    t = timeit(lambda: K.rmsnorm_fwd(x, w, 1e-5))
+    emit(op="rmsnorm_fwd", rows=16384, cols=1024, us=t * 1e3, gbs=2 * x.numel() * 2 / t / 1e6)
+    _, rstd, _ = K.rmsnorm_fwd(x, w, 1e-5)
+    t = timeit(lambda: K.rmsnorm_bwd(x, w, x, rstd))
+    emit(op="rmsnorm_bwd", rows=16384, cols=1024, us=t * 1e3, gbs=3 * x.numel() * 2 / t / 1e6)
+    lg = torch.randn(16384, 32000, device="cuda").bfloat16()
+    tg = torch.randint(0, 32000, (16384,), device="cuda")
+    t = timeit(lambda: K.xent_fwd_bwd(lg, tg, grad_scale=1.0, dlogits=lg))
+    emit(op="xent_fwd_bwd_inplace", rows=16384, vocab=32000, us=t * 1e3, gbs=2 * lg.numel() * 2 / t / 1e6)
+    n = 335_000_000
+    p = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    g = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    ms, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    st = torch.tensor([1, 1e-3, 0.9, 0.999, 1e-8, 0.1, 1.0, 0], device="cuda")
+    t = timeit(lambda: K.adam_step(p, g, ms, m, v, st, decoupled=True))
+    emit(op="adamw_step", n=n, ms=t, gbs=n * 28 / t / 1e6)
+
+
+def bench_mamba():
+    from oa_b200.ops import mamba3 as M3
+    for (B, L, H, P, Nn) in [(4, 4096, 48, 64, 128), (2, 1024, 48, 64, 128)]:
+        d = M3.Mamba3Dims(d_inner=H * P, heads=H, headdim=P, d_state=Nn, angles=32, has_z=True, chunk=256)
+        proj = (torch.randn(B * L, d.d_in_proj, device="cuda") * 0.5).bfloat16()
+        dtb = torch.rand(1, H, device="cuda")
+        Bb, Cb, D = torch.ones(H, Nn, device="cuda"), torch.ones(H, Nn, device="cuda"), torch.zeros(H, device="cuda")
+        tf = timeit(lambda: M3.core_fwd(proj, dtb, Bb, Cb, D, d, B, L, save=True), iters=5, warm=2)
+        y, saved = M3.core_fwd(proj, dtb, Bb, Cb, D, d, B, L, save=True)
+        dy = torch.randn_like(y)
+        tb = timeit(lambda: M3.core_bwd(saved, dy), iters=5, warm=2)
+        emit(op="mamba3_core", B=B, L=L, H=H, P=P, N=Nn, fwd_ms=tf, bwd_ms=tb, tokens_per_s_fwd_bwd=B * L / ((tf + tb) / 1e3))
+    K.check_status()
+
+
+def bench_tp():
+    import torch.distributed as dist
+    from oa_b200.parallel import tp as TP
+    from oa_b200.parallel.mesh import OaDeviceMesh
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    mesh = OaDeviceMesh()
+    arena = TP.OaTpArena(mesh, 1 << 30)
+    M, D, Fd = 4096, 4096, 11008
+    Fl = (Fd // world + 7) // 8 * 8
+
+    def maxr(t):
+        x = torch.tensor([t], device="cuda", dtype=torch.float64)
+        dist.all_reduce(x, op=dist.ReduceOp.MAX)
+        return float(x)
+
+    def loop(fn, n=10):
+        def run():
+            for _ in range(n):
+                fn()
+        return timeit(run, iters=7, warm=2, flush=False) / n
+
+    for name, Kd, Nn in (("qkv", D, 3 * D // world), ("gate_up", D, 2 * Fl)):
+        site = TP.OaTpAgSite(arena, M, Kd)
+        xs = torch.randn(M // world, Kd, device="cuda").bfloat16()
+        w = (torch.randn(Nn, Kd, device="cuda") * 0.02).bfloat16()
+        full = torch.empty(M, Kd, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, Nn, device="cuda", dtype=torch.bfloat16)
+        for comm in (12, 20, 32):
+            t = maxr(loop(lambda: TP.ag_gemm(site, xs, w, comm_ctas=comm)))
+            emit(op="tp_allgather_gemm_fused", site=name, world=world, M=M, N=Nn, K=Kd, comm_ctas=comm, us=t * 1e3,
+                 tflops=2 * M * Nn * Kd / t / 1e9)
+
+        def base():
+            dist.all_gather_into_tensor(full, xs)
+            K.gemm(full, w, out=out)
+
+        def base_cublas():
+            dist.all_gather_into_tensor(full, xs)
+            torch.matmul(full, w.t(), out=out)
+
+        t1, t2 = maxr(loop(base)), maxr(loop(base_cublas))
+        tg = maxr(loop(lambda: K.gemm(full, w, out=out)))
+        emit(op="tp_allgather_gemm_baseline", site=name, world=world, M=M, N=Nn, K=Kd, nccl_plus_own_gemm_us=t1 * 1e3,
+             nccl_plus_cublas_us=t2 * 1e3, gemm_only_us=tg * 1e3, nvlink_bytes=(world - 1) * (M // world) * Kd * 2)
+    for name, Kd in (("attn_out", D // world), ("ffn_down", Fl)):
+        site = TP.OaTpRsSite(arena, M, D)
+        a = torch.randn(M, Kd, device="cuda").bfloat16()
+        w = (torch.randn(D, Kd, device="cuda") * 0.02).bfloat16()
+        res = torch.randn(M // world, D, device="cuda").bfloat16()
+        part = torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
+        outs = torch.empty(M // world, D, device="cuda", dtype=torch.bfloat16)
+        t = maxr(loop(lambda: TP.gemm_rs(site, a, w, residual=res)))
+        emit(op="tp_gemm_reducescatter_fused", site=name, world=world, M=M, N=D, K=Kd, us=t * 1e3, tflops=2 * M * D * Kd / t / 1e9)
+
+        def base():
+            K.gemm(a, w, out=part)
+            dist.reduce_scatter_tensor(outs, part)
+            K.binary("add", outs, res, out=outs)
+
+        def base_cublas():
+            torch.matmul(a, w.t(), out=part)
+            dist.reduce_scatter_tensor(outs, part)
+            outs.add_(res)
+
+        t1, t2 = maxr(loop(base)), maxr(loop(base_cublas))
+        emit(op="tp_gemm_reducescatter_baseline", site=name, world=world, M=M, N=D, K=Kd, own_gemm_plus_nccl_us=t1 * 1e3,
+             cublas_plus_nccl_us=t2 * 1e3, nvlink_bytes=(world - 1) * (M // world) * D * 2)
+    torch.cuda.synchronize()
+    K.check_status()
+    mesh.Close()
+    dist.destroy_process_group()
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="gemm,flash,bw")
+    ap.add_argument("--out", default="")
+    args = ap.parse_args()
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "tp": bench_tp}
+    for name in args.only.split(","):
+        table[name.strip()]()
+    if args.out and int(os.environ.get("RANK", "0")) == 0:
+        with open(args.out, "w") as f:
+            json.dump(RESULTS, f, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

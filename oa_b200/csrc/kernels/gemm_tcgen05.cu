@@ -255,20 +255,21 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
-// Tensor-parallel mode 1, communication CTAs: push this rank's shard into every rank's staging buffer (own buffer last in
-// each round), one 128-row block at a time, and publish the block's flag with release semantics at system scope.
+// Tensor-parallel mode 1, communication CTAs: push this rank's shard into every peer's staging buffer, one 128-row block
+// at a time, and publish the block's flag with release semantics at system scope.
 __device__ __forceinline__ void tp_push_shard(const GemmParams& p, int comm_idx, unsigned long long epoch) {
   const int W = p.tp_world, r = p.tp_rank;
   const int blocks = (p.M / W) / BM;
   const int vec_per_row = p.K >> 3;
   const int total_vec = BM * vec_per_row;
   constexpr int UNROLL = 8;
-  for (int item = comm_idx; item < blocks * W; item += p.tp_comm) {
-    const int c = item / W, j = item - c * W;
-    const int peer = (r + 1 + j) % W;                    // j == W - 1 is this rank itself
+  const int R = W - 1;                                   // remote peers only: own rows are read in place by the tiles
+  for (int item = comm_idx; item < blocks * R; item += p.tp_comm) {
+    const int c = item / R, j = item - c * R;
+    const int peer = (r + 1 + j) % W;
     const __nv_bfloat16* src = p.tp_src + (size_t)c * BM * p.tp_ld_src;
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.tp_bufs.ptr[peer]) + ((size_t)r * blocks + c) * BM * p.K;
-    if (src != dst) {
+    {
       for (int v0 = threadIdx.x; v0 < total_vec; v0 += 192 * UNROLL) {
         uint4 buf[UNROLL];
 #pragma unroll
@@ -282,7 +283,7 @@ __device__ __forceinline__ void tp_push_shard(const GemmParams& p, int comm_idx,
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
           const int v = v0 + u * 192;
-          if (v < total_vec) st_peer_v4(dst + (size_t)v * 8, buf[u]);
+          if (v < total_vec) *reinterpret_cast<uint4*>(dst + (size_t)v * 8) = buf[u];   // weak store; the fence below publishes it
         }
       }
     }
@@ -290,6 +291,56 @@ __device__ __forceinline__ void tp_push_shard(const GemmParams& p, int comm_idx,
     __syncthreads();
     if (threadIdx.x == 0)
       st_release_sys(reinterpret_cast<unsigned long long*>(p.tp_flags.ptr[peer]) + (size_t)r * blocks + c, epoch);
+  }
+}
+
+// One [128 rows x 128 columns] unit of the row reduction: UN positions per thread are loaded (all `world` slots of each)
+// before the first add, so that enough bytes are in flight to cover the L2 / HBM latency.
+template <int UN>
+__device__ __forceinline__ void tp_reduce_unit(const GemmParams& p, const __nv_bfloat16* stage, int rb, int sl, int Ms, int W) {
+  for (int e0 = threadIdx.x; e0 < BM * 16; e0 += 192 * UN) {
+    uint4 part[UN][MAX_RANKS];
+    uint4 resid[UN];
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int e = e0 + u * 192;
+      const int row = rb * BM + (e >> 4), col = sl * 128 + (e & 15) * 8;
+      const bool live = e < BM * 16 && col < p.N;
+#pragma unroll
+      for (int src = 0; src < MAX_RANKS; ++src)
+        if (src < W && live) part[u][src] = ld_peer_v4(stage + ((size_t)src * Ms + row) * p.N + col);
+      if (p.residual && live) resid[u] = *reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col);
+    }
+#pragma unroll
+    for (int u = 0; u < UN; ++u) {
+      const int e = e0 + u * 192;
+      const int row = rb * BM + (e >> 4), col = sl * 128 + (e & 15) * 8;
+      if (e >= BM * 16 || col >= p.N) continue;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int src = 0; src < MAX_RANKS; ++src) {
+        if (src >= W) continue;
+        const uint4 v = part[u][src];
+        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      if (p.residual) {
+        const uint4 v = resid[u];
+        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      if (p.out_f32) {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldc + col;
+        *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      } else {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldc + col;
+        *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                                                  pack_bf16x2(acc[6], acc[7]));
+      }
+    }
   }
 }
 
@@ -312,38 +363,16 @@ __device__ __forceinline__ void tp_reduce_rows(const GemmParams& p, int n_tiles,
     const bool ok = *s_ok != 0;
     __syncthreads();
     if (!ok) break;
-    for (int e = threadIdx.x; e < BM * 16; e += 192) {
-      const int row = rb * BM + (e >> 4), col = sl * 128 + (e & 15) * 8;
-      if (col >= p.N) continue;
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int src = 0; src < W; ++src) {
-        const uint4 v = ld_peer_v4(stage + ((size_t)src * Ms + row) * p.N + col);
-        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
-      if (p.residual) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col);
-        const float2 f0 = unpack_bf16x2(v.x), f1 = unpack_bf16x2(v.y), f2 = unpack_bf16x2(v.z), f3 = unpack_bf16x2(v.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y; acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
-      if (p.out_f32) {
-        float* o = reinterpret_cast<float*>(p.out) + (size_t)row * p.ldc + col;
-        *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-      } else {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (size_t)row * p.ldc + col;
-        *reinterpret_cast<uint4*>(o) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                                                  pack_bf16x2(acc[6], acc[7]));
-      }
-    }
+    if (W <= 2) tp_reduce_unit<4>(p, stage, rb, sl, Ms, W);
+    else if (W <= 4) tp_reduce_unit<2>(p, stage, rb, sl, Ms, W);
+    else tp_reduce_unit<1>(p, stage, rb, sl, Ms, W);
   }
 }
 
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(192, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmA2, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -367,6 +396,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
   uint8_t* s_epi = smem + STAGES * Cfg::STAGE_BYTES + 256 + 1280;     // reduce-scatter epilogue staging (4 warps)
   __shared__ int s_tp_ok;
+  __shared__ unsigned long long* s_pend[4][16];   // reduce-scatter: counters of stored tiles not yet published, per epilogue warp
   if (p.group_mode == 1 && threadIdx.x == 32) {
     int run = 0;
     for (int g = 0; g < p.batch; ++g) {
@@ -381,6 +411,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.tp_mode == 1) tma_prefetch_desc(&tmA2);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -415,15 +446,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += n_compute) {
         const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
+        const CUtensorMap* mapA = &tmA;
+        int a_row0 = ti.row0;
         if (p.tp_mode == 1) {
-          // the rows of this tile were written into the local staging buffer by a communication CTA of their owner
-          const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(p.tp_flags.ptr[p.tp_rank]);
-          if (!wait_ge_sys(flags + ti.row0 / BM, tp_epoch)) {
-            report_error(p.status, OA_KERR_WAIT_PEER);
-            ok = false;
-            break;
+          const int Ms = p.M / p.tp_world;
+          if (ti.row0 / Ms == p.tp_rank) {
+            mapA = &tmA2;                   // this rank's own rows are read in place (tmA2 covers the local shard)
+            a_row0 = ti.row0 - p.tp_rank * Ms;
+          } else {
+            // the rows of this tile are pushed into the local staging buffer by a communication CTA of their owner
+            const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(p.tp_flags.ptr[p.tp_rank]);
+            if (!wait_ge_sys(flags + ti.row0 / BM, tp_epoch)) {
+              report_error(p.status, OA_KERR_WAIT_PEER);
+              ok = false;
+              break;
+            }
+            fence_proxy_async_global();   // generic-proxy writes (peer stores) before the async-proxy (TMA) reads below
           }
-          fence_proxy_async_global();     // generic-proxy writes (peer stores) before the async-proxy (TMA) reads below
         }
         for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) {
@@ -436,9 +475,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* b = sB + stage * Cfg::B_BYTES;
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_3d(a + j * (64 * BK * 2), &tmA, &full[stage], ti.row0 + j * 64, kb * BK, ti.a_batch);
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(a + j * (64 * BK * 2), mapA, &full[stage], a_row0 + j * 64, kb * BK, ti.a_batch);
           } else {
-            tma_load_3d(a, &tmA, &full[stage], kb * BK, ti.row0, ti.a_batch);
+            tma_load_3d(a, mapA, &full[stage], kb * BK, a_row0, ti.a_batch);
           }
           if (B_MN) {
 #pragma unroll
@@ -502,6 +541,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int quad = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    int n_pend = 0;
     for (int t = blockIdx.x; t < total_tiles; t += n_compute) {
       const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
       const int bi = ti.bi, ni = ti.ni, split = ti.split, kb0 = ti.kb0, kb1 = ti.kb1;
@@ -550,17 +590,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             for (int it = 0; it < 8; ++it) {
               const int idx = it * 32 + lane, rr = idx >> 3, piece = idx & 7;
               const int col = ni * BN + (c - 1) * 32 + piece * 8;
-              if (col < p.N) st_peer_v4(dst + (size_t)rr * p.N + col, *reinterpret_cast<const uint4*>(se + rr * Cfg::EPI_ROW_BYTES + piece * 16));
+              if (col < p.N)   // weak store; published by the fence + release below
+                *reinterpret_cast<uint4*>(dst + (size_t)rr * p.N + col) = *reinterpret_cast<const uint4*>(se + rr * Cfg::EPI_ROW_BYTES + piece * 16);
             }
             __syncwarp();
           }
           if (c == BN / 32 - 1) {
-            __threadfence_system();
-            __syncwarp();
-            if (lane == 0) {
-              const int Ms = p.M / p.tp_world;
-              const int owner = ti.row0 / Ms;
-              red_release_sys_add(reinterpret_cast<unsigned long long*>(p.tp_flags.ptr[owner]) + (ti.row0 - owner * Ms) / BM, 1ull);
+            // publishing a tile costs a system-scope fence (a round trip over NVLink): tiles are counted in batches
+            const int Ms = p.M / p.tp_world;
+            const int owner = ti.row0 / Ms;
+            if (lane == 0) s_pend[quad][n_pend] = reinterpret_cast<unsigned long long*>(p.tp_flags.ptr[owner]) + (ti.row0 - owner * Ms) / BM;
+            if (++n_pend == 16) {
+              __threadfence_system();
+              __syncwarp();
+              if (lane < n_pend) red_release_sys_add(s_pend[quad][lane], 1ull);
+              __syncwarp();
+              n_pend = 0;
             }
           }
         } else {
@@ -569,6 +614,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
+    }
+    if (n_pend > 0) {
+      __threadfence_system();
+      __syncwarp();
+      if (lane < n_pend) red_release_sys_add(s_pend[quad][lane], 1ull);
     }
   }
   if (p.tp_mode == 2) {
@@ -690,7 +740,8 @@ int num_sms() {
 }
 
 template <int BN, int A_MN, int B_MN>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st,
+                       const CUtensorMap* ta2 = nullptr) {
   auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -698,7 +749,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       return OA_ERR_LAUNCH;
     attr_set = true;
   }
-  kfn<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, p);
+  kfn<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, ta2 ? *ta2 : ta, p);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
@@ -871,7 +922,8 @@ extern "C" int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out
   if (mode == 1 && ((ld_src & 7) || lda != K)) return OA_ERR_ALIGN;
   const int sms = num_sms();
   if (mode == 1) {
-    if (comm_ctas <= 0) comm_ctas = 20;
+    if (comm_ctas <= 0) comm_ctas = 16;
+    if (world == 1) comm_ctas = 1;
     if (comm_ctas > sms / 2) comm_ctas = sms / 2;
   } else {
     comm_ctas = 0;
@@ -899,9 +951,15 @@ extern "C" int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out
   if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb, 0, 64, BK);
   else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, (uint32_t)bn);
   if (rc) return rc;
+  CUtensorMap ta2;
+  const CUtensorMap* pa2 = nullptr;
+  if (mode == 1) {     // this rank's own rows are read in place from the shard
+    if ((rc = make_tmap_3d_bf16(&ta2, src, (uint64_t)K, (uint64_t)(M / world), 1, (uint64_t)ld_src, 0, BK, BM))) return rc;
+    pa2 = &ta2;
+  }
   // every CTA takes part in the protocol (communication CTAs, the row reduction, the epoch hand-over): a full grid always
   cudaStream_t st = (cudaStream_t)stream;
-  if (bn == 256) rc = b_mn ? launch_gemm<256, 0, 1>(ta, tb, p, sms, st) : launch_gemm<256, 0, 0>(ta, tb, p, sms, st);
-  else           rc = b_mn ? launch_gemm<128, 0, 1>(ta, tb, p, sms, st) : launch_gemm<128, 0, 0>(ta, tb, p, sms, st);
+  if (bn == 256) rc = b_mn ? launch_gemm<256, 0, 1>(ta, tb, p, sms, st, pa2) : launch_gemm<256, 0, 0>(ta, tb, p, sms, st, pa2);
+  else           rc = b_mn ? launch_gemm<128, 0, 1>(ta, tb, p, sms, st, pa2) : launch_gemm<128, 0, 0>(ta, tb, p, sms, st, pa2);
   return rc;
 }

@@ -84,6 +84,11 @@ class OaTpAgSite(_Site):
     def gathered(self) -> torch.Tensor:
         return self.local(torch.bfloat16, (self.M, self.K))
 
+    def own_rows(self) -> torch.Tensor:
+        """This rank's rows of the staging buffer: an activation produced here needs no copy before the all-gather."""
+        Ms = self.M // self.mesh.world
+        return self.gathered()[self.mesh.rank * Ms:(self.mesh.rank + 1) * Ms]
+
 
 class OaTpRsSite(_Site):
     """Call site of a GEMM -> reduce-scatter producing [M / W, N]."""
@@ -104,6 +109,11 @@ def ag_gemm(site: OaTpAgSite, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: b
     assert x_shard.shape == (site.M // m.world, site.K)
     out = torch.empty((site.M, Nn), dtype=torch.bfloat16, device=x_shard.device)
     stage = site.gathered()
+    Ms = site.M // m.world
+    own = stage[m.rank * Ms:(m.rank + 1) * Ms]
+    if x_shard.data_ptr() != own.data_ptr():
+        K.unary("copy", x_shard, out=own)      # a producer that writes into site.own_rows() directly skips this copy
+    x_shard = own
     K._launch(N.require().oa_gemm_bf16_tp(1, stage.data_ptr(), w.data_ptr(), out.data_ptr(), site.M, Nn, site.K, site.K, w.shape[1], Nn,
                                           int(b_mn), None, 0, 0, 1.0, x_shard.data_ptr(), site.K, site.bufs, site.flags,
                                           site.sync.data_ptr(), m.world, m.rank, comm_ctas, K.status_word(m.device).data_ptr(),
