@@ -122,6 +122,39 @@ def bench_mamba():
     K.check_status()
 
 
+def bench_decode():
+    """Batch-32 greedy decoding of 256 tokens after a 2048-token prompt on the 7B-class model (one GPU, KV cache)."""
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.core.types import OaPrecision
+    from oa_b200.models import OaGptConfig, OaGptModel
+    from oa_b200.runtime.engine import OaEngineConfig, OaInitComputeEngine
+    from oa_b200.serve import OaGptDecoder
+    assert OaInitComputeEngine(OaEngineConfig(Precision=OaPrecision.BF16, DeviceIndex=0))
+    F.SetRngSeed(1)
+    cfg = OaGptConfig.Llama7B()
+    model = OaGptModel(cfg)
+    B, S, NEW = 32, 2048, 256
+    prompt = torch.randint(0, cfg.Vocab, (B, S), dtype=torch.int32, device="cuda")
+    dec = OaGptDecoder(model, batch=B, max_seq=S + NEW)
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    dec.Prefill(prompt[:, :256])                 # warm-up of every kernel shape family
+    dec.Step(prompt[:, :1])
+    torch.cuda.synchronize()
+    e[0].record()
+    logits = dec.Prefill(prompt)
+    e[1].record()
+    for _ in range(NEW):
+        nxt = logits.float().argmax(-1).to(torch.int32).reshape(-1, 1)
+        logits = dec.Step(nxt)
+    e[2].record()
+    torch.cuda.synchronize()
+    t_pre, t_dec = e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2])
+    emit(op="decode_7b_kv_cache", batch=B, prompt=S, new_tokens=NEW, prefill_ms=t_pre, prefill_tokens_per_s=B * S / t_pre * 1e3,
+         decode_ms_per_token=t_dec / NEW, decode_tokens_per_s=B * NEW / t_dec * 1e3, kv_cache_gb=dec.Cache.Bytes() / 1e9,
+         weight_gb=sum(p.NumElements() for p in model.AllParameterPtrs()) * 2 / 1e9)
+    K.check_status()
+
+
 def bench_tp():
     import torch.distributed as dist
     from oa_b200.parallel import tp as TP
@@ -202,7 +235,7 @@ def main() -> int:
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "tp": bench_tp}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "tp": bench_tp, "decode": bench_decode}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:

@@ -208,6 +208,12 @@ int oa_gated_norm_fwd(int dtype, const void* y, const void* z, long long zs, con
 int oa_gated_norm_bwd(int dtype, const void* y, const void* z, long long zs, const float* w, const float* rstd, const void* dout,
                       void* dy, void* dz, long long dzs, float* dw, long long rows, int H, int P, void* stream);
 
+// ---- KV-cache serving (decode.cu)
+int oa_kv_append(const void* k_src, const void* v_src, long long src_stride, void* k_cache, void* v_cache, int batch,
+                 int s_new, int heads, int head_dim, int pos0, int max_seq, void* stream);
+int oa_decode_attn(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out, long long out_stride,
+                   int batch, int heads, int head_dim, int len, int max_seq, float scale, void* stream);
+
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);
 int oa_ipc_free(void* p);

@@ -892,3 +892,35 @@ def rnn_scan_bwd(gates_i, w_hh, b_hh, hprev, dout, gates: int):
                                         hprev.data_ptr(), dout.contiguous().data_ptr(), dgi.data_ptr(), dgh.data_ptr(), dh0.data_ptr(),
                                         B, S, H, N.stream()), "oa_rnn_scan_bwd")
     return dgi, dgh, dh0
+
+
+# ---------------------------------------------------------------- KV-cache serving
+def kv_append(k_src: torch.Tensor, v_src: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: int, s_new: int,
+              pos0: int) -> None:
+    """Copies new key / value rows ([batch*s_new, heads*head_dim] views, row stride allowed) into the caches
+    [batch, heads, max_seq, head_dim] at positions pos0 .. pos0 + s_new."""
+    _, heads, max_seq, hd = k_cache.shape
+    if not k_cache.is_cuda:
+        for src, dst in ((k_src, k_cache), (v_src, v_cache)):
+            dst[:, :, pos0:pos0 + s_new] = src.reshape(batch, s_new, heads, hd).permute(0, 2, 1, 3).to(dst.dtype)
+        return
+    assert k_src.stride(1) == 1 and k_src.stride(0) == v_src.stride(0) and k_cache.dtype == torch.bfloat16
+    _launch(N.require().oa_kv_append(k_src.data_ptr(), v_src.data_ptr(), k_src.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), batch, s_new,
+                                     heads, hd, pos0, max_seq, N.stream()), "oa_kv_append")
+
+
+def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, length: int, scale: Optional[float] = None) -> torch.Tensor:
+    """One query token per sequence, q [batch, heads*head_dim] (row stride allowed), against the first `length` cached
+    positions; returns [batch, heads*head_dim]."""
+    batch, heads, max_seq, hd = k_cache.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(hd)
+    if not q.is_cuda:
+        qf = q.float().reshape(batch, heads, 1, hd)
+        kf, vf = k_cache[:, :, :length].float(), v_cache[:, :, :length].float()
+        p = torch.softmax((qf @ kf.transpose(-1, -2)) * scale, -1)
+        return (p @ vf).reshape(batch, heads * hd).to(q.dtype)
+    out = torch.empty((batch, heads * hd), dtype=q.dtype, device=q.device)
+    assert q.stride(1) == 1 and q.dtype == torch.bfloat16
+    _launch(N.require().oa_decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0), batch,
+                                       heads, hd, length, max_seq, float(scale), N.stream()), "oa_decode_attn")
+    return out
