@@ -43,10 +43,12 @@ class OaMetric:
     def Count(self) -> int:
         return self._count
 
+    Result = Value
+
 
 class OaMetricLoss(OaMetric):
-    def __init__(self):
-        super().__init__("loss")
+    def __init__(self, name: str = "loss"):
+        super().__init__(name)
 
 
 class OaMetricAccuracy(OaMetric):

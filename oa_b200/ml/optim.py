@@ -139,6 +139,8 @@ class OaOptimizer:
     def GetStep(self) -> int:
         return self.Step_
 
+    StepCount = GetStep
+
     def NotifyProgramReplay(self, count: int = 1) -> None:
         self.Step_ += count
 

@@ -293,6 +293,42 @@ class OaItTraining:
     def LastLoss(self) -> float:
         return self._last_loss
 
+    def StepCount(self) -> int:
+        return self._index
+
+    def Cfg(self) -> OaItTrainingConfig:
+        return self.Config
+
+    def HasEpochs(self) -> bool:
+        return self.Config.StepsPerEpoch > 0
+
+    def IsEpochBoundary(self) -> bool:
+        spe = self.Config.StepsPerEpoch
+        return spe > 0 and self._index > 0 and self._index % spe == 0
+
+    def EpochMeanLoss(self) -> float:
+        """Mean loss of the steps of the epoch that is running (or has just ended)."""
+        spe = self.Config.StepsPerEpoch
+        if not self._losses:
+            return float("nan")
+        if spe <= 0:
+            xs = self._losses
+        else:
+            done = self._index % spe or spe
+            xs = self._losses[-done:]
+        return sum(xs) / len(xs)
+
+    def LastGpuMs(self) -> float:
+        return self._gpu_ms[-1] if self._gpu_ms else 0.0
+
+    def GpuSamplesPerSecond(self) -> float:
+        ms = self.GpuMsPerStep()
+        return self.Config.BatchSize / (ms / 1e3) if ms > 0 else 0.0
+
+    def GpuSourceUnitsPerSecond(self) -> float:
+        ms = sum(self._gpu_ms)
+        return self._source_units_total / (ms / 1e3) if ms > 0 else 0.0
+
     def Losses(self) -> list:
         return list(self._losses)
 
