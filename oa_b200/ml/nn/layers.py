@@ -7,6 +7,8 @@ Checkpoint names follow the reference: `weight` / `bias` on Linear, LayerNorm, R
 """
 from __future__ import annotations
 
+import torch
+
 import math
 from typing import Optional
 
@@ -175,6 +177,9 @@ class OaMultiHeadAttention(OaModule):
     def _use_flash(self) -> bool:
         if self.Backend == OaAttentionBackend.Standard:
             return False
+        w = self.OutProj.Weight.Tensor()
+        if w.is_cuda and w.dtype == torch.bfloat16 and self.HeadDim not in (64, 128):
+            return False          # the tensor-core kernel is built for head dims 64 and 128; others take the materialised path
         return True
 
     def Attend(self, qkv: OaMatrix, batch: int, seq: int, pos_offset: int = 0) -> OaMatrix:
