@@ -1,0 +1,123 @@
+"""`oa`: the public Python surface of the framework, name for name the one the reference ships
+(Source/Python/oa/_surface.py: root `Oa*` values, the namespace modules OaFnMatrix / OaFnLoss / OaFnAutograd /
+OaFnMetric, and the `Context` scope), bound here to oa_b200.
+
+    import oa
+    oa.OaInitComputeEngine()
+    model = oa.OaNlpSuiteModel(oa.OaNlpSuiteRecipe())
+    opt = oa.OaAdamW(model.AllParameterPtrs(), 1e-2)
+    with oa.OaGradientTape() as tape: ...
+    with oa.Context(): ...            # Execute + Sync of the default context on scope exit
+
+Names of the reference surface that this build does not provide (reinforcement learning, audio, vision, crypto, plot, ui,
+the Empyrealm core) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
+"""
+from __future__ import annotations
+
+import sys
+import types
+
+import oa_b200 as _impl
+from oa_b200.core import fn_matrix as _F
+from oa_b200.core import types as _T
+from oa_b200.core.matrix import OaMatrix
+from oa_b200.ml import autograd as _AG
+from oa_b200.ml import callbacks as _CB
+from oa_b200.ml import fn_loss as _L
+from oa_b200.ml import metric as _M
+from oa_b200.ml import module as _MOD
+from oa_b200.ml import nlp_suite as _NS
+from oa_b200.ml import optim as _O
+from oa_b200.ml import training as _TR
+from oa_b200.ml import training_session as _TS
+from oa_b200.ml.byte import OaByteEmbedding, OaByteEncoder, OaByteHead
+from oa_b200.ml.checkpoint import OaCheckpointManager, OaCheckpointManagerConfig
+from oa_b200.ml.nn import layers as _NN
+from oa_b200.ml.nn.mamba3 import OaMamba3Module
+from oa_b200.ml.nn.moe import OaMoE, OaMoeExpert
+from oa_b200.ml.nn.recurrent import OaGru, OaGruCell, OaRnn, OaRnnCell
+from oa_b200.ml.tokenizer import OaBpeTokenizer
+from oa_b200.runtime import engine as _RT
+from oa_b200.utils.paths import OaFilesystem, OaPath, OaPaths
+
+__version__ = _impl.__version__
+
+# ---- root values
+OaScalarType, OaMatMulPrecision, OaMatrixShape, OaPrecision = _T.OaScalarType, _T.OaMatMulPrecision, _T.OaMatrixShape, _T.OaPrecision
+OaStatus, OaStatusCode, OaError = _T.OaStatus, _T.OaStatusCode, _T.OaError
+OaContext, OaContextGetDefault = _RT.OaContext, _RT.OaContextGetDefault
+OaInitComputeEngine, OaShutdownComputeEngine = _RT.OaInitComputeEngine, _RT.OaShutdownComputeEngine
+OaEngine, OaEngineConfig = _RT.OaEngine, _RT.OaEngineConfig
+OaGradientTape, OaGradNo = _AG.OaGradientTape, _AG.OaGradNo
+OaModule, OaParameter = _MOD.OaModule, _MOD.OaParameter
+OaOptimizer, OaOptimizerNoOp, OaOptimizerComposite = _O.OaOptimizer, _O.OaOptimizerNoOp, _O.OaOptimizerComposite
+OaAdam, OaAdamW, OaSGD, OaMuon, OaMuonAdamWConfig = _O.OaAdam, _O.OaAdamW, _O.OaSGD, _O.OaMuon, _O.OaMuonAdamWConfig
+OaItTraining, OaItTrainingConfig, OaGpuTimingStats = _TR.OaItTraining, _TR.OaItTrainingConfig, _TR.OaGpuTimingStats
+OaCallback, OaCbTraining = _TR.OaCallback, _TR.OaCbTraining
+OaCbProgressBar, OaCbSummary, OaCbValidation, OaCbCheckpoint = _CB.OaCbProgressBar, _CB.OaCbSummary, _CB.OaCbValidation, _CB.OaCbCheckpoint
+OaCbEarlyStop, OaCbLrScheduler, OaCbCsvLogger, OaCbPhase = _CB.OaCbEarlyStop, _CB.OaCbLrScheduler, _CB.OaCbCsvLogger, _CB.OaCbPhase
+OaMetric, OaMetricLoss, OaMetricAccuracy = _M.OaMetric, _M.OaMetricLoss, _M.OaMetricAccuracy
+OaTrainingSession, OaTrainingSnapshot, OaTrainingState = _TS.OaTrainingSession, _TS.OaTrainingSnapshot, _TS.OaTrainingState
+OaTrainingCommandDisposition, OaTrainingCommandResult = _TS.OaTrainingCommandDisposition, _TS.OaTrainingCommandResult
+OaTrainingMetricSample, OaTrainingValue = _TS.OaTrainingMetricSample, _TS.OaTrainingValue
+OaLinear, OaEmbedding, OaLayerNorm, OaRmsNorm, OaTransformerBlock = _NN.OaLinear, _NN.OaEmbedding, _NN.OaLayerNorm, _NN.OaRmsNorm, _NN.OaTransformerBlock
+OaMultiHeadAttention, OaFfn, OaSequential, OaDropout, OaRoPE, OaSwiGLU = _NN.OaMultiHeadAttention, _NN.OaFfn, _NN.OaSequential, _NN.OaDropout, _NN.OaRoPE, _NN.OaSwiGLU
+OaRelu, OaGelu, OaSilu, OaSoftmax, OaIdentity, OaFlatten = _NN.OaRelu, _NN.OaGelu, _NN.OaSilu, _NN.OaSoftmax, _NN.OaIdentity, _NN.OaFlatten
+OaNlpArchitecture, OaNlpTokenizerKind = _NS.OaNlpArchitecture, _NS.OaNlpTokenizerKind
+OaNlpSuiteRecipe, OaNlpSuiteModel, OaNlpSuiteSampler, OaNlpSuiteGenerate = _NS.OaNlpSuiteRecipe, _NS.OaNlpSuiteModel, _NS.OaNlpSuiteSampler, _NS.OaNlpSuiteGenerate
+OaNlpSuiteBatchSize, OaNlpSuiteContextLength, OaNlpSuiteModelWidth = _NS.OaNlpSuiteBatchSize, _NS.OaNlpSuiteContextLength, _NS.OaNlpSuiteModelWidth
+OaNlpSuiteHiddenWidth, OaNlpSuiteTrainingSteps, OaNlpSuiteRngSeed = _NS.OaNlpSuiteHiddenWidth, _NS.OaNlpSuiteTrainingSteps, _NS.OaNlpSuiteRngSeed
+OaNlpSuiteGenerationPrompt, OaNlpSuiteGenerationSourceUnits = _NS.OaNlpSuiteGenerationPrompt, _NS.OaNlpSuiteGenerationSourceUnits
+
+
+class OaActivation:
+    """Activation selector of fused Linear layers."""
+    none, Relu, Gelu, Silu = 0, 1, 2, 3
+
+
+# ---- namespace modules (Python views of the C++ namespaces)
+def _namespace(name: str, doc: str, source, names, renames=None) -> types.ModuleType:
+    m = types.ModuleType(f"oa.{name}", doc)
+    for n in names:
+        setattr(m, n, getattr(source, (renames or {}).get(n, n)))
+    m.__all__ = tuple(names)
+    sys.modules[f"oa.{name}"] = m
+    return m
+
+
+_FN_MATRIX = [n for n in dir(_F) if n[0].isupper()]
+OaFnMatrix = _namespace("OaFnMatrix", "Tensor factories and differentiable operations.", _F, _FN_MATRIX)
+OaFnLoss = _namespace("OaFnLoss", "Loss functions and their explicit backward forms.", _L,
+                      ["Bce", "BceBwd", "CrossEntropy", "CrossEntropyBwd", "MaskedCrossEntropy", "L1", "L1Bwd", "Mse", "MseBwd", "SmoothL1",
+                       "SmoothL1Bwd", "LastName"])
+OaFnAutograd = _namespace("OaFnAutograd", "Autograd recording switch.", _AG, ["IsEnabled", "SetEnabled"])
+OaFnMetric = _namespace("OaFnMetric", "Host-side metrics of device results.", _M.OaFnMetric, ["Accuracy", "ScalarLoss"])
+
+
+class Context:
+    """Executes and synchronises the default context on scope exit."""
+
+    def __enter__(self) -> "Context":
+        self._ctx = OaContextGetDefault()
+        return self
+
+    def __exit__(self, exc_type, exc_value, traceback) -> None:
+        self._ctx.Execute()
+        self._ctx.Sync()
+
+
+UNAVAILABLE = (
+    "OaEmpyrealmCore", "OaItRlTraining", "OaItRlTrainingConfig", "OaDqnLossConfig", "OaDqnLossResult", "OaGaeConfig", "OaGaeResult",
+    "OaPpoLossConfig", "OaPpoLossResult", "OaRlContinuousPolicyResult", "OaRlEnvironmentSpec", "OaRlFieldSpec", "OaRlPolicyResult",
+    "OaRlReplayBatch", "OaRlReplayBuffer", "OaRlReplayConfig", "OaRlRolloutBatch", "OaRlRolloutBuffer", "OaRlRolloutConfig", "OaRlSpaceKind",
+    "OaRlTrainingPhase", "OaSacCriticLossResult", "OaSacLossConfig", "OaFnRl", "OaFnAudio", "OaFnImage", "OaFnDetection", "OaFnHash",
+    "OaPlot", "OaViewer", "OaAudio", "OaVideo")
+
+
+def __getattr__(name: str):
+    if name in UNAVAILABLE:
+        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (reinforcement learning / audio / vision / ui) that this build does not provide")
+    raise AttributeError(f"module 'oa' has no attribute '{name}'")
+
+
+__all__ = sorted(n for n in globals() if n.startswith("Oa")) + ["Context"]

@@ -180,6 +180,13 @@ class OaItTraining:
     def RequestStop(self) -> None:
         self._stop = True
 
+    def RequestRecapture(self) -> None:
+        """Drops the captured program; the next step runs eagerly and the one after captures again."""
+        if self._program is not None:
+            self._program = OaTrainingProgram()
+            self._static_loss = None
+            self._recapture_at = self._index + 1
+
     def Index(self) -> int:
         """Number of completed steps."""
         return self._index
@@ -201,7 +208,7 @@ class OaItTraining:
             return self._finish_step(self._static_loss, stepped=True)
         if prepare is not None:
             prepare()
-        if self._program is not None and self._index >= 1:
+        if self._program is not None and self._index >= max(1, getattr(self, "_recapture_at", 1)):
             def body():
                 loss = record()
                 self.Opt_.Step()

@@ -108,3 +108,64 @@ def test_early_stop_and_resume(tmp_path):
     assert fresh.LoadLatestInto(net2, opt2)
     assert torch.equal(net2.Weight.Tensor(), net.Weight.Tensor()) and opt2.StepCount() == opt.StepCount()
     assert not OaCheckpointManager(OaCheckpointManagerConfig(Dir=str(tmp_path / "none"))).LoadLatestInto(net2, opt2)
+
+
+def test_training_session_commands_apply_at_step_boundaries():
+    import threading
+    from oa_b200.ml import training_session as TS
+    F.SetRngSeed(0)
+    net = OaLinear(4, 2)
+    opt = OaAdam(net.AllParameterPtrs(), 1e-2)
+    tr = OaItTraining(opt, OaItTrainingConfig(TotalSteps=1000, BatchSize=8))
+    done = {"ckpt": 0}
+    cfg = TS.OaTrainingSessionConfig(CommandCapacity=4)
+    cfg.Handlers.Checkpoint = lambda: (done.__setitem__("ckpt", done["ckpt"] + 1), OaStatus_ok())[1]
+    ses = TS.OaTrainingSession(tr, cfg)
+    V = TS.OaTrainingValue
+    assert ses.RegisterParameter(TS.OaTrainingParameterDesc("lr", TS.OaTrainingParameterClass.Hot, TS.OaTrainingValueKind.Float, 0.0, 1.0,
+                                                            lambda: V.FromFloat(opt.Lr()), lambda v: (opt.SetLr(v.Float), OaStatus_ok())[1]))
+    assert ses.RegisterParameter(TS.OaTrainingParameterDesc("width", TS.OaTrainingParameterClass.Immutable, TS.OaTrainingValueKind.Integer))
+    x, y = torch.randn(8, 4), torch.randn(8, 2)
+
+    def one_step():
+        tr.IsDone()
+        opt.ZeroGrad()
+        with AG.OaGradientTape() as tape:
+            loss = L.Mse(net.Forward(OaMatrix(x)), OaMatrix(y))
+            tape.Backward(loss)
+        tr.Next(loss)
+        ses.OnStepCompleted()
+
+    s1, st = ses.SetParameter("lr", V.FromFloat(0.5))
+    assert st and opt.Lr() == pytest.approx(1e-2)                 # queued, not applied yet
+    ses.SetParameter("lr", V.FromFloat(7.0))                       # out of range
+    ses.SetParameter("width", V.FromInteger(3))                    # immutable
+    ses.Checkpoint()
+    _, full = ses.Pause()
+    assert not full and full.code.name == "ResourceExhausted"      # capacity 4
+    assert ses.TryBeginStep()
+    assert opt.Lr() == pytest.approx(0.5) and done["ckpt"] == 1 and ses.Revision() == 2
+    res = ses.TakeResults()
+    assert [r.Disposition.name for r in res] == ["Applied", "Rejected", "Rejected", "Applied"]
+    assert res[1].Status.code.name == "OutOfRange" and res[2].Status.code.name == "PermissionDenied"
+    one_step()
+    snap = ses.LatestSnapshot()
+    assert snap.Step == 1 and snap.LearningRate == pytest.approx(0.5) and snap.Revision == 2
+    # stale expected revision is rejected
+    ses.Pause(expected_revision=1)
+    assert ses.TryBeginStep() and ses.TakeResults()[0].Status.code.name == "Aborted"
+    # pause from another thread, resume later: the loop blocks in WaitBeginStep meanwhile
+    ses.Pause()
+    assert not ses.TryBeginStep() and ses.State() == TS.OaTrainingState.Paused
+    t = threading.Timer(0.1, lambda: ses.Resume())
+    t.start()
+    assert ses.WaitBeginStep() and ses.State() == TS.OaTrainingState.Running
+    ses.Stop()
+    assert not ses.WaitBeginStep() and tr.IsDone()
+    ses.OnFinished(tr.LastStatus)
+    assert ses.State() == TS.OaTrainingState.Completed and not ses.Pause()[1]
+
+
+def OaStatus_ok():
+    from oa_b200.core.types import OaStatus
+    return OaStatus.Ok()
