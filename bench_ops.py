@@ -184,10 +184,8 @@ def bench_tp():
         w = (torch.randn(Nn, Kd, device="cuda") * 0.02).bfloat16()
         full = torch.empty(M, Kd, device="cuda", dtype=torch.bfloat16)
         out = torch.empty(M, Nn, device="cuda", dtype=torch.bfloat16)
-        for comm in (12, 20, 32):
-            t = maxr(loop(lambda: TP.ag_gemm(site, xs, w, comm_ctas=comm)))
-            emit(op="tp_allgather_gemm_fused", site=name, world=world, M=M, N=Nn, K=Kd, comm_ctas=comm, us=t * 1e3,
-                 tflops=2 * M * Nn * Kd / t / 1e9)
+        t = maxr(loop(lambda: TP.ag_gemm(site, xs, w)))
+        emit(op="tp_allgather_gemm_fused", site=name, world=world, M=M, N=Nn, K=Kd, us=t * 1e3, tflops=2 * M * Nn * Kd / t / 1e9)
 
         def base():
             dist.all_gather_into_tensor(full, xs)

@@ -57,10 +57,10 @@ struct GemmParams {
   int group_mode;
   const int* group_offsets;
   // Tensor-parallel modes (the GEMM and its collective are one kernel; peers are reached with plain loads / stores).
-  //   1  all-gather -> GEMM: A is the local staging copy [M, K] of the row-sharded activation.  The last tp_comm CTAs push
-  //      this rank's shard (tp_src) into every rank's staging buffer 128 rows at a time and publish a flag per block; the
-  //      TMA producer of a compute CTA waits for the flag of the block it is about to load.  M tiles are visited own
-  //      shard first, then in the order the peers' blocks arrive.
+  //   1  all-gather -> GEMM: A is the local staging copy [M, K] of the row-sharded activation.  The epilogue warps of every
+  //      CTA first push slabs of this rank's shard (tp_src) into the peers' staging buffers and count them in on the
+  //      receiver; the TMA producer waits for the counter of the 128-row block it is about to load.  M tiles are visited
+  //      own shard first (read in place), then in the order the peers' blocks arrive.
   //   2  GEMM -> reduce-scatter: every output tile belongs to the rank that owns its rows; the epilogue stores the bf16
   //      partial into slot `rank` of the owner's staging buffer and bumps the owner's per-block counter; after its tiles a
   //      CTA reduces blocks of this rank's own rows over the `world` slots (+ residual) into `out` [M / world, N].
@@ -255,42 +255,51 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
 }
 
-// Tensor-parallel mode 1, communication CTAs: push this rank's shard into every peer's staging buffer, one 128-row block
-// at a time, and publish the block's flag with release semantics at system scope.
-__device__ __forceinline__ void tp_push_shard(const GemmParams& p, int comm_idx, unsigned long long epoch) {
+// Tensor-parallel mode 1: the four epilogue warps of EVERY CTA push a share of this rank's shard into the peers' staging
+// buffers before their first accumulator is ready (they would idle through the first main loop anyway), so the NVLink
+// traffic is issued from all SMs at once.  An item is one [128 rows x 512 columns] slab for one peer; peers are served
+// nearest first (rank+1, rank+2, ...), which is the order in which the receivers consume the blocks.  Each slab is
+// published by a release-add on the receiver's per-block counter.
+constexpr int TP_SLAB = 512;
+__device__ __forceinline__ void tp_push_shard(const GemmParams& p, unsigned long long epoch) {
   const int W = p.tp_world, r = p.tp_rank;
   const int blocks = (p.M / W) / BM;
-  const int vec_per_row = p.K >> 3;
-  const int total_vec = BM * vec_per_row;
+  const int n_slabs = (p.K + TP_SLAB - 1) / TP_SLAB;
+  const int et = (int)threadIdx.x - 64;                  // 0..127 over warps 2..5
+  const int per_peer = blocks * n_slabs;
   constexpr int UNROLL = 8;
-  const int R = W - 1;                                   // remote peers only: own rows are read in place by the tiles
-  for (int item = comm_idx; item < blocks * R; item += p.tp_comm) {
-    const int c = item / R, j = item - c * R;
+  for (int item = blockIdx.x; item < per_peer * (W - 1); item += gridDim.x) {
+    const int j = item / per_peer, rem = item - j * per_peer;
+    const int c = rem / n_slabs, sl = rem - c * n_slabs;
     const int peer = (r + 1 + j) % W;
-    const __nv_bfloat16* src = p.tp_src + (size_t)c * BM * p.tp_ld_src;
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.tp_bufs.ptr[peer]) + ((size_t)r * blocks + c) * BM * p.K;
-    {
-      for (int v0 = threadIdx.x; v0 < total_vec; v0 += 192 * UNROLL) {
-        uint4 buf[UNROLL];
+    const int col0 = sl * TP_SLAB;
+    const int vec_per_row = min(TP_SLAB, p.K - col0) >> 3;
+    const int total_vec = BM * vec_per_row;
+    const __nv_bfloat16* src = p.tp_src + (size_t)c * BM * p.tp_ld_src + col0;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.tp_bufs.ptr[peer]) + ((size_t)r * blocks + c) * BM * p.K + col0;
+    for (int v0 = et; v0 < total_vec; v0 += 128 * UNROLL) {
+      uint4 buf[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-          const int v = v0 + u * 192;
-          if (v < total_vec) {
-            const int row = v / vec_per_row, cv = v - row * vec_per_row;
-            buf[u] = *reinterpret_cast<const uint4*>(src + (size_t)row * p.tp_ld_src + cv * 8);
-          }
+      for (int u = 0; u < UNROLL; ++u) {
+        const int v = v0 + u * 128;
+        if (v < total_vec) {
+          const int row = v / vec_per_row, cv = v - row * vec_per_row;
+          buf[u] = *reinterpret_cast<const uint4*>(src + (size_t)row * p.tp_ld_src + cv * 8);
         }
+      }
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-          const int v = v0 + u * 192;
-          if (v < total_vec) *reinterpret_cast<uint4*>(dst + (size_t)v * 8) = buf[u];   // weak store; the fence below publishes it
+      for (int u = 0; u < UNROLL; ++u) {
+        const int v = v0 + u * 128;
+        if (v < total_vec) {
+          const int row = v / vec_per_row, cv = v - row * vec_per_row;
+          *reinterpret_cast<uint4*>(dst + (size_t)row * p.K + cv * 8) = buf[u];   // weak store; the fence below publishes it
         }
       }
     }
     __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0)
-      st_release_sys(reinterpret_cast<unsigned long long*>(p.tp_flags.ptr[peer]) + (size_t)r * blocks + c, epoch);
+    asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps only
+    if (et == 0)
+      red_release_sys_add(reinterpret_cast<unsigned long long*>(p.tp_flags.ptr[peer]) + (size_t)r * blocks + c, 1ull);
   }
 }
 
@@ -431,14 +440,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = p.group_mode == 1 ? s_prefix[p.batch] : tiles_per_batch * p.batch;
-  const int n_compute = (int)gridDim.x - (p.tp_mode == 1 ? p.tp_comm : 0);   // the last tp_comm CTAs only move data
-  const bool is_comm = p.tp_mode == 1 && (int)blockIdx.x >= n_compute;
+  const int n_compute = (int)gridDim.x;
   unsigned long long tp_epoch = 0;
   if (p.tp_mode) tp_epoch = *reinterpret_cast<volatile unsigned long long*>(p.tp_sync) + 1;
 
-  if (is_comm) {
-    tp_push_shard(p, (int)blockIdx.x - n_compute, tp_epoch);
-  } else if (warp == 0) {
+  if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer
       int stage = 0;
@@ -456,7 +462,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             // the rows of this tile are pushed into the local staging buffer by a communication CTA of their owner
             const unsigned long long* flags = reinterpret_cast<const unsigned long long*>(p.tp_flags.ptr[p.tp_rank]);
-            if (!wait_ge_sys(flags + ti.row0 / BM, tp_epoch)) {
+            const unsigned long long n_slabs = (unsigned long long)((p.K + TP_SLAB - 1) / TP_SLAB);
+            if (!wait_ge_sys(flags + ti.row0 / BM, tp_epoch * n_slabs)) {
               report_error(p.status, OA_KERR_WAIT_PEER);
               ok = false;
               break;
@@ -542,6 +549,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     int n_pend = 0;
+    if (p.tp_mode == 1) tp_push_shard(p, tp_epoch);
     for (int t = blockIdx.x; t < total_tiles; t += n_compute) {
       const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
       const int bi = ti.bi, ni = ti.ni, split = ti.split, kb0 = ti.kb0, kb1 = ti.kb1;
@@ -921,13 +929,7 @@ extern "C" int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out
   if ((N & 7) || (K & 7) || (ldc & (out_f32 ? 3 : 7)) || (residual && (ldr & 7))) return OA_ERR_ALIGN;
   if (mode == 1 && ((ld_src & 7) || lda != K)) return OA_ERR_ALIGN;
   const int sms = num_sms();
-  if (mode == 1) {
-    if (comm_ctas <= 0) comm_ctas = 16;
-    if (world == 1) comm_ctas = 1;
-    if (comm_ctas > sms / 2) comm_ctas = sms / 2;
-  } else {
-    comm_ctas = 0;
-  }
+  comm_ctas = 0;      // kept in the signature for callers; the push is spread over the epilogue warps of all CTAs
   const int bn = (N >= 256) ? 256 : 128;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
