@@ -155,6 +155,37 @@ def bench_decode():
     K.check_status()
 
 
+def bench_prof():
+    """A small fixed workload for profiler captures: every hot kernel twice (operands larger than L2, about 1 GB held)."""
+    a = torch.randn(8192, 4096, device="cuda").bfloat16()
+    b = torch.randn(4096, 4096, device="cuda").bfloat16()
+    out = torch.empty(8192, 4096, device="cuda", dtype=torch.bfloat16)
+    B, H, S, hd = 8, 16, 2048, 64
+    D = H * hd
+    qkv = torch.randn(B * S, 3 * D, device="cuda").bfloat16()
+    q, k, v = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
+    x = torch.randn(65536, 1024, device="cuda").bfloat16()
+    w = torch.randn(1024, device="cuda").bfloat16()
+    lg = torch.randn(4096, 32000, device="cuda").bfloat16()
+    tg = torch.randint(0, 32000, (4096,), device="cuda")
+    n = 64_000_000
+    p_ = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    g_ = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    ms, m, vv = (torch.zeros(n, device="cuda") for _ in range(3))
+    st = torch.tensor([1, 1e-3, 0.9, 0.999, 1e-8, 0.1, 1.0, 0], device="cuda")
+    for _ in range(2):
+        K.gemm(a, b, out=out)
+        o, lse = K.flash_fwd(q, k, v, B, S, H, hd, causal=True)
+        K.flash_bwd(q, k, v, o, o, lse, B, S, H, hd, causal=True, dqkv=torch.empty_like(qkv))
+        _, rstd, _ = K.rmsnorm_fwd(x, w, 1e-5)
+        K.rmsnorm_bwd(x, w, x, rstd)
+        K.xent_fwd_bwd(lg, tg, grad_scale=1.0, dlogits=lg)
+        K.adam_step(p_, g_, ms, m, vv, st, decoupled=True)
+    torch.cuda.synchronize()
+    K.check_status()
+    emit(op="prof_workload", done=True)
+
+
 def bench_tp():
     import torch.distributed as dist
     from oa_b200.parallel import tp as TP
@@ -233,7 +264,7 @@ def main() -> int:
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "tp": bench_tp, "decode": bench_decode}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:
