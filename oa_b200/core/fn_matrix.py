@@ -880,14 +880,15 @@ def RoPE(x: OaMatrix, heads: int, head_dim: int, seq: int, pos_offset: int = 0, 
 
 
 def FlashAttentionPacked(qkv: OaMatrix, batch: int, seq: int, heads: int, head_dim: int, *, causal: bool = True,
-                         rope_theta: float = 0.0, pos_offset: int = 0) -> OaMatrix:
+                         rope_theta: float = 0.0, pos_offset: int = 0, consume_input: bool = False) -> OaMatrix:
     """Attention over a packed projection output [B*S, 3*H*hd] (q | k | v side by side); returns [B*S, H*hd].
-    With rope_theta > 0 rotate-half RoPE is applied to q and k in place first."""
+    With rope_theta > 0 rotate-half RoPE is applied to q and k in place first (on a copy while autograd records, unless
+    the caller owns the projection output and passes consume_input: nothing else reads it)."""
     _ctx_add("FlashAttentionCausal" if causal else "FlashAttention")
     t = qkv.Tensor()
     D = heads * head_dim
     if rope_theta > 0:
-        if AG.IsEnabled() and qkv.RequiresGrad():
+        if AG.IsEnabled() and qkv.RequiresGrad() and not consume_input:
             t = K.unary("copy", _c(t))
         K.rope_(t[:, : 2 * D], 2 * heads, head_dim, seq, pos_offset=pos_offset, theta=rope_theta)
     q, k, v = t[:, :D], t[:, D:2 * D], t[:, 2 * D:]

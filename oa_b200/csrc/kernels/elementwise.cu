@@ -233,6 +233,43 @@ __global__ void rope_kernel(T* x, long long rows, int row_stride, int n_heads, i
   }
 }
 
+// bf16 fast path: one thread owns 8 consecutive pair indices j of one row, computes their 8 (cos, sin) once and applies
+// them to every head of the row with 16-byte accesses (the angle depends on the position and on j only).
+__global__ void __launch_bounds__(256)
+rope_bf16_vec_kernel(__nv_bfloat16* x, long long rows, int row_stride, int n_heads, int hd, int seq_len, int pos_offset, float theta,
+                     int backward) {
+  const int half = hd >> 1, jv = half >> 3;                 // 8-wide vectors per half head
+  const long long total = rows * jv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int v = (int)(i % jv);
+    const long long r = i / jv;
+    const float pos = (float)((int)(r % seq_len) + pos_offset);
+    float c[8], s[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float freq = __powf(theta, -2.f * (float)(v * 8 + k) / (float)hd);
+      sincosf(pos * freq, &s[k], &c[k]);
+      if (backward) s[k] = -s[k];
+    }
+    __nv_bfloat16* row = x + r * row_stride + v * 8;
+    for (int h = 0; h < n_heads; ++h) {
+      uint4* pa = reinterpret_cast<uint4*>(row + h * hd);
+      uint4* pb = reinterpret_cast<uint4*>(row + h * hd + half);
+      const uint4 ua = *pa, ub = *pb;
+      const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+      uint32_t oa[4], ob[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 a = unpack_bf16x2(wa[k]), b = unpack_bf16x2(wb[k]);
+        oa[k] = pack_bf16x2(a.x * c[2 * k] - b.x * s[2 * k], a.y * c[2 * k + 1] - b.y * s[2 * k + 1]);
+        ob[k] = pack_bf16x2(b.x * c[2 * k] + a.x * s[2 * k], b.y * c[2 * k + 1] + a.y * s[2 * k + 1]);
+      }
+      *pa = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+      *pb = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+    }
+  }
+}
+
 // out[i,:] = table[ids[i],:] (+ pos_table[i % seq_len,:])
 template <typename T>
 __global__ void embedding_fwd_kernel(const T* __restrict__ table, const int* __restrict__ ids, T* __restrict__ out,
@@ -538,6 +575,11 @@ extern "C" int oa_swiglu_bwd(int dtype, const void* gu, const void* dout, void* 
 extern "C" int oa_rope(int dtype, void* x, long long rows, int row_stride, int n_heads, int head_dim, int seq_len,
                        int pos_offset, float theta, int backward, void* stream) {
   if (head_dim % 2) return OA_ERR_ARG;
+  if (dtype == OA_BF16 && head_dim % 16 == 0 && row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    rope_bf16_vec_kernel<<<grid_for(rows * (head_dim / 16), 256), 256, 0, ST>>>((__nv_bfloat16*)x, rows, row_stride, n_heads, head_dim,
+                                                                                 seq_len, pos_offset, theta, backward);
+    return CHECK_LAUNCH();
+  }
   DISPATCH_T(dtype, rope_kernel<T><<<grid_for(rows * n_heads * head_dim / 2, 256), 256, 0, ST>>>(
                         (T*)x, rows, row_stride, n_heads, head_dim, seq_len, pos_offset, theta, backward));
   return CHECK_LAUNCH();

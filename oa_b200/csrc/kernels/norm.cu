@@ -132,6 +132,79 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __
   }
 }
 
+// bf16 fast path for cols = ITER * 256: a lane always owns the same 8 * ITER columns, so the row stays in registers
+// between the two passes (packed bf16), the weight is loaded once, and the dw partial sums live in registers across all
+// rows of the warp instead of read-modify-write traffic on shared memory.
+template <int ITER>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ dy,
+                       const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx, long long rows, const __nv_bfloat16* __restrict__ dres,
+                       float* __restrict__ partial) {
+  extern __shared__ float s_dw[];  // [NORM_WARPS][cols]
+  constexpr int cols = ITER * 256;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint4 wp[ITER];
+  float acc[ITER][8];
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    wp[it] = *reinterpret_cast<const uint4*>(w + it * 256 + lane * 8);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[it][j] = 0.f;
+  }
+  const long long warp_global = (long long)blockIdx.x * NORM_WARPS + warp;
+  const long long warp_stride = (long long)gridDim.x * NORM_WARPS;
+  for (long long row = warp_global; row < rows; row += warp_stride) {
+    uint4 xp[ITER], dp[ITER], rp[ITER];
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      xp[it] = *reinterpret_cast<const uint4*>(x + row * cols + it * 256 + lane * 8);
+      dp[it] = *reinterpret_cast<const uint4*>(dy + row * cols + it * 256 + lane * 8);
+      if (dres) rp[it] = *reinterpret_cast<const uint4*>(dres + row * cols + it * 256 + lane * 8);
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const uint32_t xs[4] = {xp[it].x, xp[it].y, xp[it].z, xp[it].w}, ds[4] = {dp[it].x, dp[it].y, dp[it].z, dp[it].w},
+                     ws[4] = {wp[it].x, wp[it].y, wp[it].z, wp[it].w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 xv = unpack_bf16x2(xs[k]), dv = unpack_bf16x2(ds[k]), wv = unpack_bf16x2(ws[k]);
+        dot += dv.x * wv.x * xv.x + dv.y * wv.y * xv.y;
+      }
+    }
+    dot = warp_sum(dot) * rstd / (float)cols;
+#pragma unroll
+    for (int it = 0; it < ITER; ++it) {
+      const uint32_t xs[4] = {xp[it].x, xp[it].y, xp[it].z, xp[it].w}, ds[4] = {dp[it].x, dp[it].y, dp[it].z, dp[it].w},
+                     ws[4] = {wp[it].x, wp[it].y, wp[it].z, wp[it].w}, rs[4] = {rp[it].x, rp[it].y, rp[it].z, rp[it].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 xv = unpack_bf16x2(xs[k]), dv = unpack_bf16x2(ds[k]), wv = unpack_bf16x2(ws[k]);
+        const float xh0 = xv.x * rstd, xh1 = xv.y * rstd;
+        acc[it][2 * k] += dv.x * xh0;
+        acc[it][2 * k + 1] += dv.y * xh1;
+        float r0 = rstd * (dv.x * wv.x - xh0 * dot), r1 = rstd * (dv.y * wv.y - xh1 * dot);
+        if (dres) { const float2 rv = unpack_bf16x2(rs[k]); r0 += rv.x; r1 += rv.y; }
+        o[k] = pack_bf16x2(r0, r1);
+      }
+      *reinterpret_cast<uint4*>(dx + row * cols + it * 256 + lane * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < ITER; ++it)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_dw[(size_t)warp * cols + it * 256 + lane * 8 + j] = acc[it][j];
+  __syncthreads();
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_WARPS; ++k) s += s_dw[(size_t)k * cols + c];
+    partial[(size_t)blockIdx.x * cols + c] = s;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(NORM_THREADS)
 layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b, T* __restrict__ y,
@@ -308,6 +381,21 @@ extern "C" int oa_rmsnorm_bwd(int dtype, const void* x, const void* w, const voi
   if (dtype == OA_F32) {
     if ((rc = set_smem(rmsnorm_bwd_kernel<float>, smem))) return rc;
     rmsnorm_bwd_kernel<float><<<blocks, NORM_THREADS, smem, ST>>>((const float*)x, (const float*)w, (const float*)dy, rstd, (float*)dx, rows, cols, (const float*)dres, scratch, warps);
+  } else if (dtype == OA_BF16 && warps == NORM_WARPS && cols % 256 == 0 && cols / 256 <= 4 &&
+             ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(w) |
+               reinterpret_cast<uintptr_t>(dres)) & 15) == 0) {
+    const __nv_bfloat16 *bx = (const __nv_bfloat16*)x, *bw = (const __nv_bfloat16*)w, *bd = (const __nv_bfloat16*)dy, *br = (const __nv_bfloat16*)dres;
+    __nv_bfloat16* bo = (__nv_bfloat16*)dx;
+#define OA_RMS_BWD_REG(IT)                                                                          \
+    if ((rc = set_smem(rmsnorm_bwd_reg_kernel<IT>, smem))) return rc;                                \
+    rmsnorm_bwd_reg_kernel<IT><<<blocks, NORM_THREADS, smem, ST>>>(bx, bw, bd, rstd, bo, rows, br, scratch)
+    switch (cols / 256) {
+      case 1: OA_RMS_BWD_REG(1); break;
+      case 2: OA_RMS_BWD_REG(2); break;
+      case 3: OA_RMS_BWD_REG(3); break;
+      default: OA_RMS_BWD_REG(4); break;
+    }
+#undef OA_RMS_BWD_REG
   } else if (dtype == OA_BF16) {
     if ((rc = set_smem(rmsnorm_bwd_kernel<__nv_bfloat16>, smem))) return rc;
     rmsnorm_bwd_kernel<__nv_bfloat16><<<blocks, NORM_THREADS, smem, ST>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, cols, (const __nv_bfloat16*)dres, scratch, warps);

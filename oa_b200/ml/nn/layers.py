@@ -185,7 +185,7 @@ class OaMultiHeadAttention(OaModule):
     def Attend(self, qkv: OaMatrix, batch: int, seq: int, pos_offset: int = 0) -> OaMatrix:
         if self._use_flash():
             return F.FlashAttentionPacked(qkv, batch, seq, self.NumHeads, self.HeadDim, causal=self.Causal,
-                                          rope_theta=self.RopeTheta, pos_offset=pos_offset)
+                                          rope_theta=self.RopeTheta, pos_offset=pos_offset, consume_input=True)
         D, H = self.DModel, self.NumHeads
         q, k, v = F.Split(qkv, [D, D, D], -1)
         if self.RopeTheta > 0:

@@ -68,7 +68,7 @@ class OaTpBlock(OaModule):
         """x [rows / W, D] (this rank's row shard) -> same shape."""
         h = self.LnAttn.Forward(x)
         qkv = TP.ColumnParallelLinear(h, self.Qkv.Data, self.s_qkv, self.s_qkv_b, "TpQkv")
-        attn = F.FlashAttentionPacked(qkv, batch, seq, self.HeadsLocal, self.HeadDim, causal=True, rope_theta=self.Cfg.RopeTheta)
+        attn = F.FlashAttentionPacked(qkv, batch, seq, self.HeadsLocal, self.HeadDim, causal=True, rope_theta=self.Cfg.RopeTheta, consume_input=True)
         x = TP.RowParallelLinear(attn, self.Out.Data, self.s_out, self.s_out_b, residual=x, name="TpAttnOut")
         h = self.LnFfn.Forward(x)
         up = TP.ColumnParallelLinear(h, self.Up.Data, self.s_up, self.s_up_b, "TpFfnUp")
