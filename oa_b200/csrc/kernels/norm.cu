@@ -311,19 +311,29 @@ layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
   }
 }
 
+// out[c] (+)= sum_p partial[p, c]: 32 columns x 8 row groups per CTA (block 256), shared-memory reduce over the groups.
 template <typename D>
-__global__ void partial_rows_sum_kernel(const float* __restrict__ partial, D* __restrict__ out, int nparts, int cols,
-                                        int accumulate) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+__global__ void __launch_bounds__(256)
+partial_rows_sum_kernel(const float* __restrict__ partial, D* __restrict__ out, int nparts, int cols, int accumulate) {
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += partial[(size_t)p * cols + c];
-  if constexpr (sizeof(D) == 4) {
-    if (accumulate) s += out[c];
-    out[c] = s;
-  } else {
-    if (accumulate) s += __bfloat162float(out[c]);
-    out[c] = __float2bfloat16_rn(s);
+  if (c < cols)
+    for (int p = ry; p < nparts; p += 8) s += partial[(size_t)p * cols + c];
+  red[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][cx];
+    if constexpr (sizeof(D) == 4) {
+      if (accumulate) t += out[c];
+      out[c] = t;
+    } else {
+      if (accumulate) t += __bfloat162float(out[c]);
+      out[c] = __float2bfloat16_rn(t);
+    }
   }
 }
 
@@ -401,8 +411,8 @@ extern "C" int oa_rmsnorm_bwd(int dtype, const void* x, const void* w, const voi
     rmsnorm_bwd_kernel<__nv_bfloat16><<<blocks, NORM_THREADS, smem, ST>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, cols, (const __nv_bfloat16*)dres, scratch, warps);
   } else return OA_ERR_UNSUPPORTED;
   if (dw) {
-    if (dw_dtype == OA_F32) partial_rows_sum_kernel<float><<<(cols + 127) / 128, 128, 0, ST>>>(scratch, (float*)dw, blocks, cols, accumulate_dw);
-    else partial_rows_sum_kernel<__nv_bfloat16><<<(cols + 127) / 128, 128, 0, ST>>>(scratch, (__nv_bfloat16*)dw, blocks, cols, accumulate_dw);
+    if (dw_dtype == OA_F32) partial_rows_sum_kernel<float><<<(cols + 31) / 32, 256, 0, ST>>>(scratch, (float*)dw, blocks, cols, accumulate_dw);
+    else partial_rows_sum_kernel<__nv_bfloat16><<<(cols + 31) / 32, 256, 0, ST>>>(scratch, (__nv_bfloat16*)dw, blocks, cols, accumulate_dw);
   }
   return CHECK_LAUNCH();
 }
@@ -441,11 +451,11 @@ extern "C" int oa_layernorm_bwd(int dtype, const void* x, const void* w, const v
   } else return OA_ERR_UNSUPPORTED;
   float* part_db = scratch + (size_t)blocks * cols;
   if (dw_dtype == OA_F32) {
-    if (dw) partial_rows_sum_kernel<float><<<(cols + 127) / 128, 128, 0, ST>>>(scratch, (float*)dw, blocks, cols, accumulate_dw);
-    if (db) partial_rows_sum_kernel<float><<<(cols + 127) / 128, 128, 0, ST>>>(part_db, (float*)db, blocks, cols, accumulate_dw);
+    if (dw) partial_rows_sum_kernel<float><<<(cols + 31) / 32, 256, 0, ST>>>(scratch, (float*)dw, blocks, cols, accumulate_dw);
+    if (db) partial_rows_sum_kernel<float><<<(cols + 31) / 32, 256, 0, ST>>>(part_db, (float*)db, blocks, cols, accumulate_dw);
   } else {
-    if (dw) partial_rows_sum_kernel<__nv_bfloat16><<<(cols + 127) / 128, 128, 0, ST>>>(scratch, (__nv_bfloat16*)dw, blocks, cols, accumulate_dw);
-    if (db) partial_rows_sum_kernel<__nv_bfloat16><<<(cols + 127) / 128, 128, 0, ST>>>(part_db, (__nv_bfloat16*)db, blocks, cols, accumulate_dw);
+    if (dw) partial_rows_sum_kernel<__nv_bfloat16><<<(cols + 31) / 32, 256, 0, ST>>>(scratch, (__nv_bfloat16*)dw, blocks, cols, accumulate_dw);
+    if (db) partial_rows_sum_kernel<__nv_bfloat16><<<(cols + 31) / 32, 256, 0, ST>>>(part_db, (__nv_bfloat16*)db, blocks, cols, accumulate_dw);
   }
   return CHECK_LAUNCH();
 }
