@@ -34,6 +34,8 @@ from oa_b200.ml.byte import OaByteEmbedding, OaByteEncoder, OaByteHead
 from oa_b200.ml.checkpoint import OaCheckpointManager, OaCheckpointManagerConfig
 from oa_b200.ml.nn import layers as _NN
 from oa_b200.ml.nn.mamba3 import OaMamba3Module
+from oa_b200.ml.nn.conv import (OaAdaptiveAvgPool2d, OaAvgPool2d, OaBatchNorm2d, OaConv1d, OaConv2d, OaConvTranspose1d, OaConvTranspose2d, OaMaxPool2d,
+                                 OaUpsample)
 from oa_b200.ml.nn.moe import OaMoE, OaMoeExpert
 from oa_b200.ml.nn.recurrent import OaGru, OaGruCell, OaRnn, OaRnnCell
 from oa_b200.ml.tokenizer import OaBpeTokenizer

@@ -208,6 +208,18 @@ int oa_gated_norm_fwd(int dtype, const void* y, const void* z, long long zs, con
 int oa_gated_norm_bwd(int dtype, const void* y, const void* z, long long zs, const float* w, const float* rstd, const void* dout,
                       void* dy, void* dz, long long dzs, float* dw, long long rows, int H, int P, void* stream);
 
+// ---- convolution / pooling support (conv.cu); NCHW, columns [N*Ho*Wo, C*kh*kw]
+int oa_im2col(int dtype, const void* x, void* cols, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw,
+              int dh, int dw, void* stream);
+int oa_col2im(int dtype, const void* cols, void* x, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw,
+              int dh, int dw, void* stream);
+int oa_pool2d_fwd(int dtype, int mode, const void* x, void* y, int* idx, int N, int C, int H, int W, int kh, int kw, int sh,
+                  int sw, int ph, int pw, void* stream);
+int oa_pool2d_bwd(int dtype, int mode, const void* dy, const int* idx, void* dx, int N, int C, int H, int W, int kh, int kw,
+                  int sh, int sw, int ph, int pw, void* stream);
+int oa_upsample_nearest(int dtype, const void* in, void* out, long long planes, int H, int W, int fy, int fx, int backward,
+                        void* stream);
+
 // ---- KV-cache serving (decode.cu)
 int oa_kv_append(const void* k_src, const void* v_src, long long src_stride, void* k_cache, void* v_cache, int batch,
                  int s_new, int heads, int head_dim, int pos0, int max_seq, void* stream);
