@@ -20,6 +20,7 @@
 //
 // Replaces the reference's GemmTiled / GemmCmSgBf16 / GemmCmWgBf16 family
 // (Source/Private/Oa/Core/Shader/Compute/Blas/Gemm/*.slang) with one kernel family.
+#include <cstdlib>
 #include "common.cuh"
 #include "api.h"
 #include <mutex>
@@ -651,6 +652,175 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): a cluster of two CTAs computes one 256 x 256 tile.  Each CTA loads its own 128 rows of
+// A and its own 128 of the 256 B rows (32 KB per stage instead of 48 KB, so the ring is 6 deep and the L2 -> SM traffic
+// per FLOP drops by a third); the even CTA issues tcgen05.mma.cta_group::2 (M = 256) for the pair; each CTA's TMEM holds
+// its 128 accumulator rows and its own epilogue warps drain them.  Loads carry no multicast: the pair shares B because
+// the MMA reads both halves, not because a copy is broadcast.  Used for plain 2-D problems with enough 256 x 256 tiles.
+struct PairCfg {
+  static constexpr int STAGES = 6;
+  static constexpr int A_BYTES = BM * BK * 2;            // this CTA's 128 rows of A
+  static constexpr int B_BYTES = 128 * BK * 2;           // this CTA's 128 of the tile's 256 rows of B
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 512;                  // two 256-column accumulators
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using Cfg = PairCfg;
+  constexpr int STAGES = Cfg::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * Cfg::A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = bars;                 // used in the even CTA: bytes of both CTAs' loads
+  uint64_t* empty = bars + STAGES;       // per CTA: the pair's MMA has consumed this CTA's stage
+  uint64_t* tfull = bars + 2 * STAGES;   // per CTA: accumulator ready
+  uint64_t* tempty = bars + 2 * STAGES + 2;   // even CTA: 8 epilogue warps (4 per CTA) have drained the accumulator
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int m_tiles = (p.M + 255) / 256, n_tiles = (p.N + 255) / 256;
+  const int total_tiles = m_tiles * n_tiles;
+  const int kb_total = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc_pair<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                    // both CTAs' barriers exist before anything arrives on them from the other side
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- TMA producer (both CTAs; the bytes are credited to the even CTA's barrier)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        int mi, ni;
+        tile_coords(t, m_tiles, n_tiles, 8, mi, ni);
+        const int row0 = mi * 256 + (int)rank * 128, n0 = ni * 256 + (int)rank * 128;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
+          if (leader) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
+          uint8_t* a = sA + stage * Cfg::A_BYTES;
+          uint8_t* b = sB + stage * Cfg::B_BYTES;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_3d_pair(a + j * (64 * BK * 2), &tmA, &full[stage], row0 + j * 64, kb * BK, 0);
+          } else {
+            tma_load_3d_pair(a, &tmA, &full[stage], kb * BK, row0, 0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) tma_load_3d_pair(b + j * (64 * BK * 2), &tmB, &full[stage], n0 + j * 64, kb * BK, 0);
+          } else {
+            tma_load_3d_pair(b, &tmB, &full[stage], kb * BK, n0, 0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ---------------- MMA issuer of the pair
+      constexpr uint32_t idesc = umma_idesc_bf16(256, 256, A_MN, B_MN);
+      constexpr uint32_t a_lbo = A_MN ? BK * 128 : 16, a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;
+      constexpr uint32_t b_lbo = B_MN ? BK * 128 : 16, b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) { report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * Cfg::A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * Cfg::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
+            const uint64_t db = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
+            umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          const uint32_t e = smem_u32(&empty[stage]);
+          umma_commit_pair(e);                         // this CTA's stage is free ...
+          umma_commit_pair(map_to_cta(e, 1));          // ... and so is the odd CTA's
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        const uint32_t f = smem_u32(&tfull[acc]);
+        umma_commit_pair(f);
+        umma_commit_pair(map_to_cta(f, 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue warps of both CTAs: each drains its own 128 accumulator rows
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < total_tiles; t += n_pairs) {
+      int mi, ni;
+      tile_coords(t, m_tiles, n_tiles, 8, mi, ni);
+      bool ok = mbar_wait(&tfull[acc], acc_phase);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+      tc_fence_after();
+      const int row = mi * 256 + (int)rank * 128 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (c == 7) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[acc]) & kPeerBitMask);    // the even CTA's barrier
+        }
+        epilogue_chunk<256>(p, r, row, ni * 256 + c * 32, 0, 0);
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                    // neither CTA leaves (or frees TMEM) while the other may still touch it
+  if (warp == 1) { tc_fence_after(); tmem_dealloc_pair<Cfg::TMEM_COLS>(tmem_base); }
+}
+
+template <int A_MN, int B_MN>
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+  auto kfn = gemm_pair_bf16_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
+    attr_set = true;
+  }
+  kfn<<<grid, 192, PairCfg::SMEM_BYTES, st>>>(ta, tb, p);
+  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+}
+
 // Fixed-order reduction of split-K partials (deterministic), then the plain store / accumulate epilogue.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, void* out, int ldc,
                                      int out_f32, int accumulate, int batch, long long sc_batch) {
@@ -827,6 +997,25 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
   }
   CUtensorMap ta, tb;
   int rc;
+  // CTA-pair kernel: plain 2-D problems with at least one 256 x 256 tile per CTA pair (OA_GEMM_PAIR=0 switches it off)
+  static const bool pair_enabled = []() { const char* e = std::getenv("OA_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+  const long long tiles2 = (long long)((M + 255) / 256) * ((N + 255) / 256);
+  if (pair_enabled && !force_bn && batch == 1 && p.splits == 1 && M >= 256 && N >= 256 && tiles2 >= sms / 2 && (sms & 1) == 0) {
+    if (a_mn) rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, 1, (uint64_t)lda, 0, 64, BK);
+    else      rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, 1, (uint64_t)lda, 0, BK, BM);
+    if (rc) return rc;
+    if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb, 0, 64, BK);
+    else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 128);
+    if (rc) return rc;
+    cudaStream_t pst = (cudaStream_t)stream;
+    const int pgrid = (int)(tiles2 * 2 < sms ? tiles2 * 2 : sms);
+    switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
+      case 0: return launch_gemm_pair<0, 0>(ta, tb, p, pgrid, pst);
+      case 1: return launch_gemm_pair<0, 1>(ta, tb, p, pgrid, pst);
+      case 2: return launch_gemm_pair<1, 0>(ta, tb, p, pgrid, pst);
+      default: return launch_gemm_pair<1, 1>(ta, tb, p, pgrid, pst);
+    }
+  }
   if (a_mn) rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, batch, (uint64_t)lda, sa_batch, 64, BK);
   else      rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, batch, (uint64_t)lda, sa_batch, BK, BM);
   if (rc) return rc;

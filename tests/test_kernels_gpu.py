@@ -47,6 +47,23 @@ def test_gemm_bf16_layouts(a_mn, b_mn, M, N, K_):
     _close(out, ref, 1e-2, what=f"gemm a_mn={a_mn} b_mn={b_mn} {M}x{N}x{K_}")
 
 
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
+    """Shapes with at least 74 tiles of 256 x 256 take the CTA-pair (cta_group::2) kernel; ragged M, N and K edges."""
+    torch.manual_seed(3)
+    M, N, K_ = 2200, 2624, 328
+    a = _rand(K_, M) if a_mn else _rand(M, K_)
+    b = _rand(K_, N, scale=0.05) if b_mn else _rand(N, K_, scale=0.05)
+    bias, res = _rand(N), _rand(M, N)
+    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, residual=res, act=K.ACT_GELU)
+    ref = K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn, bias=bias.cpu().float(), residual=res.cpu().float(), act=K.ACT_GELU)
+    _close(out, ref, 1e-2, what=f"pair gemm a_mn={a_mn} b_mn={b_mn}")
+    out32 = torch.zeros(M, N, dtype=torch.float32, device=DEV)
+    K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out32)
+    K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out32, accumulate=True)
+    _close(out32, 2 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn), 1e-2, what="pair gemm fp32 accumulate")
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_bf16_epilogues(bn):
     torch.manual_seed(1)
