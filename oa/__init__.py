@@ -9,8 +9,7 @@ OaFnMetric, and the `Context` scope), bound here to oa_b200.
     with oa.OaGradientTape() as tape: ...
     with oa.Context(): ...            # Execute + Sync of the default context on scope exit
 
-Names of the reference surface that this build does not provide (reinforcement learning, audio, vision, crypto, plot, ui,
-the Empyrealm core) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
+Names of the reference surface that this build does not provide (audio, vision, crypto, plot, ui, the Empyrealm core) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
 """
 from __future__ import annotations
 
@@ -39,6 +38,8 @@ from oa_b200.ml.nn.conv import (OaAdaptiveAvgPool2d, OaAvgPool2d, OaBatchNorm2d,
 from oa_b200.ml.nn.moe import OaMoE, OaMoeExpert
 from oa_b200.ml.nn.recurrent import OaGru, OaGruCell, OaRnn, OaRnnCell
 from oa_b200.ml.tokenizer import OaBpeTokenizer
+from oa_b200.ml import rl as _RL
+from oa_b200.ml.rl import fn_rl as _FRL
 from oa_b200.runtime import engine as _RT
 from oa_b200.utils.paths import OaFilesystem, OaPath, OaPaths
 
@@ -72,6 +73,19 @@ OaNlpSuiteHiddenWidth, OaNlpSuiteTrainingSteps, OaNlpSuiteRngSeed = _NS.OaNlpSui
 OaNlpSuiteGenerationPrompt, OaNlpSuiteGenerationSourceUnits = _NS.OaNlpSuiteGenerationPrompt, _NS.OaNlpSuiteGenerationSourceUnits
 
 
+# ---- reinforcement learning
+for _n in ("OaItRlTraining", "OaItRlTrainingConfig", "OaDqnLossConfig", "OaDqnLossResult", "OaGaeConfig", "OaGaeResult", "OaPpoLossConfig",
+           "OaPpoLossResult", "OaRlContinuousPolicyResult", "OaRlEnvironmentSpec", "OaRlFieldSpec", "OaRlPolicyResult", "OaRlReplayBatch",
+           "OaRlReplayBuffer", "OaRlReplayConfig", "OaRlRolloutBatch", "OaRlRolloutBuffer", "OaRlRolloutConfig", "OaRlSpaceKind",
+           "OaRlTrainingPhase", "OaSacCriticLossResult", "OaSacLossConfig", "OaRlEnvironment", "OaRlEnvironmentTransition",
+           "OaRlTransition", "OaRlReplayTransition", "OaRlActorCritic", "OaRlActorCriticOutput", "OaCategoricalActorCritic",
+           "OaCategoricalActorCriticConfig", "OaRlCollector", "OaRlCollectorConfig", "OaRlCollectorMetrics", "OaRlEvaluationConfig",
+           "OaRlEvaluationMetrics", "OaPpoTrainer", "OaPpoTrainerConfig", "OaPpoTrainerMetrics", "OaDqnTrainer", "OaDqnTrainerConfig",
+           "OaDqnTrainerMetrics", "OaSacTrainer", "OaSacTrainerConfig", "OaSacTrainerMetrics", "OaCartPoleConfig", "OaCartPoleEnvironment"):
+    globals()[_n] = getattr(_RL, _n)
+del _n
+
+
 class OaActivation:
     """Activation selector of fused Linear layers."""
     none, Relu, Gelu, Silu = 0, 1, 2, 3
@@ -92,6 +106,12 @@ OaFnMatrix = _namespace("OaFnMatrix", "Tensor factories and differentiable opera
 OaFnLoss = _namespace("OaFnLoss", "Loss functions and their explicit backward forms.", _L,
                       ["Bce", "BceBwd", "CrossEntropy", "CrossEntropyBwd", "MaskedCrossEntropy", "L1", "L1Bwd", "Mse", "MseBwd", "SmoothL1",
                        "SmoothL1Bwd", "LastName"])
+for _n in ("PpoClippedPolicy", "PpoClippedPolicyBwd", "Ppo", "Dqn", "SacCritic", "SacActor"):
+    setattr(OaFnLoss, _n, getattr(_FRL, _n))
+OaFnLoss.__all__ = OaFnLoss.__all__ + ("PpoClippedPolicy", "PpoClippedPolicyBwd", "Ppo", "Dqn", "SacCritic", "SacActor")
+OaFnRl = _namespace("OaFnRl", "Advantage estimation, policy distributions, transforms and evaluation.", _RL.OaFnRl,
+                    ["Gae", "GaeInto", "NormalizeAdvantages", "SampleCategoricalPolicy", "EvaluateCategoricalPolicy", "SampleTanhNormalPolicy",
+                     "EvaluateTanhNormalPolicy", "NormalizeObservation", "ScaleAction", "ClipReward", "SampleLogits", "EvaluateCategorical"])
 OaFnAutograd = _namespace("OaFnAutograd", "Autograd recording switch.", _AG, ["IsEnabled", "SetEnabled"])
 OaFnMetric = _namespace("OaFnMetric", "Host-side metrics of device results.", _M.OaFnMetric, ["Accuracy", "ScalarLoss"])
 
@@ -108,17 +128,12 @@ class Context:
         self._ctx.Sync()
 
 
-UNAVAILABLE = (
-    "OaEmpyrealmCore", "OaItRlTraining", "OaItRlTrainingConfig", "OaDqnLossConfig", "OaDqnLossResult", "OaGaeConfig", "OaGaeResult",
-    "OaPpoLossConfig", "OaPpoLossResult", "OaRlContinuousPolicyResult", "OaRlEnvironmentSpec", "OaRlFieldSpec", "OaRlPolicyResult",
-    "OaRlReplayBatch", "OaRlReplayBuffer", "OaRlReplayConfig", "OaRlRolloutBatch", "OaRlRolloutBuffer", "OaRlRolloutConfig", "OaRlSpaceKind",
-    "OaRlTrainingPhase", "OaSacCriticLossResult", "OaSacLossConfig", "OaFnRl", "OaFnAudio", "OaFnImage", "OaFnDetection", "OaFnHash",
-    "OaPlot", "OaViewer", "OaAudio", "OaVideo")
+UNAVAILABLE = ("OaEmpyrealmCore", "OaFnAudio", "OaFnImage", "OaFnDetection", "OaFnHash", "OaPlot", "OaViewer", "OaAudio", "OaVideo")
 
 
 def __getattr__(name: str):
     if name in UNAVAILABLE:
-        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (reinforcement learning / audio / vision / ui) that this build does not provide")
+        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (audio / vision / crypto / ui / Empyrealm) that this build does not provide")
     raise AttributeError(f"module 'oa' has no attribute '{name}'")
 
 

@@ -226,6 +226,31 @@ int oa_kv_append(const void* k_src, const void* v_src, long long src_stride, voi
 int oa_decode_attn(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out, long long out_stride,
                    int batch, int heads, int head_dim, int len, int max_seq, float scale, void* stream);
 
+// ---- reinforcement learning (rl.cu): vector CartPole, GAE, rollout / replay storage, loss targets, categorical sampling
+int oa_rl_cartpole_reset(void* state, void* done, void* steps, void* episode, int envs, unsigned seed_lo, unsigned seed_hi,
+                         int only_done, void* stream);
+int oa_rl_cartpole_step(const void* action, void* state, void* trans_obs, void* reward, void* terminated, void* truncated,
+                        void* done, void* steps, int envs, int max_steps, float gravity, float cart_mass, float pole_mass,
+                        float half_len, float force, float dt, float x_limit, float angle_limit, void* stream);
+int oa_rl_gae(const void* reward, const void* value, const void* next_value, const void* terminated, const void* truncated,
+              void* adv, void* ret, int T, int E, float gamma, float lambda, void* stream);
+int oa_rl_rollout_append(const void* obs, const void* action, const void* reward, const void* value, const void* next_value,
+                         const void* logp, const void* term, const void* trunc, void* o_obs, void* o_action, void* o_reward,
+                         void* o_value, void* o_next_value, void* o_logp, void* o_term, void* o_trunc, void* o_valid, int envs,
+                         int obs_elems, int slot, void* stream);
+int oa_rl_replay(int mode, const void* obs, const void* action, const void* next_obs, const void* reward, const void* term,
+                 const void* trunc, void* o_obs, void* o_action, void* o_next_obs, void* o_reward, void* o_term, void* o_trunc,
+                 void* o_index, int rows, int obs_elems, int act_elems, int capacity, int cursor, int size, unsigned seed_lo,
+                 unsigned seed_hi, void* stream);
+int oa_rl_ppo_clip(const void* new_lp, const void* old_lp, const void* adv, void* out, int n, float eps, int backward,
+                   void* stream);
+int oa_rl_dqn_target(const void* reward, const void* next_q, const void* terminated, void* out, int batch, int actions,
+                     float discount, void* stream);
+int oa_rl_sac_target(const void* reward, const void* q1, const void* q2, const void* logp, const void* terminated, void* out,
+                     int batch, float discount, float alpha, void* stream);
+int oa_rl_sample_categorical(const void* logits, void* action, int rows, int actions, float temperature, unsigned seed_lo,
+                             unsigned seed_hi, int greedy, void* stream);
+
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);
 int oa_ipc_free(void* p);

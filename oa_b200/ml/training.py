@@ -180,6 +180,15 @@ class OaItTraining:
     def RequestStop(self) -> None:
         self._stop = True
 
+    def StopRequested(self) -> bool:
+        return self._stop
+
+    def TotalSteps(self) -> int:
+        return self.Config.TotalSteps
+
+    def IsValid(self) -> bool:
+        return bool(self.LastStatus)
+
     def RequestRecapture(self) -> None:
         """Drops the captured program; the next step runs eagerly and the one after captures again."""
         if self._program is not None:

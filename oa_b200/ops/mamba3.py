@@ -7,6 +7,7 @@ tensors run the kernels of csrc/kernels/mamba3.cu.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -119,6 +120,16 @@ def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     return t.contiguous() if t.dtype == torch.float32 else K.cast(t.contiguous(), torch.float32)
 
 
+def _use_ssd(proj: torch.Tensor, d: "Mamba3Dims", L: int) -> bool:
+    """The chunked tensor-core scan serves bf16 training on CUDA when the sequence is a whole number of chunks; fp32
+    inputs, ragged lengths and decode prefill (which needs the recurrent state) use the sequential kernels.
+    OA_MAMBA3_SSD=0 forces the sequential kernels."""
+    if os.environ.get("OA_MAMBA3_SSD", "1") == "0" or not proj.is_cuda or proj.dtype != torch.bfloat16:
+        return False
+    from . import mamba3_ssd as SSD
+    return SSD.supported(d, L, SSD.CHUNK)
+
+
 class Saved:
     __slots__ = ("proj", "params", "pre", "Hck", "Tck", "dims", "B", "L")
 
@@ -144,6 +155,18 @@ def core_fwd(proj: torch.Tensor, dt_bias, Bb, Cb, D, d: Mamba3Dims, B: int, L: i
     K._launch(lib.oa_mamba3_pre_fwd(K.dt(proj), proj.data_ptr(), d.d_in_proj, dtb.data_ptr(), rows, H, Nn, A, d.d_inner, d.eps, d.dt_min,
                                     d.dt_max, d.afloor, Bn.data_ptr(), Cn.data_ptr(), rstd.data_ptr(), dt.data_ptr(), adt.data_ptr(),
                                     trap.data_ptr(), angle.data_ptr(), st_), "oa_mamba3_pre_fwd")
+    if final is None and _use_ssd(proj, d, L):
+        # chunked tensor-core path: the same preprocessed inputs, GEMM-shaped scan
+        from . import mamba3_ssd as SSD
+        o = d.offsets()
+        v4 = lambda c0: proj[:, c0:c0 + d.d_inner].reshape(B, L, H, P)
+        r3 = lambda t, w: t.reshape(B, L, w)
+        y4, sv = SSD.ssd_fwd(v4(o[1]), v4(o[0]) if d.has_z else None, r3(Bn, Nn), r3(Cn, Nn), r3(dt, H), r3(adt, H), r3(trap, H),
+                             r3(angle, max(A, 1))[..., :A], Bb32, Cb32, D32, d, B, L, SSD.CHUNK)
+        s = Saved()
+        s.proj, s.params, s.dims, s.B, s.L = proj, (dtb, Bb32, Cb32, D32), d, B, L
+        s.pre, s.ssd = (Bn, Cn, rstd, dt, adt, trap, angle), (sv if save else None)
+        return y4.reshape(rows, d.d_inner).to(proj.dtype), s
     nC = (L + d.chunk - 1) // d.chunk
     Hck = f(B, H, nC, P, Nn) if save else None
     Tck = f(B, H, nC, max(A, 1)) if save else None
@@ -161,7 +184,7 @@ def core_fwd(proj: torch.Tensor, dt_bias, Bb, Cb, D, d: Mamba3Dims, B: int, L: i
                                      B, L, H, P, Nn, A, d.chunk, st_), "oa_mamba3_scan_fwd")
     s = Saved()
     s.proj, s.params, s.dims, s.B, s.L = proj, (dtb, Bb32, Cb32, D32), d, B, L
-    s.pre, s.Hck, s.Tck = (Bn, Cn, rstd, dt, adt, trap, angle), Hck, Tck
+    s.pre, s.Hck, s.Tck, s.ssd = (Bn, Cn, rstd, dt, adt, trap, angle), Hck, Tck, None
     return y, s
 
 
@@ -204,6 +227,24 @@ def core_bwd(s: Saved, dy: torch.Tensor, dproj: Optional[torch.Tensor] = None):
             dproj[:, :d.d_inner].zero_()
     es = proj.element_size()
     o = d.offsets()
+    if s.ssd is not None:
+        from . import mamba3_ssd as SSD
+        g = SSD.ssd_bwd(s.ssd, dy.reshape(B, L, H, P))
+        dproj[:, o[1]:o[1] + d.d_inner] = g["x"].reshape(rows, d.d_inner)
+        if d.has_z:
+            dproj[:, o[0]:o[0] + d.d_inner] = g["z"].reshape(rows, d.d_inner)
+        c32 = lambda t: t.reshape(rows, -1).float().contiguous()
+        dBn, dCn, ddt, dadt, dtrap = c32(g["Bn"]), c32(g["Cn"]), c32(g["dt"]), c32(g["adt"]), c32(g["trap"])
+        if A:
+            dangle = c32(g["angle"])
+        dBb, dCb = g["Bb"].contiguous(), g["Cb"].contiguous()
+        if D32 is not None:
+            dD = g["D"]
+        K._launch(lib.oa_mamba3_pre_bwd(K.dt(proj), proj.data_ptr(), dproj.data_ptr(), d.d_in_proj, dtb.data_ptr(), rows, H, Nn, A, d.d_inner,
+                                        d.eps, d.dt_min, d.dt_max, d.afloor, Bn.data_ptr(), Cn.data_ptr(), rstd.data_ptr(), dBn.data_ptr(),
+                                        dCn.data_ptr(), ddt.data_ptr(), dadt.data_ptr(), dtrap.data_ptr(), dangle.data_ptr(),
+                                        ddtb.data_ptr(), st_), "oa_mamba3_pre_bwd")
+        return dproj, ddtb, dBb.view(H, Nn), dCb.view(H, Nn), (dD if D32 is not None else None)
     scratch = K.scratch(dev, 4 * int(lib.oa_mamba3_scratch_floats(B, H, P, Nn, d.chunk)), "mamba3_bwd")
     dy = dy.contiguous()
     K._launch(lib.oa_mamba3_scan_bwd(K.dt(proj), proj.data_ptr() + o[1] * es, proj.data_ptr() + o[0] * es if d.has_z else None,
