@@ -38,6 +38,9 @@ from oa_b200.ml.nn.conv import (OaAdaptiveAvgPool2d, OaAvgPool2d, OaBatchNorm2d,
 from oa_b200.ml.nn.moe import OaMoE, OaMoeExpert
 from oa_b200.ml.nn.recurrent import OaGru, OaGruCell, OaRnn, OaRnnCell
 from oa_b200.ml.tokenizer import OaBpeTokenizer
+from oa_b200.ml.nn.vq import (OaResidualVectorQuantizer, OaResidualVqResult, OaVectorQuantizer, OaVectorQuantizerConfig, OaVqAssignResult,
+                              OaVqResult)
+from oa_b200.ml.nn.flow import (OaFlowDenoiser, OaFlowDenoiserConfig, OaFlowTimeEmbedding, OaFlowTransformer, OaFlowTransformerConfig)
 from oa_b200.ml import rl as _RL
 from oa_b200.ml.rl import fn_rl as _FRL
 from oa_b200.runtime import engine as _RT

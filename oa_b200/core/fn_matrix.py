@@ -935,3 +935,64 @@ def Embedding(table: OaMatrix, ids: OaMatrix, pos_table: Optional[OaMatrix] = No
         return (gt if tt.dtype == torch.float32 else K.cast(gt, tt.dtype), None, gp)
 
     return AG.attach("Embedding", out, [table, ids, pos_table], back)
+
+
+# ======================================================================= quantisation, VQ, sampling (thin entry points)
+def ComputeScaleQ4_0(m: OaMatrix) -> OaMatrix:
+    """Per-32-element-block scale max|x| / 7 (1 for an all-zero block)  (Source/Public/Oa/Ml/FnMatrix.h:786-789)."""
+    from ..ops import quant as Q
+    _ctx_add("ComputeScaleQ4_0")
+    return _w(Q.q4_0_scale(m.Tensor()))
+
+
+def QuantizeQ4_0(m: OaMatrix, scale: OaMatrix) -> OaMatrix:
+    """Packed Q4_0 bytes [blocks * 16]: two 4-bit codes per byte, code = clamp(round(x / scale), -7, 7) + 7."""
+    from ..ops import quant as Q
+    _ctx_add("QuantizeQ4_0")
+    return _w(Q.q4_0_quantize(m.Tensor(), scale.Tensor()))
+
+
+def DequantizeQ4_0(packed: OaMatrix, scale: OaMatrix, count: int) -> OaMatrix:
+    from ..ops import quant as Q
+    _ctx_add("DequantizeQ4_0")
+    return _w(Q.q4_0_dequantize(packed.Tensor(), scale.Tensor(), int(count)))
+
+
+def QuantizeQ8_0(m: OaMatrix) -> OaMatrix:
+    """Q8_0 blocks of 34 bytes (fp16 scale + 32 int8)."""
+    from ..ops import quant as Q
+    _ctx_add("QuantizeQ8_0")
+    return _w(Q.q8_0_quantize(m.Tensor()))
+
+
+def DequantizeQ8_0(blocks: OaMatrix) -> OaMatrix:
+    from ..ops import quant as Q
+    _ctx_add("DequantizeQ8_0")
+    return _w(Q.q8_0_dequantize(blocks.Tensor()))
+
+
+def QuantizeInt8(m: OaMatrix, scale: OaMatrix) -> OaMatrix:
+    from ..ops import quant as Q
+    _ctx_add("QuantizeInt8")
+    return _w(Q.int8_quantize(m.Tensor(), scale.Tensor()))
+
+
+def DequantizeInt8(q: OaMatrix, scale: OaMatrix) -> OaMatrix:
+    from ..ops import quant as Q
+    _ctx_add("DequantizeInt8")
+    return _w(Q.int8_dequantize(q.Tensor(), scale.Tensor()))
+
+
+def VqAssign(ze: OaMatrix, codebook: OaMatrix):
+    from ..ml.nn import vq as VQ
+    return VQ.VqAssign(ze, codebook)
+
+
+def VqEmaUpdate(ze, idx, embed_sum, cluster_size, codebook, decay: float, eps: float, dead_threshold: float, seed: int, normalize: bool) -> None:
+    from ..ml.nn import vq as VQ
+    VQ.VqEmaUpdate(ze, idx, embed_sum, cluster_size, codebook, decay, eps, dead_threshold, seed, normalize)
+
+
+def SampleLogits(logits: OaMatrix, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> OaMatrix:
+    from ..ml.rl import fn_rl as FR
+    return FR.SampleLogits(logits, temperature, top_k, top_p, seed)

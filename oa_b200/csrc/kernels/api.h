@@ -251,6 +251,16 @@ int oa_rl_sac_target(const void* reward, const void* q1, const void* q2, const v
 int oa_rl_sample_categorical(const void* logits, void* action, int rows, int actions, float temperature, unsigned seed_lo,
                              unsigned seed_hi, int greedy, void* stream);
 
+// ---- vector quantisation (vq.cu)
+int oa_vq_code_norm(const void* codebook, void* enorm, int K, int D, void* stream);
+int oa_vq_argmin_gather(const void* dot, const void* enorm, const void* codebook, void* idx, void* zq, int N, int K, int D,
+                        void* stream);
+int oa_vq_ema_update(const void* ze, const void* idx, void* embed_sum, void* cluster_size, void* codebook, int N, int D, int K,
+                     float decay, float eps, float dead_thresh, unsigned seed, int normalize, void* stream);
+
+// ---- block quantisation (quant.cu): op 0..6 = Q4_0 scales / quantize / dequantize, Q8_0 quantize / dequantize, int8 q / dq
+int oa_quantize(int op, const void* in, const void* scale, void* out, long long count, void* stream);
+
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);
 int oa_ipc_free(void* p);

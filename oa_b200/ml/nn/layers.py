@@ -141,6 +141,10 @@ class OaAttentionBackend:
     Auto, Standard, Flash = 0, 1, 2
 
 
+class OaAttentionMode:
+    Causal, Bidirectional = 0, 1
+
+
 class OaMultiHeadAttention(OaModule):
     """Causal multi-head self-attention with q/k/v/out Linear children.
 
@@ -182,8 +186,10 @@ class OaMultiHeadAttention(OaModule):
             return False          # the tensor-core kernel is built for head dims 64 and 128; others take the materialised path
         return True
 
-    def Attend(self, qkv: OaMatrix, batch: int, seq: int, pos_offset: int = 0) -> OaMatrix:
-        if self._use_flash():
+    def Attend(self, qkv: OaMatrix, batch: int, seq: int, pos_offset: int = 0, mask: Optional[OaMatrix] = None) -> OaMatrix:
+        """`mask`, when given, is an additive [B*H*S, S] (or [S, S]) mask: it takes the materialised path and replaces the
+        causal mask (MultiHeadAttention::ForwardMasked of the reference)."""
+        if mask is None and self._use_flash():
             return F.FlashAttentionPacked(qkv, batch, seq, self.NumHeads, self.HeadDim, causal=self.Causal,
                                           rope_theta=self.RopeTheta, pos_offset=pos_offset, consume_input=True)
         D, H = self.DModel, self.NumHeads
@@ -193,20 +199,23 @@ class OaMultiHeadAttention(OaModule):
             k = F.RoPE(k, H, self.HeadDim, seq, pos_offset, self.RopeTheta)
         qh, kh, vh = (F.SplitHeads(t, batch, seq, H) for t in (q, k, v))
         scores = F.Bmm(qh, F.Transpose(kh, 1, 2))
-        mask = None
-        if self.Causal:
+        if mask is None and self.Causal:
             mask = F.CausalMask(seq, scores.Dtype())       # [S, S], repeated over batch and heads by the kernel
         probs = F.SoftmaxScaledMasked(scores, 1.0 / math.sqrt(self.HeadDim), mask)
         return F.MergeHeads(F.Bmm(probs, vh), batch, seq, H)
 
+    def ForwardMasked(self, x: OaMatrix, additive_mask: OaMatrix, batch: Optional[int] = None, seq: Optional[int] = None,
+                      residual: Optional[OaMatrix] = None) -> OaMatrix:
+        return self.Forward(x, batch, seq, residual, 0, additive_mask)
+
     def Forward(self, x: OaMatrix, batch: Optional[int] = None, seq: Optional[int] = None, residual: Optional[OaMatrix] = None,
-                pos_offset: int = 0) -> OaMatrix:
+                pos_offset: int = 0, mask: Optional[OaMatrix] = None) -> OaMatrix:
         """x: [B*S, D] (pass batch, seq) or [B, S, D]."""
         shape3 = x.Rank() == 3
         if shape3:
             batch, seq = x.Size(0), x.Size(1)
             x = x.Reshape([batch * seq, self.DModel])
-        a = self.Attend(self.ProjectQkv(x), batch, seq, pos_offset)
+        a = self.Attend(self.ProjectQkv(x), batch, seq, pos_offset, mask)
         o = self.OutProj
         y = F.Linear(a, o.Weight.Data, o.Bias.Data if o.Bias else None, residual=residual)
         return y.Reshape([batch, seq, self.DModel]) if shape3 else y
@@ -241,6 +250,7 @@ class OaTransformerBlock(OaModule):
                  attention_backend: int = OaAttentionBackend.Auto):
         super().__init__()
         self.DModel, self.SeqLen, self.FfnKind = d_model, seq_len, ffn
+        self.AdaptiveModulation, self.ConditionDim = None, 0
         mk_norm = (lambda: OaLayerNorm(d_model, eps)) if norm == "layer" else (lambda: OaRmsNorm(d_model, eps))
         self.Moe = None
         if moe is not None:
@@ -255,12 +265,67 @@ class OaTransformerBlock(OaModule):
         self.Attention = self.RegisterModule("attention", OaMultiHeadAttention(d_model, num_heads, seq_len, bias, True, rope_theta,
                                                                                init_std, attention_backend))
 
-    def Forward(self, x: OaMatrix, batch: Optional[int] = None, seq: Optional[int] = None, pos_offset: int = 0) -> OaMatrix:
+    # ---- attention mode, sequence length, adaptive conditioning (Transformer.cpp:93-147, 171-185)
+    def SetAttentionMode(self, mode: int) -> None:
+        self.Attention.Causal = mode == OaAttentionMode.Causal
+
+    def SetSeqLen(self, seq_len: int) -> None:
+        if seq_len <= 0:
+            raise ValueError("sequence length must be positive")
+        self.SeqLen = seq_len
+
+    def EnableAdaptiveConditioning(self, condition_dim: int) -> None:
+        """AdaLN-Zero: a zero-initialised Linear(condition -> 6*D) yields shift / scale / gate for the attention and FFN
+        branches, so an untrained block starts as the identity of its residual path."""
+        if condition_dim <= 0:
+            raise ValueError("adaptive condition dimension must be positive")
+        if self.AdaptiveModulation is not None:
+            if self.ConditionDim != condition_dim:
+                raise ValueError("adaptive conditioning is already configured with a different dimension")
+            return
+        self.ConditionDim = condition_dim
+        lin = OaLinear(condition_dim, 6 * self.DModel)
+        lin.Weight.Data.Tensor().zero_()
+        self.AdaptiveModulation = self.RegisterModule("adaptive_modulation", lin)
+
+    def ForwardMasked(self, x: OaMatrix, additive_mask: OaMatrix, batch: Optional[int] = None, seq: Optional[int] = None) -> OaMatrix:
+        return self.Forward(x, batch, seq, 0, additive_mask)
+
+    def _ffn_delta(self, h: OaMatrix) -> OaMatrix:
+        if self.Moe is not None:
+            return self.Moe.Forward(h)
+        if self.FfnKind == "gelu":
+            return FF.FfnGelu(h, self.Ffn1.Weight.Data, self.Ffn1.Bias.Data if self.Ffn1.Bias else None, self.Ffn2.Weight.Data,
+                              self.Ffn2.Bias.Data if self.Ffn2.Bias else None)
+        f = self.Ffn
+        return FF.FfnSwiglu(h, f.Gate.Weight.Data, f.Up.Weight.Data, f.Down.Weight.Data)
+
+    def ForwardConditioned(self, x: OaMatrix, condition: OaMatrix, additive_mask: Optional[OaMatrix] = None) -> OaMatrix:
+        """x [B*S, D], condition [B, C]: x + gate_a * Attn(norm(x) * (1 + scale_a) + shift_a), then the same for the FFN."""
+        if self.AdaptiveModulation is None:
+            raise ValueError("adaptive conditioning must be enabled before ForwardConditioned")
+        rows, S, D = x.Size(0), self.SeqLen, self.DModel
+        if x.Rank() != 2 or x.Size(1) != D or S <= 0 or rows % S or condition.Rank() != 2 or condition.Size(0) != rows // S \
+                or condition.Size(1) != self.ConditionDim:
+            raise ValueError("conditioned input must be [B*S, D] with condition [B, C]")
+        mod = F.RepeatInterleave(self.AdaptiveModulation.Forward(condition), S, 0)
+        sh_a, sc_a, g_a, sh_f, sc_f, g_f = F.Split(mod, [D] * 6, 1)
+        h = F.Add(F.Mul(self.LnAttn.Forward(x), F.AddScalar(sc_a, 1.0)), sh_a)
+        x = F.Add(x, F.Mul(self.Attention.Forward(h, rows // S, S, mask=additive_mask), g_a))
+        h = self.LnFfn.Forward(x) if self.Moe is None and self.FfnKind == "gelu" else (self.Ffn.Norm.Forward(x) if self.Moe is None else x)
+        h = F.Add(F.Mul(h, F.AddScalar(sc_f, 1.0)), sh_f)
+        return F.Add(x, F.Mul(self._ffn_delta(h), g_f))
+
+    def Forward(self, x: OaMatrix, batch: Optional[int] = None, seq: Optional[int] = None, pos_offset: int = 0,
+                mask: Optional[OaMatrix] = None) -> OaMatrix:
         shape3 = x.Rank() == 3
         if shape3:
             batch, seq = x.Size(0), x.Size(1)
             x = x.Reshape([batch * seq, self.DModel])
-        x = self.Attention.Forward(self.LnAttn.Forward(x), batch, seq, residual=x, pos_offset=pos_offset)
+        if batch is None:
+            seq = self.SeqLen
+            batch = x.Size(0) // seq
+        x = self.Attention.Forward(self.LnAttn.Forward(x), batch, seq, residual=x, pos_offset=pos_offset, mask=mask)
         if self.Moe is not None:
             x = self.Moe.Forward(x)
         elif self.FfnKind == "gelu":
