@@ -9,7 +9,7 @@ OaFnMetric, and the `Context` scope), bound here to oa_b200.
     with oa.OaGradientTape() as tape: ...
     with oa.Context(): ...            # Execute + Sync of the default context on scope exit
 
-Names of the reference surface that this build does not provide (audio, vision, crypto, plot, ui, the Empyrealm core) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
+Names of the reference surface that this build does not provide (audio, vision, crypto, plot, ui) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
 """
 from __future__ import annotations
 
@@ -33,6 +33,7 @@ from oa_b200.ml.byte import OaByteEmbedding, OaByteEncoder, OaByteHead
 from oa_b200.ml.checkpoint import OaCheckpointManager, OaCheckpointManagerConfig
 from oa_b200.ml.nn import layers as _NN
 from oa_b200.ml.nn.mamba3 import OaMamba3Module
+from oa_b200.ml.nn.empyrealm import OaEmpyrealmCore, OaEmpyrealmModule
 from oa_b200.ml.nn.conv import (OaAdaptiveAvgPool2d, OaAvgPool2d, OaBatchNorm2d, OaConv1d, OaConv2d, OaConvTranspose1d, OaConvTranspose2d, OaMaxPool2d,
                                  OaUpsample)
 from oa_b200.ml.nn.moe import OaMoE, OaMoeExpert
@@ -131,12 +132,12 @@ class Context:
         self._ctx.Sync()
 
 
-UNAVAILABLE = ("OaEmpyrealmCore", "OaFnAudio", "OaFnImage", "OaFnDetection", "OaFnHash", "OaPlot", "OaViewer", "OaAudio", "OaVideo")
+UNAVAILABLE = ("OaFnAudio", "OaFnImage", "OaFnDetection", "OaFnHash", "OaPlot", "OaViewer", "OaAudio", "OaVideo")
 
 
 def __getattr__(name: str):
     if name in UNAVAILABLE:
-        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (audio / vision / crypto / ui / Empyrealm) that this build does not provide")
+        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (audio / vision / crypto / ui) that this build does not provide")
     raise AttributeError(f"module 'oa' has no attribute '{name}'")
 
 

@@ -109,7 +109,8 @@ class OaMamba3Module(OaModule):
         return out.Reshape([batch, seq, self.DModel])
 
     # ---- decoding
-    def ResetState(self) -> None:
+    def ResetState(self, batch: int = 0) -> None:
+        """Drops the recurrent decode state; the next Step allocates it for whatever batch it receives."""
         self._state = None
 
     def Step(self, x: OaMatrix) -> OaMatrix:

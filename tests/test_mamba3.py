@@ -288,3 +288,45 @@ def test_core_uses_chunked_scan_for_bf16_training():
         err = (g.float() - r.float().reshape(g.shape)).abs().max().item()
         assert err <= 4e-2 * max(1.0, r.float().abs().max().item()), (nm, err)
     K.check_status()
+
+
+def test_empyrealm_core_modes_cpu():
+    """Byte mode, custom-projection mode and embedded-only mode share the mixer + residual path."""
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.core.matrix import OaMatrix
+    from oa_b200.ml import autograd as AG
+    from oa_b200.ml.nn.empyrealm import OaEmpyrealmCore
+    from oa_b200.ml.nn.layers import OaLinear
+    F.SetRngSeed(11)
+    core = OaEmpyrealmCore(50, 16, d_state=8, headdim=8)
+    ids = OaMatrix(torch.randint(0, 50, (2, 6), dtype=torch.int32))
+    tape = AG.OaGradientTape()
+    out = core.Forward(ids)
+    tape.Backward(F.Sum(F.Mul(out, out)))
+    tape.Close()
+    assert tuple(out.Tensor().shape) == (12, 16)
+    names = [n.Name for n in core.AllNamedParameterPtrs()]
+    assert any(n.startswith("embed.") for n in names) and any(n.startswith("mixer.") for n in names)
+    assert all(n.Param.Data.GradTensor() is not None for n in core.AllNamedParameterPtrs())
+    emb = core.Embed.Forward(ids).Tensor().reshape(2, 6, 16)
+    mixed = core.Mixer().Forward(OaMatrix(emb)).Tensor().reshape(12, 16)
+    assert torch.allclose(out.Tensor(), mixed + emb.reshape(12, 16), atol=1e-6)            # residual around the mixer
+    # sequences of a batch do not leak into each other
+    ids2 = ids.Tensor().clone()
+    ids2[1] = (ids2[1] + 7) % 50
+    out2 = core.Forward(OaMatrix(ids2)).Tensor()
+    assert torch.equal(out2[:6], out.Tensor()[:6]) and not torch.equal(out2[6:], out.Tensor()[6:])
+    only = OaEmpyrealmCore.EmbeddedOnly(16, d_state=8, headdim=8)
+    assert not any(n.Name.startswith("embed.") for n in only.AllNamedParameterPtrs())
+    with pytest.raises(RuntimeError):
+        only.Forward(ids)
+    assert tuple(only.ForwardEmbedded(OaMatrix(torch.randn(2, 6, 16))).Tensor().shape) == (12, 16)
+    assert tuple(only.ForwardEmbedded(OaMatrix(torch.randn(9, 16))).Tensor().shape) == (9, 16)
+
+    class Pose(OaLinear):
+        def Forward(self, x):
+            return super().Forward(x.Reshape([x.Size(0) * x.Size(1), x.Size(2)])).Reshape([x.Size(0), x.Size(1), 16])
+
+    custom = OaEmpyrealmCore(Pose(5, 16), 16, d_state=8, headdim=8)
+    assert tuple(custom.Forward(OaMatrix(torch.randn(3, 4, 5))).Tensor().shape) == (12, 16)
+    custom.ResetState(3)
