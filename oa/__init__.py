@@ -116,6 +116,9 @@ OaFnLoss.__all__ = OaFnLoss.__all__ + ("PpoClippedPolicy", "PpoClippedPolicyBwd"
 OaFnRl = _namespace("OaFnRl", "Advantage estimation, policy distributions, transforms and evaluation.", _RL.OaFnRl,
                     ["Gae", "GaeInto", "NormalizeAdvantages", "SampleCategoricalPolicy", "EvaluateCategoricalPolicy", "SampleTanhNormalPolicy",
                      "EvaluateTanhNormalPolicy", "NormalizeObservation", "ScaleAction", "ClipReward", "SampleLogits", "EvaluateCategorical"])
+from oa_b200.crypto import fn_hash as _FH
+OaFnHash = _namespace("OaFnHash", "Batched SHAKE / Keccak hashing and the SHAKE-256 Merkle root.", _FH,
+                      ["Shake256", "Shake128", "KeccakF1600", "MerkleRoot"])
 OaFnAutograd = _namespace("OaFnAutograd", "Autograd recording switch.", _AG, ["IsEnabled", "SetEnabled"])
 OaFnMetric = _namespace("OaFnMetric", "Host-side metrics of device results.", _M.OaFnMetric, ["Accuracy", "ScalarLoss"])
 
@@ -132,7 +135,7 @@ class Context:
         self._ctx.Sync()
 
 
-UNAVAILABLE = ("OaFnAudio", "OaFnImage", "OaFnDetection", "OaFnHash", "OaPlot", "OaViewer", "OaAudio", "OaVideo")
+UNAVAILABLE = ("OaFnAudio", "OaFnImage", "OaFnDetection", "OaPlot", "OaViewer", "OaAudio", "OaVideo")
 
 
 def __getattr__(name: str):

@@ -261,6 +261,11 @@ int oa_vq_ema_update(const void* ze, const void* idx, void* embed_sum, void* clu
 // ---- block quantisation (quant.cu): op 0..6 = Q4_0 scales / quantize / dequantize, Q8_0 quantize / dequantize, int8 q / dq
 int oa_quantize(int op, const void* in, const void* scale, void* out, long long count, void* stream);
 
+// ---- hashing (hash.cu): batched Keccak-f[1600], SHAKE-128/256 of fixed-length rows, one Merkle level of SHAKE-256 pairs
+int oa_keccak_f1600(const void* in, void* out, int n, void* stream);
+int oa_shake(int bits, const void* msg, void* out, int n, int msg_len, int msg_stride, int out_len, int out_stride, void* stream);
+int oa_merkle_level(const void* in, void* out, int n_in, void* stream);
+
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);
 int oa_ipc_free(void* p);
