@@ -131,7 +131,7 @@ def _use_ssd(proj: torch.Tensor, d: "Mamba3Dims", L: int) -> bool:
 
 
 class Saved:
-    __slots__ = ("proj", "params", "pre", "Hck", "Tck", "dims", "B", "L")
+    __slots__ = ("proj", "params", "pre", "Hck", "Tck", "dims", "B", "L", "ssd")
 
 
 def core_fwd(proj: torch.Tensor, dt_bias, Bb, Cb, D, d: Mamba3Dims, B: int, L: int, save: bool = True, final: Optional[dict] = None):
