@@ -266,6 +266,36 @@ int oa_keccak_f1600(const void* in, void* out, int n, void* stream);
 int oa_shake(int bits, const void* msg, void* out, int n, int msg_len, int msg_stride, int out_len, int out_stride, void* stream);
 int oa_merkle_level(const void* in, void* out, int n_in, void* stream);
 
+// ---- chunked Mamba-3 scan glue (mamba3_ssd.cu); chunk layout = [B*H*nC, 128, *]
+int oa_ssd_prep_fwd(const void* x, long long ldx, const void* Bn, const void* Cn, const void* Bb, const void* Cb, const void* dt,
+                    const void* adt, const void* trap, const void* theta, void* Ct, void* Bt, void* Ce, void* X, void* Xw, void* cum,
+                    void* gamma, void* scale, void* w, void* qk, int B, int L, int H, int P, int N, int A, void* stream);
+int oa_ssd_mask_fwd(const void* Gm, const void* cum, const void* scale, const void* gamma, const void* qk, const void* Dh, void* M,
+                    int G, int H, int nC, void* stream);
+int oa_ssd_state_fwd(const void* S, const void* cum, void* Hin, int BH, int nC, int PN, void* stream);
+int oa_ssd_state_bwd(const void* T, const void* cum, const void* Hin, void* dHout, void* dcumQ, int BH, int nC, int PN, void* stream);
+int oa_ssd_out_fwd(const void* Y, const void* z, long long ldz, void* y, void* yraw, long long ldy, int B, int L, int H, int P,
+                   void* stream);
+int oa_ssd_dy_prep(const void* dy, const void* yraw, long long ldy, const void* z, long long ldz, void* dz, long long lddz, void* dY,
+                   int B, int L, int H, int P, void* stream);
+int oa_ssd_mask_bwd(const void* dM, const void* Gm, const void* cum, const void* scale, void* dG, void* row_mm, void* col_mm,
+                    void* col_ge, void* diag, int G, void* stream);
+int oa_ssd_prep_bwd(const void* dCt, const void* dBt, const void* dCe, const void* Ct, const void* Bt, const void* cum, const void* dqk,
+                    const void* theta, void* dCn, void* dBn, void* dCb, void* dBb, void* dtheta, void* dcum_ce, int B, int L, int H,
+                    int N, int A, void* stream);
+int oa_ssd_dx_out(const void* dX, const void* dXw, const void* X, const void* w, void* dx, long long lddx, void* dw, int B, int L, int H,
+                  int P, void* stream);
+
+// ---- audio DSP (audio.cu)
+int oa_audio_stft_frame(const void* x, void* frames, int channels, long long samples, int n_frames, int fft, int hop, int win, int kind,
+                        int pad, void* stream);
+int oa_audio_magnitude(const void* reim, void* spec, long long rows, int bins, void* stream);
+int oa_audio_fade(const void* x, void* out, long long count, long long samples, long long fade_in, long long fade_out, void* stream);
+int oa_audio_mix(const void* a, const void* b, void* out, long long count, float ga, float gb, void* stream);
+int oa_audio_resample(const void* x, void* out, int channels, long long in_samples, long long out_samples, unsigned in_r, unsigned out_r,
+                      int half_width, void* stream);
+int oa_audio_envelope(const void* x, void* out, int channels, long long samples, int bins, void* stream);
+
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);
 int oa_ipc_free(void* p);

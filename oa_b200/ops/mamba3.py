@@ -158,14 +158,19 @@ def core_fwd(proj: torch.Tensor, dt_bias, Bb, Cb, D, d: Mamba3Dims, B: int, L: i
     if final is None and _use_ssd(proj, d, L):
         # chunked tensor-core path: the same preprocessed inputs, GEMM-shaped scan
         from . import mamba3_ssd as SSD
+        s = Saved()
+        s.proj, s.params, s.dims, s.B, s.L = proj, (dtb, Bb32, Cb32, D32), d, B, L
+        s.pre, s.Hck, s.Tck = (Bn, Cn, rstd, dt, adt, trap, angle), None, None
+        if os.environ.get("OA_MAMBA3_SSD_FUSED", "1") != "0":
+            y, sv = SSD.ssd_fwd_cuda(proj, Bn, Cn, dt, adt, trap, angle, Bb32, Cb32, D32, d, B, L, save)
+            s.ssd = sv
+            return y, s
         o = d.offsets()
         v4 = lambda c0: proj[:, c0:c0 + d.d_inner].reshape(B, L, H, P)
         r3 = lambda t, w: t.reshape(B, L, w)
         y4, sv = SSD.ssd_fwd(v4(o[1]), v4(o[0]) if d.has_z else None, r3(Bn, Nn), r3(Cn, Nn), r3(dt, H), r3(adt, H), r3(trap, H),
                              r3(angle, max(A, 1))[..., :A], Bb32, Cb32, D32, d, B, L, SSD.CHUNK)
-        s = Saved()
-        s.proj, s.params, s.dims, s.B, s.L = proj, (dtb, Bb32, Cb32, D32), d, B, L
-        s.pre, s.ssd = (Bn, Cn, rstd, dt, adt, trap, angle), (sv if save else None)
+        s.ssd = sv if save else None
         return y4.reshape(rows, d.d_inner).to(proj.dtype), s
     nC = (L + d.chunk - 1) // d.chunk
     Hck = f(B, H, nC, P, Nn) if save else None
@@ -229,10 +234,13 @@ def core_bwd(s: Saved, dy: torch.Tensor, dproj: Optional[torch.Tensor] = None):
     o = d.offsets()
     if s.ssd is not None:
         from . import mamba3_ssd as SSD
-        g = SSD.ssd_bwd(s.ssd, dy.reshape(B, L, H, P))
-        dproj[:, o[1]:o[1] + d.d_inner] = g["x"].reshape(rows, d.d_inner)
-        if d.has_z:
-            dproj[:, o[0]:o[0] + d.d_inner] = g["z"].reshape(rows, d.d_inner)
+        if isinstance(s.ssd, SSD.SsdSavedCuda):
+            g = SSD.ssd_bwd_cuda(s.ssd, proj, dy, dproj)
+        else:
+            g = SSD.ssd_bwd(s.ssd, dy.reshape(B, L, H, P))
+            dproj[:, o[1]:o[1] + d.d_inner] = g["x"].reshape(rows, d.d_inner)
+            if d.has_z:
+                dproj[:, o[0]:o[0] + d.d_inner] = g["z"].reshape(rows, d.d_inner)
         c32 = lambda t: t.reshape(rows, -1).float().contiguous()
         dBn, dCn, ddt, dadt, dtrap = c32(g["Bn"]), c32(g["Cn"]), c32(g["dt"]), c32(g["adt"]), c32(g["trap"])
         if A:

@@ -239,3 +239,137 @@ def ssd_bwd(s: SsdSaved, dy: torch.Tensor):
     out["dt"] = ddt
     out["trap"] = dtr * s.tr * (1 - s.tr)
     return out
+
+
+# ====================================================================================== fused CUDA path (bf16 projection)
+def _unchunk_small(t: torch.Tensor, B: int, L: int, H: int) -> torch.Tensor:
+    """[G, Q] -> [B, L, H]"""
+    return t.reshape(B, H, L // CHUNK, CHUNK).permute(0, 2, 3, 1).reshape(B, L, H)
+
+
+class SsdSavedCuda:
+    __slots__ = ("Ct", "Bt", "Ce", "X", "Xw", "M", "Hin", "cum", "gamma", "scale", "w", "qk", "theta", "yraw", "dims", "B", "L", "dt",
+                 "trap", "angle", "Dh")
+
+
+def ssd_fwd_cuda(proj: torch.Tensor, Bn, Cn, dt, adt, trap, angle, Bb, Cb, D, d: M3.Mamba3Dims, B: int, L: int, save: bool = True):
+    """The chunked scan with the glue in csrc/kernels/mamba3_ssd.cu.  proj bf16 [B*L, d_in_proj]; Bn, Cn [B*L, N];
+    dt, adt, trap [B*L, H]; angle [B*L, max(A, 1)] (fp32).  Returns (y bf16 [B*L, d_inner], saved)."""
+    from .. import _native as N
+    lib, st, dev = N.require(), N.stream(), proj.device
+    H, P, Nn, A = d.heads, d.headdim, d.d_state, d.angles
+    Q, nC, rows = CHUNK, L // CHUNK, B * L
+    G = B * H * nC
+    o = d.offsets()
+    es = proj.element_size()
+    theta = None
+    if A:
+        theta = torch.cumsum(angle.reshape(B, L, 1, -1)[..., :A] * dt.reshape(B, L, H, 1), 1)
+        theta = (theta - TWO_PI * torch.round(theta / TWO_PI)).contiguous()
+    bf = lambda *s: torch.empty(s, dtype=torch.bfloat16, device=dev)
+    f32 = lambda *s: torch.empty(s, dtype=torch.float32, device=dev)
+    Ct, Bt, Ce, X, Xw = bf(G, Q, Nn), bf(G, Q, Nn), bf(G, Q, Nn), bf(G, Q, P), bf(G, Q, P)
+    cum, gamma, scale, w, qk = f32(G, Q), f32(G, Q), f32(G, Q), f32(G, Q), f32(G, Q)
+    K._launch(lib.oa_ssd_prep_fwd(proj.data_ptr() + o[1] * es, d.d_in_proj, Bn.data_ptr(), Cn.data_ptr(), Bb.data_ptr(), Cb.data_ptr(),
+                                  dt.data_ptr(), adt.data_ptr(), trap.data_ptr(), N.ptr(theta), Ct.data_ptr(), Bt.data_ptr(), Ce.data_ptr(),
+                                  X.data_ptr(), Xw.data_ptr(), cum.data_ptr(), gamma.data_ptr(), scale.data_ptr(), w.data_ptr(),
+                                  qk.data_ptr(), B, L, H, P, Nn, A, st), "oa_ssd_prep_fwd")
+    Gm = K.bgemm(Ct, Bt, out_dtype=torch.float32)
+    M = bf(G, Q, Q)
+    K._launch(lib.oa_ssd_mask_fwd(Gm.data_ptr(), cum.data_ptr(), scale.data_ptr(), gamma.data_ptr(), qk.data_ptr(), N.ptr(D), M.data_ptr(),
+                                  G, H, nC, st), "oa_ssd_mask_fwd")
+    del Gm
+    Y = K.bgemm(M, X, b_mn=True, out_dtype=torch.float32)
+    S = K.bgemm(Xw, Bt, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    Hin = bf(G, P, Nn)
+    K._launch(lib.oa_ssd_state_fwd(S.data_ptr(), cum.data_ptr(), Hin.data_ptr(), B * H, nC, P * Nn, st), "oa_ssd_state_fwd")
+    del S
+    K.bgemm(Ce, Hin, out=Y, accumulate=True)
+    y = bf(rows, d.d_inner)
+    yraw = bf(rows, d.d_inner) if d.has_z else None
+    K._launch(lib.oa_ssd_out_fwd(Y.data_ptr(), proj.data_ptr() + o[0] * es if d.has_z else None, d.d_in_proj, y.data_ptr(), N.ptr(yraw),
+                                 d.d_inner, B, L, H, P, st), "oa_ssd_out_fwd")
+    if not save:
+        return y, None
+    s = SsdSavedCuda()
+    s.Ct, s.Bt, s.Ce, s.X, s.Xw, s.M, s.Hin = Ct, Bt, Ce, X, Xw, M, Hin
+    s.cum, s.gamma, s.scale, s.w, s.qk, s.theta, s.yraw = cum, gamma, scale, w, qk, theta, yraw
+    s.dims, s.B, s.L, s.dt, s.trap, s.angle, s.Dh = d, B, L, dt, trap, angle, D
+    return y, s
+
+
+def ssd_bwd_cuda(s: SsdSavedCuda, proj: torch.Tensor, dy: torch.Tensor, dproj: torch.Tensor) -> dict:
+    """Writes dx (and dz) into their columns of dproj and returns the fp32 gradients the preprocess backward needs:
+    Bn, Cn [B*L, N], dt, adt, trap [B*L, H], angle [B*L, max(A, 1)], Bb, Cb [H, N], D [H]."""
+    from .. import _native as N
+    lib, st, dev = N.require(), N.stream(), dy.device
+    d, B, L = s.dims, s.B, s.L
+    H, P, Nn, A = d.heads, d.headdim, d.d_state, d.angles
+    Q, nC, rows = CHUNK, L // CHUNK, B * L
+    G = B * H * nC
+    o = d.offsets()
+    es = proj.element_size()
+    bf = lambda *sh: torch.empty(sh, dtype=torch.bfloat16, device=dev)
+    f32 = lambda *sh: torch.empty(sh, dtype=torch.float32, device=dev)
+    z32 = lambda *sh: torch.zeros(sh, dtype=torch.float32, device=dev)
+    dy = dy.contiguous()
+    dY = bf(G, Q, P)
+    K._launch(lib.oa_ssd_dy_prep(dy.data_ptr(), N.ptr(s.yraw), d.d_inner, proj.data_ptr() + o[0] * es if d.has_z else None, d.d_in_proj,
+                                 dproj.data_ptr() + o[0] * es if d.has_z else None, d.d_in_proj, dY.data_ptr(), B, L, H, P, st),
+              "oa_ssd_dy_prep")
+    dM = K.bgemm(dY, s.X, out_dtype=torch.float32)
+    dX = K.bgemm(s.M, dY, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    dCe = K.bgemm(dY, s.Hin, b_mn=True, out_dtype=torch.float32)
+    T = K.bgemm(dY, s.Ce, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    dHout, dcumQ = bf(G, P, Nn), z32(G)
+    K._launch(lib.oa_ssd_state_bwd(T.data_ptr(), s.cum.data_ptr(), s.Hin.data_ptr(), dHout.data_ptr(), dcumQ.data_ptr(), B * H, nC, P * Nn, st),
+              "oa_ssd_state_bwd")
+    del T
+    dXw = K.bgemm(s.Bt, dHout, out_dtype=torch.float32)
+    dBt = K.bgemm(s.Xw, dHout, b_mn=True, out_dtype=torch.float32)
+    Gm = K.bgemm(s.Ct, s.Bt, out_dtype=torch.float32)
+    dG, row_mm, col_mm, col_ge, diag = bf(G, Q, Q), f32(G, Q), f32(G, Q), f32(G, Q), f32(G, Q)
+    K._launch(lib.oa_ssd_mask_bwd(dM.data_ptr(), Gm.data_ptr(), s.cum.data_ptr(), s.scale.data_ptr(), dG.data_ptr(), row_mm.data_ptr(),
+                                  col_mm.data_ptr(), col_ge.data_ptr(), diag.data_ptr(), G, st), "oa_ssd_mask_bwd")
+    del dM, Gm
+    dCt = K.bgemm(dG, s.Bt, b_mn=True, out_dtype=torch.float32)
+    K.bgemm(dG, s.Ct, a_mn=True, b_mn=True, out=dBt, accumulate=True)
+    dqk = diag * s.gamma
+    dCn, dBn, dCb, dBb = z32(rows, Nn), z32(rows, Nn), z32(H, Nn), z32(H, Nn)
+    dtheta = f32(B, L, H, A) if A else None
+    dcum_ce = f32(G, Q)
+    K._launch(lib.oa_ssd_prep_bwd(dCt.data_ptr(), dBt.data_ptr(), dCe.data_ptr(), s.Ct.data_ptr(), s.Bt.data_ptr(), s.cum.data_ptr(),
+                                  dqk.data_ptr(), N.ptr(s.theta), dCn.data_ptr(), dBn.data_ptr(), dCb.data_ptr(), dBb.data_ptr(),
+                                  N.ptr(dtheta), dcum_ce.data_ptr(), B, L, H, Nn, A, st), "oa_ssd_prep_bwd")
+    del dCt, dBt, dCe
+    dw = f32(G, Q)
+    K._launch(lib.oa_ssd_dx_out(dX.data_ptr(), dXw.data_ptr(), s.X.data_ptr(), s.w.data_ptr(), dproj.data_ptr() + o[1] * es, d.d_in_proj,
+                                dw.data_ptr(), B, L, H, P, st), "oa_ssd_dx_out")
+    # ---- per-token scalar tail ([G, Q] / [B, L, H] sized tensors)
+    cumQ = s.cum[:, -1:]
+    dww = dw * s.w
+    dscale = col_ge + dw * torch.exp(cumQ - s.cum)
+    dcum = row_mm - col_mm + dcum_ce - dww
+    dcum[:, -1:] += dcumQ[:, None] + dww.sum(1, keepdim=True)
+    dadt = _unchunk_small(torch.flip(torch.cumsum(torch.flip(dcum, [1]), 1), [1]), B, L, H)
+    dgamma_l, dscale_l = _unchunk_small(diag * s.qk, B, L, H), _unchunk_small(dscale, B, L, H)
+    out = {"Bn": dBn, "Cn": dCn, "Bb": dBb, "Cb": dCb, "adt": dadt.reshape(rows, H).contiguous()}
+    out["D"] = diag.reshape(B, H, nC * Q).sum((0, 2)) if s.Dh is not None else None
+    dt3, trap3 = s.dt.reshape(B, L, H), s.trap.reshape(B, L, H)
+    tr = torch.sigmoid(trap3)
+    ddt = torch.zeros_like(dt3)
+    if A:
+        gth = torch.flip(torch.cumsum(torch.flip(dtheta, [1]), 1), [1])
+        ang = s.angle.reshape(B, L, -1)[..., :A]
+        out["angle"] = (gth * dt3[..., None]).sum(2).reshape(rows, A).contiguous()
+        ddt = ddt + (gth * ang[:, :, None, :]).sum(-1)
+    else:
+        out["angle"] = torch.zeros(rows, 1, dtype=torch.float32, device=dev)
+    dgam = dgamma_l + dscale_l
+    ddt = ddt + dgam * tr
+    dtr = dgam * dt3
+    ddt[:, 1:] += dscale_l[:, :-1] * (1 - tr[:, 1:])
+    dtr[:, 1:] -= dscale_l[:, :-1] * dt3[:, 1:]
+    out["dt"] = ddt.reshape(rows, H).contiguous()
+    out["trap"] = (dtr * tr * (1 - tr)).reshape(rows, H).contiguous()
+    return out
