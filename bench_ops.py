@@ -122,6 +122,22 @@ def bench_mamba():
     K.check_status()
 
 
+def bench_mamba_once():
+    """One forward + backward of the Mamba-3 core at B=2, L=4096 (no timing loop): the workload of the per-launch profile."""
+    from oa_b200.ops import mamba3 as M3
+    B, L, H, P, Nn = 2, 4096, 48, 64, 128
+    d = M3.Mamba3Dims(d_inner=H * P, heads=H, headdim=P, d_state=Nn, angles=32, has_z=True, chunk=256)
+    proj = (torch.randn(B * L, d.d_in_proj, device="cuda") * 0.5).bfloat16()
+    dtb = torch.rand(1, H, device="cuda")
+    Bb, Cb, D = torch.ones(H, Nn, device="cuda"), torch.ones(H, Nn, device="cuda"), torch.zeros(H, device="cuda")
+    for _ in range(2):
+        y, saved = M3.core_fwd(proj, dtb, Bb, Cb, D, d, B, L, save=True)
+        M3.core_bwd(saved, torch.randn_like(y))
+    torch.cuda.synchronize()
+    K.check_status()
+    emit(op="mamba3_core_once", B=B, L=L, status="ok")
+
+
 def bench_decode():
     """Batch-32 greedy decoding of 256 tokens after a 2048-token prompt on the 7B-class model (one GPU, KV cache)."""
     from oa_b200.core import fn_matrix as F
@@ -264,7 +280,7 @@ def main() -> int:
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:

@@ -9,7 +9,7 @@ OaFnMetric, and the `Context` scope), bound here to oa_b200.
     with oa.OaGradientTape() as tape: ...
     with oa.Context(): ...            # Execute + Sync of the default context on scope exit
 
-Names of the reference surface that this build does not provide (audio, vision, crypto, plot, ui) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
+Names of the reference surface that this build does not provide (vision, plot, ui) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
 """
 from __future__ import annotations
 
@@ -117,6 +117,12 @@ OaFnRl = _namespace("OaFnRl", "Advantage estimation, policy distributions, trans
                     ["Gae", "GaeInto", "NormalizeAdvantages", "SampleCategoricalPolicy", "EvaluateCategoricalPolicy", "SampleTanhNormalPolicy",
                      "EvaluateTanhNormalPolicy", "NormalizeObservation", "ScaleAction", "ClipReward", "SampleLogits", "EvaluateCategorical"])
 from oa_b200.crypto import fn_hash as _FH
+from oa_b200.audio import fn_audio as _FA
+from oa_b200.audio.fn_audio import (OaAudio, OaChannelLayout, OaChannelsForLayout, OaLayoutForChannels, OaMelConfig, OaMfccConfig,
+                                    OaNormalizeAudioConfig, OaResampleConfig, OaStftConfig)
+OaFnAudio = _namespace("OaFnAudio", "Waveform operations and audio features (STFT, mel, MFCC).", _FA,
+                       ["Normalize", "Resample", "Gain", "Clip", "PreEmphasis", "ToMono", "Fade", "Mix", "AmplitudeToDb", "WaveformEnvelope",
+                        "Stft", "MelSpectrogram", "Mfcc"])
 OaFnHash = _namespace("OaFnHash", "Batched SHAKE / Keccak hashing and the SHAKE-256 Merkle root.", _FH,
                       ["Shake256", "Shake128", "KeccakF1600", "MerkleRoot"])
 OaFnAutograd = _namespace("OaFnAutograd", "Autograd recording switch.", _AG, ["IsEnabled", "SetEnabled"])
@@ -135,12 +141,12 @@ class Context:
         self._ctx.Sync()
 
 
-UNAVAILABLE = ("OaFnAudio", "OaFnImage", "OaFnDetection", "OaPlot", "OaViewer", "OaAudio", "OaVideo")
+UNAVAILABLE = ("OaFnImage", "OaFnDetection", "OaPlot", "OaViewer", "OaVideo")
 
 
 def __getattr__(name: str):
     if name in UNAVAILABLE:
-        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (audio / vision / crypto / ui) that this build does not provide")
+        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (vision / plot / ui) that this build does not provide")
     raise AttributeError(f"module 'oa' has no attribute '{name}'")
 
 

@@ -283,6 +283,9 @@ int oa_ssd_mask_bwd(const void* dM, const void* Gm, const void* cum, const void*
 int oa_ssd_prep_bwd(const void* dCt, const void* dBt, const void* dCe, const void* Ct, const void* Bt, const void* cum, const void* dqk,
                     const void* theta, void* dCn, void* dBn, void* dCb, void* dBb, void* dtheta, void* dcum_ce, int B, int L, int H,
                     int N, int A, void* stream);
+int oa_ssd_theta_fwd(const void* angle, int lda, const void* dt, void* tot, void* theta, int B, int L, int H, int A, void* stream);
+int oa_ssd_theta_bwd(const void* dtheta, const void* angle, int lda, const void* dt, void* tot, void* dangle, void* ddt, int B, int L,
+                     int H, int A, void* stream);
 int oa_ssd_dx_out(const void* dX, const void* dXw, const void* X, const void* w, void* dx, long long lddx, void* dw, int B, int L, int H,
                   int P, void* stream);
 

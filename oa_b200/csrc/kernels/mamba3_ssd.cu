@@ -408,6 +408,71 @@ __global__ void __launch_bounds__(256) ssd_dx_out_kernel(const float* __restrict
   }
 }
 
+// ------------------------------------------------------------------------------------------------ rotary phase scans
+// theta[b,l,h,a] = sum_{l' <= l} angle[b,l',a] dt[b,l',h], reduced to (-pi, pi].  Two passes over chunks of 128 tokens:
+// pass 0 writes the per-chunk totals, pass 1 adds the totals of the earlier chunks and writes the running sum.  One warp
+// per (b, chunk, h), lanes over a.  The backward kernel is the mirror image: suffix sums g of dtheta, folded straight into
+// d angle[b,l,a] += sum_h g dt and d dt[b,l,h] = sum_a g angle (the suffix sums themselves are never stored).
+__global__ void __launch_bounds__(256) ssd_theta_fwd_kernel(const float* __restrict__ angle, int lda, const float* __restrict__ dt,
+                                                            float* __restrict__ tot, float* __restrict__ theta, SsdDims d, int pass) {
+  const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (wid >= d.B * d.nC * d.H) return;
+  const int h = wid % d.H, c = (wid / d.H) % d.nC, b = wid / (d.H * d.nC);
+  const long long row0 = (long long)b * d.L + (long long)c * SQ;
+  for (int a = lane; a < d.A; a += 32) {
+    float run = 0.f;
+    if (pass == 1)
+      for (int cp = 0; cp < c; ++cp) run += tot[(((long long)b * d.nC + cp) * d.H + h) * d.A + a];
+    for (int t = 0; t < SQ; ++t) {
+      const long long r = row0 + t;
+      run += angle[r * lda + a] * dt[r * d.H + h];
+      if (pass == 1) theta[(r * d.H + h) * d.A + a] = run - 6.283185307179586f * rintf(run * 0.15915494309189535f);
+    }
+    if (pass == 0) tot[(((long long)b * d.nC + c) * d.H + h) * d.A + a] = run;
+  }
+}
+
+__global__ void __launch_bounds__(256) ssd_theta_bwd_kernel(const float* __restrict__ dtheta, const float* __restrict__ angle, int lda,
+                                                            const float* __restrict__ dt, float* __restrict__ tot,
+                                                            float* __restrict__ dangle, float* __restrict__ ddt, SsdDims d, int pass) {
+  const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (wid >= d.B * d.nC * d.H) return;
+  const int h = wid % d.H, c = (wid / d.H) % d.nC, b = wid / (d.H * d.nC);
+  const long long row0 = (long long)b * d.L + (long long)c * SQ;
+  if (pass == 0) {
+    for (int a = lane; a < d.A; a += 32) {
+      float run = 0.f;
+      for (int t = 0; t < SQ; ++t) run += dtheta[((row0 + t) * d.H + h) * d.A + a];
+      tot[(((long long)b * d.nC + c) * d.H + h) * d.A + a] = run;
+    }
+    return;
+  }
+  // A <= 32 * 4 supported: each lane carries up to 4 running suffix sums
+  float run[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const int a = lane + 32 * q;
+    if (a < d.A)
+      for (int cp = c + 1; cp < d.nC; ++cp) run[q] += tot[(((long long)b * d.nC + cp) * d.H + h) * d.A + a];
+  }
+  for (int t = SQ - 1; t >= 0; --t) {
+    const long long r = row0 + t;
+    const float dtv = dt[r * d.H + h];
+    float acc = 0.f;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int a = lane + 32 * q;
+      if (a < d.A) {
+        run[q] += dtheta[(r * d.H + h) * d.A + a];
+        atomicAdd(dangle + r * lda + a, run[q] * dtv);
+        acc += run[q] * angle[r * lda + a];
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) ddt[r * d.H + h] = acc;
+  }
+}
+
 inline bool ssd_dims_ok(const SsdDims& d) {
   return d.B > 0 && d.L > 0 && d.H > 0 && d.P > 0 && d.N > 0 && d.A >= 0 && d.L % SQ == 0 && d.nC == d.L / SQ && d.N % 4 == 0 && d.P % 2 == 0 &&
          2 * d.A <= d.N;
@@ -509,6 +574,29 @@ int oa_ssd_dx_out(const void* dX, const void* dXw, const void* X, const void* w,
   if (!ssd_dims_ok(d)) return OA_ERR_ARG;
   ssd_dx_out_kernel<<<B * H * d.nC, 256, 0, (cudaStream_t)stream>>>((const float*)dX, (const float*)dXw, (const __nv_bfloat16*)X,
                                                                     (const float*)w, (__nv_bfloat16*)dx, lddx, (float*)dw, d);
+  return ssd_status();
+}
+
+// theta [B*L, H, A] from angle [B*L, lda] and dt [B*L, H]; tot is scratch [B, nC, H, A]
+int oa_ssd_theta_fwd(const void* angle, int lda, const void* dt, void* tot, void* theta, int B, int L, int H, int A, void* stream) {
+  SsdDims d{B, L, H, 2, 2 * A > 4 ? ((2 * A + 3) / 4) * 4 : 4, A, L / SQ};
+  if (!ssd_dims_ok(d) || A <= 0 || lda < A) return OA_ERR_ARG;
+  const int warps = B * d.nC * H, grid = (warps + 7) / 8;
+  ssd_theta_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)angle, lda, (const float*)dt, (float*)tot, (float*)theta, d, 0);
+  ssd_theta_fwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)angle, lda, (const float*)dt, (float*)tot, (float*)theta, d, 1);
+  return ssd_status();
+}
+
+// dangle [B*L, lda] (+=, zeroed by the caller) and ddt [B*L, H] (=) from dtheta; A <= 128
+int oa_ssd_theta_bwd(const void* dtheta, const void* angle, int lda, const void* dt, void* tot, void* dangle, void* ddt, int B, int L,
+                     int H, int A, void* stream) {
+  SsdDims d{B, L, H, 2, 2 * A > 4 ? ((2 * A + 3) / 4) * 4 : 4, A, L / SQ};
+  if (!ssd_dims_ok(d) || A <= 0 || A > 128 || lda < A) return OA_ERR_ARG;
+  const int warps = B * d.nC * H, grid = (warps + 7) / 8;
+  ssd_theta_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)dtheta, (const float*)angle, lda, (const float*)dt,
+                                                              (float*)tot, (float*)dangle, (float*)ddt, d, 0);
+  ssd_theta_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)dtheta, (const float*)angle, lda, (const float*)dt,
+                                                              (float*)tot, (float*)dangle, (float*)ddt, d, 1);
   return ssd_status();
 }
 

@@ -262,12 +262,13 @@ def ssd_fwd_cuda(proj: torch.Tensor, Bn, Cn, dt, adt, trap, angle, Bb, Cb, D, d:
     G = B * H * nC
     o = d.offsets()
     es = proj.element_size()
-    theta = None
-    if A:
-        theta = torch.cumsum(angle.reshape(B, L, 1, -1)[..., :A] * dt.reshape(B, L, H, 1), 1)
-        theta = (theta - TWO_PI * torch.round(theta / TWO_PI)).contiguous()
     bf = lambda *s: torch.empty(s, dtype=torch.bfloat16, device=dev)
     f32 = lambda *s: torch.empty(s, dtype=torch.float32, device=dev)
+    theta = None
+    if A:
+        theta, tot = f32(B, L, H, A), f32(B, nC, H, A)
+        K._launch(lib.oa_ssd_theta_fwd(angle.data_ptr(), angle.shape[-1], dt.data_ptr(), tot.data_ptr(), theta.data_ptr(), B, L, H, A, st),
+                  "oa_ssd_theta_fwd", 2)
     Ct, Bt, Ce, X, Xw = bf(G, Q, Nn), bf(G, Q, Nn), bf(G, Q, Nn), bf(G, Q, P), bf(G, Q, P)
     cum, gamma, scale, w, qk = f32(G, Q), f32(G, Q), f32(G, Q), f32(G, Q), f32(G, Q)
     K._launch(lib.oa_ssd_prep_fwd(proj.data_ptr() + o[1] * es, d.d_in_proj, Bn.data_ptr(), Cn.data_ptr(), Bb.data_ptr(), Cb.data_ptr(),
@@ -357,13 +358,14 @@ def ssd_bwd_cuda(s: SsdSavedCuda, proj: torch.Tensor, dy: torch.Tensor, dproj: t
     out["D"] = diag.reshape(B, H, nC * Q).sum((0, 2)) if s.Dh is not None else None
     dt3, trap3 = s.dt.reshape(B, L, H), s.trap.reshape(B, L, H)
     tr = torch.sigmoid(trap3)
-    ddt = torch.zeros_like(dt3)
     if A:
-        gth = torch.flip(torch.cumsum(torch.flip(dtheta, [1]), 1), [1])
-        ang = s.angle.reshape(B, L, -1)[..., :A]
-        out["angle"] = (gth * dt3[..., None]).sum(2).reshape(rows, A).contiguous()
-        ddt = ddt + (gth * ang[:, :, None, :]).sum(-1)
+        lda = s.angle.shape[-1]
+        dangle, ddt, tot = z32(rows, lda), f32(B, L, H), f32(B, nC, H, A)
+        K._launch(lib.oa_ssd_theta_bwd(dtheta.data_ptr(), s.angle.data_ptr(), lda, s.dt.data_ptr(), tot.data_ptr(), dangle.data_ptr(),
+                                       ddt.data_ptr(), B, L, H, A, st), "oa_ssd_theta_bwd", 2)
+        out["angle"] = dangle
     else:
+        ddt = torch.zeros_like(dt3)
         out["angle"] = torch.zeros(rows, 1, dtype=torch.float32, device=dev)
     dgam = dgamma_l + dscale_l
     ddt = ddt + dgam * tr

@@ -146,7 +146,7 @@ class OaContext:
         eng = OaEngine.GetGlobal()
         if ctx is None or ctx._engine is not eng:
             if eng is None:
-                raise OaError(OaStatus.Error(OaStatusCode.FailedPrecondition, "compute engine is not initialised"))
+                eng = get_engine()          # lazily created with defaults, like every tensor factory does
             ctx = OaContext(eng)
             cls._tls.ctx = ctx
         return ctx
