@@ -246,26 +246,27 @@ __global__ void __launch_bounds__(256) ssd_dy_prep_kernel(const __nv_bfloat16* _
 // ------------------------------------------------------------------------------------------------------ mask backward
 // Per chunk, with L = strict lower triangle:  dG = dM e^{..} scale (on L);  dMM = dM * M (on L)
 //   row_mm[t] = sum_s dMM;  col_mm[s] = sum_t dMM;  col_ge[s] = sum_t dM G e^{..} (on L);  diag[t] = dM[t,t]
-constexpr int SQP = SQ + 1;
+// Warp w owns rows w, w+8, ...; lane owns columns 4*lane .. 4*lane+3: row sums are warp reductions, column sums stay in
+// registers over the warp's 16 rows and are combined across the 8 warps through 8 KB of shared memory.
 __global__ void __launch_bounds__(256) ssd_mask_bwd_kernel(const float* __restrict__ dM, const float* __restrict__ Gm,
                                                            const float* __restrict__ cum, const float* __restrict__ scale,
                                                            __nv_bfloat16* __restrict__ dG, float* __restrict__ row_mm,
                                                            float* __restrict__ col_mm, float* __restrict__ col_ge,
                                                            float* __restrict__ diag) {
-  extern __shared__ float smem[];
-  float* s_mm = smem;                       // [SQ][SQP] dM * G * E * scale
-  float* s_ge = smem + SQ * SQP;            // [SQ][SQP] dM * G * E
   __shared__ float s_cum[SQ], s_scale[SQ];
-  const int g = blockIdx.x, tid = threadIdx.x;
+  __shared__ float s_cm[8][SQ], s_cg[8][SQ];
+  const int g = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid < SQ) { s_cum[tid] = cum[(long long)g * SQ + tid]; s_scale[tid] = scale[(long long)g * SQ + tid]; }
   __syncthreads();
   const float* dMg = dM + (long long)g * SQ * SQ;
   const float* Gg = Gm + (long long)g * SQ * SQ;
   __nv_bfloat16* dGg = dG + (long long)g * SQ * SQ;
-  for (int i = tid; i < SQ * SQ / 4; i += 256) {
-    const int t = i >> 5, s0 = (i & 31) * 4;
-    float o[4] = {0.f, 0.f, 0.f, 0.f};
-    float mm[4] = {0.f, 0.f, 0.f, 0.f}, ge[4] = {0.f, 0.f, 0.f, 0.f};
+  const int s0 = lane * 4;
+  float cs[4], sc[4], cmm[4] = {0.f, 0.f, 0.f, 0.f}, cge[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { cs[j] = s_cum[s0 + j]; sc[j] = s_scale[s0 + j]; }
+  for (int t = warp; t < SQ; t += 8) {
+    float o[4] = {0.f, 0.f, 0.f, 0.f}, rsum = 0.f;
     if (s0 <= t) {
       const float4 dm = *reinterpret_cast<const float4*>(dMg + t * SQ + s0);
       const float4 gg = *reinterpret_cast<const float4*>(Gg + t * SQ + s0);
@@ -273,31 +274,29 @@ __global__ void __launch_bounds__(256) ssd_mask_bwd_kernel(const float* __restri
       const float ct = s_cum[t];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int s = s0 + j;
-        if (s < t) {
-          const float e = __expf(ct - s_cum[s]);
-          o[j] = dmv[j] * e * s_scale[s];
-          ge[j] = dmv[j] * gv[j] * e;
-          mm[j] = ge[j] * s_scale[s];
-        } else if (s == t) {
+        const int sidx = s0 + j;
+        if (sidx < t) {
+          const float e = __expf(ct - cs[j]);
+          o[j] = dmv[j] * e * sc[j];
+          const float ge = dmv[j] * gv[j] * e, mm = ge * sc[j];
+          cge[j] += ge; cmm[j] += mm; rsum += mm;
+        } else if (sidx == t) {
           diag[(long long)g * SQ + t] = dmv[j];
         }
       }
     }
     *reinterpret_cast<uint2*>(dGg + t * SQ + s0) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
-#pragma unroll
-    for (int j = 0; j < 4; ++j) { s_mm[t * SQP + s0 + j] = mm[j]; s_ge[t * SQP + s0 + j] = ge[j]; }
+    rsum = warp_sum(rsum);
+    if (lane == 0) row_mm[(long long)g * SQ + t] = rsum;
   }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { s_cm[warp][s0 + j] = cmm[j]; s_cg[warp][s0 + j] = cge[j]; }
   __syncthreads();
-  if (tid < SQ) {                            // row sums: thread t walks its row (stride-1 in smem, conflict-free by padding)
-    float r = 0.f;
-    for (int s = 0; s < tid; ++s) r += s_mm[tid * SQP + s];
-    row_mm[(long long)g * SQ + tid] = r;
-  } else {                                   // column sums: thread s walks its column
-    const int s = tid - SQ;
-    float cm = 0.f, cg = 0.f;
-    for (int t = s + 1; t < SQ; ++t) { cm += s_mm[t * SQP + s]; cg += s_ge[t * SQP + s]; }
-    col_mm[(long long)g * SQ + s] = cm; col_ge[(long long)g * SQ + s] = cg;
+  if (tid < SQ) {
+    float a = 0.f, b2 = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) { a += s_cm[w8][tid]; b2 += s_cg[w8][tid]; }
+    col_mm[(long long)g * SQ + tid] = a; col_ge[(long long)g * SQ + tid] = b2;
   }
 }
 
@@ -307,78 +306,95 @@ struct SsdPrepBwd {
   const __nv_bfloat16 *Ct, *Bt;                  // saved rotated operands
   const float *cum, *dqk;                        // [G, Q]
   const float* theta;                            // [B*L, H, A]
-  float *dCn, *dBn;                              // [B*L, N]  (atomic: summed over heads)
+  float *dCn, *dBn;                              // [B*L, N]  (summed over heads; stored, not accumulated)
   float *dCb, *dBb;                              // [H, N]    (atomic: summed over batch and time)
   float* dtheta;                                 // [B*L, H, A]
   float* dcum_ce;                                // [G, Q]  sum_n dCe C~ e^cum
   SsdDims d;
 };
 
+// One CTA owns 32 token rows of a chunk for ALL heads: the sums over heads (dCn, dBn) stay in registers and are stored once,
+// without atomics.  Warp w owns rows w, w+8, w+16, w+24 of the 32; lane owns state columns 4*lane .. 4*lane+3 (N <= 128).
 __global__ void __launch_bounds__(256) ssd_prep_bwd_kernel(SsdPrepBwd a) {
   const SsdDims& d = a.d;
-  const int g = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c = g % d.nC, bh = g / d.nC, h = bh % d.H, b = bh / d.H;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q4 = blockIdx.x & 3, bc = blockIdx.x >> 2, c = bc % d.nC, b = bc / d.nC;
   const long long row0 = (long long)b * d.L + (long long)c * SQ;
   const int N4 = d.N >> 2;
-  extern __shared__ float s_bias[];               // [8 warps][2][N] partial bias gradients
-  float* my_cb = s_bias + (warp * 2) * d.N;
-  float* my_bb = my_cb + d.N;
-  for (int n = lane; n < d.N; n += 32) { my_cb[n] = 0.f; my_bb[n] = 0.f; }
-  __syncwarp();
-  for (int t = warp; t < SQ; t += 8) {
-    const long long r = row0 + t, og = (long long)g * SQ + t;
-    const float ecum = __expf(a.cum[og]), dqk = a.dqk[og];
-    float dce = 0.f;
-    for (int n4 = lane; n4 < N4; n4 += 32) {
-      const long long o = og * d.N + n4 * 4;
-      const float4 dc = *reinterpret_cast<const float4*>(a.dCt + o), db = *reinterpret_cast<const float4*>(a.dBt + o);
-      const float4 de = *reinterpret_cast<const float4*>(a.dCe + o);
-      const uint2 cu = *reinterpret_cast<const uint2*>(a.Ct + o), bu = *reinterpret_cast<const uint2*>(a.Bt + o);
-      const float2 c01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&cu.x));
-      const float2 c23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&cu.y));
-      const float2 b01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bu.x));
-      const float2 b23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bu.y));
-      const float cv[4] = {c01.x, c01.y, c23.x, c23.y}, bv[4] = {b01.x, b01.y, b23.x, b23.y};
-      const float dev[4] = {de.x, de.y, de.z, de.w};
-      float gc[4] = {dc.x, dc.y, dc.z, dc.w}, gb[4] = {db.x, db.y, db.z, db.w};
+  const bool live = lane < N4;
+  __shared__ float s_cb[8][SQ], s_bb[8][SQ];         // per-warp bias partials of the current head
+  float accC[4][4], accB[4][4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        dce += dev[j] * cv[j];
-        gc[j] += dev[j] * ecum + dqk * bv[j];
-        gb[j] += dqk * cv[j];
-      }
-      const int k0 = n4 * 2;
-      if (k0 < d.A) {
-        const float* th = a.theta + (r * d.H + h) * d.A;
-        float* dth = a.dtheta + (r * d.H + h) * d.A;
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int q = 0; q < 2; ++q) {
-          if (k0 + q < d.A) {
-            float sn, cs;
-            sincosf(th[k0 + q], &sn, &cs);
-            const int j = 2 * q;
-            dth[k0 + q] = (-gc[j] * cv[j + 1] + gc[j + 1] * cv[j]) + (-gb[j] * bv[j + 1] + gb[j + 1] * bv[j]);
-            float u0 = gc[j] * cs + gc[j + 1] * sn, u1 = -gc[j] * sn + gc[j + 1] * cs; gc[j] = u0; gc[j + 1] = u1;
-            u0 = gb[j] * cs + gb[j + 1] * sn; u1 = -gb[j] * sn + gb[j + 1] * cs; gb[j] = u0; gb[j + 1] = u1;
+    for (int j = 0; j < 4; ++j) { accC[i][j] = 0.f; accB[i][j] = 0.f; }
+  for (int h = 0; h < d.H; ++h) {
+    const long long g = ((long long)b * d.H + h) * d.nC + c;
+    float pc[4] = {0.f, 0.f, 0.f, 0.f}, pb[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int t = q4 * 32 + warp + 8 * i;
+      const long long r = row0 + t, og = g * SQ + t;
+      const float ecum = __expf(a.cum[og]), dqk = a.dqk[og];
+      float dce = 0.f;
+      if (live) {
+        const long long o = og * d.N + lane * 4;
+        const float4 dc = *reinterpret_cast<const float4*>(a.dCt + o), db = *reinterpret_cast<const float4*>(a.dBt + o);
+        const float4 de = *reinterpret_cast<const float4*>(a.dCe + o);
+        const uint2 cu = *reinterpret_cast<const uint2*>(a.Ct + o), bu = *reinterpret_cast<const uint2*>(a.Bt + o);
+        const float2 c01 = unpack_bf16x2(cu.x), c23 = unpack_bf16x2(cu.y), b01 = unpack_bf16x2(bu.x), b23 = unpack_bf16x2(bu.y);
+        const float cv[4] = {c01.x, c01.y, c23.x, c23.y}, bv[4] = {b01.x, b01.y, b23.x, b23.y};
+        const float dev[4] = {de.x, de.y, de.z, de.w};
+        float gc[4] = {dc.x, dc.y, dc.z, dc.w}, gb[4] = {db.x, db.y, db.z, db.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dce += dev[j] * cv[j];
+          gc[j] += dev[j] * ecum + dqk * bv[j];
+          gb[j] += dqk * cv[j];
+        }
+        const int k0 = lane * 2;
+        if (k0 < d.A) {
+          const float* th = a.theta + (r * d.H + h) * d.A;
+          float* dth = a.dtheta + (r * d.H + h) * d.A;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            if (k0 + q < d.A) {
+              float sn, cs;
+              sincosf(th[k0 + q], &sn, &cs);
+              const int j = 2 * q;
+              dth[k0 + q] = (-gc[j] * cv[j + 1] + gc[j + 1] * cv[j]) + (-gb[j] * bv[j + 1] + gb[j + 1] * bv[j]);
+              float u0 = gc[j] * cs + gc[j + 1] * sn, u1 = -gc[j] * sn + gc[j + 1] * cs; gc[j] = u0; gc[j + 1] = u1;
+              u0 = gb[j] * cs + gb[j + 1] * sn; u1 = -gb[j] * sn + gb[j + 1] * cs; gb[j] = u0; gb[j + 1] = u1;
+            }
           }
         }
-      }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        atomicAdd(a.dCn + r * d.N + n4 * 4 + j, gc[j]);
-        atomicAdd(a.dBn + r * d.N + n4 * 4 + j, gb[j]);
-        my_cb[n4 * 4 + j] += gc[j];
-        my_bb[n4 * 4 + j] += gb[j];
+        for (int j = 0; j < 4; ++j) { accC[i][j] += gc[j]; accB[i][j] += gb[j]; pc[j] += gc[j]; pb[j] += gb[j]; }
       }
+      dce = warp_sum(dce);
+      if (lane == 0) a.dcum_ce[og] = dce * ecum;
     }
-    dce = warp_sum(dce);
-    if (lane == 0) a.dcum_ce[og] = dce * ecum;
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { s_cb[warp][lane * 4 + j] = pc[j]; s_bb[warp][lane * 4 + j] = pb[j]; }
+    }
+    __syncthreads();
+    if (tid < d.N) {
+      float sc = 0.f, sb = 0.f;
+#pragma unroll
+      for (int w8 = 0; w8 < 8; ++w8) { sc += s_cb[w8][tid]; sb += s_bb[w8][tid]; }
+      atomicAdd(a.dCb + (long long)h * d.N + tid, sc);
+      atomicAdd(a.dBb + (long long)h * d.N + tid, sb);
+    }
+    __syncthreads();
   }
-  __syncthreads();
-  for (int n = tid; n < 2 * d.N; n += 256) {
-    float s = 0.f;
-    for (int w8 = 0; w8 < 8; ++w8) s += s_bias[(w8 * 2) * d.N + n];      // [warp][cb | bb][N] laid out as 2N per warp
-    atomicAdd((n < d.N ? a.dCb : a.dBb) + (long long)h * d.N + (n < d.N ? n : n - d.N), s);
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const long long r = row0 + q4 * 32 + warp + 8 * i;
+      *reinterpret_cast<float4*>(a.dCn + r * d.N + lane * 4) = make_float4(accC[i][0], accC[i][1], accC[i][2], accC[i][3]);
+      *reinterpret_cast<float4*>(a.dBn + r * d.N + lane * 4) = make_float4(accB[i][0], accB[i][1], accB[i][2], accB[i][3]);
+    }
   }
 }
 
@@ -544,13 +560,7 @@ int oa_ssd_dy_prep(const void* dy, const void* yraw, long long ldy, const void* 
 int oa_ssd_mask_bwd(const void* dM, const void* Gm, const void* cum, const void* scale, void* dG, void* row_mm, void* col_mm,
                     void* col_ge, void* diag, int G, void* stream) {
   if (G <= 0) return OA_ERR_ARG;
-  const int smem = 2 * SQ * SQP * (int)sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(ssd_mask_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return OA_ERR_DRIVER;
-    attr_set = true;
-  }
-  ssd_mask_bwd_kernel<<<G, 256, smem, (cudaStream_t)stream>>>((const float*)dM, (const float*)Gm, (const float*)cum, (const float*)scale,
+  ssd_mask_bwd_kernel<<<G, 256, 0, (cudaStream_t)stream>>>((const float*)dM, (const float*)Gm, (const float*)cum, (const float*)scale,
                                                               (__nv_bfloat16*)dG, (float*)row_mm, (float*)col_mm, (float*)col_ge,
                                                               (float*)diag);
   return ssd_status();
@@ -560,11 +570,11 @@ int oa_ssd_prep_bwd(const void* dCt, const void* dBt, const void* dCe, const voi
                     const void* theta, void* dCn, void* dBn, void* dCb, void* dBb, void* dtheta, void* dcum_ce, int B, int L, int H,
                     int N, int A, void* stream) {
   SsdDims d{B, L, H, 2, N, A, L / SQ};
-  if (!ssd_dims_ok(d) || (A > 0 && (!theta || !dtheta))) return OA_ERR_ARG;
+  if (!ssd_dims_ok(d) || N > 128 || (A > 0 && (!theta || !dtheta))) return OA_ERR_ARG;
   SsdPrepBwd a{(const float*)dCt, (const float*)dBt, (const float*)dCe, (const __nv_bfloat16*)Ct, (const __nv_bfloat16*)Bt,
                (const float*)cum, (const float*)dqk, (const float*)theta, (float*)dCn, (float*)dBn, (float*)dCb, (float*)dBb,
                (float*)dtheta, (float*)dcum_ce, d};
-  ssd_prep_bwd_kernel<<<B * H * d.nC, 256, 16 * N * sizeof(float), (cudaStream_t)stream>>>(a);
+  ssd_prep_bwd_kernel<<<B * d.nC * 4, 256, 0, (cudaStream_t)stream>>>(a);
   return ssd_status();
 }
 

@@ -68,7 +68,7 @@ def _unchunks(t, B, L, H, Q):
 
 
 def supported(d: M3.Mamba3Dims, L: int, Q: int = 128) -> bool:
-    return L % Q == 0 and d.headdim % 8 == 0 and d.d_state % 8 == 0
+    return L % Q == 0 and d.headdim % 8 == 0 and d.d_state % 8 == 0 and d.d_state <= 128 and d.angles <= 128
 
 
 def ssd_fwd(x, z, Bn, Cn, dt, adt, trap, angle, Bb, Cb, D, d: M3.Mamba3Dims, B: int, L: int, Q: int = 128, gemm_dtype=None):
@@ -336,7 +336,7 @@ def ssd_bwd_cuda(s: SsdSavedCuda, proj: torch.Tensor, dy: torch.Tensor, dproj: t
     dCt = K.bgemm(dG, s.Bt, b_mn=True, out_dtype=torch.float32)
     K.bgemm(dG, s.Ct, a_mn=True, b_mn=True, out=dBt, accumulate=True)
     dqk = diag * s.gamma
-    dCn, dBn, dCb, dBb = z32(rows, Nn), z32(rows, Nn), z32(H, Nn), z32(H, Nn)
+    dCn, dBn, dCb, dBb = f32(rows, Nn), f32(rows, Nn), z32(H, Nn), z32(H, Nn)
     dtheta = f32(B, L, H, A) if A else None
     dcum_ce = f32(G, Q)
     K._launch(lib.oa_ssd_prep_bwd(dCt.data_ptr(), dBt.data_ptr(), dCe.data_ptr(), s.Ct.data_ptr(), s.Bt.data_ptr(), s.cum.data_ptr(),
