@@ -94,8 +94,8 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="oa_b200")
-    ap.add_argument("--model", default="gpt350m", choices=["gpt350m", "tiny", "mamba3", "mamba3-tiny", "moe"])
-    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--model", default="gpt350m", choices=["gpt350m", "tiny", "mamba3", "mamba3-tiny", "moe", "char"])
+    ap.add_argument("--micro-batch", type=int, default=0, help="sequences per GPU; 0 = the configuration's own (8 GPT, 4 Mamba-3 / MoE, 16 char LM)")
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"])
@@ -129,16 +129,21 @@ def main() -> int:
     from oa_b200.models import OaGptConfig, OaGptModel
     from oa_b200.runtime.engine import OaContextGetDefault, OaEngineConfig, OaInitComputeEngine
 
-    cfg_e = OaEngineConfig(Precision=OaPrecision.BF16, DeviceIndex=local_rank)
+    if args.micro_batch <= 0:
+        args.micro_batch = {"mamba3": 4, "moe": 4, "char": 16}.get(args.model, 8)
+    cfg_e = OaEngineConfig(Precision=OaPrecision.FP32 if args.model == "char" else OaPrecision.BF16, DeviceIndex=local_rank)
     assert OaInitComputeEngine(cfg_e)
     from oa_b200.models import OaMamba3Config, OaMamba3LmModel
     names = {"gpt350m": "dense GPT 24x1024, 16 heads, FFN 4096 GELU, RMSNorm, RoPE, vocab 32000", "tiny": "tiny",
              "mamba3": "Mamba-3 32x1536, state 128, expand 2, head dim 64, chunk 256, vocab 32000", "mamba3-tiny": "mamba3-tiny",
+             "char": "char-level Transformer LM, FP32: vocab 256, d 128, 4 layers, 4 heads, FFN 512 GELU, pre-LayerNorm, learned positions",
              "moe": "sparse MoE 16x2048, 64 experts top-2, SwiGLU 1408, 1 shared expert, vocab 32000 (single-GPU experts)"}
     if args.model in ("mamba3", "mamba3-tiny"):
         mcfg = OaMamba3Config.Mamba3_32x1536() if args.model == "mamba3" else OaMamba3Config(1024, 256, 2, 32, 2, 16, 256, 64)
     elif args.model == "moe":
         mcfg = OaGptConfig.Moe16x2048()
+    elif args.model == "char":
+        mcfg = OaGptConfig.CharLm()
     else:
         mcfg = OaGptConfig.Gpt350M() if args.model == "gpt350m" else OaGptConfig(1024, 256, 2, 4, 1024, 256, "rms", "gelu", 10000.0, False, 1e-5, 0.02)
     if args.seq:
@@ -245,7 +250,7 @@ def main() -> int:
     out = {
         "metric": "train tokens/s (device-timed, max over ranks)", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform token ids, random-init N(0,0.02) weights)",
+        "scaling": "weak", "vs_baseline": None, "dtype": "fp32" if args.model == "char" else "bf16", "data": "synthetic (uniform token ids, random-init N(0,0.02) weights)",
         "config": {"model": names[args.model],
                    "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}", "optimizer": "AdamW fp32 master",
                    "l2": "inputs larger than L2 (activations and weights >> 126 MB per step)",

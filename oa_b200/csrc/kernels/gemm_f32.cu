@@ -17,17 +17,24 @@ __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                 long long sam, long long sak, long long sbn, long long sbk, int ldc, long long batch_a,
                 long long batch_b, long long batch_c, const float* __restrict__ bias, int act, int accumulate,
-                float alpha) {
+                float alpha, int k_chunk) {
   __shared__ float sA[FK][FT + 1];
   __shared__ float sB[FK][FT + 1];
   const int b = blockIdx.z;
-  A += (long long)b * batch_a;
-  B += (long long)b * batch_b;
-  C += (long long)b * batch_c;
+  // k_chunk > 0: split-K mode - blockIdx.z is the K slice (batch 1) and C is the slice's own [M, ldc] partial buffer
+  const int k_lo = k_chunk > 0 ? b * k_chunk : 0;
+  const int k_hi = k_chunk > 0 ? min(K, k_lo + k_chunk) : K;
+  if (k_chunk > 0) {
+    C += (long long)b * batch_c;
+  } else {
+    A += (long long)b * batch_a;
+    B += (long long)b * batch_b;
+    C += (long long)b * batch_c;
+  }
   const int m0 = blockIdx.y * FT, n0 = blockIdx.x * FT;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4] = {};
-  for (int k0 = 0; k0 < K; k0 += FK) {
+  for (int k0 = k_lo; k0 < k_hi; k0 += FK) {
     // 64x16 elements per operand, 256 threads -> 4 loads each
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -36,11 +43,11 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
       // choose the faster-varying index to follow the contiguous dimension of each operand
       if (sak == 1) { kk = idx & 15; r = idx >> 4; } else { r = idx & 63; kk = idx >> 6; }
       int gm = m0 + r, gk = k0 + kk;
-      sA[kk][r] = (gm < M && gk < K) ? A[gm * sam + gk * sak] : 0.f;
+      sA[kk][r] = (gm < M && gk < k_hi) ? A[gm * sam + gk * sak] : 0.f;
       if (sbk == 1) { kk = idx & 15; r = idx >> 4; } else { r = idx & 63; kk = idx >> 6; }
       int gn = n0 + r;
       gk = k0 + kk;
-      sB[kk][r] = (gn < N && gk < K) ? B[gn * sbn + gk * sbk] : 0.f;
+      sB[kk][r] = (gn < N && gk < k_hi) ? B[gn * sbn + gk * sbk] : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -75,6 +82,36 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
   }
 }
 
+// C[m,n] = alpha * sum_s part[s][m,n] (+ C): fixed slice order, so the split-K result is reproducible
+__global__ void gemm_f32_splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ C, int M, int N, int ldc, int splits,
+                                              int accumulate, float alpha) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)M * N) return;
+  const int m = (int)(i / N), n = (int)(i % N);
+  float s = 0.f;
+  for (int k = 0; k < splits; ++k) s += part[((long long)k * M + m) * N + n];
+  float* c = C + (long long)m * ldc + n;
+  *c = accumulate ? *c + s * alpha : s * alpha;
+}
+
+// Scratch for split-K partials: allocated outside stream capture only, sizes rounded up to a power of two, and an outgrown
+// buffer is kept (a captured graph may still hold its address), so at most 64 + 32 + ... MB are ever held.
+static float* g_splitk_buf = nullptr;
+static size_t g_splitk_bytes = 0;
+
+static float* splitk_scratch(size_t bytes, cudaStream_t st) {
+  if (bytes <= g_splitk_bytes) return g_splitk_buf;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return nullptr;
+  if (bytes > (64u << 20)) return nullptr;
+  size_t cap = 1u << 20;
+  while (cap < bytes) cap <<= 1;
+  float* p = nullptr;
+  if (cudaMalloc(&p, cap) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  g_splitk_buf = p; g_splitk_bytes = cap;
+  return p;
+}
+
 }  // namespace oa
 
 extern "C" int oa_gemm_f32(const float* A, const float* B, float* C, int M, int N, int K, long long sam, long long sak,
@@ -83,7 +120,28 @@ extern "C" int oa_gemm_f32(const float* A, const float* B, float* C, int M, int 
   if (M <= 0 || N <= 0 || batch <= 0) return OA_OK;
   if (K < 0 || batch > 65535) return OA_ERR_ARG;
   dim3 grid((N + oa::FT - 1) / oa::FT, (M + oa::FT - 1) / oa::FT, batch);
-  oa::gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, B, C, M, N, K, sam, sak, sbn, sbk, ldc, batch_a, batch_b,
-                                                              batch_c, bias, act, accumulate, alpha);
+  cudaStream_t st = (cudaStream_t)stream;
+  // Few output tiles and a long reduction (weight gradients of small models): slice K over more CTAs, then reduce the slices
+  const int tiles = (int)(grid.x * grid.y);
+  if (batch == 1 && !bias && act == OA_ACT_NONE && tiles < 64 && K >= 512) {
+    int splits = (256 + tiles - 1) / tiles;
+    if (splits > K / 128) splits = K / 128;
+    if (splits > 64) splits = 64;
+    if (splits >= 2) {
+      const int k_chunk = (((K + splits - 1) / splits) + oa::FK - 1) / oa::FK * oa::FK;
+      splits = (K + k_chunk - 1) / k_chunk;
+      float* part = oa::splitk_scratch((size_t)splits * M * N * sizeof(float), st);
+      if (part && splits >= 2) {
+        grid.z = splits;
+        oa::gemm_f32_kernel<<<grid, 256, 0, st>>>(A, B, part, M, N, K, sam, sak, sbn, sbk, N, 0, 0, (long long)M * N, nullptr,
+                                                  OA_ACT_NONE, 0, 1.0f, k_chunk);
+        const long long n = (long long)M * N;
+        oa::gemm_f32_splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(part, C, M, N, ldc, splits, accumulate, alpha);
+        return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+      }
+    }
+  }
+  oa::gemm_f32_kernel<<<grid, 256, 0, st>>>(A, B, C, M, N, K, sam, sak, sbn, sbk, ldc, batch_a, batch_b, batch_c, bias, act,
+                                            accumulate, alpha, 0);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }

@@ -38,13 +38,13 @@ constexpr int XENT_THREADS = 256;
 template <typename T>
 __global__ void __launch_bounds__(XENT_THREADS)
 xent_kernel(const T* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss, T* dlogits,
-            int vocab, int ld, float grad_scale, int ignore_index) {
+            int vocab, int ld, float grad_scale, int ignore_index, int vec_ok) {
   constexpr int V = XIO<T>::VEC;
   __shared__ float red_m[XENT_THREADS / 32], red_s[XENT_THREADS / 32];
   const long long row = blockIdx.x;
   const T* p = logits + row * ld;
   const int tgt = targets[row];
-  const int nvec = vocab / V;
+  const int nvec = vec_ok ? vocab / V : 0;        // rows that do not start on a 16-byte boundary take the scalar loops
   const bool ignored = (tgt == ignore_index);
   const bool oor = !ignored && (tgt < 0 || tgt >= vocab);
   // read before any thread can overwrite the logits with the gradient (dlogits may alias logits)
@@ -130,12 +130,14 @@ using namespace oa;
 extern "C" int oa_xent_fwd_bwd(int dtype, const void* logits, const int* targets, float* row_loss, void* dlogits,
                                long long rows, int vocab, int ld, float grad_scale, int ignore_index, void* stream) {
   if (rows <= 0) return OA_OK;
-  if (ld % 8 || (reinterpret_cast<uintptr_t>(logits) & 15)) return OA_ERR_ALIGN;
+  const int es = dtype == OA_F32 ? 4 : 2;
+  const int vec_ok = ((long long)ld * es) % 16 == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0 &&
+                     (!dlogits || (reinterpret_cast<uintptr_t>(dlogits) & 15) == 0);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == OA_F32)
-    xent_kernel<float><<<(unsigned)rows, XENT_THREADS, 0, st>>>((const float*)logits, targets, row_loss, (float*)dlogits, vocab, ld, grad_scale, ignore_index);
+    xent_kernel<float><<<(unsigned)rows, XENT_THREADS, 0, st>>>((const float*)logits, targets, row_loss, (float*)dlogits, vocab, ld, grad_scale, ignore_index, vec_ok);
   else if (dtype == OA_BF16)
-    xent_kernel<__nv_bfloat16><<<(unsigned)rows, XENT_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets, row_loss, (__nv_bfloat16*)dlogits, vocab, ld, grad_scale, ignore_index);
+    xent_kernel<__nv_bfloat16><<<(unsigned)rows, XENT_THREADS, 0, st>>>((const __nv_bfloat16*)logits, targets, row_loss, (__nv_bfloat16*)dlogits, vocab, ld, grad_scale, ignore_index, vec_ok);
   else return OA_ERR_UNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }

@@ -143,7 +143,9 @@ class OaMoE(OaModule):
         normed = self.Norm.Forward(x)
         logits = self.Router.Forward(normed)
         sel_bias = self.RoutingBias.Tensor().reshape(-1) if self.BalanceGamma > 0 else None
-        if self.SparseExecution:
+        tn = normed.Tensor()
+        # the grouped tensor-core kernels are bf16; an fp32 model on the GPU takes the dense formulation (same function)
+        if self.SparseExecution and (not tn.is_cuda or tn.dtype == torch.bfloat16):
             out = _routed_experts(normed, logits, self.GateUpW.Data, self.GateUpB.Data if self.GateUpB else None, self.DownW.Data,
                                   self.DownB.Data if self.DownB else None, self.ExpertsPerToken, sel_bias, x, self)
         else:

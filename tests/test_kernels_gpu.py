@@ -307,3 +307,15 @@ def test_philox_dropout():
     assert torch.equal(x, y)
     d = K.dropout(torch.ones(100000, device=DEV), 0.25, 7, 0)
     assert 0.73 < (d > 0).float().mean().item() < 0.77
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_xent_rows_not_16_byte_aligned(dtype):
+    """A vocabulary of 27 (the character tokenizer) gives rows that start off a 16-byte boundary: the scalar loops run."""
+    torch.manual_seed(8)
+    x = _rand(96, 27, dtype=dtype, scale=2.0)
+    tg = torch.randint(0, 27, (96,), device=DEV)
+    loss, dl = K.xent_fwd_bwd(x, tg, grad_scale=1.0 / 96)
+    lossr, dlr = K.xent_fwd_bwd(x.cpu().float(), tg.cpu(), grad_scale=1.0 / 96)
+    _close(loss, lossr, 1e-2 if dtype == torch.bfloat16 else 1e-5, what="xent loss, vocab 27")
+    _close(dl, dlr, 2e-2 if dtype == torch.bfloat16 else 1e-6, what="xent grad, vocab 27")
