@@ -38,6 +38,7 @@ class OaDataParallel:
         self.world, self.rank = self.mesh.world, self.mesh.rank
         self.max_blocks = max_blocks
         self._sym: dict[int, object] = {}
+        self._summed: dict[int, torch.Tensor] = {}
         if mode == "fused":
             optimizer.SetArenaAllocator(self._alloc)
         optimizer._build()
@@ -47,13 +48,15 @@ class OaDataParallel:
         for a in self.arenas:
             dist.broadcast(a.flat, src=0, group=self.mesh.group)
         if mode == "fused":
-            for a in self.arenas:
-                if a.dtype != torch.bfloat16:
-                    raise ValueError("the fused data-parallel step needs bf16 parameters (fp32 masters are kept per shard)")
             self.ch_grads = self.mesh.NewChannel()
             self.ch_params = self.mesh.NewChannel()
             self._shards = []
             for i, a in enumerate(self.arenas):
+                if a.dtype != torch.bfloat16:
+                    # small fp32 arenas (biases, per-head scalars): replicated update - every rank sums all ranks' gradients
+                    # with peer loads and applies the same AdamW step; no sharding, no all-gather
+                    self._shards.append(None)
+                    continue
                 n = a.numel
                 assert n % (8 * self.world) == 0
                 sn = n // self.world
@@ -92,7 +95,22 @@ class OaDataParallel:
         K.optim_advance(opt._state)
         self.ch_grads.Signal()
         status = K.status_word(self.mesh.device)
-        for a, (lo, sn, master, m, v) in zip(self.arenas, self._shards):
+        replicated = [i for i, sh in enumerate(self._shards) if sh is None]
+        if replicated:
+            self.ch_grads.Wait()                       # every rank's gradients are complete
+            for i in replicated:
+                a = self.arenas[i]
+                ctx.Add("DpPeerReduceAdam")
+                gbuf = self._sym[a.grad.data_ptr()]
+                summed = self._summed.setdefault(i, torch.empty(a.numel, dtype=a.dtype, device=a.device))
+                N.check(lib.oa_peer_reduce(K.dt(a.grad), gbuf.ptr_array, summed.data_ptr(), 0, a.numel, self.world, 0, N.stream()),
+                        "oa_peer_reduce")
+                N.count_launch()
+                K.adam_step(a.flat, summed, a.master, opt._m[i], opt._v[i], opt._state, decoupled=opt.Decoupled)
+        for a, sh in zip(self.arenas, self._shards):
+            if sh is None:
+                continue
+            lo, sn, master, m, v = sh
             ctx.Add("DpReduceScatterAdamAllGather")
             gbuf, pbuf = self._sym[a.grad.data_ptr()], self._sym[a.flat.data_ptr()]
             N.check(lib.oa_dp_reduce_adam_gather(gbuf.ptr_array, pbuf.ptr_array, master.data_ptr(), m.data_ptr(), v.data_ptr(), lo, sn,
@@ -123,7 +141,12 @@ class OaDataParallel:
         st.Type = opt.TypeName
         st.Lr, st.Beta1, st.Beta2, st.Eps, st.WeightDecay, st.Step = opt.Lr_, opt.Beta1_, opt.Beta2_, opt.Eps_, opt.WeightDecay_, opt.Step_
         ms, vs = [], []
-        for a, (lo, sn, master, m, v) in zip(self.arenas, self._shards):
+        for i, (a, sh) in enumerate(zip(self.arenas, self._shards)):
+            if sh is None:
+                ms.append(a.gather(opt._m[i]))
+                vs.append(a.gather(opt._v[i]))
+                continue
+            lo, sn, master, m, v = sh
             ms.append(a.gather(self._gather_full(m, a.numel)))
             vs.append(a.gather(self._gather_full(v, a.numel)))
         st.AdamM, st.AdamV = np.concatenate(ms), np.concatenate(vs)
@@ -138,8 +161,13 @@ class OaDataParallel:
         s = oam.GetOptimizer()
         opt.Lr_, opt.Beta1_, opt.Beta2_, opt.Eps_, opt.WeightDecay_, opt.Step_ = s.Lr, s.Beta1, s.Beta2, s.Eps, s.WeightDecay, s.Step
         pos_m = pos_v = 0
-        for a, (lo, sn, master, m, v) in zip(self.arenas, self._shards):
+        for i, (a, sh) in enumerate(zip(self.arenas, self._shards)):
             full = torch.empty(a.numel, dtype=torch.float32, device=a.device)
+            if sh is None:
+                pos_m = a.scatter(opt._m[i], s.AdamM, pos_m)
+                pos_v = a.scatter(opt._v[i], s.AdamV, pos_v)
+                continue
+            lo, sn, master, m, v = sh
             pos_m = a.scatter(full, s.AdamM, pos_m)
             m.copy_(full[lo:lo + sn])
             pos_v = a.scatter(full, s.AdamV, pos_v)
