@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", choices=["ep", "tp"], required=True)
+    ap.add_argument("--mode", choices=["ep", "tp", "tp-decode"], required=True)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--accum", type=int, default=32)
@@ -51,6 +51,41 @@ def main() -> int:
     F.SetRngSeed(20260714)
     gen = torch.Generator().manual_seed(99 if args.mode == "tp" else 1234 + rank)   # TP ranks see the same batch
 
+    if args.mode == "tp-decode":
+        # batch-32 greedy decoding of 256 tokens after a 2048-token prompt, weights / KV cache / heads sharded over the ranks
+        from oa_b200.parallel.tp_model import OaTpGptModel
+        from oa_b200.serve.tp_decoder import OaTpGptDecoder
+        cfg = OaGptConfig.Llama7B()
+        if args.layers:
+            cfg.NLayers = args.layers
+        Bd, prompt_len, new = 32, 2048, 256
+        model = OaTpGptModel(cfg, mesh, 1)
+        dec = OaTpGptDecoder(model, Bd, prompt_len + new)
+        prompt = torch.randint(0, cfg.Vocab, (Bd, prompt_len), generator=gen, dtype=torch.int32).to(dev)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        dec.Generate(prompt[:, :256], 8)                       # warm-up
+        dist.barrier()
+        torch.cuda.synchronize()
+        ev[0].record()
+        logits = dec.Prefill(prompt)
+        ev[1].record()
+        for _ in range(new):
+            logits = dec.Step(logits.float().argmax(-1).to(torch.int32))
+        ev[2].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        K.check_status()
+        if rank == 0:
+            print(json.dumps({"metric": "greedy decode tokens/s (device-timed, max over ranks)", "value": Bd * new / (float(t[1]) / 1e3),
+                              "unit": "tokens/s", "n_gpus": world, "ms_per_token": float(t[1]) / new, "prefill_ms": float(t[0]),
+                              "prefill_tokens_per_s": Bd * prompt_len / (float(t[0]) / 1e3), "dtype": "bf16",
+                              "config": {"model": "7B-class Transformer 32x4096", "layers": cfg.NLayers, "batch": Bd, "prompt": prompt_len,
+                                         "new_tokens": new, "parallelism": f"tp{world}, one-shot all-reduce over peer memory"},
+                              "kv_cache_gib_per_gpu": round(dec.Cache.Bytes() / 2 ** 30, 2)}), flush=True)
+        mesh.Close()
+        dist.destroy_process_group()
+        return 0
     if args.mode == "ep":
         from oa_b200.parallel.dp import OaDataParallel
         from oa_b200.parallel.ep import OaExpertParallel

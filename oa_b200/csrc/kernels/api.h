@@ -313,6 +313,9 @@ int oa_dp_reduce_adam_gather(const void* const* grad_peers, const void* const* p
                              int* status, int max_blocks, void* stream);
 int oa_peer_reduce(int dtype, const void* const* in_peers, void* out, long long lo, long long n, int world, int op,
                    void* stream);
+int oa_peer_allreduce_oneshot(const void* const* slots_peers, const void* const* counters_peers, const void* src,
+                              const void* residual, void* out, void* sync2, long long n, long long slot_elems, int world,
+                              int rank, int max_ctas, int* status, void* stream);
 int oa_peer_push(const void* const* dst_peers, long long dst_off_bytes, const void* src, long long nbytes, int world,
                  void* stream);
 

@@ -167,6 +167,78 @@ __global__ void peer_push_kernel(PeerTable dst, long long dst_off_bytes, const v
   }
 }
 
+// ---- one-shot all-reduce for small bf16 messages (tensor-parallel decoding: a [batch, d_model] partial sum per GEMM)
+// ONE kernel: CTA c pushes its 2048-element range of `src` into slot `rank` of every rank's staging buffer, adds 1 to counter c
+// of every rank (release), waits until its own counter c shows all `world` pushes of this call (bounded), then sums the `world`
+// slots of its range in fp32 (+ residual) into `out`.  A CTA only ever waits for the same-index CTAs of the peers, never for a
+// CTA of its own grid, so no co-residency is assumed.  Two staging halves alternate by call parity: a rank can only start
+// call k+2 after every rank has pushed for call k+1, i.e. after every rank finished reading call k.  The call index lives
+// in device memory (sync[0] = calls completed, sync[1] = CTAs done in the current call, sync[2 + c] = calls in which CTA c
+// took part: messages of different sizes use different numbers of CTAs), so the kernel replays in a graph.
+struct ArParams {
+  PeerTable slots;        // every rank's staging buffer: [2 halves][world slots][slot_elems] bf16
+  PeerTable counters;     // every rank's counter array: u64 per CTA
+  const __nv_bfloat16* src;
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* out;
+  unsigned long long* sync;
+  int* status;
+  long long n, slot_elems;
+  int world, rank;
+};
+
+__global__ void __launch_bounds__(256) peer_allreduce_oneshot_kernel(ArParams p) {
+  __shared__ int s_ok;
+  const unsigned long long call = p.sync[0];
+  const long long half_off = (long long)(call & 1) * p.world * p.slot_elems;
+  const long long i0 = ((long long)blockIdx.x * 256 + threadIdx.x) * 8;
+  const bool live = i0 < p.n;                            // n is a multiple of 8
+  if (live) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p.src + i0);
+    for (int q = 0; q < p.world; ++q) {
+      const int r = (p.rank + q) % p.world;              // start with the own slot, spread the peers
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.slots.ptr[r]) + half_off + (long long)p.rank * p.slot_elems + i0) = v;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < p.world; ++r)
+      red_release_sys_add(reinterpret_cast<unsigned long long*>(p.counters.ptr[r]) + blockIdx.x, 1ull);
+    const unsigned long long seen = p.sync[2 + blockIdx.x];
+    const bool ok = wait_ge_sys(reinterpret_cast<const unsigned long long*>(p.counters.ptr[p.rank]) + blockIdx.x,
+                                (seen + 1) * (unsigned long long)p.world);
+    p.sync[2 + blockIdx.x] = seen + 1;
+    if (!ok) report_error(p.status, OA_KERR_WAIT_PEER);
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  if (live && s_ok) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    const __nv_bfloat16* mine = reinterpret_cast<const __nv_bfloat16*>(p.slots.ptr[p.rank]) + half_off + i0;
+    for (int r = 0; r < p.world; ++r) {
+      const uint4 v = ld_peer_v4(mine + (long long)r * p.slot_elems);     // peer-written data: read through L2
+      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    if (p.residual) {
+      const uint4 v = *reinterpret_cast<const uint4*>(p.residual + i0);
+      const float2 a = unpack_bf16x2(v.x), b = unpack_bf16x2(v.y), c = unpack_bf16x2(v.z), d = unpack_bf16x2(v.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+    *reinterpret_cast<uint4*>(p.out + i0) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned long long done = atomicAdd(&p.sync[1], 1ull) + 1ull;
+    if (done == gridDim.x) { p.sync[1] = 0ull; __threadfence(); p.sync[0] = call + 1ull; }
+  }
+}
+
 }  // namespace oa
 
 using namespace oa;
@@ -254,5 +326,22 @@ extern "C" int oa_peer_push(const void* const* dst_peers, long long dst_off_byte
   long long blocks = (nbytes / 16 + 255) / 256;
   if (blocks > 148 * 4) blocks = 148 * 4;
   peer_push_kernel<<<(int)blocks, 256, 0, ST>>>(make_table(dst_peers, world), dst_off_bytes, src, nbytes, world);
+  return CHECK_LAUNCH();
+}
+
+// out = sum over ranks of src (+ residual), n bf16 elements (multiple of 8, n <= slot_elems); see peer_allreduce_oneshot_kernel.
+extern "C" int oa_peer_allreduce_oneshot(const void* const* slots_peers, const void* const* counters_peers, const void* src,
+                                         const void* residual, void* out, void* sync2, long long n, long long slot_elems, int world,
+                                         int rank, int max_ctas, int* status, void* stream) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return OA_ERR_ARG;
+  if (n <= 0 || (n & 7) || n > slot_elems || (slot_elems & 7)) return OA_ERR_ALIGN;
+  const long long ctas = (n / 8 + 255) / 256;
+  if (ctas > max_ctas) return OA_ERR_ARG;
+  ArParams p;
+  p.slots = make_table(slots_peers, world);
+  p.counters = make_table(counters_peers, world);
+  p.src = (const __nv_bfloat16*)src; p.residual = (const __nv_bfloat16*)residual; p.out = (__nv_bfloat16*)out;
+  p.sync = (unsigned long long*)sync2; p.status = status; p.n = n; p.slot_elems = slot_elems; p.world = world; p.rank = rank;
+  peer_allreduce_oneshot_kernel<<<(int)ctas, 256, 0, ST>>>(p);
   return CHECK_LAUNCH();
 }

@@ -27,3 +27,7 @@ def test_expert_parallel_matches_single_device():
 
 def test_tensor_parallel_kernels_and_model():
     assert "TP_CHECK_OK" in _run("tp_check.py")
+
+
+def test_tensor_parallel_decoding():
+    assert "TP_DECODE_CHECK_OK" in _run("tp_decode_check.py")
