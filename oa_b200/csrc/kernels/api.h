@@ -74,7 +74,7 @@ int oa_fill(int dtype, void* y, long long n, float value, void* stream);
 int oa_swiglu_fwd(int dtype, const void* gate_up, void* out, long long rows, int F, void* stream);
 int oa_swiglu_bwd(int dtype, const void* gate_up, const void* dout, void* dgate_up, long long rows, int F, void* stream);
 int oa_rope(int dtype, void* x, long long rows, int row_stride, int n_heads, int head_dim, int seq_len, int pos_offset,
-            float theta, int backward, void* stream);
+            float theta, int backward, const int* pos_dev, void* stream);
 int oa_embedding_fwd(int dtype, const void* table, const int* ids, void* out, long long n_ids, int dim, int vocab,
                      const void* pos_table, int seq_len, void* stream);
 int oa_embedding_bwd(int dtype, const void* dout, const int* ids, float* dtable_f32, long long n_ids, int dim,
@@ -222,9 +222,9 @@ int oa_upsample_nearest(int dtype, const void* in, void* out, long long planes, 
 
 // ---- KV-cache serving (decode.cu)
 int oa_kv_append(const void* k_src, const void* v_src, long long src_stride, void* k_cache, void* v_cache, int batch,
-                 int s_new, int heads, int head_dim, int pos0, int max_seq, void* stream);
+                 int s_new, int heads, int head_dim, int pos0, int max_seq, const int* pos_dev, void* stream);
 int oa_decode_attn(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out, long long out_stride,
-                   int batch, int heads, int head_dim, int len, int max_seq, float scale, void* stream);
+                   int batch, int heads, int head_dim, int len, int max_seq, float scale, const int* pos_dev, void* stream);
 
 // ---- reinforcement learning (rl.cu): vector CartPole, GAE, rollout / replay storage, loss targets, categorical sampling
 int oa_rl_cartpole_reset(void* state, void* done, void* steps, void* episode, int envs, unsigned seed_lo, unsigned seed_hi,

@@ -12,8 +12,10 @@ namespace oa {
 
 __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_src, const __nv_bfloat16* __restrict__ v_src, long long src_stride,
                                  __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, int batch, int s_new, int heads, int hd,
-                                 int pos0, int max_seq) {
-  // one thread per 8 elements of one (token, head) row
+                                 int pos0, int max_seq, const int* __restrict__ pos_dev) {
+  // one thread per 8 elements of one (token, head) row; pos_dev (optional) adds a device-resident offset so that a decode
+  // step captured in a CUDA graph advances without host-side parameters
+  if (pos_dev) pos0 += *pos_dev;
   const int vec = hd >> 3;
   const long long total = (long long)batch * s_new * heads * vec;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -23,6 +25,7 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_src, const 
     const int s = (int)(r % s_new);
     const int b = (int)(r / s_new);
     const long long src = ((long long)b * s_new + s) * src_stride + h * hd + v * 8;
+    if (pos0 + s >= max_seq) continue;           // a full cache drops the token (the host checks capacity before replaying)
     const long long dst = (((long long)b * heads + h) * max_seq + pos0 + s) * hd + v * 8;
     *reinterpret_cast<uint4*>(kc + dst) = *reinterpret_cast<const uint4*>(k_src + src);
     *reinterpret_cast<uint4*>(vc + dst) = *reinterpret_cast<const uint4*>(v_src + src);
@@ -33,7 +36,8 @@ template <int HD>
 __global__ void __launch_bounds__(128)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ kc,
                    const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out, long long out_stride, int heads, int len,
-                   int max_seq, float scale_log2) {
+                   int max_seq, float scale_log2, const int* __restrict__ pos_dev) {
+  if (pos_dev) len = min(len + *pos_dev, max_seq);
   constexpr int PER = HD / 32;                  // head-dim elements per lane in the p.v phase
   __shared__ float s_q[HD];
   __shared__ float s_m[4], s_l[4];
@@ -113,21 +117,22 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long q_stride, cons
 using namespace oa;
 
 extern "C" int oa_kv_append(const void* k_src, const void* v_src, long long src_stride, void* k_cache, void* v_cache, int batch,
-                            int s_new, int heads, int head_dim, int pos0, int max_seq, void* stream) {
+                            int s_new, int heads, int head_dim, int pos0, int max_seq, const int* pos_dev, void* stream) {
   if (head_dim % 8 || src_stride % 8) return OA_ERR_ALIGN;
-  if (pos0 < 0 || pos0 + s_new > max_seq) return OA_ERR_ARG;
+  if (pos0 < 0 || (!pos_dev && pos0 + s_new > max_seq)) return OA_ERR_ARG;
   if (batch <= 0 || s_new <= 0) return OA_OK;
   const long long total = (long long)batch * s_new * heads * (head_dim / 8);
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   kv_append_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, src_stride,
                                                                  (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, batch, s_new, heads,
-                                                                 head_dim, pos0, max_seq);
+                                                                 head_dim, pos0, max_seq, pos_dev);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
 extern "C" int oa_decode_attn(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out, long long out_stride,
-                              int batch, int heads, int head_dim, int len, int max_seq, float scale, void* stream) {
+                              int batch, int heads, int head_dim, int len, int max_seq, float scale, const int* pos_dev,
+                              void* stream) {
   if (len <= 0 || len > max_seq) return OA_ERR_ARG;
   if (batch <= 0) return OA_OK;
   const float sl2 = scale * 1.4426950408889634f;
@@ -135,10 +140,10 @@ extern "C" int oa_decode_attn(const void* q, long long q_stride, const void* k_c
   const int grid = batch * heads;
   if (head_dim == 128)
     decode_attn_kernel<128><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                                                  (__nv_bfloat16*)out, out_stride, heads, len, max_seq, sl2);
+                                                  (__nv_bfloat16*)out, out_stride, heads, len, max_seq, sl2, pos_dev);
   else if (head_dim == 64)
     decode_attn_kernel<64><<<grid, 128, 0, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                                                 (__nv_bfloat16*)out, out_stride, heads, len, max_seq, sl2);
+                                                 (__nv_bfloat16*)out, out_stride, heads, len, max_seq, sl2, pos_dev);
   else return OA_ERR_UNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }

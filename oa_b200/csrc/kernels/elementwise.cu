@@ -212,7 +212,8 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ gu, const T* __restrict_
 // `backward` applies the inverse rotation (the transpose of the forward one).
 template <typename T>
 __global__ void rope_kernel(T* x, long long rows, int row_stride, int n_heads, int hd, int seq_len, int pos_offset,
-                            float theta, int backward) {
+                            float theta, int backward, const int* __restrict__ pos_dev) {
+  if (pos_dev) pos_offset += *pos_dev;           // device-resident position (graph-replayed decode steps)
   int half = hd / 2;
   long long total = rows * n_heads * half;
   long long stride = (long long)gridDim.x * blockDim.x;
@@ -237,7 +238,8 @@ __global__ void rope_kernel(T* x, long long rows, int row_stride, int n_heads, i
 // them to every head of the row with 16-byte accesses (the angle depends on the position and on j only).
 __global__ void __launch_bounds__(256)
 rope_bf16_vec_kernel(__nv_bfloat16* x, long long rows, int row_stride, int n_heads, int hd, int seq_len, int pos_offset, float theta,
-                     int backward) {
+                     int backward, const int* __restrict__ pos_dev) {
+  if (pos_dev) pos_offset += *pos_dev;
   const int half = hd >> 1, jv = half >> 3;                 // 8-wide vectors per half head
   const long long total = rows * jv;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -573,15 +575,15 @@ extern "C" int oa_swiglu_bwd(int dtype, const void* gu, const void* dout, void* 
   return CHECK_LAUNCH();
 }
 extern "C" int oa_rope(int dtype, void* x, long long rows, int row_stride, int n_heads, int head_dim, int seq_len,
-                       int pos_offset, float theta, int backward, void* stream) {
+                       int pos_offset, float theta, int backward, const int* pos_dev, void* stream) {
   if (head_dim % 2) return OA_ERR_ARG;
   if (dtype == OA_BF16 && head_dim % 16 == 0 && row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
     rope_bf16_vec_kernel<<<grid_for(rows * (head_dim / 16), 256), 256, 0, ST>>>((__nv_bfloat16*)x, rows, row_stride, n_heads, head_dim,
-                                                                                 seq_len, pos_offset, theta, backward);
+                                                                                 seq_len, pos_offset, theta, backward, pos_dev);
     return CHECK_LAUNCH();
   }
   DISPATCH_T(dtype, rope_kernel<T><<<grid_for(rows * n_heads * head_dim / 2, 256), 256, 0, ST>>>(
-                        (T*)x, rows, row_stride, n_heads, head_dim, seq_len, pos_offset, theta, backward));
+                        (T*)x, rows, row_stride, n_heads, head_dim, seq_len, pos_offset, theta, backward, pos_dev));
   return CHECK_LAUNCH();
 }
 extern "C" int oa_embedding_fwd(int dtype, const void* table, const int* ids, void* out, long long n_ids, int dim,

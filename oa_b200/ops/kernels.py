@@ -375,10 +375,13 @@ def swiglu_bwd(gate_up: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
 
 
 def rope_(x: torch.Tensor, n_heads: int, head_dim: int, seq_len: int, *, pos_offset: int = 0, theta: float = 10000.0,
-          backward: bool = False) -> torch.Tensor:
-    """In-place rotate-half RoPE on a [rows, >= n_heads*head_dim] view (row stride may exceed the width)."""
+          backward: bool = False, pos_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """In-place rotate-half RoPE on a [rows, >= n_heads*head_dim] view (row stride may exceed the width).  `pos_dev`
+    (int32 [1] on the device) is added to pos_offset inside the kernel: decode steps replayed from a CUDA graph."""
     rows = x.shape[0]
     if not x.is_cuda:
+        if pos_dev is not None:
+            pos_offset += int(pos_dev.item())
         half = head_dim // 2
         pos = (torch.arange(rows) % seq_len + pos_offset).float()
         freq = theta ** (-2.0 * torch.arange(half).float() / head_dim)
@@ -394,7 +397,7 @@ def rope_(x: torch.Tensor, n_heads: int, head_dim: int, seq_len: int, *, pos_off
         return x
     assert x.stride(1) == 1
     _launch(N.require().oa_rope(dt(x), x.data_ptr(), rows, x.stride(0), n_heads, head_dim, seq_len, pos_offset, float(theta),
-                                int(backward), N.stream()), "oa_rope")
+                                int(backward), N.ptr(pos_dev), N.stream()), "oa_rope")
     return x
 
 
@@ -896,25 +899,30 @@ def rnn_scan_bwd(gates_i, w_hh, b_hh, hprev, dout, gates: int):
 
 # ---------------------------------------------------------------- KV-cache serving
 def kv_append(k_src: torch.Tensor, v_src: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: int, s_new: int,
-              pos0: int) -> None:
+              pos0: int, pos_dev: Optional[torch.Tensor] = None) -> None:
     """Copies new key / value rows ([batch*s_new, heads*head_dim] views, row stride allowed) into the caches
     [batch, heads, max_seq, head_dim] at positions pos0 .. pos0 + s_new."""
     _, heads, max_seq, hd = k_cache.shape
     if not k_cache.is_cuda:
+        if pos_dev is not None:
+            pos0 += int(pos_dev.item())
         for src, dst in ((k_src, k_cache), (v_src, v_cache)):
             dst[:, :, pos0:pos0 + s_new] = src.reshape(batch, s_new, heads, hd).permute(0, 2, 1, 3).to(dst.dtype)
         return
     assert k_src.stride(1) == 1 and k_src.stride(0) == v_src.stride(0) and k_cache.dtype == torch.bfloat16
     _launch(N.require().oa_kv_append(k_src.data_ptr(), v_src.data_ptr(), k_src.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), batch, s_new,
-                                     heads, hd, pos0, max_seq, N.stream()), "oa_kv_append")
+                                     heads, hd, pos0, max_seq, N.ptr(pos_dev), N.stream()), "oa_kv_append")
 
 
-def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, length: int, scale: Optional[float] = None) -> torch.Tensor:
+def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, length: int, scale: Optional[float] = None,
+                pos_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One query token per sequence, q [batch, heads*head_dim] (row stride allowed), against the first `length` cached
     positions; returns [batch, heads*head_dim]."""
     batch, heads, max_seq, hd = k_cache.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
     if not q.is_cuda:
+        if pos_dev is not None:
+            length += int(pos_dev.item())
         qf = q.float().reshape(batch, heads, 1, hd)
         kf, vf = k_cache[:, :, :length].float(), v_cache[:, :, :length].float()
         p = torch.softmax((qf @ kf.transpose(-1, -2)) * scale, -1)
@@ -922,5 +930,5 @@ def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, l
     out = torch.empty((batch, heads * hd), dtype=q.dtype, device=q.device)
     assert q.stride(1) == 1 and q.dtype == torch.bfloat16
     _launch(N.require().oa_decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0), batch,
-                                       heads, hd, length, max_seq, float(scale), N.stream()), "oa_decode_attn")
+                                       heads, hd, length, max_seq, float(scale), N.ptr(pos_dev), N.stream()), "oa_decode_attn")
     return out

@@ -49,19 +49,48 @@ def _skinny_linear(x: OaMatrix, w: OaMatrix, residual: Optional[OaMatrix] = None
     return OaMatrix(y)
 
 
+class _GraphedStep:
+    """One decode step captured in a CUDA graph.  The position lives on the device (`pos`, int32 [1]): RoPE, the cache
+    append and the attention length read it inside their kernels and the graph's last node adds one, so replaying needs no
+    host-side parameter.  `ids` is the static input, the captured function's result the static output."""
+
+    def __init__(self, device, batch: int):
+        self.pos = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ids = torch.zeros((batch, 1), dtype=torch.int32, device=device)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.out = None
+
+    def run(self, ids: torch.Tensor, fn):
+        self.ids.copy_(ids.reshape(self.ids.shape))
+        if self.graph is None:
+            fn(self.ids)                              # eager once: lazily created buffers (workspaces) exist before the capture
+            self.pos.sub_(1)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                self.out = fn(self.ids)
+            self.graph = g
+        self.graph.replay()
+        return self.out
+
+
 class OaGptDecoder:
-    def __init__(self, model: OaGptModel, batch: int, max_seq: int):
+    def __init__(self, model: OaGptModel, batch: int, max_seq: int, use_graph: bool = True):
         self.Model, self.Cfg = model, model.Cfg
         c = self.Cfg
         w = model.Embed.Weight.Tensor()
         self.Cache = OaKvCache(c.NLayers, batch, c.NHeads, max_seq, c.DModel // c.NHeads, w.dtype, w.device)
+        self._graphed = _GraphedStep(w.device, batch) if use_graph and w.is_cuda and w.dtype == torch.bfloat16 else None
+        self._pos_dev: Optional[torch.Tensor] = None      # set while a graphed step records / replays
 
     # ---- one block on new tokens
     def _block(self, i: int, x: OaMatrix, batch: int, s_new: int) -> OaMatrix:
         b = self.Model.Blocks[i]
         a = b.Attention
         H, hd, D = a.NumHeads, a.HeadDim, a.DModel
-        pos0 = self.Cache.Length
+        pos0, pd = self.Cache.Length, self._pos_dev
+        if pd is not None:
+            pos0 = 0                                  # the device-resident position carries the offset
         h = b.LnAttn.Forward(x)
         qw, kw, vw = a.QProj.Weight.Tensor(), a.KProj.Weight.Tensor(), a.VProj.Weight.Tensor()
         step = D * D * qw.element_size()
@@ -81,9 +110,9 @@ class OaGptDecoder:
             K.kv_append(t[:, D:2 * D], t[:, 2 * D:], self.Cache.K[i], self.Cache.V[i], batch, s_new, 0)
         else:
             if a.RopeTheta > 0:
-                K.rope_(t[:, : 2 * D], 2 * H, hd, 1, pos_offset=pos0, theta=a.RopeTheta)
-            K.kv_append(t[:, D:2 * D], t[:, 2 * D:], self.Cache.K[i], self.Cache.V[i], batch, 1, pos0)
-            attn = OaMatrix(K.decode_attn(t[:, :D], self.Cache.K[i], self.Cache.V[i], pos0 + 1))
+                K.rope_(t[:, : 2 * D], 2 * H, hd, 1, pos_offset=pos0, theta=a.RopeTheta, pos_dev=pd)
+            K.kv_append(t[:, D:2 * D], t[:, 2 * D:], self.Cache.K[i], self.Cache.V[i], batch, 1, pos0, pos_dev=pd)
+            attn = OaMatrix(K.decode_attn(t[:, :D], self.Cache.K[i], self.Cache.V[i], pos0 + 1, pos_dev=pd))
         o = a.OutProj
         if s_new == 1 and o.Bias is None:
             x = _skinny_linear(attn, o.Weight.Data, residual=x)
@@ -122,10 +151,33 @@ class OaGptDecoder:
 
     def Prefill(self, prompt: torch.Tensor) -> torch.Tensor:
         self.Cache.Reset()
-        return self._forward(prompt)
+        out = self._forward(prompt)
+        if self._graphed is not None:
+            self._graphed.pos.fill_(self.Cache.Length)
+        return out
+
+    def _graph_body(self, ids: torch.Tensor) -> torch.Tensor:
+        self._pos_dev = self._graphed.pos
+        try:
+            length = self.Cache.Length
+            out = self._forward(ids)
+            self.Cache.Length = length                  # the host-side length advances once per Step, not per recording
+            self._graphed.pos.add_(1)
+            return out
+        finally:
+            self._pos_dev = None
 
     def Step(self, ids: torch.Tensor) -> torch.Tensor:
-        return self._forward(ids.reshape(-1, 1))
+        """One token per sequence.  On CUDA (bf16, learned-position-free models) the step replays a captured graph; the
+        returned logits tensor is then the graph's static output and is overwritten by the next Step."""
+        g = self._graphed
+        if g is None or self.Model.PosEmbed is not None or ids.numel() != g.ids.numel():
+            return self._forward(ids.reshape(-1, 1))
+        if self.Cache.Length + 1 > self.Cache.MaxSeq:
+            raise ValueError("KV cache is full")
+        out = g.run(ids, self._graph_body)
+        self.Cache.Length += 1
+        return out
 
     def Generate(self, prompt: torch.Tensor, new_tokens: int) -> torch.Tensor:
         """Greedy decoding: prompt [B, S] int32 -> [B, S + new_tokens]."""

@@ -22,7 +22,7 @@ from ..ml import autograd as AG
 from ..ops import kernels as K
 from ..parallel.mesh import OaDeviceMesh
 from ..parallel.tp_model import OaTpGptModel
-from .decoder import OaKvCache, _skinny_linear
+from .decoder import OaKvCache, _GraphedStep, _skinny_linear
 
 
 class OaOneShotAllReduce:
@@ -54,13 +54,16 @@ class OaOneShotAllReduce:
 
 
 class OaTpGptDecoder:
-    def __init__(self, model: OaTpGptModel, batch: int, max_seq: int):
+    def __init__(self, model: OaTpGptModel, batch: int, max_seq: int, use_graph: bool = True):
         self.Model, self.Cfg, self.Mesh = model, model.Cfg, model.Mesh
         c, W = self.Cfg, model.Mesh.world
         self.HeadsLocal, self.HeadDim = c.NHeads // W, c.DModel // c.NHeads
         w = model.Embed.Data.Tensor()
         self.Cache = OaKvCache(c.NLayers, batch, self.HeadsLocal, max_seq, self.HeadDim, w.dtype, w.device)
         self.AllReduce = OaOneShotAllReduce(model.Mesh, batch * c.DModel) if W > 1 and batch * c.DModel <= 131072 else None
+        # the decode step replays as a CUDA graph when its all-reduces are the graph-safe one-shot kernels
+        self._graphed = _GraphedStep(w.device, batch) if use_graph and w.is_cuda and (W == 1 or self.AllReduce is not None) else None
+        self._pos_dev: Optional[torch.Tensor] = None
 
     def _reduce(self, partial: torch.Tensor, residual: torch.Tensor, small: bool) -> OaMatrix:
         if self.Mesh.world == 1:
@@ -74,7 +77,9 @@ class OaTpGptDecoder:
         b = self.Model.Blocks[i]
         Hl, hd = self.HeadsLocal, self.HeadDim
         Dl = Hl * hd
-        pos0 = self.Cache.Length
+        pos0, pd = self.Cache.Length, self._pos_dev
+        if pd is not None:
+            pos0 = 0
         small = s_new == 1
         lin = _skinny_linear if small else (lambda a, w_: F.Linear(a, w_, None))
         h = b.LnAttn.Forward(x)
@@ -85,9 +90,9 @@ class OaTpGptDecoder:
             attn = F.FlashAttentionPacked(qkv, batch, s_new, Hl, hd, causal=True, rope_theta=self.Cfg.RopeTheta)
             K.kv_append(t[:, Dl:2 * Dl], t[:, 2 * Dl:], self.Cache.K[i], self.Cache.V[i], batch, s_new, 0)
         else:
-            K.rope_(t[:, : 2 * Dl], 2 * Hl, hd, 1, pos_offset=pos0, theta=self.Cfg.RopeTheta)
-            K.kv_append(t[:, Dl:2 * Dl], t[:, 2 * Dl:], self.Cache.K[i], self.Cache.V[i], batch, 1, pos0)
-            attn = OaMatrix(K.decode_attn(t[:, :Dl], self.Cache.K[i], self.Cache.V[i], pos0 + 1))
+            K.rope_(t[:, : 2 * Dl], 2 * Hl, hd, 1, pos_offset=pos0, theta=self.Cfg.RopeTheta, pos_dev=pd)
+            K.kv_append(t[:, Dl:2 * Dl], t[:, 2 * Dl:], self.Cache.K[i], self.Cache.V[i], batch, 1, pos0, pos_dev=pd)
+            attn = OaMatrix(K.decode_attn(t[:, :Dl], self.Cache.K[i], self.Cache.V[i], pos0 + 1, pos_dev=pd))
         x = self._reduce(F._c(lin(attn, b.Out.Data).Tensor()), x.Tensor(), small)
         h = b.LnFfn.Forward(x)
         up = lin(h, b.Up.Data)
@@ -96,6 +101,18 @@ class OaTpGptDecoder:
 
     def _forward(self, ids: torch.Tensor) -> torch.Tensor:
         """ids [B, s_new] int32 (the same on every rank) -> logits of the last new position [B, vocab] (gathered)."""
+        return self._gather(self._forward_local(ids), ids.shape[0])
+
+    def _gather(self, local: torch.Tensor, batch: int) -> torch.Tensor:
+        W = self.Mesh.world
+        if W == 1:
+            return local
+        parts = torch.empty((W,) + tuple(local.shape), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(parts, local, group=self.Mesh.group)
+        return parts.permute(1, 0, 2).reshape(batch, -1)
+
+    def _forward_local(self, ids: torch.Tensor) -> torch.Tensor:
+        """This rank's vocabulary shard of the logits [B, vocab / W]."""
         m = self.Model
         batch, s_new = ids.shape
         if self.Cache.Length + s_new > self.Cache.MaxSeq:
@@ -107,20 +124,35 @@ class OaTpGptDecoder:
             self.Cache.Length += s_new
             last = x.Tensor().reshape(batch, s_new, -1)[:, -1].contiguous() if s_new > 1 else x.Tensor()
             h = m.LnFinal.Forward(OaMatrix(last))
-            local = (_skinny_linear(h, m.Head.Data) if s_new == 1 else F.Linear(h, m.Head.Data, None)).Tensor().contiguous()
-            W = self.Mesh.world
-            if W == 1:
-                return local
-            parts = torch.empty((W,) + tuple(local.shape), dtype=local.dtype, device=local.device)
-            dist.all_gather_into_tensor(parts, local, group=self.Mesh.group)
-            return parts.permute(1, 0, 2).reshape(batch, -1)
+            return (_skinny_linear(h, m.Head.Data) if s_new == 1 else F.Linear(h, m.Head.Data, None)).Tensor().contiguous()
 
     def Prefill(self, prompt: torch.Tensor) -> torch.Tensor:
         self.Cache.Reset()
-        return self._forward(prompt)
+        out = self._forward(prompt)
+        if self._graphed is not None:
+            self._graphed.pos.fill_(self.Cache.Length)
+        return out
+
+    def _graph_body(self, ids: torch.Tensor) -> torch.Tensor:
+        self._pos_dev = self._graphed.pos
+        try:
+            length = self.Cache.Length
+            out = self._forward_local(ids)
+            self.Cache.Length = length
+            self._graphed.pos.add_(1)
+            return out
+        finally:
+            self._pos_dev = None
 
     def Step(self, ids: torch.Tensor) -> torch.Tensor:
-        return self._forward(ids.reshape(-1, 1))
+        g = self._graphed
+        if g is None or ids.numel() != g.ids.numel():
+            return self._forward(ids.reshape(-1, 1))
+        if self.Cache.Length + 1 > self.Cache.MaxSeq:
+            raise ValueError("KV cache is full")
+        local = g.run(ids, self._graph_body)            # the captured step ends at the local logits; the gather runs eagerly
+        self.Cache.Length += 1
+        return self._gather(local, g.ids.shape[0])
 
     def Generate(self, prompt: torch.Tensor, new_tokens: int) -> torch.Tensor:
         """Greedy decoding: prompt [B, S] int32 -> [B, S + new_tokens] (identical on every rank)."""
