@@ -116,6 +116,8 @@ OaFnLoss.__all__ = OaFnLoss.__all__ + ("PpoClippedPolicy", "PpoClippedPolicyBwd"
 OaFnRl = _namespace("OaFnRl", "Advantage estimation, policy distributions, transforms and evaluation.", _RL.OaFnRl,
                     ["Gae", "GaeInto", "NormalizeAdvantages", "SampleCategoricalPolicy", "EvaluateCategoricalPolicy", "SampleTanhNormalPolicy",
                      "EvaluateTanhNormalPolicy", "NormalizeObservation", "ScaleAction", "ClipReward", "SampleLogits", "EvaluateCategorical"])
+from oa_b200.core.registry import (OaDifferentiation, OaEffects, OaKernelInfo, OaKernelRegistry, OaLowering, OaOperationContract,
+                                   OaOperationKind, OaOperationRegistry)
 from oa_b200.crypto import fn_hash as _FH
 from oa_b200.audio import fn_audio as _FA
 from oa_b200.audio.fn_audio import (OaAudio, OaChannelLayout, OaChannelsForLayout, OaLayoutForChannels, OaMelConfig, OaMfccConfig,

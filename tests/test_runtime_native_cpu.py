@@ -130,3 +130,25 @@ def test_plan_cache_elects_by_median_and_persists(tmp_path):
     assert not st and st.code.name == "DataLoss" and e.Size() == 0
     assert not e.Load(str(tmp_path / "missing.bin"))
     assert c.Stats()[0] >= 1
+
+
+def test_kernel_registry_and_operation_contracts():
+    from oa_b200.core import registry as R
+    assert R.Fnv1a("") == 0xCBF29CE484222325 and R.Fnv1a("a") == 0xAF63DC4C8601EC8C          # FNV-1a 64 test vectors
+    ks = R.OaKernelRegistry.All()
+    assert len(ks) > 100 and len({k.Id for k in ks}) == len(ks) and len({k.Name for k in ks}) == len(ks)
+    g = R.OaKernelRegistry.Find("oa_gemm_bf16_batched")
+    assert g is not None and g.Provider == "gemm_tcgen05.cu" and R.OaKernelRegistry.FindById(g.Id).Name == g.Name
+    same_cat = [k for k in ks if k.Category == g.Category]
+    assert all(k.Id >> 16 == g.Id >> 16 for k in same_cat) and sorted(k.Id & 0xFFFF for k in same_cat) == list(range(len(same_cat)))
+    assert R.OaKernelRegistry.Find("oa_rl_gae").Provider == "rl.cu" and R.OaKernelRegistry.Find("nope") is None
+    ops = R.OaOperationRegistry.All()
+    assert len(ops) > 80
+    lin = R.OaOperationRegistry.Find("Linear")
+    assert lin.Kind == R.OaOperationKind.Gemm and lin.Differentiation == R.OaDifferentiation.Analytic and lin.Lowering == R.OaLowering.Gemm
+    assert lin.Hash == R.Fnv1a("Linear") and R.OaOperationRegistry.FindByHash(lin.Hash).Name == "Linear"
+    assert R.OaOperationRegistry.Find("Zeros").Differentiation == R.OaDifferentiation.NoGradient
+    assert R.OaOperationRegistry.Find("AddInPlace").Effects == R.OaEffects.MutatesInput
+    assert R.OaOperationRegistry.Find("Dropout").Effects == R.OaEffects.Random
+    assert R.OaOperationRegistry.Find("Loss.CrossEntropy").Kind == R.OaOperationKind.Loss
+    assert R.OaOperationRegistry.Find("Tanh").Differentiation == R.OaDifferentiation.Analytic
