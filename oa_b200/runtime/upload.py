@@ -6,7 +6,7 @@ is reused only after its copy finished (the ring blocks on the slot's own event,
 stream waits on the token, not the host.  `OaPrefetcher` wraps a batch iterator and keeps `depth` batches in flight."""
 from __future__ import annotations
 
-from typing import Iterable, Iterator, Optional
+from typing import Iterable, Iterator, List, Optional, Sequence
 
 import torch
 
@@ -36,6 +36,7 @@ class OaUploadRing:
         self._events = [None] * self.Slots
         self._stream = torch.cuda.Stream(self.Device) if self.Cuda else None
         self._next = 0
+        self._batch_host, self._batch_events, self._batch_next = [None, None], [None, None], 0
         self.BytesUploaded = 0
 
     def Upload(self, host: torch.Tensor, out: Optional[torch.Tensor] = None):
@@ -64,8 +65,53 @@ class OaUploadRing:
         self._events[i] = ev
         return dst, OaCompletionToken(ev)
 
+    def UploadMany(self, hosts: Sequence[torch.Tensor]):
+        """Uploads a batch of small host tensors with one packed copy per dtype: the tensors are concatenated into a
+        pinned staging buffer (double-buffered, grow-only), cross the bus as a single transfer, and come back as views of
+        one device allocation.  Returns (list of device tensors in input order, OaCompletionToken).  Many 4 KiB uploads
+        cost one launch of the copy engine this way instead of one each."""
+        if not hosts:
+            return [], OaCompletionToken()
+        groups = {}
+        for i, h in enumerate(hosts):
+            groups.setdefault(h.dtype, []).append(i)
+        outs: List[Optional[torch.Tensor]] = [None] * len(hosts)
+        ev = None
+        for dt, ids in groups.items():
+            flat = [hosts[i].reshape(-1) for i in ids]
+            counts = [f.numel() for f in flat]
+            total = sum(counts)
+            nbytes = total * flat[0].element_size()
+            stage = self._batch_stage(nbytes)[:nbytes].view(dt)
+            torch.cat(flat, out=stage)
+            self.BytesUploaded += nbytes
+            if self.Cuda:
+                dev = torch.empty(total, dtype=dt, device=self.Device)
+                with torch.cuda.stream(self._stream):
+                    dev.copy_(stage, non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(self._stream)
+                dev.record_stream(self._stream)
+                self._batch_events[self._batch_next ^ 1] = ev
+            else:
+                dev = stage.clone()
+            for i, piece in zip(ids, dev.split_with_sizes(counts)):
+                outs[i] = piece if hosts[i].dim() == 1 else piece.view(hosts[i].shape)
+        return outs, OaCompletionToken(ev)
+
+    def _batch_stage(self, nbytes: int) -> torch.Tensor:
+        i = self._batch_next
+        self._batch_next = i ^ 1
+        if self._batch_events[i] is not None:
+            self._batch_events[i].synchronize()               # the previous transfer out of this buffer has left the host
+            self._batch_events[i] = None
+        if self._batch_host[i] is None or self._batch_host[i].numel() < nbytes:
+            cap = 1 << max(12, (nbytes - 1).bit_length())
+            self._batch_host[i] = torch.empty(cap, dtype=torch.uint8, pin_memory=self.Cuda)
+        return self._batch_host[i]
+
     def Synchronize(self) -> None:
-        for ev in self._events:
+        for ev in list(self._events) + list(self._batch_events):
             if ev is not None:
                 ev.synchronize()
 

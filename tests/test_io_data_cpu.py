@@ -111,6 +111,13 @@ def test_upload_ring_and_prefetcher():
     assert ring.BytesUploaded == 5 * (4 * 8 * 4 + 4 * 4)
     with pytest.raises(ValueError):
         ring.Upload(torch.zeros(1 << 20))
+    # batched form: mixed dtypes and shapes, one packed transfer per dtype, staging buffers reused across calls
+    hosts = [torch.randn(5), torch.arange(6).reshape(2, 3), torch.randn(2, 2), torch.arange(3)]
+    for _ in range(3):
+        outs, tok = ring.UploadMany(hosts)
+        tok.Wait()
+        assert all(o.dtype == h.dtype and o.shape == h.shape and torch.equal(o, h) for o, h in zip(outs, hosts))
+    assert ring.UploadMany([])[0] == []
 
 
 def test_ml_training_with_gradient_accumulation():
