@@ -107,6 +107,31 @@ def bench_bw():
     emit(op="adamw_step", n=n, ms=t, gbs=n * 28 / t / 1e6)
 
 
+def bench_image():
+    """Image kernels on a batch of 8 RGB 1080p frames (199 MB, larger than L2): algorithmic bytes = one read + one write."""
+    from oa_b200.core.matrix import OaMatrix
+    from oa_b200.vision import fn_detection as D
+    from oa_b200.vision import fn_image as I
+    x = OaMatrix(torch.rand(8, 3, 1080, 1920, device="cuda"))
+    nbytes = x.Tensor().numel() * 4
+    k7 = OaMatrix(torch.rand(7, 7, device="cuda"))
+    cases = {"brightness_contrast": lambda: I.BrightnessContrast(x, 0.1, 1.2), "gaussian_blur_sigma2 (13 taps, separable)": lambda: I.GaussianBlur(x, 2.0),
+             "convolve2d_7x7": lambda: I.Convolve2d(x, k7), "erode_5x5": lambda: I.Erode(x, 5, 5), "median_5x5": lambda: I.MedianBlur(x, 5),
+             "bilateral_5x5": lambda: I.BilateralFilter(x, 5), "flip": lambda: I.Flip(x, True, False)}
+    for name, fn in cases.items():
+        t = timeit(fn, iters=9, warm=3)
+        emit(op="image." + name, shape=[8, 3, 1080, 1920], ms=t, gbs=2 * nbytes / t / 1e6)
+    t = timeit(lambda: I.Resize(x, 960, 540), iters=9, warm=3)
+    emit(op="image.resize_bilinear_half", shape=[8, 3, 1080, 1920], ms=t, gbs=1.25 * nbytes / t / 1e6)
+    n = 20000
+    boxes = torch.cat([torch.rand(n, 2, device="cuda") * 1000, torch.rand(n, 2, device="cuda") * 60 + 4], 1)
+    scores = torch.rand(n, device="cuda")
+    classes = torch.randint(0, 80, (n,), device="cuda", dtype=torch.int32)
+    t = timeit(lambda: D.Nms(OaMatrix(boxes), OaMatrix(scores), OaMatrix(classes), D.OaNmsConfig(MaxDetections=300)), iters=9, warm=3, flush=False)
+    emit(op="detection.nms", boxes=n, classes=80, max_detections=300, ms=t)
+    K.check_status()
+
+
 def bench_mamba():
     from oa_b200.ops import mamba3 as M3
     for (B, L, H, P, Nn) in [(4, 4096, 48, 64, 128), (2, 1024, 48, 64, 128)]:
@@ -280,7 +305,7 @@ def main() -> int:
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:

@@ -9,7 +9,7 @@ OaFnMetric, and the `Context` scope), bound here to oa_b200.
     with oa.OaGradientTape() as tape: ...
     with oa.Context(): ...            # Execute + Sync of the default context on scope exit
 
-Names of the reference surface that this build does not provide (vision, plot, ui) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
+Names of the reference surface that this build does not provide (video codecs, plot, ui, renderer) are listed in `oa.UNAVAILABLE`; touching one raises an AttributeError that says so.
 """
 from __future__ import annotations
 
@@ -127,6 +127,22 @@ OaFnAudio = _namespace("OaFnAudio", "Waveform operations and audio features (STF
                         "Stft", "MelSpectrogram", "Mfcc"])
 OaFnHash = _namespace("OaFnHash", "Batched SHAKE / Keccak hashing and the SHAKE-256 Merkle root.", _FH,
                       ["Shake256", "Shake128", "KeccakF1600", "MerkleRoot"])
+from oa_b200.vision import fn_detection as _FD
+from oa_b200.vision import fn_image as _FI
+from oa_b200.vision import (OaBorderMode, OaDetectionMetricsResult, OaImage, OaImageFormat, OaImageFormatChannels, OaImageLayout,
+                            OaInterpolationMode, OaNmsConfig, OaNmsResult, OaNormalizationParams, OaSegmentationMetricsResult)
+OaFnImage = _namespace("OaFnImage", "Image operations on planar fp32 NCHW tensors and the semantic OaImage overloads.", _FI,
+                       ["AdaptiveThresholdGaussian", "AdaptiveThresholdMean", "AlphaBlend", "AverageBlur", "BilateralFilter",
+                        "BrightnessContrast", "CenterCrop", "ChannelReorder", "Clamp", "ColorTwist", "Composite", "ConvertColor", "Convolve2d",
+                        "Crop", "Dilate", "Erase", "Erode", "Flip", "GammaContrast", "GaussianBlur", "GaussianNoise", "Grayscale", "InRange",
+                        "Invert", "Laplacian", "MedianBlur", "MorphologyBlackHat", "MorphologyClose", "MorphologyGradient", "MorphologyOpen",
+                        "MorphologyTopHat", "Normalize", "Pad", "Posterize", "Remap", "Resize", "ResizeBatch", "ResizeNormalize", "Rotate",
+                        "SaltPepperNoise", "Scharr", "SegmentationOverlay", "SeparableConvolve2d", "Sharpen", "Sobel", "Solarize",
+                        "ThresholdBinary", "ThresholdBinaryInv", "ThresholdToZero", "ThresholdToZeroInv", "ThresholdTruncate", "UnsharpMask",
+                        "WarpAffine", "WarpPerspective"])
+OaFnVision = OaFnImage            # the reference keeps this older name as an alias
+OaFnDetection = _namespace("OaFnDetection", "Box IoU, NMS, confusion matrices and detection / segmentation metrics.", _FD,
+                           ["BinaryMaskCounts", "BoxIou", "ConfusionMatrix", "Evaluate", "EvaluateSegmentation", "Nms"])
 OaFnAutograd = _namespace("OaFnAutograd", "Autograd recording switch.", _AG, ["IsEnabled", "SetEnabled"])
 OaFnMetric = _namespace("OaFnMetric", "Host-side metrics of device results.", _M.OaFnMetric, ["Accuracy", "ScalarLoss"])
 
@@ -143,12 +159,12 @@ class Context:
         self._ctx.Sync()
 
 
-UNAVAILABLE = ("OaFnImage", "OaFnDetection", "OaPlot", "OaViewer", "OaVideo")
+UNAVAILABLE = ("OaPlot", "OaViewer", "OaVideo", "OaRenderer")
 
 
 def __getattr__(name: str):
     if name in UNAVAILABLE:
-        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (vision / plot / ui) that this build does not provide")
+        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (video / plot / ui / renderer) that this build does not provide")
     raise AttributeError(f"module 'oa' has no attribute '{name}'")
 
 

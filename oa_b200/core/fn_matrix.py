@@ -996,3 +996,117 @@ def VqEmaUpdate(ze, idx, embed_sum, cluster_size, codebook, decay: float, eps: f
 def SampleLogits(logits: OaMatrix, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> OaMatrix:
     from ..ml.rl import fn_rl as FR
     return FR.SampleLogits(logits, temperature, top_k, top_p, seed)
+
+
+# ======================================================================= channel-axis LayerNorm of [B, C, T] tensors
+def _channel_norm_fwd(tx: torch.Tensor, tw: torch.Tensor, tb: Optional[torch.Tensor], B: int, C: int, L: int, eps: float, relu: bool):
+    x3 = _c(tx).reshape(B, C, L)
+    if not x3.is_cuda:
+        xf = x3.float()
+        mean = xf.mean(1)
+        rstd = torch.rsqrt(xf.var(1, unbiased=False) + eps)
+        y = (xf - mean[:, None]) * rstd[:, None] * tw.float().reshape(1, C, 1) + (tb.float().reshape(1, C, 1) if tb is not None else 0.0)
+        if relu:
+            y = torch.relu(y)
+        return y.to(tx.dtype), mean.contiguous(), rstd.contiguous()
+    y = torch.empty_like(x3)
+    mean = torch.empty((B, L), dtype=torch.float32, device=x3.device)
+    rstd = torch.empty((B, L), dtype=torch.float32, device=x3.device)
+    K._launch(N.require().oa_channel_norm_fwd(K.dt(x3), x3.data_ptr(), _c(tw).data_ptr(), N.ptr(_c(tb) if tb is not None else None), y.data_ptr(),
+                                              mean.data_ptr(), rstd.data_ptr(), B, C, L, float(eps), int(relu), N.stream()), "oa_channel_norm_fwd")
+    return y, mean, rstd
+
+
+def _channel_norm_bwd(tx, tw, tg, ty_relu, mean, rstd, B: int, C: int, L: int):
+    x3, g3 = _c(tx).reshape(B, C, L), _c(tg).reshape(B, C, L)
+    if not x3.is_cuda:
+        gf = g3.float()
+        if ty_relu is not None:
+            gf = gf * (ty_relu.reshape(B, C, L).float() > 0)
+        xhat = (x3.float() - mean[:, None]) * rstd[:, None]
+        gw = gf * tw.float().reshape(1, C, 1)
+        dx = rstd[:, None] * (gw - gw.mean(1, keepdim=True) - xhat * (gw * xhat).mean(1, keepdim=True))
+        return dx.to(tx.dtype), (gf * xhat).sum((0, 2)), gf.sum((0, 2))
+    dx = torch.empty_like(x3)
+    dw = torch.empty(C, dtype=torch.float32, device=x3.device)
+    db = torch.empty(C, dtype=torch.float32, device=x3.device)
+    yr = _c(ty_relu).reshape(B, C, L) if ty_relu is not None else None
+    K._launch(N.require().oa_channel_norm_bwd(K.dt(x3), x3.data_ptr(), _c(tw).data_ptr(), g3.data_ptr(), N.ptr(yr), mean.data_ptr(), rstd.data_ptr(),
+                                              dx.data_ptr(), dw.data_ptr(), db.data_ptr(), B, C, L, N.stream()), "oa_channel_norm_bwd", 2)
+    return dx, dw, db
+
+
+def _channel_norm(name: str, x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], B: int, C: int, L: int, eps: float, relu: bool) -> OaMatrix:
+    _ctx_add(name)
+    tx, tw = x.Tensor(), w.Tensor()
+    if tx.numel() != B * C * L or tw.numel() != C:
+        raise ValueError(f"{name}: x has {tx.numel()} elements, expected {B}x{C}x{L}; weight has {tw.numel()}, expected {C}")
+    y, mean, rstd = _channel_norm_fwd(tx, tw, b.Tensor() if b is not None else None, B, C, L, eps, relu)
+    out = _w(y.reshape(tx.shape))
+
+    def back(g):
+        dx, dw, db = _channel_norm_bwd(tx, tw, g, y if relu else None, mean, rstd, B, C, L)
+        return (dx.reshape(tx.shape), dw.to(tw.dtype).reshape(tw.shape), db.to(tw.dtype).reshape(b.Tensor().shape) if b is not None else None)
+
+    return AG.attach(name, out, [x, w, b], back)
+
+
+def ChannelNorm(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], batch: int, channels: int, seq_len: int, eps: float = 1e-5) -> OaMatrix:
+    """LayerNorm over the channel axis of [B, C, T] in one kernel, no transposes (Source/Public/Oa/Ml/FnMatrix.h:544-550)."""
+    return _channel_norm("ChannelNorm", x, w, b, batch, channels, seq_len, eps, False)
+
+
+def ChannelNormRelu(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], batch: int, channels: int, seq_len: int, eps: float = 1e-5) -> OaMatrix:
+    """ChannelNorm with the ReLU applied in the same kernel (Source/Public/Oa/Ml/FnMatrix.h:556-561)."""
+    return _channel_norm("ChannelNormRelu", x, w, b, batch, channels, seq_len, eps, True)
+
+
+def ChannelNormBwd(x: OaMatrix, w: OaMatrix, grad_out: OaMatrix, batch: int, channels: int, seq_len: int, eps: float = 1e-5):
+    """Explicit backward: returns (DX, DWeight, DBias) (Source/Public/Oa/Ml/FnMatrix.h:552-555)."""
+    tx, tw = x.Tensor(), w.Tensor()
+    _, mean, rstd = _channel_norm_fwd(tx, tw, None, batch, channels, seq_len, eps, False)
+    dx, dw, db = _channel_norm_bwd(tx, tw, grad_out.Tensor(), None, mean, rstd, batch, channels, seq_len)
+    return _w(dx.reshape(tx.shape)), _w(dw.to(tw.dtype)), _w(db.to(tw.dtype))
+
+
+def ChannelNormReluBwd(x: OaMatrix, w: OaMatrix, fwd_out: OaMatrix, grad_out: OaMatrix, batch: int, channels: int, seq_len: int, eps: float = 1e-5):
+    tx, tw = x.Tensor(), w.Tensor()
+    _, mean, rstd = _channel_norm_fwd(tx, tw, None, batch, channels, seq_len, eps, False)
+    dx, dw, db = _channel_norm_bwd(tx, tw, grad_out.Tensor(), fwd_out.Tensor(), mean, rstd, batch, channels, seq_len)
+    return _w(dx.reshape(tx.shape)), _w(dw.to(tw.dtype)), _w(db.to(tw.dtype))
+
+
+# ======================================================================= 1-D convolution as im2col + one GEMM
+def Im2Col1d(x: OaMatrix, k: int, stride: int, padding: int, dilation: int = 1) -> OaMatrix:
+    """[N, InC, L] -> [N*OutL, InC*K] (row = n*OutL + ol, column = ic*K + k); differentiable, backward = Col2Im1d
+    (Source/Public/Oa/Ml/FnMatrix.h:588-593)."""
+    from ..ml.nn import conv as CV
+    n, c, l = x.Tensor().shape
+    return CV.Im2Col(x.Reshape([n, c, 1, l]), (1, k), (1, stride), (0, padding), (1, dilation))
+
+
+def Col2Im1d(dcols: OaMatrix, n: int, c: int, l: int, k: int, stride: int, padding: int, dilation: int, out_l: int) -> OaMatrix:
+    """Adjoint of Im2Col1d: [N*OutL, InC*K] -> [N, InC, L], overlapping windows accumulate (Source/Public/Oa/Ml/FnMatrix.h:595-600)."""
+    from ..ml.nn import conv as CV
+    from ..ops import conv as CO
+    if CO.out_size(l, k, stride, padding, dilation) != out_l:
+        raise ValueError("Col2Im1d: OutL does not match the convolution geometry")
+    return CV.Col2Im(dcols, (n, c, 1, l), (1, k), (1, stride), (0, padding), (1, dilation)).Reshape([n, c, l])
+
+
+def _conv1d_gemm(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], stride: int, padding: int, dilation: int, relu: bool) -> OaMatrix:
+    n, c, l = x.Tensor().shape
+    o, _, k = w.Tensor().shape
+    cols = Im2Col1d(x, k, stride, padding, dilation)
+    y = Linear(cols, w.Reshape([o, c * k]), b, K.ACT_RELU if relu else K.ACT_NONE, "Conv1dReluGemm" if relu else "Conv1dGemm")
+    return Permute(y.Reshape([n, cols.Size(0) // n, o]), [0, 2, 1])
+
+
+def Conv1dGemm(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], stride: int = 1, padding: int = 0, dilation: int = 1) -> OaMatrix:
+    """x [N, InC, L], w [OutC, InC, K] -> [N, OutC, OutL]: im2col and one GEMM on the tensor cores (Source/Public/Oa/Ml/FnMatrix.h:571-580)."""
+    return _conv1d_gemm(x, w, b, stride, padding, dilation, False)
+
+
+def Conv1dReluGemm(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], stride: int = 1, padding: int = 0, dilation: int = 1) -> OaMatrix:
+    """Conv1dGemm with the ReLU in the GEMM epilogue (Source/Public/Oa/Ml/FnMatrix.h:582-586)."""
+    return _conv1d_gemm(x, w, b, stride, padding, dilation, True)

@@ -299,6 +299,42 @@ int oa_audio_resample(const void* x, void* out, int channels, long long in_sampl
                       int half_width, void* stream);
 int oa_audio_envelope(const void* x, void* out, int channels, long long samples, int bins, void* stream);
 
+// ---- channel-axis LayerNorm of [B, C, T] tensors (channel_norm.cu)
+int oa_channel_norm_fwd(int dtype, const void* x, const void* w, const void* bias, void* y, void* mean, void* rstd, int B, int C, int L, float eps,
+                        int relu, void* stream);
+int oa_channel_norm_bwd(int dtype, const void* x, const void* w, const void* g, const void* y_relu, const void* mean, const void* rstd, void* dx,
+                        void* dw_f32, void* db_f32, int B, int C, int L, void* stream);
+
+// ---- image operations (image.cu)
+int oa_image_pointwise(const void* x, void* out, long long n, int op, float p0, float p1, float p2, void* stream);
+int oa_image_channels(const void* x, void* out, int batch, int cin, int cout, long long plane, const float* matrix20, const int* sel4,
+                      const void* twist, int mode, void* stream);
+int oa_image_blend(const void* a, const void* b, const void* mask, void* out, int batch, int channels, int H, int W, int op, float alpha,
+                   int mask_channels, int rx, int ry, int rw, int rh, float value, void* stream);
+int oa_image_overlay(const void* img, const void* labels, const void* palette, void* out, int batch, int channels, long long plane,
+                     int classes, float alpha, void* stream);
+int oa_image_noise(const void* x, void* out, long long n, int op, float p0, float p1, float p2, unsigned long long seed, void* stream);
+int oa_image_tile_filter(const void* x, void* out, int planes, int H, int W, int kw, int kh, int mode, int border, float border_value,
+                         const void* k0, const void* k1, float p0, float p1, float p2, void* stream);
+int oa_image_index_map(const void* x, void* out, int planes, int Hi, int Wi, int Ho, int Wo, int op, int a0, int a1, int border,
+                       float border_value, void* stream);
+int oa_image_resize(const void* x, void* out, int planes, int channels, int Hi, int Wi, int Ho, int Wo, int mode, const float* mean3,
+                    const float* std3, void* stream);
+int oa_image_warp(const void* x, const void* map, void* out, int batch, int channels, int Hi, int Wi, int Ho, int Wo, int op, int map_batch,
+                  int interp, int border, float border_value, void* stream);
+
+// ---- detection post-processing and metrics (detection.cu)
+int oa_det_box_iou(const void* a, const void* b, void* out, int n, int m, void* stream);
+int oa_det_nms(const void* boxes, const void* scores, const void* classes, int n, float iou_thr, float score_thr, int max_det, int agnostic,
+               void* indices, void* count, void* alive_scratch, void* stream);
+int oa_det_confusion(const void* predicted, const void* target, long long n, int classes, void* out_zeroed, void* stream);
+int oa_det_binary_counts(const void* predicted, const void* target, long long n, void* out_zeroed, void* stream);
+int oa_det_segmentation_metrics(const void* confusion, int classes, void* per_class, void* mean_iou, void* accuracy, void* stream);
+int oa_det_evaluate(const void* pboxes, const void* pscores, const void* pclasses, const void* pimages, const void* order, int P,
+                    const void* tboxes, const void* tclasses, const void* timages, int G, const void* thresholds, int T, int classes,
+                    float score_thr, void* matched_scratch, void* curve_scratch, void* counts, void* metrics, void* map_by_threshold,
+                    void* mean_map, void* stream);
+
 // ---- peer-memory communication (comm.cu): IPC buffers, epoch flags, fused data-parallel step
 int oa_ipc_alloc(size_t bytes, void** out);
 int oa_ipc_free(void* p);

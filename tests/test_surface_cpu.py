@@ -24,7 +24,8 @@ def test_root_names_and_namespaces():
         assert hasattr(oa.OaFnLoss, n), n
     assert oa.OaFnAutograd.IsEnabled() is False
     with pytest.raises(AttributeError, match="does not provide"):
-        oa.OaFnImage
+        oa.OaPlot
+    assert len(oa.OaFnImage.__all__) >= 50 and oa.OaFnVision is oa.OaFnImage and hasattr(oa.OaFnDetection, "Nms")
     for n in ("OaRlReplayBuffer", "OaRlRolloutBuffer", "OaPpoLossConfig", "OaItRlTraining", "OaGaeConfig", "OaRlSpaceKind", "OaFnRl"):
         assert hasattr(oa, n), n
     import oa.OaFnMatrix as ns          # namespace modules are importable
