@@ -206,6 +206,34 @@ __device__ __forceinline__ float float_from_key(unsigned k) {
   return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
 }
 
+__device__ __forceinline__ void sort2(float& a, float& b) {
+  const float lo = fminf(a, b), hi = fmaxf(a, b);
+  a = lo; b = hi;
+}
+
+// Median of a K x K window (K = 3, 5, 7) by forgetful selection: a working set of K*K/2 + 2 samples lives in registers; its
+// minimum and maximum can never be the median, so each step drops both and takes the next sample from shared memory.  All
+// loops unroll, every index is a compile-time constant.
+template <int K>
+__device__ __forceinline__ float median_small(const float (*halo)[TF_HALO + 1], int r, int tx) {
+  constexpr int N = K * K, M0 = N / 2 + 2;
+  float w[M0];
+#pragma unroll
+  for (int j = 0; j < M0; ++j) w[j] = halo[r + j / K][tx + j % K];
+#pragma unroll
+  for (int m = M0; m >= 3; --m) {
+#pragma unroll
+    for (int i = 0; i + 1 < m; ++i) sort2(w[i], w[i + 1]);            // maximum to w[m-1]
+#pragma unroll
+    for (int i = m - 2; i > 0; --i) sort2(w[i - 1], w[i]);            // minimum to w[0]
+    if (m > 3) {
+      const int j = M0 + (M0 - m);                                    // next unread sample (constant after unrolling)
+      w[0] = halo[r + j / K][tx + j % K];
+    }
+  }
+  return w[1];
+}
+
 // One CTA (32 x 8 threads) per 32x32 output tile of one plane.  kw x kh window (odd, <= 31), coefficient pointers by mode:
 // TF_CONV2D k0 = [kh, kw]; TF_SEPARABLE k0 = horizontal [kw], k1 = vertical [kh].  p0..p2: bilateral (sigma_space, sigma_color),
 // adaptive (sigma_space, offset C, max value).
@@ -274,6 +302,8 @@ __global__ void __launch_bounds__(256) image_tile_filter_kernel(const float* __r
         for (int ky = 0; ky < kh; ++ky)
           for (int kx = 0; kx < kw; ++kx) acc = fmaf(coef[ky * kw + kx], halo[r + ky][tx + kx], acc);
         result = acc;
+      } else if (mode == TF_MEDIAN && kw == kh && kw <= 7) {
+        result = kw == 1 ? halo[r][tx] : kw == 3 ? median_small<3>(halo, r, tx) : kw == 5 ? median_small<5>(halo, r, tx) : median_small<7>(halo, r, tx);
       } else if (mode == TF_MEDIAN) {
         // rank selection by bisection over the order-preserving bit pattern: no per-thread sample array
         const int rank = (kw * kh) / 2;
@@ -375,6 +405,12 @@ __global__ void image_resize_kernel(const float* __restrict__ x, float* __restri
   }
 }
 
+// (m0 * x + m1 * y) + m2 with every product and sum rounded on its own (no contraction into fused multiply-adds), so that
+// nearest-neighbour warps pick the same source pixel as the same expression evaluated elsewhere in fp32
+__device__ __forceinline__ float affine_row(const float* __restrict__ m, float x, float y) {
+  return __fadd_rn(__fadd_rn(__fmul_rn(m[0], x), __fmul_rn(m[1], y)), m[2]);
+}
+
 // op 0 remap (map [Nm,2,Ho,Wo]: x plane then y plane, Nm = 1 or N); 1 inverse affine 2x3; 2 inverse perspective 3x3
 __global__ void image_warp_kernel(const float* __restrict__ x, const float* __restrict__ map, float* __restrict__ out, int batch,
                                   int channels, int Hi, int Wi, int Ho, int Wo, int op, int map_batch, int interp, int border,
@@ -390,13 +426,13 @@ __global__ void image_warp_kernel(const float* __restrict__ x, const float* __re
       const long long base = (map_batch == 1 ? 0 : b) * 2 * plane_o + p;
       sx = map[base]; sy = map[base + plane_o];
     } else if (op == 1) {
-      sx = map[0] * xx + map[1] * y + map[2];
-      sy = map[3] * xx + map[4] * y + map[5];
+      sx = affine_row(map, (float)xx, (float)y);
+      sy = affine_row(map + 3, (float)xx, (float)y);
     } else {
-      const float den = map[6] * xx + map[7] * y + map[8];
+      const float den = affine_row(map + 6, (float)xx, (float)y);
       valid = fabsf(den) > 1e-12f;
-      sx = valid ? (map[0] * xx + map[1] * y + map[2]) / den : 0.f;
-      sy = valid ? (map[3] * xx + map[4] * y + map[5]) / den : 0.f;
+      sx = valid ? __fdiv_rn(affine_row(map, (float)xx, (float)y), den) : 0.f;
+      sy = valid ? __fdiv_rn(affine_row(map + 3, (float)xx, (float)y), den) : 0.f;
     }
     const float* src = x + pl * Hi * Wi;
     float v;
