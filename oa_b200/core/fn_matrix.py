@@ -18,6 +18,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from .. import _native as N
 from ..ml import autograd as AG
 from ..ops import kernels as K
 from ..runtime import engine as RT

@@ -237,6 +237,9 @@ __device__ __forceinline__ float median_small(const float (*halo)[TF_HALO + 1], 
 // One CTA (32 x 8 threads) per 32x32 output tile of one plane.  kw x kh window (odd, <= 31), coefficient pointers by mode:
 // TF_CONV2D k0 = [kh, kw]; TF_SEPARABLE k0 = horizontal [kw], k1 = vertical [kh].  p0..p2: bilateral (sigma_space, sigma_color),
 // adaptive (sigma_space, offset C, max value).
+// HEAVY = false compiles only the correlation and morphology modes (fewer registers, more resident CTAs); HEAVY = true the
+// neighbourhood modes (median, bilateral, adaptive thresholds).
+template <bool HEAVY>
 __global__ void __launch_bounds__(256) image_tile_filter_kernel(const float* __restrict__ x, float* __restrict__ out, int planes, int H,
                                                                 int W, int kw, int kh, int mode, int border, float border_value,
                                                                 const float* __restrict__ k0, const float* __restrict__ k1, float p0,
@@ -263,7 +266,7 @@ __global__ void __launch_bounds__(256) image_tile_filter_kernel(const float* __r
       halo[hy][hx] = load_border(src, y0 + hy - ry, x0 + hx - rx, H, W, border, border_value);
     }
     __syncthreads();
-    if (mode == TF_SEPARABLE || mode == TF_MIN || mode == TF_MAX) {
+    if (!HEAVY && (mode == TF_SEPARABLE || mode == TF_MIN || mode == TF_MAX)) {
       // horizontal pass over every halo row, then the vertical pass over the 32 columns
       for (int i = t; i < hh * TF_TILE; i += 256) {
         const int hy = i / TF_TILE, cx = i - hy * TF_TILE;
@@ -297,7 +300,7 @@ __global__ void __launch_bounds__(256) image_tile_filter_kernel(const float* __r
       const int oy = y0 + r, ox = x0 + tx;
       if (oy >= H || ox >= W) continue;
       float result;
-      if (mode == TF_CONV2D) {
+      if constexpr (!HEAVY) {
         float acc = 0.f;
         for (int ky = 0; ky < kh; ++ky)
           for (int kx = 0; kx < kw; ++kx) acc = fmaf(coef[ky * kw + kx], halo[r + ky][tx + kx], acc);
@@ -508,8 +511,14 @@ int oa_image_tile_filter(const void* x, void* out, int planes, int H, int W, int
                          const void* k0, const void* k1, float p0, float p1, float p2, void* stream) {
   if (kw < 1 || kh < 1 || kw > 31 || kh > 31 || !(kw & 1) || !(kh & 1) || planes < 1) return (int)cudaErrorInvalidValue;
   dim3 grid((W + TF_TILE - 1) / TF_TILE, (H + TF_TILE - 1) / TF_TILE, planes > 4096 ? 4096 : planes);
-  image_tile_filter_kernel<<<grid, dim3(32, 8), 0, (cudaStream_t)stream>>>((const float*)x, (float*)out, planes, H, W, kw, kh, mode, border,
-                                                                           border_value, (const float*)k0, (const float*)k1, p0, p1, p2);
+  if (mode <= TF_MAX)
+    image_tile_filter_kernel<false><<<grid, dim3(32, 8), 0, (cudaStream_t)stream>>>((const float*)x, (float*)out, planes, H, W, kw, kh, mode,
+                                                                                    border, border_value, (const float*)k0, (const float*)k1,
+                                                                                    p0, p1, p2);
+  else
+    image_tile_filter_kernel<true><<<grid, dim3(32, 8), 0, (cudaStream_t)stream>>>((const float*)x, (float*)out, planes, H, W, kw, kh, mode,
+                                                                                   border, border_value, (const float*)k0, (const float*)k1,
+                                                                                   p0, p1, p2);
   return (int)cudaGetLastError();
 }
 
