@@ -163,6 +163,22 @@ def bench_mamba_once():
     emit(op="mamba3_core_once", B=B, L=L, status="ok")
 
 
+def bench_decode_attn():
+    """Single-query attention over the KV cache of one layer of the 7B-class decode case: streamed kernel against the
+    one-CTA-per-head kernel (bytes = K and V rows read once)."""
+    B, H, S, L, hd = 32, 32, 2304, 2200, 128
+    kc = torch.randn(B, H, S, hd, device="cuda").bfloat16()
+    vc = torch.randn(B, H, S, hd, device="cuda").bfloat16()
+    q = torch.randn(B, H * hd, device="cuda").bfloat16()
+    nbytes = 2 * B * H * L * hd * 2
+    for name in ("stream", "v1"):
+        os.environ["OA_DECODE_ATTN"] = name
+        t = timeit(lambda: K.decode_attn(q, kc, vc, L), iters=15, warm=4)
+        emit(op="decode_attn." + name, batch=B, heads=H, length=L, head_dim=hd, us=t * 1e3, gbs=nbytes / t / 1e6)
+    os.environ.pop("OA_DECODE_ATTN", None)
+    K.check_status()
+
+
 def bench_decode():
     """Batch-32 greedy decoding of 256 tokens after a 2048-token prompt on the 7B-class model (one GPU, KV cache)."""
     from oa_b200.core import fn_matrix as F
@@ -305,7 +321,7 @@ def main() -> int:
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image, "decode_attn": bench_decode_attn}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:

@@ -225,6 +225,10 @@ int oa_kv_append(const void* k_src, const void* v_src, long long src_stride, voi
                  int s_new, int heads, int head_dim, int pos0, int max_seq, const int* pos_dev, void* stream);
 int oa_decode_attn(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out, long long out_stride,
                    int batch, int heads, int head_dim, int len, int max_seq, float scale, const int* pos_dev, void* stream);
+size_t oa_decode_attn_stream_scratch_bytes(int batch, int heads, int head_dim, int splits);
+int oa_decode_attn_stream(const void* q, long long q_stride, const void* k_cache, const void* v_cache, void* out, long long out_stride,
+                          int batch, int heads, int head_dim, int len, int max_seq, float scale, const int* pos_dev, void* partial,
+                          int splits, int* status, void* stream);
 
 // ---- reinforcement learning (rl.cu): vector CartPole, GAE, rollout / replay storage, loss targets, categorical sampling
 int oa_rl_cartpole_reset(void* state, void* done, void* steps, void* episode, int envs, unsigned seed_lo, unsigned seed_hi,

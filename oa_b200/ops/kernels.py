@@ -8,6 +8,7 @@ to PyTorch math: a missing library or an unsupported shape raises.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -929,6 +930,30 @@ def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, l
         return (p @ vf).reshape(batch, heads * hd).to(q.dtype)
     out = torch.empty((batch, heads * hd), dtype=q.dtype, device=q.device)
     assert q.stride(1) == 1 and q.dtype == torch.bfloat16
-    _launch(N.require().oa_decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0), batch,
-                                       heads, hd, length, max_seq, float(scale), N.ptr(pos_dev), N.stream()), "oa_decode_attn")
+    lib = N.require()
+    if hd in (64, 128) and k_cache.is_contiguous() and v_cache.is_contiguous() and os.environ.get("OA_DECODE_ATTN", "stream") == "stream":
+        splits = decode_attn_splits(batch * heads, max_seq)
+        part = scratch(q.device, lib.oa_decode_attn_stream_scratch_bytes(batch, heads, hd, splits), "decode_attn_partial")
+        _launch(lib.oa_decode_attn_stream(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0),
+                                          batch, heads, hd, length, max_seq, float(scale), N.ptr(pos_dev), part.data_ptr(), splits,
+                                          status_word(q.device).data_ptr(), N.stream()), "oa_decode_attn_stream", 2)
+        return out
+    _launch(lib.oa_decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0), batch,
+                               heads, hd, length, max_seq, float(scale), N.ptr(pos_dev), N.stream()), "oa_decode_attn")
     return out
+
+
+def decode_attn_splits(n_bh: int, max_seq: int, slots: int = 2 * 148) -> int:
+    """How many pieces each (sequence, head) is cut into for the streamed decode kernel: the smallest count (up to 8) whose
+    items fill the persistent CTAs' last round to 95 % while a piece keeps at least 256 positions; else the best filling."""
+    best, best_eff = 1, 0.0
+    for s in range(1, 9):
+        if s > 1 and max_seq // s < 256:
+            break
+        waves = n_bh * s / slots
+        eff = waves / math.ceil(waves)
+        if eff >= 0.95:
+            return s
+        if eff > best_eff + 1e-9:
+            best, best_eff = s, eff
+    return best

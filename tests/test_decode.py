@@ -56,6 +56,40 @@ def test_decode_kernels(hd):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("hd", [64, 128])
+def test_streamed_decode_attention_lengths_and_splits(hd, monkeypatch):
+    """The streamed kernel against the fp32 reference for lengths around tile and split edges, with a device-resident
+    position, more items than persistent CTAs, and against the one-CTA-per-head kernel it replaces."""
+    torch.manual_seed(1)
+    B, H, S = 5, 8, 1100
+    kc = (torch.randn(B, H, S, hd, device="cuda") * 0.5).bfloat16()
+    vc = torch.randn(B, H, S, hd, device="cuda").bfloat16()
+    q = torch.randn(B, H * hd, device="cuda").bfloat16()
+    kcc, vcc, qc = kc.cpu(), vc.cpu(), q.cpu()
+    tile = 64 if hd == 128 else 128
+    for L in (1, 7, tile - 1, tile, tile + 1, 3 * tile + 5, 517, 1024, 1100):
+        out = K.decode_attn(q, kc, vc, L)
+        ref = K.decode_attn(qc, kcc, vcc, L)
+        assert (out.float().cpu() - ref.float()).abs().max().item() < 2e-2, L
+    pos = torch.tensor([300], dtype=torch.int32, device="cuda")
+    out = K.decode_attn(q, kc, vc, 217, pos_dev=pos)
+    assert (out.float().cpu() - K.decode_attn(qc, kcc, vcc, 517).float()).abs().max().item() < 2e-2
+    monkeypatch.setenv("OA_DECODE_ATTN", "v1")
+    old = K.decode_attn(q, kc, vc, 517)
+    monkeypatch.delenv("OA_DECODE_ATTN")
+    assert (old.float() - K.decode_attn(q, kc, vc, 517).float()).abs().max().item() < 2e-2
+    # 40 x 16 heads x 2 splits = 1280 items over 296 persistent CTAs: several items per CTA through one pipeline
+    B2, H2, S2 = 40, 16, 600
+    k2 = (torch.randn(B2, H2, S2, hd, device="cuda") * 0.5).bfloat16()
+    v2 = torch.randn(B2, H2, S2, hd, device="cuda").bfloat16()
+    q2 = torch.randn(B2, H2 * hd, device="cuda").bfloat16()
+    out = K.decode_attn(q2, k2, v2, 555)
+    ref = K.decode_attn(q2.cpu(), k2.cpu(), v2.cpu(), 555)
+    assert (out.float().cpu() - ref.float()).abs().max().item() < 2e-2
+    K.check_status()
+
+
+@pytest.mark.gpu
 def test_cached_generation_gpu_bf16():
     from oa_b200.runtime import engine as RT
     F.SetRngSeed(5)
