@@ -63,6 +63,19 @@ def bench_gemm():
     K.check_status()
 
 
+def bench_gemm_small_m():
+    """Weight-streaming GEMMs of a decode step (32 rows): time against weight bytes, own kernel and cuBLAS."""
+    for (M, N, Kk) in [(32, 12288, 4096), (32, 4096, 4096), (32, 22016, 4096), (32, 4096, 11008), (32, 32000, 4096)]:
+        a = torch.randn(M, Kk, device="cuda").bfloat16()
+        b = torch.randn(N, Kk, device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        t = timeit(lambda: K.gemm(a, b, out=out))
+        t2 = timeit(lambda: torch.matmul(a, b.t(), out=out))
+        emit(op="gemm_bf16_small_m", M=M, N=N, K=Kk, us=t * 1e3, weight_gbs=N * Kk * 2 / t / 1e6, cublas_us=t2 * 1e3,
+             cublas_weight_gbs=N * Kk * 2 / t2 / 1e6)
+    K.check_status()
+
+
 def bench_flash():
     import torch.nn.functional as Fn
     for (B, H, S, hd) in [(8, 16, 2048, 64), (1, 32, 4096, 128)]:
@@ -321,7 +334,7 @@ def main() -> int:
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image, "decode_attn": bench_decode_attn}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image, "decode_attn": bench_decode_attn, "gemm_small_m": bench_gemm_small_m}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:
