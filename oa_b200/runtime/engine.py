@@ -158,6 +158,14 @@ class OaContext:
     def Stream(self):
         return self._stream if self._stream is not None else (torch.cuda.current_stream() if self._engine.IsCuda() else None)
 
+    def Session(self):
+        """The execution session of this context (stable resource frame, reusable graphs, batch hazards); created on
+        first use so that contexts which never capture a step pay nothing."""
+        if getattr(self, "_session", None) is None:
+            from .session import OaExecutionSession
+            self._session = OaExecutionSession(self._engine.Device())
+        return self._session
+
     def Add(self, kernel: str, reads=(), writes=()) -> None:
         """Notes one recorded kernel node. Buffers are identified by their storage address."""
         self._interval_nodes += 1
