@@ -147,6 +147,17 @@ OaFnAutograd = _namespace("OaFnAutograd", "Autograd recording switch.", _AG, ["I
 OaFnMetric = _namespace("OaFnMetric", "Host-side metrics of device results.", _M.OaFnMetric, ["Accuracy", "ScalarLoss"])
 
 
+# ---- host primitives, streams and the native executor pieces
+from oa_b200.core.host import (OaAlignedBuffer, OaChannel, OaCoreInfo, OaCpuTopology, OaMemcpyNT, OaMemEqual, OaSimd, OaTask, OaThreadPool,
+                               OaThreadPoolConfig)
+from oa_b200.runtime.graph import OaAccess, OaComputeGraph
+from oa_b200.runtime.session import (OaAnalyzeSemanticLowering, OaExecutionPlan, OaExecutionSession, OaSemanticGraph,
+                                     OaSemanticLoweringAnalysis, OaValidateSemanticLowering)
+from oa_b200.runtime.stream import (OaCompletionToken, OaComputeClass, OaDispatch, OaDispatchHint, OaExternalMemory, OaExternalMemoryHandle,
+                                    OaFence, OaInferencePool, OaInferencePoolConfig, OaScheduler, OaStream, OaStreamPool,
+                                    OaTimelineSemaphore, OaWorkItem, OaWorkQueue)
+
+
 class Context:
     """Executes and synchronises the default context on scope exit."""
 
