@@ -158,6 +158,14 @@ from oa_b200.runtime.stream import (OaCompletionToken, OaComputeClass, OaDispatc
                                     OaTimelineSemaphore, OaWorkItem, OaWorkQueue)
 
 
+# ---- data layer
+from oa_b200.data.dataframe import OaDataFrame, OaDataOhlcv, OaRecordOhlcv, OaSeries, OaTimeSeries
+from oa_b200.data.datasets import (OaAsyncReader, OaDsDailyDialog, OaDsHumanMl3d, OaDsMnist, OaDsSharded, OaDsSubset, OaDsTinyShakespeare,
+                                   OaFnDataset, OaHumanMl3dCaption, OaHumanMl3dEvaluateMotion, OaHumanMl3dMotionMetrics, OaHumanMl3dMpjpeCm,
+                                   OaHumanMl3dRecoverWorldJoints, OaIoUringReader, OaReadFileParallel)
+from oa_b200.data.stores import OaContractTicker, OaDataSummary, OaKeyValueStore, OaOhlcvStore, OaSqlStore, OaStoreKind
+
+
 class Context:
     """Executes and synchronises the default context on scope exit."""
 
