@@ -166,6 +166,12 @@ from oa_b200.data.datasets import (OaAsyncReader, OaDsDailyDialog, OaDsHumanMl3d
 from oa_b200.data.stores import OaContractTicker, OaDataSummary, OaKeyValueStore, OaOhlcvStore, OaSqlStore, OaStoreKind
 
 
+# ---- extensions: animation language model, precision policy
+from oa_b200.extensions.alm import (OaAlmAg, OaAlmDatasetConfig, OaAlmFfnType, OaAlmPriorAg, OaAlmPriorConfig, OaAlmTokenizerAg,
+                                    OaAlmTokenizerConfig, OaClipTextAg, OaClipTextConfig, OaClipTextWeightName, OaClipTokenizer)
+from oa_b200.ml.precision import (OaLoadStoreStrideBytes, OaLookupPrecision, OaPipelineNameIsF32Variant, OaPrecisionDtype, OaPrecisionTag)
+
+
 class Context:
     """Executes and synchronises the default context on scope exit."""
 

@@ -107,3 +107,14 @@ def test_external_memory_handle_record():
     assert h.IsValid() and OaExternalMemoryHandle.Unpack(h.Pack()) == h and not OaExternalMemoryHandle().IsValid()
     with pytest.raises(ValueError):
         OaExternalMemoryHandle.Unpack(b"short")
+
+
+def test_precision_policy():
+    from oa_b200.core.types import OaPrecision
+    from oa_b200.ml.precision import (OaLoadStoreStrideBytes, OaLookupPrecision, OaPipelineNameIsF32Variant, OaPrecisionDtype,
+                                      OaPrecisionTag)
+    assert OaLookupPrecision("AdamwMixed") == OaPrecisionTag.Mixed and OaLookupPrecision("rmsnorm_fwd_kernel") == OaPrecisionTag.Bf16
+    assert OaPrecisionDtype(OaPrecisionTag.Bf16, OaPrecision.BF16) == 1 and OaPrecisionDtype(OaPrecisionTag.Mixed, OaPrecision.BF16) == 0
+    assert OaPrecisionDtype(OaPrecisionTag.Bf16, OaPrecision.FP32) == 0
+    assert OaLoadStoreStrideBytes(OaPrecisionTag.Bf16, OaPrecision.BF16) == 2 and OaLoadStoreStrideBytes(OaPrecisionTag.Fp32, OaPrecision.BF16) == 4
+    assert OaPipelineNameIsF32Variant("Gemm_f32") and not OaPipelineNameIsF32Variant("f32") and not OaPipelineNameIsF32Variant("Gemm_bf16")
