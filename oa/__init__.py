@@ -136,7 +136,7 @@ OaFnImage = _namespace("OaFnImage", "Image operations on planar fp32 NCHW tensor
                         "BrightnessContrast", "CenterCrop", "ChannelReorder", "Clamp", "ColorTwist", "Composite", "ConvertColor", "Convolve2d",
                         "Crop", "Dilate", "Erase", "Erode", "Flip", "GammaContrast", "GaussianBlur", "GaussianNoise", "Grayscale", "InRange",
                         "Invert", "Laplacian", "MedianBlur", "MorphologyBlackHat", "MorphologyClose", "MorphologyGradient", "MorphologyOpen",
-                        "MorphologyTopHat", "Normalize", "Pad", "Posterize", "Remap", "Resize", "ResizeBatch", "ResizeNormalize", "Rotate",
+                        "MorphologyTopHat", "Normalize", "Pad", "Posterize", "Remap", "Resize", "ResizeBatch", "ResizeBilinearBwd", "ResizeNearestBwd", "ResizeNormalize", "Rotate",
                         "SaltPepperNoise", "Scharr", "SegmentationOverlay", "SeparableConvolve2d", "Sharpen", "Sobel", "Solarize",
                         "ThresholdBinary", "ThresholdBinaryInv", "ThresholdToZero", "ThresholdToZeroInv", "ThresholdTruncate", "UnsharpMask",
                         "WarpAffine", "WarpPerspective"])

@@ -322,6 +322,7 @@ int oa_image_tile_filter(const void* x, void* out, int planes, int H, int W, int
                          const void* k0, const void* k1, float p0, float p1, float p2, void* stream);
 int oa_image_index_map(const void* x, void* out, int planes, int Hi, int Wi, int Ho, int Wo, int op, int a0, int a1, int border,
                        float border_value, void* stream);
+int oa_image_resize_bwd(const void* grad_out, void* grad_in, int planes, int Hi, int Wi, int Ho, int Wo, int mode, void* stream);
 int oa_image_resize(const void* x, void* out, int planes, int channels, int Hi, int Wi, int Ho, int Wo, int mode, const float* mean3,
                     const float* std3, void* stream);
 int oa_image_warp(const void* x, const void* map, void* out, int batch, int channels, int Hi, int Wi, int Ho, int Wo, int op, int map_batch,

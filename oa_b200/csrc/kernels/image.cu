@@ -457,6 +457,48 @@ __global__ void image_warp_kernel(const float* __restrict__ x, const float* __re
   }
 }
 
+// Gradient of image_resize_kernel with respect to its input, as a gather: one thread per INPUT pixel sums, in a fixed
+// order, the output gradients that read it (no atomics, so the result is bit-reproducible).  The candidate output rows /
+// columns come from inverting the coordinate map with a margin; each candidate is re-run through the forward map, so
+// the weights are exactly the forward pass's.
+__device__ __forceinline__ float resize_axis_weight(int o, int r, float scale, int n_in, int mode) {
+  if (mode == 0) return min((int)floorf((float)o * scale), n_in - 1) == r ? 1.f : 0.f;
+  const float f = fminf(fmaxf(((float)o + 0.5f) * scale - 0.5f, 0.f), (float)(n_in - 1));
+  const int i0 = (int)floorf(f), i1 = min(i0 + 1, n_in - 1);
+  const float w = f - (float)i0;
+  return (i0 == r ? 1.f - w : 0.f) + (i1 == r ? w : 0.f);
+}
+
+__global__ void image_resize_bwd_kernel(const float* __restrict__ g, float* __restrict__ dx, int planes, int Hi, int Wi, int Ho, int Wo, int mode) {
+  const long long plane_i = (long long)Hi * Wi, total = (long long)planes * plane_i;
+  const float scale_y = (float)Hi / (float)Ho, scale_x = (float)Wi / (float)Wo;
+  const float inv_y = (float)Ho / (float)Hi, inv_x = (float)Wo / (float)Wi;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long pl = i / plane_i, p = i - pl * plane_i;
+    const int r = (int)(p / Wi), c = (int)(p % Wi);
+    // outputs whose source coordinate can fall within one input pixel of (r, c); edge pixels also collect the clamped tail
+    int y_lo = max((int)floorf(((float)r - 1.f) * inv_y) - 2, 0), y_hi = min((int)ceilf(((float)r + 2.f) * inv_y) + 2, Ho - 1);
+    int x_lo = max((int)floorf(((float)c - 1.f) * inv_x) - 2, 0), x_hi = min((int)ceilf(((float)c + 2.f) * inv_x) + 2, Wo - 1);
+    if (r == 0) y_lo = 0;
+    if (r == Hi - 1) y_hi = Ho - 1;
+    if (c == 0) x_lo = 0;
+    if (c == Wi - 1) x_hi = Wo - 1;
+    const float* gp = g + pl * (long long)Ho * Wo;
+    float acc = 0.f;
+    for (int y = y_lo; y <= y_hi; ++y) {
+      const float wy = resize_axis_weight(y, r, scale_y, Hi, mode);
+      if (wy == 0.f) continue;
+      float row = 0.f;
+      for (int x = x_lo; x <= x_hi; ++x) {
+        const float wx = resize_axis_weight(x, c, scale_x, Wi, mode);
+        if (wx != 0.f) row += wx * gp[(long long)y * Wo + x];
+      }
+      acc += wy * row;
+    }
+    dx[i] = acc;
+  }
+}
+
 static inline int grid_for(long long n, int block = 256) {
   long long g = (n + block - 1) / block;
   return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
@@ -535,6 +577,12 @@ int oa_image_resize(const void* x, void* out, int planes, int channels, int Hi, 
   image_resize_kernel<<<grid_for((long long)planes * Ho * Wo), 256, 0, (cudaStream_t)stream>>>(
       (const float*)x, (float*)out, planes, channels, Hi, Wi, Ho, Wo, mode, norm ? mean3[0] : 0.f, norm ? mean3[1] : 0.f, norm ? mean3[2] : 0.f,
       norm ? std3[0] : 1.f, norm ? std3[1] : 1.f, norm ? std3[2] : 1.f, norm);
+  return (int)cudaGetLastError();
+}
+
+int oa_image_resize_bwd(const void* grad_out, void* grad_in, int planes, int Hi, int Wi, int Ho, int Wo, int mode, void* stream) {
+  image_resize_bwd_kernel<<<grid_for((long long)planes * Hi * Wi), 256, 0, (cudaStream_t)stream>>>((const float*)grad_out, (float*)grad_in, planes,
+                                                                                                     Hi, Wi, Ho, Wo, mode);
   return (int)cudaGetLastError();
 }
 

@@ -827,13 +827,59 @@ def _resize(t: torch.Tensor, Wo: int, Ho: int, mode: int, norm: Optional[OaNorma
     return out.contiguous()
 
 
+def _resize_axis_matrix(n_in: int, n_out: int, mode: int) -> torch.Tensor:
+    """[n_out, n_in] fp32 matrix of the resize along one axis (the forward pass is Wy @ x @ Wx^T)."""
+    o = torch.arange(n_out, dtype=torch.float32)
+    scale = torch.tensor(n_in / n_out, dtype=torch.float32)
+    m = torch.zeros(n_out, n_in, dtype=torch.float32)
+    rows = torch.arange(n_out)
+    if mode == 0:
+        m[rows, torch.floor(o * scale).long().clamp_max(n_in - 1)] = 1.0
+        return m
+    f = ((o + 0.5) * scale - 0.5).clamp(0, n_in - 1)
+    i0 = torch.floor(f).long()
+    i1 = (i0 + 1).clamp_max(n_in - 1)
+    w = f - i0.float()
+    m.index_put_((rows, i0), 1.0 - w, accumulate=True)
+    m.index_put_((rows, i1), w, accumulate=True)
+    return m
+
+
+def _resize_bwd(grad: torch.Tensor, H: int, W: int, mode: int) -> torch.Tensor:
+    g = grad.contiguous().float()
+    Nn, C, Ho, Wo = g.shape
+    if g.is_cuda:
+        dx = torch.empty((Nn, C, H, W), dtype=torch.float32, device=g.device)
+        K._launch(N.require().oa_image_resize_bwd(g.data_ptr(), dx.data_ptr(), Nn * C, H, W, Ho, Wo, mode, N.stream()), "oa_image_resize_bwd")
+        return dx
+    wy, wx = _resize_axis_matrix(H, Ho, mode), _resize_axis_matrix(W, Wo, mode)
+    return torch.einsum("oh,ncow,wv->nchv", wy, g, wx).contiguous()
+
+
+def ResizeBilinearBwd(GradOutput: OaMatrix, InputHeight: int, InputWidth: int) -> OaMatrix:
+    """Gradient of the bilinear `Resize` with respect to its [N, C, InputHeight, InputWidth] input."""
+    return OaMatrix(_resize_bwd(_t(GradOutput), int(InputHeight), int(InputWidth), 1))
+
+
+def ResizeNearestBwd(GradOutput: OaMatrix, InputHeight: int, InputWidth: int) -> OaMatrix:
+    """Gradient of the nearest-neighbour `Resize`: every input pixel collects the outputs that copied it."""
+    return OaMatrix(_resize_bwd(_t(GradOutput), int(InputHeight), int(InputWidth), 0))
+
+
 def Resize(Image, Width: int, Height: int, Interpolation: OaInterpolationMode = OaInterpolationMode.Bilinear):
-    """Nearest (floor of the scaled coordinate) or bilinear (half-pixel centres, clamped edges) resize."""
+    """Nearest (floor of the scaled coordinate) or bilinear (half-pixel centres, clamped edges) resize.  Records on the
+    gradient tape when the input requires a gradient."""
     if isinstance(Image, OaImage):
         return _on_image(Image, lambda m: Resize(m, Width, Height, Interpolation))
     if not _is_image(Image) or Width <= 0 or Height <= 0 or int(Interpolation) not in (0, 1):
         return Image
-    return OaMatrix(_resize(_t(Image), int(Width), int(Height), int(Interpolation)))
+    t = _t(Image)
+    out = OaMatrix(_resize(t, int(Width), int(Height), int(Interpolation)))
+    if isinstance(Image, OaMatrix) and Image.RequiresGrad():
+        from ..ml import autograd as AG
+        H, W, mode = t.shape[-2], t.shape[-1], int(Interpolation)
+        return AG.attach("Resize", out, [Image], lambda g: (_resize_bwd(g.reshape(out.Tensor().shape), H, W, mode).reshape(Image.Tensor().shape),))
+    return out
 
 
 def ResizeBatch(Images: Sequence[OaMatrix], TargetWidth: int, TargetHeight: int,

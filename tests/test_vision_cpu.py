@@ -238,3 +238,26 @@ def test_detection_evaluation_hand_worked():
     assert float(res.PerClass.Tensor()[0, 1, 3]) == 0
     assert torch.allclose(res.MeanAveragePrecisionByThreshold.Tensor(), torch.tensor([ap, 51 / 101]), atol=1e-5)
     assert abs(float(res.MeanAveragePrecision.Tensor()) - (ap + 51 / 101) / 2) < 1e-5
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("shape", [((5, 7), (11, 4)), ((8, 8), (3, 16)), ((6, 9), (6, 9)), ((1, 4), (5, 1))])
+def test_resize_backward_is_the_adjoint_of_resize(mode, shape):
+    """<Resize(x), g> == <x, ResizeBwd(g)> for random x, g, and the tape delivers the same gradient."""
+    from oa_b200.ml import autograd as AG
+    (H, W), (Ho, Wo) = shape
+    gen = torch.Generator().manual_seed(H * 100 + Wo)
+    x = torch.randn(2, 3, H, W, generator=gen)
+    g = torch.randn(2, 3, Ho, Wo, generator=gen)
+    from oa_b200.core import fn_matrix as F
+    FI = I
+    y = FI.Resize(OaMatrix(x), Wo, Ho, mode).Tensor()
+    bwd = (FI.ResizeBilinearBwd if mode else FI.ResizeNearestBwd)(OaMatrix(g), H, W).Tensor()
+    assert bwd.shape == x.shape and torch.allclose((y * g).sum(), (x * bwd).sum(), rtol=1e-4, atol=1e-4)
+    xm = OaMatrix(x.clone())
+    xm.SetRequiresGrad(True)
+    with AG.OaGradientTape() as tape:
+        out = FI.Resize(xm, Wo, Ho, mode)
+        loss = F.Sum(F.Mul(out, OaMatrix(g)))
+    tape.Backward(loss)
+    assert torch.allclose(xm.GradMatrix().Tensor(), bwd, atol=1e-5)

@@ -146,3 +146,12 @@ def test_detection_kernels():
     assert torch.allclose(rc.MeanAveragePrecisionByThreshold.Tensor(), rg.MeanAveragePrecisionByThreshold.Tensor().cpu(), atol=1e-5)
     assert torch.allclose(rc.MeanAveragePrecision.Tensor(), rg.MeanAveragePrecision.Tensor().cpu(), atol=1e-5)
     assert float(rc.MeanAveragePrecision.Tensor()) > 0.1
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_resize_backward_kernel(mode):
+    """The gather kernel against the dense axis-matrix formulation on CPU, up- and down-scaling, odd sizes."""
+    fn = I.ResizeBilinearBwd if mode else I.ResizeNearestBwd
+    for (H, W), (Ho, Wo) in (((70, 45), (33, 101)), ((16, 16), (64, 64)), ((64, 48), (7, 5)), ((5, 9), (5, 9)), ((1, 3), (4, 1))):
+        g = OaMatrix(torch.randn(2, 3, Ho, Wo, generator=torch.Generator().manual_seed(H + Wo)))
+        both(lambda m: fn(m, H, W), g, atol=2e-4)
