@@ -85,7 +85,8 @@ for _n in ("OaItRlTraining", "OaItRlTrainingConfig", "OaDqnLossConfig", "OaDqnLo
            "OaRlTransition", "OaRlReplayTransition", "OaRlActorCritic", "OaRlActorCriticOutput", "OaCategoricalActorCritic",
            "OaCategoricalActorCriticConfig", "OaRlCollector", "OaRlCollectorConfig", "OaRlCollectorMetrics", "OaRlEvaluationConfig",
            "OaRlEvaluationMetrics", "OaPpoTrainer", "OaPpoTrainerConfig", "OaPpoTrainerMetrics", "OaDqnTrainer", "OaDqnTrainerConfig",
-           "OaDqnTrainerMetrics", "OaSacTrainer", "OaSacTrainerConfig", "OaSacTrainerMetrics", "OaCartPoleConfig", "OaCartPoleEnvironment"):
+           "OaDqnTrainerMetrics", "OaSacTrainer", "OaSacTrainerConfig", "OaSacTrainerMetrics", "OaCartPoleConfig", "OaCartPoleEnvironment",
+           "OaLunarLander3dConfig", "OaLunarLander3dEnvironment"):
     globals()[_n] = getattr(_RL, _n)
 del _n
 

@@ -236,6 +236,12 @@ int oa_rl_cartpole_reset(void* state, void* done, void* steps, void* episode, in
 int oa_rl_cartpole_step(const void* action, void* state, void* trans_obs, void* reward, void* terminated, void* truncated,
                         void* done, void* steps, int envs, int max_steps, float gravity, float cart_mass, float pole_mass,
                         float half_len, float force, float dt, float x_limit, float angle_limit, void* stream);
+// LunarLander3d (lunar.cu).  cfg_f: 75 host floats, cfg_n: 6 host ints, spawn8: 8 host floats; the rest is device memory.
+int oa_rl_lunar_step(const float* cfg_f, const int* cfg_n, const void* terrain, const void* action, const void* external_stop, void* state_f,
+                     void* state_u, void* trans_obs, void* obs, void* reward, void* terminated, void* truncated, void* end_reason, int envs,
+                     void* stream);
+int oa_rl_lunar_reset(const float* cfg_f, const int* cfg_n, const float* spawn8, const void* terrain, void* state_f, void* state_u, void* obs,
+                      int envs, unsigned seed_lo, unsigned seed_hi, int only_done, void* stream);
 int oa_rl_gae(const void* reward, const void* value, const void* next_value, const void* terminated, const void* truncated,
               void* adv, void* ret, int T, int E, float gamma, float lambda, void* stream);
 int oa_rl_rollout_append(const void* obs, const void* action, const void* reward, const void* value, const void* next_value,

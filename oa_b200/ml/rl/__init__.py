@@ -1,6 +1,6 @@
 """Reinforcement learning: environments, advantage estimation, policies, storage, losses and the PPO / DQN / SAC trainers
 (Source/Public/Oa/Ml/Rl/*.h of the reference)."""
-from .environment import (OaCartPoleConfig, OaCartPoleEnvironment, OaRlEnvironment, OaRlEnvironmentSpec, OaRlEnvironmentTransition,
+from .environment import (OaCartPoleConfig, OaCartPoleEnvironment, OaLunarLander3dConfig, OaLunarLander3dEnvironment, OaRlEnvironment, OaRlEnvironmentSpec, OaRlEnvironmentTransition,
                           OaRlFieldSpec, OaRlSpaceKind)
 from .fn_rl import (OaDqnLossConfig, OaDqnLossResult, OaGaeConfig, OaGaeResult, OaPpoLossConfig, OaPpoLossResult,
                     OaRlContinuousPolicyResult, OaRlPolicyResult, OaSacCriticLossResult, OaSacLossConfig)

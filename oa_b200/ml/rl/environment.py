@@ -331,3 +331,112 @@ class OaCartPoleEnvironment(OaRlEnvironment):
 
     def RollbackRecordedState_(self) -> None:
         self._pending_seed = self._seed
+
+
+# ------------------------------------------------------------------------------------------ LunarLander3d
+from ...ops import lunar as LL
+
+
+@dataclass
+class OaLunarLander3dConfig:
+    """Vector LunarLander3d: lanes, seeds and the physics / reward / terrain constants (`ops.lunar.LunarParams`)."""
+    Environments: int = 1
+    Seed: int = 1
+    TerrainSeed: int = 1
+    Params: LL.LunarParams = field(default_factory=LL.LunarParams)
+    Spawn: tuple = LL.SPAWN_DEFAULT
+
+    def Validate(self) -> OaStatus:
+        p = self.Params
+        positive = (p.PolicyDt, p.Mass, *p.Inertia, p.MainThrust, p.AttitudeTorque, p.FuelCapacity, p.CellSize, p.PositionScale, p.VelocityScale,
+                    p.AngularScale, p.TerrainClearanceScale, p.FootClearanceScale, p.MaxContactImpulse)
+        if self.Environments <= 0 or p.Substeps <= 0 or p.ContactIterations <= 0 or p.CellsX <= 0 or p.CellsZ <= 0 or p.MaxEpisodeSteps <= 0 \
+                or len(p.Supports) != 7 or len(self.Spawn) != 8 or not all(math.isfinite(v) and v > 0 for v in positive):
+            return _invalid("LunarLander3d configuration must be finite and positive, with seven supports")
+        if not 0 <= p.Restitution <= 1 or p.Friction < 0 or not 0 < p.RewardGamma <= 1 or p.TaskMaximumY <= p.TaskMinimumY:
+            return _invalid("LunarLander3d restitution, friction, discount or altitude band out of range")
+        return OaStatus.Ok()
+
+
+class OaLunarLander3dEnvironment(OaRlEnvironment):
+    """Observation [E, 33] fp32, action Int32 in {0 coast, 1 main engine, 2/3 pitch, 4/5 roll, 6/7 yaw}.  An episode ends
+    (terminated) on a safe landing held for SafeDwellSteps, a hull impact, a hard foot impact, leaving the task volume, a
+    numerical failure or an invalid action, and is truncated at MaxEpisodeSteps or by an external stop flag.  Finished
+    lanes idle with zero reward until ResetCompleted re-spawns them."""
+
+    def __init__(self, config: Optional[OaLunarLander3dConfig] = None, engine: Optional[RT.OaEngine] = None):
+        super().__init__(engine)
+        self.Config = config or OaLunarLander3dConfig()
+        st = self.Config.Validate()
+        if not st:
+            raise ValueError(st.message)
+        E, dev, p = self.Config.Environments, self._engine.Device(), self.Config.Params
+        self._terrain = LL.make_terrain(p, self.Config.TerrainSeed).to(dev)
+        self._sf = torch.zeros(E, LL.STATE_F32, dtype=torch.float32, device=dev)
+        self._su = torch.zeros(E, LL.STATE_U32, dtype=torch.int32, device=dev)
+        self._obs_t = torch.zeros(E, LL.OBS_WIDTH, dtype=torch.float32, device=dev)
+        self._stop = torch.zeros(E, dtype=torch.uint8, device=dev)
+        self._obs = OaMatrix(self._obs_t)
+        self._seed = self._pending_seed = self.Config.Seed
+        self._spec = OaRlEnvironmentSpec(
+            Observation=OaRlFieldSpec.Box("observation", (LL.OBS_WIDTH,), OaScalarType.Float32, -1.0, 1.0),
+            Action=OaRlFieldSpec.Discrete("action", 8),
+            Reward=OaRlFieldSpec.Box("reward", ()),
+            Terminated=OaRlFieldSpec.Binary("terminated"),
+            Truncated=OaRlFieldSpec.Binary("truncated"))
+
+    @staticmethod
+    def Create(config: Optional[OaLunarLander3dConfig] = None):
+        cfg = config or OaLunarLander3dConfig()
+        st = cfg.Validate()
+        return (OaLunarLander3dEnvironment(cfg), st) if st else (None, st)
+
+    def Spec(self) -> OaRlEnvironmentSpec: return self._spec
+    def Environments(self) -> int: return self.Config.Environments
+    def Observation(self) -> OaMatrix: return self._obs
+    def Terrain(self) -> OaMatrix: return OaMatrix(self._terrain)
+    def StateF32(self) -> OaMatrix: return OaMatrix(self._sf)
+    def StateU32(self) -> OaMatrix: return OaMatrix(self._su)
+    def EndReason(self) -> OaMatrix: return OaMatrix(self._su[:, LL.U_REASON])
+    def EpisodeReturn(self) -> OaMatrix: return OaMatrix(self._sf[:, LL.S_RETURN])
+    def Done(self) -> OaMatrix: return OaMatrix(((self._su[:, LL.U_TERM] != 0) | (self._su[:, LL.U_TRUNC] != 0)).to(torch.uint8))
+
+    def RequestStop(self, lanes: Optional[Sequence[int]] = None) -> None:
+        """Truncate the given lanes (all by default) at their next step."""
+        if lanes is None:
+            self._stop.fill_(1)
+        else:
+            self._stop[torch.as_tensor(list(lanes), dtype=torch.long, device=self._stop.device)] = 1
+
+    def RecordResetEnvironment_(self, seed: int) -> OaStatus:
+        self._pending_seed = seed if seed else self.Config.Seed
+        F._ctx_add("RlLunarLander3dReset")
+        LL.reset(self.Config.Params, self._terrain, self._sf, self._su, self._obs_t, self._pending_seed, False, self.Config.Spawn)
+        self._stop.zero_()
+        return OaStatus.Ok()
+
+    def RecordStepEnvironment_(self, action: OaMatrix):
+        E, dev = self.Config.Environments, self._sf.device
+        F._ctx_add("RlLunarLander3dStep")
+        t_obs = torch.empty(E, LL.OBS_WIDTH, dtype=torch.float32, device=dev)
+        reward = torch.empty(E, dtype=torch.float32, device=dev)
+        term = torch.empty(E, dtype=torch.uint8, device=dev)
+        trunc = torch.empty(E, dtype=torch.uint8, device=dev)
+        reason = torch.empty(E, dtype=torch.int32, device=dev)
+        LL.step(self.Config.Params, self._terrain, action.Tensor().to(torch.int32), self._stop, self._sf, self._su, t_obs, self._obs_t, reward,
+                term, trunc, reason)
+        tr = OaRlEnvironmentTransition(OaMatrix(t_obs), OaMatrix(self._obs_t.clone()), OaMatrix(reward), OaMatrix(term), OaMatrix(trunc))
+        return tr, OaStatus.Ok()
+
+    def RecordResetCompleted_(self) -> OaStatus:
+        F._ctx_add("RlLunarLander3dReset")
+        done = (self._su[:, LL.U_TERM] != 0) | (self._su[:, LL.U_TRUNC] != 0)
+        LL.reset(self.Config.Params, self._terrain, self._sf, self._su, self._obs_t, self._pending_seed, True, self.Config.Spawn)
+        self._stop[done] = 0
+        return OaStatus.Ok()
+
+    def CommitRecordedState_(self) -> None:
+        self._seed = self._pending_seed
+
+    def RollbackRecordedState_(self) -> None:
+        self._pending_seed = self._seed
