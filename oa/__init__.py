@@ -173,6 +173,12 @@ from oa_b200.extensions.alm import (OaAlmAg, OaAlmDatasetConfig, OaAlmFfnType, O
 from oa_b200.ml.precision import (OaLoadStoreStrideBytes, OaLookupPrecision, OaPipelineNameIsF32Variant, OaPrecisionDtype, OaPrecisionTag)
 
 
+# ---- codecs and transport
+from oa_b200.audio.codec import OaAudioDecoder, OaAudioEncoder
+from oa_b200.network import OaTcpFramed, OaTcpListener, OaTcpStream
+from oa_b200.vision.codec import OaImageCodec
+
+
 class Context:
     """Executes and synchronises the default context on scope exit."""
 
