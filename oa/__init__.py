@@ -179,6 +179,11 @@ from oa_b200.network import OaTcpFramed, OaTcpListener, OaTcpStream
 from oa_b200.vision.codec import OaImageCodec
 
 
+# ---- animation
+from oa_b200.animation import (OaCurveColor, OaCurveFloat, OaCurveQuat, OaCurveVec3, OaEasing, OaFrameRate, OaKeyInterpolation, OaKeyframe,
+                               OaKeyframeTrack, OaTimeCode, OaTimeDirection, OaTimeTransform, OaTimeline, OaTimelineState)
+
+
 class Context:
     """Executes and synchronises the default context on scope exit."""
 
