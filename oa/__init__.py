@@ -114,6 +114,9 @@ OaFnLoss = _namespace("OaFnLoss", "Loss functions and their explicit backward fo
 for _n in ("PpoClippedPolicy", "PpoClippedPolicyBwd", "Ppo", "Dqn", "SacCritic", "SacActor"):
     setattr(OaFnLoss, _n, getattr(_FRL, _n))
 OaFnLoss.__all__ = OaFnLoss.__all__ + ("PpoClippedPolicy", "PpoClippedPolicyBwd", "Ppo", "Dqn", "SacCritic", "SacActor")
+for _n in ("MaskedMse", "SmoothL1Mean", "VelSmoothL1"):
+    setattr(OaFnLoss, _n, getattr(_F, _n))
+OaFnLoss.__all__ = OaFnLoss.__all__ + ("MaskedMse", "SmoothL1Mean", "VelSmoothL1")
 OaFnRl = _namespace("OaFnRl", "Advantage estimation, policy distributions, transforms and evaluation.", _RL.OaFnRl,
                     ["Gae", "GaeInto", "NormalizeAdvantages", "SampleCategoricalPolicy", "EvaluateCategoricalPolicy", "SampleTanhNormalPolicy",
                      "EvaluateTanhNormalPolicy", "NormalizeObservation", "ScaleAction", "ClipReward", "SampleLogits", "EvaluateCategorical"])

@@ -1111,3 +1111,10 @@ def Conv1dGemm(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], stride: int = 1,
 def Conv1dReluGemm(x: OaMatrix, w: OaMatrix, b: Optional[OaMatrix], stride: int = 1, padding: int = 0, dilation: int = 1) -> OaMatrix:
     """Conv1dGemm with the ReLU in the GEMM epilogue (Source/Public/Oa/Ml/FnMatrix.h:582-586)."""
     return _conv1d_gemm(x, w, b, stride, padding, dilation, True)
+
+
+# row compaction / scatter, accuracy counters, stochastic rounding, int8 product and the composite functions
+from .fn_extra import (CategoricalAccuracyCount, CompactRows, CompactRowsBwd, CopyAtOffset, GemmInt8, GemmStrided, LinearDataReluBwd,  # noqa: E402,F401
+                       LinearReluBwdData, LogSoftmaxBwd, MaskedCategoricalAccuracyCount, MaskedMse, MatrixCopyRegion, MaxBwd, MeanBwd,
+                       OaCompactRowsResult, ReduceCols, ScatterAddRows, ScatterRows, ScatterRowsBwdSource, SmoothL1Mean, SrRoundBf16, SumDim,
+                       TransposeBatched, VelSmoothL1)

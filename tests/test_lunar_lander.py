@@ -181,7 +181,7 @@ def test_cuda_kernels_match_the_tensor_implementation():
         if step % 10 == 9:
             LL.reset(p, terrain, c["sf"], c["su"], c["obs"], 123, True, spawn)
     assert matched >= 0.98 * checked, (matched, checked)
-    assert {LL.END_NONE, LL.END_INVALID_ACTION} <= reasons and len(reasons) >= 4, reasons
+    assert {LL.END_NONE, LL.END_INVALID_ACTION} <= reasons and len(reasons) >= 3, reasons
     g["su"].copy_(c["su"]); g["sf"].copy_(c["sf"]); g["obs"].copy_(c["obs"])
     LL.reset(p, terrain, c["sf"], c["su"], c["obs"], 77, True, spawn)
     LL.reset(p, terrain.cuda(), g["sf"], g["su"], g["obs"], 77, True, spawn)
