@@ -187,6 +187,12 @@ from oa_b200.animation import (OaCurveColor, OaCurveFloat, OaCurveQuat, OaCurveV
                                OaKeyframeTrack, OaTimeCode, OaTimeDirection, OaTimeTransform, OaTimeline, OaTimelineState)
 
 
+# ---- logging, performance records
+from oa_b200.utils.log import (OA_LOG_DEBUG, OA_LOG_ERROR, OA_LOG_INFO, OA_LOG_TRACE, OA_LOG_WARN, OaGetComponentName, OaLog, OaLogComponent,
+                               OaLogLevel, OaLogSummary, OaMetricsWriter)
+from oa_b200.utils.perf import OaNvtxRange, OaPerfRecord, OaPerfStat, OaPerfStore
+
+
 class Context:
     """Executes and synchronises the default context on scope exit."""
 

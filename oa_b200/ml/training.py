@@ -13,6 +13,7 @@ Philox nodes.
 from __future__ import annotations
 
 import os
+import contextlib
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Optional
@@ -211,7 +212,8 @@ class OaItTraining:
             if prepare is not None:
                 prepare()
             t0 = time.perf_counter()
-            self._program.Replay()
+            with self._range("step.replay"):
+                self._program.Replay()
             self.Opt_.NotifyProgramReplay()
             self.Phase.SubmitMs = (time.perf_counter() - t0) * 1e3
             return self._finish_step(self._static_loss, stepped=True)
@@ -233,13 +235,22 @@ class OaItTraining:
             self.Opt_.NotifyProgramReplay()
             return self._finish_step(self._static_loss, stepped=True)
         t0 = time.perf_counter()
-        loss = record()
+        with self._range("step.body"):
+            loss = record()
         self.Phase.BodyMs = (time.perf_counter() - t0) * 1e3
         return self.Next(loss)
 
+    def _range(self, name: str):
+        """Profiler range around a phase of the step when OA_NVTX is set (a system profiler then shows the phases)."""
+        if not envflag.IsSet("OA_NVTX"):
+            return contextlib.nullcontext()
+        from ..utils.perf import OaNvtxRange
+        return OaNvtxRange(name)
+
     def Next(self, loss: OaMatrix) -> float:
         t0 = time.perf_counter()
-        self.Opt_.Step()
+        with self._range("step.optimizer"):
+            self.Opt_.Step()
         self.Phase.OptimizerMs = (time.perf_counter() - t0) * 1e3
         return self._finish_step(loss, stepped=True)
 
