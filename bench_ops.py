@@ -329,12 +329,56 @@ def bench_tp():
     dist.destroy_process_group()
 
 
+def bench_misc():
+    """LunarLander3d stepping (lanes per second), row compaction / scatter / accuracy counters / stochastic rounding and the
+    resize backward kernel, each on inputs larger than L2; algorithmic bytes as stated per case."""
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.core.matrix import OaMatrix
+    from oa_b200.ops import lunar as LL
+    from oa_b200.vision import fn_image as I
+    p = LL.LunarParams()
+    terrain = LL.make_terrain(p, 1).cuda()
+    E = 1 << 18
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device="cuda")
+    sf, su, tr, obs = z(E, 32), z(E, 16, dt=torch.int32), z(E, 33), z(E, 33)
+    rew, term, trunc, reason, stop = z(E), z(E, dt=torch.uint8), z(E, dt=torch.uint8), z(E, dt=torch.int32), z(E, dt=torch.uint8)
+    LL.reset(p, terrain, sf, su, obs, 7, False)
+    action = torch.randint(0, 8, (E,), device="cuda", dtype=torch.int32)
+
+    def step():
+        LL.step(p, terrain, action, stop, sf, su, tr, obs, rew, term, trunc, reason)
+        LL.reset(p, terrain, sf, su, obs, 7, True)
+    t = timeit(step, iters=9, warm=3)
+    emit(op="rl.lunar_lander3d_step+reset", lanes=E, ms=t, lanes_per_s=E / t * 1e3, gbs=E * (2 * 192 + 2 * 132 + 4 + 10) / t / 1e6)
+    T, D = 1 << 20, 64
+    x = OaMatrix(torch.randn(T, D, device="cuda", dtype=torch.bfloat16))
+    mask = OaMatrix((torch.rand(T, device="cuda") > 0.5).float())
+    r = F.CompactRows(x, mask)
+    nb = T * D * 2
+    t = timeit(lambda: F.CompactRows(x, mask), iters=9, warm=3)
+    emit(op="rows.compact", shape=[T, D], dtype="bf16", ms=t, gbs=(nb + nb / 2 + nb) / t / 1e6)             # read x, write half, zero-fill
+    base = OaMatrix(torch.zeros(T, D, device="cuda", dtype=torch.bfloat16))
+    t = timeit(lambda: F.ScatterRows(base, r.Values, r), iters=9, warm=3)
+    emit(op="rows.scatter", shape=[T, D], dtype="bf16", ms=t, gbs=(2 * nb + nb) / t / 1e6)                  # clone base, move half in and out
+    logits = OaMatrix(torch.randn(1 << 15, 8192, device="cuda", dtype=torch.bfloat16))
+    labels = OaMatrix(torch.randint(0, 8192, (1 << 15,), device="cuda", dtype=torch.int32))
+    t = timeit(lambda: F.CategoricalAccuracyCount(logits, labels), iters=9, warm=3)
+    emit(op="accuracy_count", shape=[1 << 15, 8192], dtype="bf16", ms=t, gbs=(1 << 15) * 8192 * 2 / t / 1e6)
+    w = OaMatrix(torch.randn(1 << 27, device="cuda"))
+    t = timeit(lambda: F.SrRoundBf16(w, 3), iters=9, warm=3)
+    emit(op="sr_round_bf16", n=1 << 27, ms=t, gbs=(1 << 27) * 6 / t / 1e6)
+    g = OaMatrix(torch.rand(8, 3, 540, 960, device="cuda"))
+    t = timeit(lambda: I.ResizeBilinearBwd(g, 1080, 1920), iters=9, warm=3)
+    emit(op="image.resize_bilinear_bwd_2x", shape=[8, 3, 1080, 1920], ms=t, gbs=(8 * 3 * 540 * 960 * 4 + 8 * 3 * 1080 * 1920 * 4) / t / 1e6)
+    K.check_status()
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image, "decode_attn": bench_decode_attn, "gemm_small_m": bench_gemm_small_m}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image, "decode_attn": bench_decode_attn, "gemm_small_m": bench_gemm_small_m, "misc": bench_misc}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:
