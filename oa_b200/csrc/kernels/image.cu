@@ -476,24 +476,44 @@ __global__ void image_resize_bwd_kernel(const float* __restrict__ g, float* __re
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long pl = i / plane_i, p = i - pl * plane_i;
     const int r = (int)(p / Wi), c = (int)(p % Wi);
-    // outputs whose source coordinate can fall within one input pixel of (r, c); edge pixels also collect the clamped tail
-    int y_lo = max((int)floorf(((float)r - 1.f) * inv_y) - 2, 0), y_hi = min((int)ceilf(((float)r + 2.f) * inv_y) + 2, Ho - 1);
-    int x_lo = max((int)floorf(((float)c - 1.f) * inv_x) - 2, 0), x_hi = min((int)ceilf(((float)c + 2.f) * inv_x) + 2, Wo - 1);
+    // outputs whose source coordinate lies within one input pixel of (r, c), plus one of margin; the edge pixels also
+    // collect the outputs whose coordinate was clamped onto them
+    int y_lo = max((int)floorf(((float)r - 0.5f) * inv_y - 0.5f) - 1, 0);
+    int y_hi = min((int)ceilf(fmaxf(((float)r + 1.5f) * inv_y - 0.5f, (float)(r + 1) * inv_y)) + 1, Ho - 1);
+    int x_lo = max((int)floorf(((float)c - 0.5f) * inv_x - 0.5f) - 1, 0);
+    int x_hi = min((int)ceilf(fmaxf(((float)c + 1.5f) * inv_x - 0.5f, (float)(c + 1) * inv_x)) + 1, Wo - 1);
     if (r == 0) y_lo = 0;
     if (r == Hi - 1) y_hi = Ho - 1;
     if (c == 0) x_lo = 0;
     if (c == Wi - 1) x_hi = Wo - 1;
     const float* gp = g + pl * (long long)Ho * Wo;
     float acc = 0.f;
-    for (int y = y_lo; y <= y_hi; ++y) {
-      const float wy = resize_axis_weight(y, r, scale_y, Hi, mode);
-      if (wy == 0.f) continue;
-      float row = 0.f;
-      for (int x = x_lo; x <= x_hi; ++x) {
-        const float wx = resize_axis_weight(x, c, scale_x, Wi, mode);
-        if (wx != 0.f) row += wx * gp[(long long)y * Wo + x];
+    const int nx = x_hi - x_lo + 1;
+    if (nx <= 8) {                                   // the usual case: column weights once, in registers
+      float wxs[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wxs[j] = j < nx ? resize_axis_weight(x_lo + j, c, scale_x, Wi, mode) : 0.f;
+      for (int y = y_lo; y <= y_hi; ++y) {
+        const float wy = resize_axis_weight(y, r, scale_y, Hi, mode);
+        if (wy == 0.f) continue;
+        const float* grow = gp + (long long)y * Wo + x_lo;
+        float row = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (wxs[j] != 0.f) row += wxs[j] * grow[j];
+        acc += wy * row;
       }
-      acc += wy * row;
+    } else {
+      for (int y = y_lo; y <= y_hi; ++y) {
+        const float wy = resize_axis_weight(y, r, scale_y, Hi, mode);
+        if (wy == 0.f) continue;
+        float row = 0.f;
+        for (int x = x_lo; x <= x_hi; ++x) {
+          const float wx = resize_axis_weight(x, c, scale_x, Wi, mode);
+          if (wx != 0.f) row += wx * gp[(long long)y * Wo + x];
+        }
+        acc += wy * row;
+      }
     }
     dx[i] = acc;
   }

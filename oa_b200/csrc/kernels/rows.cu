@@ -14,8 +14,10 @@ __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 
 // Exclusive prefix sum of a 0/1 mask by ONE block: position[r] = number of selected rows before r, count[0] = total.
-// One block keeps the order stable and the result independent of the launch shape; a million rows take ~1000 rounds
-// of a 1024-wide scan, which is tens of microseconds.
+// One block keeps the order stable and the result independent of the launch shape.  Every thread takes 16 consecutive
+// rows per round, so a round covers 16384 rows and a million rows take 64 rounds (a few microseconds each).
+constexpr int SCAN_PER_THREAD = 16;
+
 __global__ void __launch_bounds__(1024)
 rows_scan_kernel(const unsigned char* __restrict__ mask, int* __restrict__ position, int* __restrict__ count, int rows) {
   __shared__ int warp_sums[32];
@@ -23,10 +25,14 @@ rows_scan_kernel(const unsigned char* __restrict__ mask, int* __restrict__ posit
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) carry = 0;
   __syncthreads();
-  for (int base = 0; base < rows; base += 1024) {
-    const int r = base + threadIdx.x;
-    const int flag = (r < rows && mask[r] != 0) ? 1 : 0;
-    int incl = flag;
+  for (int base = 0; base < rows; base += 1024 * SCAN_PER_THREAD) {
+    const int r0 = base + threadIdx.x * SCAN_PER_THREAD;
+    unsigned flags = 0;                                  // bit i = row r0 + i is selected
+#pragma unroll
+    for (int i = 0; i < SCAN_PER_THREAD; ++i)
+      if (r0 + i < rows && mask[r0 + i] != 0) flags |= 1u << i;
+    const int mine = __popc(flags);
+    int incl = mine;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       const int up = __shfl_up_sync(0xffffffffu, incl, d);
@@ -44,10 +50,12 @@ rows_scan_kernel(const unsigned char* __restrict__ mask, int* __restrict__ posit
       warp_sums[lane] = s;                      // inclusive sums of the warps
     }
     __syncthreads();
-    const int before = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - flag;
-    if (r < rows) position[r] = before;
+    const int before = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - mine;
+#pragma unroll
+    for (int i = 0; i < SCAN_PER_THREAD; ++i)
+      if (r0 + i < rows) position[r0 + i] = before + __popc(flags & ((1u << i) - 1u));
     __syncthreads();
-    if (threadIdx.x == 1023) carry = before + flag;
+    if (threadIdx.x == 1023) carry = before + mine;
     __syncthreads();
   }
   if (threadIdx.x == 0) count[0] = carry;
