@@ -10,6 +10,8 @@
 
 namespace oa {
 
+template <typename T> __device__ __forceinline__ T zero_of() { return T(0); }
+template <> __device__ __forceinline__ uint4 zero_of<uint4>() { return make_uint4(0u, 0u, 0u, 0u); }
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 
@@ -85,7 +87,7 @@ __global__ void rows_scatter_kernel(const T* __restrict__ packed, const int* __r
     const int p = (int)(i / width), c = (int)(i - (long long)p * width);
     const int r = index[p];
     if (r < 0 || r >= out_rows) continue;
-    if (ADD) atomicAdd(&out[(long long)r * width + c], packed[i]);
+    if constexpr (ADD) atomicAdd(&out[(long long)r * width + c], packed[i]);
     else out[(long long)r * width + c] = packed[i];
   }
 }
@@ -98,7 +100,7 @@ __global__ void rows_gather_kernel(const T* __restrict__ src, const int* __restr
   const long long total = (long long)capacity * width;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int p = (int)(i / width), c = (int)(i - (long long)p * width);
-    T v = T(0);
+    T v = zero_of<T>();
     if (p < n) {
       const int r = index[p];
       if (r >= 0 && r < src_rows) v = src[(long long)r * width + c];
@@ -173,6 +175,11 @@ gemm_int8_kernel(const signed char* __restrict__ a, const signed char* __restric
   if (c_f32 != nullptr) c_f32[(long long)m * N + n] = (float)acc * (row_scale ? row_scale[m] : 1.f) * (col_scale ? col_scale[n] : 1.f);
 }
 
+// Rows whose byte width is a multiple of 16 (and whose buffers are 16-byte aligned) move as 16-byte vectors.
+static inline bool rows_vectorisable(const void* a, const void* b, int width, int elem_bytes) {
+  return ((long long)width * elem_bytes) % 16 == 0 && (((uintptr_t)a | (uintptr_t)b) & 15) == 0;
+}
+
 static inline int rows_grid(long long n) {
   long long g = (n + 255) / 256;
   return (int)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
@@ -190,6 +197,12 @@ int oa_rows_scan(const void* mask, void* position, void* count, int rows, void* 
 int oa_rows_compact(const void* x, const void* mask, const void* position, void* packed, void* index, int rows, int width, int elem_bytes,
                     void* stream) {
   if (rows <= 0 || width <= 0) return rows == 0 ? 0 : OA_ERR_ARG;
+  if (rows_vectorisable(x, packed, width, elem_bytes)) {
+    const int vecs = (int)((long long)width * elem_bytes / 16);
+    rows_compact_kernel<uint4><<<rows_grid((long long)rows * vecs), 256, 0, (cudaStream_t)stream>>>(
+        (const uint4*)x, (const unsigned char*)mask, (const int*)position, (uint4*)packed, (int*)index, rows, vecs);
+    return (int)cudaGetLastError();
+  }
   const int g = rows_grid((long long)rows * width);
   if (elem_bytes == 4)
     rows_compact_kernel<float><<<g, 256, 0, (cudaStream_t)stream>>>((const float*)x, (const unsigned char*)mask, (const int*)position, (float*)packed,
@@ -205,8 +218,15 @@ int oa_rows_compact(const void* x, const void* mask, const void* position, void*
 int oa_rows_scatter(const void* packed, const void* index, const void* count, void* out, int capacity, int out_rows, int width, int dtype, int add,
                     void* stream) {
   if (capacity <= 0 || width <= 0) return capacity == 0 ? 0 : OA_ERR_ARG;
-  const int g = rows_grid((long long)capacity * width);
   cudaStream_t s = (cudaStream_t)stream;
+  const int eb = dtype == OA_F32 ? 4 : 2;
+  if (!add && (dtype == OA_F32 || dtype == OA_BF16) && rows_vectorisable(packed, out, width, eb)) {
+    const int vecs = (int)((long long)width * eb / 16);
+    rows_scatter_kernel<uint4, false><<<rows_grid((long long)capacity * vecs), 256, 0, s>>>((const uint4*)packed, (const int*)index, (const int*)count,
+                                                                                          (uint4*)out, capacity, out_rows, vecs);
+    return (int)cudaGetLastError();
+  }
+  const int g = rows_grid((long long)capacity * width);
   if (dtype == OA_F32) {
     if (add) rows_scatter_kernel<float, true><<<g, 256, 0, s>>>((const float*)packed, (const int*)index, (const int*)count, (float*)out, capacity, out_rows, width);
     else rows_scatter_kernel<float, false><<<g, 256, 0, s>>>((const float*)packed, (const int*)index, (const int*)count, (float*)out, capacity, out_rows, width);
@@ -223,6 +243,12 @@ int oa_rows_scatter(const void* packed, const void* index, const void* count, vo
 int oa_rows_gather(const void* src, const void* index, const void* count, void* packed, int capacity, int src_rows, int width, int elem_bytes,
                    void* stream) {
   if (capacity <= 0 || width <= 0) return capacity == 0 ? 0 : OA_ERR_ARG;
+  if (rows_vectorisable(src, packed, width, elem_bytes)) {
+    const int vecs = (int)((long long)width * elem_bytes / 16);
+    rows_gather_kernel<uint4><<<rows_grid((long long)capacity * vecs), 256, 0, (cudaStream_t)stream>>>(
+        (const uint4*)src, (const int*)index, (const int*)count, (uint4*)packed, capacity, src_rows, vecs);
+    return (int)cudaGetLastError();
+  }
   const int g = rows_grid((long long)capacity * width);
   if (elem_bytes == 4)
     rows_gather_kernel<float><<<g, 256, 0, (cudaStream_t)stream>>>((const float*)src, (const int*)index, (const int*)count, (float*)packed, capacity,

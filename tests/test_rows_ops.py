@@ -40,6 +40,19 @@ def _compact_suite(device):
     rb = F.CompactRows(_m(xb, device), _m(mb, device))
     nb = int(rb.Count.Tensor()[0])
     assert nb == int(mb.sum()) and torch.equal(rb.Values.Tensor()[:nb].cpu(), xb[torch.nonzero(mb).reshape(-1)])
+    # rows whose byte width is a multiple of 16 take the 16-byte vector path on the GPU
+    for shape, dt in (((300, 64), torch.bfloat16), ((50, 8), torch.float32), ((129, 4), torch.float32)):
+        xv = torch.randn(*shape, generator=g).to(dt)
+        mv = (torch.rand(shape[0], generator=g) > 0.4).float()
+        sv = torch.nonzero(mv).reshape(-1)
+        rv = F.CompactRows(_m(xv, device), _m(mv, device))
+        nv = int(rv.Count.Tensor()[0])
+        assert nv == sv.numel() and torch.equal(rv.Values.Tensor()[:nv].cpu(), xv[sv]) and float(rv.Values.Tensor()[nv:].float().abs().sum()) == 0
+        basev = torch.ones(*shape).to(dt)
+        scv = F.ScatterRows(_m(basev, device), rv.Values, rv).Tensor().cpu()
+        assert torch.equal(scv, torch.where(mv[:, None] != 0, xv, basev))
+        gv = F.ScatterRowsBwdSource(_m(xv, device), rv.RowMap, rv.Count).Tensor().cpu()
+        assert torch.equal(gv[:nv], xv[sv]) and float(gv[nv:].float().abs().sum()) == 0
     # gradients through the tape: d/dx sum(w * compact(x)) and through ScatterRows
     xm = _m(x.clone(), device); xm.SetRequiresGrad(True)
     w = torch.randn(37, 5, generator=g)
