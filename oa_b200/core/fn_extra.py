@@ -58,7 +58,8 @@ def _compact(x: torch.Tensor, mask: torch.Tensor):
         count = torch.empty(1, dtype=torch.int32, device=x.device)
         values = torch.zeros_like(x)
         rowmap = torch.zeros(T, dtype=torch.int32, device=x.device)
-        K._launch(lib.oa_rows_scan(mask.data_ptr(), pos.data_ptr(), count.data_ptr(), T, N.stream()), "oa_rows_scan")
+        scratch = torch.empty(int(lib.oa_rows_scan_scratch_ints(T)), dtype=torch.int32, device=x.device)
+        K._launch(lib.oa_rows_scan(mask.data_ptr(), pos.data_ptr(), count.data_ptr(), scratch.data_ptr(), T, N.stream()), "oa_rows_scan")
         K._launch(lib.oa_rows_compact(x.data_ptr(), mask.data_ptr(), pos.data_ptr(), values.data_ptr(), rowmap.data_ptr(), T, D,
                                       x.element_size(), N.stream()), "oa_rows_compact")
     else:

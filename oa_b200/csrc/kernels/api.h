@@ -237,7 +237,8 @@ int oa_rl_cartpole_step(const void* action, void* state, void* trans_obs, void* 
                         void* done, void* steps, int envs, int max_steps, float gravity, float cart_mass, float pole_mass,
                         float half_len, float force, float dt, float x_limit, float angle_limit, void* stream);
 // ---- rows.cu: row compaction / scatter with a device-resident count, accuracy counters, stochastic rounding, int8 GEMM
-int oa_rows_scan(const void* mask, void* position, void* count, int rows, void* stream);
+size_t oa_rows_scan_scratch_ints(int rows);
+int oa_rows_scan(const void* mask, void* position, void* count, void* scratch, int rows, void* stream);
 int oa_rows_compact(const void* x, const void* mask, const void* position, void* packed, void* index, int rows, int width, int elem_bytes,
                     void* stream);
 int oa_rows_scatter(const void* packed, const void* index, const void* count, void* out, int capacity, int out_rows, int width, int dtype, int add,

@@ -15,52 +15,83 @@ template <> __device__ __forceinline__ uint4 zero_of<uint4>() { return make_uint
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// Exclusive prefix sum of a 0/1 mask by ONE block: position[r] = number of selected rows before r, count[0] = total.
-// One block keeps the order stable and the result independent of the launch shape.  Every thread takes 16 consecutive
-// rows per round, so a round covers 16384 rows and a million rows take 64 rounds (a few microseconds each).
+// Exclusive prefix sum of a 0/1 mask: position[r] = number of selected rows before r, count[0] = total.  Three launches
+// without any wait between blocks: (1) every block counts its 16,384 rows, (2) one block turns the block counts into
+// block offsets, (3) every block scans its own rows and adds its offset.  The order is stable and the result does not
+// depend on the launch shape.
 constexpr int SCAN_PER_THREAD = 16;
+constexpr int SCAN_BLOCK_ROWS = 1024 * SCAN_PER_THREAD;
 
-__global__ void __launch_bounds__(1024)
-rows_scan_kernel(const unsigned char* __restrict__ mask, int* __restrict__ position, int* __restrict__ count, int rows) {
-  __shared__ int warp_sums[32];
-  __shared__ int carry;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) carry = 0;
-  __syncthreads();
-  for (int base = 0; base < rows; base += 1024 * SCAN_PER_THREAD) {
-    const int r0 = base + threadIdx.x * SCAN_PER_THREAD;
-    unsigned flags = 0;                                  // bit i = row r0 + i is selected
+__device__ __forceinline__ unsigned scan_flags(const unsigned char* __restrict__ mask, int r0, int rows) {
+  unsigned flags = 0;                                  // bit i = row r0 + i is selected
 #pragma unroll
-    for (int i = 0; i < SCAN_PER_THREAD; ++i)
-      if (r0 + i < rows && mask[r0 + i] != 0) flags |= 1u << i;
-    const int mine = __popc(flags);
-    int incl = mine;
+  for (int i = 0; i < SCAN_PER_THREAD; ++i)
+    if (r0 + i < rows && mask[r0 + i] != 0) flags |= 1u << i;
+  return flags;
+}
+
+// Inclusive sum over the 1024 threads of a block; every thread gets its own inclusive value, *total the block's sum.
+__device__ __forceinline__ int block_inclusive_scan(int mine, int* warp_sums, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += up;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int s = warp_sums[lane];
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-      const int up = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += up;
+      const int up = __shfl_up_sync(0xffffffffu, s, d);
+      if (lane >= d) s += up;
     }
-    if (lane == 31) warp_sums[warp] = incl;
-    __syncthreads();
-    if (warp == 0) {
-      int s = warp_sums[lane];
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, s, d);
-        if (lane >= d) s += up;
-      }
-      warp_sums[lane] = s;                      // inclusive sums of the warps
-    }
-    __syncthreads();
-    const int before = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - mine;
-#pragma unroll
-    for (int i = 0; i < SCAN_PER_THREAD; ++i)
-      if (r0 + i < rows) position[r0 + i] = before + __popc(flags & ((1u << i) - 1u));
-    __syncthreads();
-    if (threadIdx.x == 1023) carry = before + mine;
-    __syncthreads();
+    warp_sums[lane] = s;
+  }
+  __syncthreads();
+  const int out = incl + (warp > 0 ? warp_sums[warp - 1] : 0);
+  *total = warp_sums[31];
+  __syncthreads();                                      // warp_sums may be reused by the caller's next round
+  return out;
+}
+
+__global__ void __launch_bounds__(1024)
+rows_block_count_kernel(const unsigned char* __restrict__ mask, int* __restrict__ block_counts, int rows) {
+  __shared__ int warp_sums[32];
+  const int r0 = blockIdx.x * SCAN_BLOCK_ROWS + threadIdx.x * SCAN_PER_THREAD;
+  int total;
+  block_inclusive_scan(__popc(scan_flags(mask, r0, rows)), warp_sums, &total);
+  if (threadIdx.x == 0) block_counts[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(1024)
+rows_block_offsets_kernel(const int* __restrict__ block_counts, int* __restrict__ block_offsets, int* __restrict__ count, int nblocks) {
+  __shared__ int warp_sums[32];
+  int carry = 0;                                        // identical in every thread
+  for (int base = 0; base < nblocks; base += 1024) {
+    const int b = base + threadIdx.x;
+    const int mine = b < nblocks ? block_counts[b] : 0;
+    int total;
+    const int incl = block_inclusive_scan(mine, warp_sums, &total);
+    if (b < nblocks) block_offsets[b] = carry + incl - mine;
+    carry += total;
   }
   if (threadIdx.x == 0) count[0] = carry;
+}
+
+__global__ void __launch_bounds__(1024)
+rows_block_positions_kernel(const unsigned char* __restrict__ mask, const int* __restrict__ block_offsets, int* __restrict__ position, int rows) {
+  __shared__ int warp_sums[32];
+  const int r0 = blockIdx.x * SCAN_BLOCK_ROWS + threadIdx.x * SCAN_PER_THREAD;
+  const unsigned flags = scan_flags(mask, r0, rows);
+  const int mine = __popc(flags);
+  int total;
+  const int before = block_offsets[blockIdx.x] + block_inclusive_scan(mine, warp_sums, &total) - mine;
+#pragma unroll
+  for (int i = 0; i < SCAN_PER_THREAD; ++i)
+    if (r0 + i < rows) position[r0 + i] = before + __popc(flags & ((1u << i) - 1u));
 }
 
 // packed[position[r], :] = x[r, :] and index[position[r]] = r for every selected row r.
@@ -187,9 +218,18 @@ static inline int rows_grid(long long n) {
 
 extern "C" {
 
-int oa_rows_scan(const void* mask, void* position, void* count, int rows, void* stream) {
+size_t oa_rows_scan_scratch_ints(int rows) { return 2 * (size_t)((rows + SCAN_BLOCK_ROWS - 1) / SCAN_BLOCK_ROWS) + 2; }
+
+// scratch: oa_rows_scan_scratch_ints(rows) int32 values of device memory
+int oa_rows_scan(const void* mask, void* position, void* count, void* scratch, int rows, void* stream) {
   if (rows < 0) return OA_ERR_ARG;
-  rows_scan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((const unsigned char*)mask, (int*)position, (int*)count, rows);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int nblocks = (rows + SCAN_BLOCK_ROWS - 1) / SCAN_BLOCK_ROWS;
+  int* block_counts = (int*)scratch;
+  int* block_offsets = block_counts + nblocks + 1;
+  if (nblocks > 0) rows_block_count_kernel<<<nblocks, 1024, 0, s>>>((const unsigned char*)mask, block_counts, rows);
+  rows_block_offsets_kernel<<<1, 1024, 0, s>>>(block_counts, block_offsets, (int*)count, nblocks);
+  if (nblocks > 0) rows_block_positions_kernel<<<nblocks, 1024, 0, s>>>((const unsigned char*)mask, block_offsets, (int*)position, rows);
   return (int)cudaGetLastError();
 }
 

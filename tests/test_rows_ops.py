@@ -41,7 +41,7 @@ def _compact_suite(device):
     nb = int(rb.Count.Tensor()[0])
     assert nb == int(mb.sum()) and torch.equal(rb.Values.Tensor()[:nb].cpu(), xb[torch.nonzero(mb).reshape(-1)])
     # rows whose byte width is a multiple of 16 take the 16-byte vector path on the GPU
-    for shape, dt in (((300, 64), torch.bfloat16), ((50, 8), torch.float32), ((129, 4), torch.float32)):
+    for shape, dt in (((300, 64), torch.bfloat16), ((50, 8), torch.float32), ((129, 4), torch.float32), ((40000, 8), torch.float32)):   # the last spans three scan blocks
         xv = torch.randn(*shape, generator=g).to(dt)
         mv = (torch.rand(shape[0], generator=g) > 0.4).float()
         sv = torch.nonzero(mv).reshape(-1)
