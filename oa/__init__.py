@@ -179,7 +179,9 @@ from oa_b200.ml.precision import (OaLoadStoreStrideBytes, OaLookupPrecision, OaP
 # ---- codecs and transport
 from oa_b200.audio.codec import OaAudioDecoder, OaAudioEncoder
 from oa_b200.network import OaTcpFramed, OaTcpListener, OaTcpStream
-from oa_b200.vision.codec import OaImageCodec
+from oa_b200.vision.codec import OaFilter, OaImageBatch, OaImageCodec, OaImageDecoder, OaImageEncoder, OaImageIo, OaPixelFormat
+from oa_b200.crypto.hashes import OaHash, OaHasher
+OaLinearWeightBiasBwdResult = _F.OaLinearWeightBiasBwdResult
 
 
 # ---- animation
@@ -205,12 +207,21 @@ class Context:
         self._ctx.Sync()
 
 
-UNAVAILABLE = ("OaPlot", "OaViewer", "OaVideo", "OaRenderer")
+UNAVAILABLE = ("OaPlot", "OaViewer", "OaVideo", "OaRenderer",
+               # video codecs and containers, camera / screen capture: the reference drives the vendor's decode engine and the
+               # desktop through a graphics API
+               "OaCameraCapture", "OaCameraCaptureConfig", "OaContainerInfo", "OaContainerKind", "OaScreenCapture", "OaScreenCaptureConfig",
+               "OaScreenCaptureCursor", "OaScreenCaptureTarget", "OaVideoCodec", "OaVideoConfig", "OaVideoDecodeCapabilities",
+               "OaVideoEncodeCapabilities", "OaVideoEncodeProfile", "OaVideoFrame", "OaVideoFrameResource", "OaVideoPacket",
+               "OaVideoRateControl", "OaVideoRecorder", "OaVideoRecorderConfig", "OaVideoStream", "OaVideoStreamOptions",
+               "OaVideoStreamStats", "OaYCbCrModel",
+               # ML-DSA signatures: the reference links liboqs, which is not part of this build
+               "OaKeypair", "OaPublicKey", "OaSecretKey", "OaSignature", "OaGenerateKeypair", "OaSign", "OaVerify")
 
 
 def __getattr__(name: str):
     if name in UNAVAILABLE:
-        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (video / plot / ui / renderer) that this build does not provide")
+        raise AttributeError(f"oa.{name} belongs to a part of the reference surface (video and capture, plot / ui / renderer, ML-DSA signatures) that this build does not provide")
     raise AttributeError(f"module 'oa' has no attribute '{name}'")
 
 

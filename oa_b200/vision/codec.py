@@ -8,6 +8,7 @@ graphics API and are unavailable here.
 """
 from __future__ import annotations
 
+import enum
 import struct
 import zlib
 from typing import Optional, Tuple
@@ -219,7 +220,7 @@ def EncodePnm(img: np.ndarray) -> bytes:
     return (b"P5" if c == 1 else b"P6") + f"\n{w} {h}\n255\n".encode() + np.ascontiguousarray(img).tobytes()
 
 
-class OaImageCodec:
+class OaImageIo:
     """Decode to / encode from `OaImage` (uint8 HWC on the host; `ToFloat` gives the planar fp32 NCHW form the image
     operations work on)."""
 
@@ -234,7 +235,7 @@ class OaImageCodec:
 
     @staticmethod
     def DecodeMemory(data: bytes) -> Tuple[Optional[OaImage], OaStatus]:
-        kind = OaImageCodec.Detect(data)
+        kind = OaImageIo.Detect(data)
         if kind in ("jpeg", "webp"):
             return None, OaStatus(OaStatusCode.Unimplemented, f"{kind} decoding is not part of this build")
         fn = {"png": DecodePng, "bmp": DecodeBmp, "tga": DecodeTga, "pnm": DecodePnm}.get(kind)
@@ -252,7 +253,7 @@ class OaImageCodec:
     def DecodeFile(path: str) -> Tuple[Optional[OaImage], OaStatus]:
         try:
             with open(path, "rb") as f:
-                return OaImageCodec.DecodeMemory(f.read())
+                return OaImageIo.DecodeMemory(f.read())
         except OSError as e:
             return None, OaStatus(OaStatusCode.NotFound, str(e))
 
@@ -284,13 +285,13 @@ class OaImageCodec:
         if fn is None:
             return None, OaStatus(OaStatusCode.Unimplemented, f"no encoder for '{kind}'")
         try:
-            return fn(OaImageCodec._pixels(image)), OaStatus.Ok()
+            return fn(OaImageIo._pixels(image)), OaStatus.Ok()
         except (ValueError, KeyError) as e:
             return None, OaStatus(OaStatusCode.InvalidArgument, str(e))
 
     @staticmethod
     def EncodeFile(image, path: str) -> OaStatus:
-        blob, st = OaImageCodec.EncodeMemory(image, path.rsplit(".", 1)[-1])
+        blob, st = OaImageIo.EncodeMemory(image, path.rsplit(".", 1)[-1])
         if blob is None:
             return st
         with open(path, "wb") as f:
@@ -302,3 +303,102 @@ class OaImageCodec:
         """uint8 HWC -> fp32 [1, C, H, W] in [0, 1]."""
         t = image.AsMatrix().Tensor()
         return OaMatrix((t.permute(2, 0, 1).float() / 255.0).unsqueeze(0).contiguous())
+
+
+# ------------------------------------------------------------------------------------------ the reference's codec surface
+class OaImageCodec(enum.IntEnum):
+    Auto = 0
+    Jpeg = 1
+    Png = 2
+    Webp = 3
+    Bmp = 4
+    Tga = 5
+
+
+class OaPixelFormat(enum.IntEnum):
+    """Storage formats of image tensors (distinct from OaImageFormat, which names the meaning of the channels)."""
+    NV12 = 0
+    RGB8 = 1
+    RGBA8 = 2
+    BF16 = 3
+    F32 = 4
+
+
+class OaFilter(enum.IntEnum):
+    Nearest = 0
+    Linear = 1
+
+
+_KIND = {OaImageCodec.Png: "png", OaImageCodec.Bmp: "bmp", OaImageCodec.Tga: "tga"}
+
+
+def _convert(image: OaImage, fmt: OaImageFormat) -> OaImage:
+    """Decoded pixels brought to the requested channel meaning (grey <-> colour, alpha added or dropped)."""
+    t = image.AsMatrix().Tensor()
+    want = {OaImageFormat.Gray: 1, OaImageFormat.Rgb: 3, OaImageFormat.Rgba: 4}.get(fmt)
+    c = t.shape[2]
+    if want is None or want == c:
+        return image
+    if c == 1:
+        t = t.expand(-1, -1, 3)
+        c = 3
+    if want == 1:
+        w = torch.tensor([0.299, 0.587, 0.114])
+        t = (t[:, :, :3].float() * w).sum(2, keepdim=True).round().clamp(0, 255).to(torch.uint8)
+    elif want == 3:
+        t = t[:, :, :3]
+    elif want == 4 and c == 3:
+        t = torch.cat([t, torch.full_like(t[:, :, :1], 255)], 2)
+    return OaImage(OaMatrix(t.contiguous()), OaImageLayout.Hwc, fmt)
+
+
+class OaImageDecoder:
+    @staticmethod
+    def Supports(codec: OaImageCodec) -> bool:
+        return OaImageCodec(codec) in (OaImageCodec.Auto, OaImageCodec.Png, OaImageCodec.Bmp, OaImageCodec.Tga)
+
+    @staticmethod
+    def LoadMemory(Data: bytes, Format: OaImageFormat = OaImageFormat.Rgb) -> OaImage:
+        img, st = OaImageIo.DecodeMemory(bytes(Data))
+        if img is None:
+            raise RuntimeError(st.message)
+        return _convert(img, Format)
+
+    @staticmethod
+    def LoadFile(Path, Format: OaImageFormat = OaImageFormat.Rgb) -> OaImage:
+        img, st = OaImageIo.DecodeFile(str(Path))
+        if img is None:
+            raise RuntimeError(st.message)
+        return _convert(img, Format)
+
+
+class OaImageEncoder:
+    @staticmethod
+    def Supports(codec: OaImageCodec) -> bool:
+        return OaImageCodec(codec) in _KIND
+
+    @staticmethod
+    def Encode(Image: OaImage, Codec: OaImageCodec, Quality: int = 90) -> bytes:
+        """`Quality` applies to lossy codecs only; the codecs built here are lossless."""
+        if not OaImageEncoder.Supports(Codec):
+            raise RuntimeError(f"no encoder for {OaImageCodec(Codec).name} in this build")
+        blob, st = OaImageIo.EncodeMemory(Image, _KIND[OaImageCodec(Codec)])
+        if blob is None:
+            raise RuntimeError(st.message)
+        return blob
+
+    @staticmethod
+    def SaveFile(Path, Image: OaImage, Quality: int = 90) -> None:
+        st = OaImageIo.EncodeFile(Image, str(Path))
+        if not st.IsOk():
+            raise RuntimeError(st.message)
+
+
+class OaImageBatch(OaImage):
+    """An OaImage that must carry a batch axis (NCHW or NHWC)."""
+
+    def Validate(self) -> bool:
+        return self.Layout() in (OaImageLayout.Nchw, OaImageLayout.Nhwc) and super().Validate()
+
+    def Dtype(self):
+        return None if self.IsEmpty() else self.AsMatrix().Tensor().dtype

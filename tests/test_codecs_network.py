@@ -12,7 +12,7 @@ from oa_b200.audio.fn_audio import OaAudio, OaChannelLayout
 from oa_b200.core.matrix import OaMatrix
 from oa_b200.core.types import OaStatusCode
 from oa_b200.network import OaTcpFramed, OaTcpListener, OaTcpStream
-from oa_b200.vision.codec import DecodePng, OaImageCodec, _PNG_SIG
+from oa_b200.vision.codec import DecodePng, OaImageIo as OaImageCodec, _PNG_SIG
 from oa_b200.vision.fn_image import OaImage, OaImageFormat, OaImageLayout
 
 
@@ -133,3 +133,41 @@ def test_framed_tcp_echo():
     assert listener.Accept(timeout=0.05)[1].code == OaStatusCode.DeadlineExceeded
     listener.Close()
     assert OaTcpStream.Connect("127.0.0.1", 1, timeout=1.0)[0] is None
+
+
+def test_reference_codec_surface_and_hash_types(tmp_path):
+    import oa
+    px = np.random.default_rng(9).integers(0, 256, size=(6, 5, 3), dtype=np.uint8)
+    img = OaImage(OaMatrix(torch.from_numpy(px)), OaImageLayout.Hwc, OaImageFormat.Rgb)
+    blob = oa.OaImageEncoder.Encode(img, oa.OaImageCodec.Png)
+    assert oa.OaImageDecoder.Supports(oa.OaImageCodec.Png) and not oa.OaImageDecoder.Supports(oa.OaImageCodec.Jpeg)
+    assert oa.OaImageEncoder.Supports(oa.OaImageCodec.Tga) and not oa.OaImageEncoder.Supports(oa.OaImageCodec.Webp)
+    back = oa.OaImageDecoder.LoadMemory(blob)
+    assert np.array_equal(back.AsMatrix().Tensor().numpy(), px) and back.Format() == OaImageFormat.Rgb
+    grey = oa.OaImageDecoder.LoadMemory(blob, OaImageFormat.Gray).AsMatrix().Tensor()
+    want = np.round(px[:, :, 0] * 0.299 + px[:, :, 1] * 0.587 + px[:, :, 2] * 0.114)
+    assert grey.shape == (6, 5, 1) and np.abs(grey[:, :, 0].numpy().astype(np.int32) - want).max() <= 1
+    rgba = oa.OaImageDecoder.LoadMemory(blob, OaImageFormat.Rgba).AsMatrix().Tensor()
+    assert rgba.shape == (6, 5, 4) and bool((rgba[:, :, 3] == 255).all())
+    oa.OaImageEncoder.SaveFile(tmp_path / "x.bmp", img)
+    assert np.array_equal(oa.OaImageDecoder.LoadFile(tmp_path / "x.bmp").AsMatrix().Tensor().numpy(), px)
+    with pytest.raises(RuntimeError):
+        oa.OaImageEncoder.Encode(img, oa.OaImageCodec.Jpeg)
+    with pytest.raises(RuntimeError):
+        oa.OaImageDecoder.LoadMemory(b"\xff\xd8\xff\xe0....")
+    batch = oa.OaImageBatch(OaMatrix(torch.rand(2, 3, 4, 4)), OaImageLayout.Nchw, OaImageFormat.Rgb)
+    assert batch.Validate() and batch.BatchSize() == 2 and batch.Dtype() == torch.float32
+    assert not oa.OaImageBatch(OaMatrix(torch.rand(3, 4, 4)), OaImageLayout.Chw, OaImageFormat.Rgb).Validate()
+    assert oa.OaPixelFormat.NV12 == 0 and oa.OaFilter.Linear == 1
+    import hashlib
+    h = oa.OaHasher().Update(b"ab").Update(b"c").Finalize()
+    assert h.Bytes() == hashlib.shake_256(b"abc").digest(32) and h == oa.OaHash.FromHex(h.ToHex()) and len(h.ToShortHex()) == 8
+    assert oa.OaHash.Zero().IsZero() and not h.IsZero() and repr(h).startswith("OaHash(") and oa.OaHash.Of(b"abc") == h
+    with pytest.raises(ValueError):
+        oa.OaHash(b"short")
+    hs = oa.OaHasher(); hs.Update(b"x"); hs.Reset()
+    assert hs.Finalize() == oa.OaHash.Of(b"")
+    assert oa.OaLinearWeightBiasBwdResult is not None
+    for name in ("OaVideoStream", "OaSign", "OaScreenCapture"):
+        with pytest.raises(AttributeError):
+            getattr(oa, name)
