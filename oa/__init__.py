@@ -155,10 +155,12 @@ OaFnMetric = _namespace("OaFnMetric", "Host-side metrics of device results.", _M
 from oa_b200.core.host import (OaAlignedBuffer, OaChannel, OaCoreInfo, OaCpuTopology, OaMemcpyNT, OaMemEqual, OaSimd, OaTask, OaThreadPool,
                                OaThreadPoolConfig)
 from oa_b200.runtime.graph import OaAccess, OaComputeGraph
+from oa_b200.runtime.device import (DescribeDevice as OaDescribeDevice, OaDeviceBuilder, OaDeviceHardwareInfo, OaDeviceInfo, OaDevicePerformance,
+                                    OaDeviceSoftwareInfo, OaDeviceType, OaFeatureModule)
 from oa_b200.runtime.session import (OaAnalyzeSemanticLowering, OaExecutionPlan, OaExecutionSession, OaSemanticGraph,
                                      OaSemanticLoweringAnalysis, OaValidateSemanticLowering)
 from oa_b200.runtime.stream import (OaCompletionToken, OaComputeClass, OaDispatch, OaDispatchHint, OaExternalMemory, OaExternalMemoryHandle,
-                                    OaFence, OaInferencePool, OaInferencePoolConfig, OaScheduler, OaStream, OaStreamPool,
+                                    OaFence, OaInferencePool, OaInferencePoolConfig, OaPqcPool, OaPqcPoolConfig, OaScheduler, OaSecureBuffer, OaStream, OaStreamPool,
                                     OaTimelineSemaphore, OaWorkItem, OaWorkQueue)
 
 

@@ -552,3 +552,106 @@ class OaExternalMemory:
         elif self._owned:
             lib.oa_ipc_free(ctypes.c_void_p(self._ptr))
         self._ptr = 0
+
+
+# ------------------------------------------------------------------------------------------ hashing / signature pool
+@dataclass
+class OaPqcPoolConfig:
+    MaxConcurrentSigns: int = 64
+    MaxConcurrentHashes: int = 64
+    NttSlotSize: int = 1024
+    HashSlotSize: int = 200          # one Keccak state
+    KeyCapacity: int = 64 << 10
+
+
+class OaSecureBuffer:
+    """A slice of the key arena that is overwritten with zeros when released."""
+
+    def __init__(self, view: Optional[torch.Tensor]):
+        self._v = view
+
+    def IsValid(self) -> bool: return self._v is not None
+    def Size(self) -> int: return 0 if self._v is None else self._v.numel()
+    def Tensor(self) -> Optional[torch.Tensor]: return self._v
+
+    def Release(self) -> None:
+        if self._v is not None:
+            self._v.zero_()
+            self._v = None
+
+    def __del__(self):
+        self.Release()
+
+
+class OaPqcPool:
+    """Fixed slots for transform and hash states plus a bump arena for key material (Runtime/Pool.h:70-114): a batch of
+    hashing or signing work takes its scratch from here instead of allocating.  Slot occupancy is a 64-bit bitmap per
+    kind, as in the reference, so at most 64 slots of each kind exist."""
+
+    def __init__(self):
+        self._cfg: Optional[OaPqcPoolConfig] = None
+        self._ntt = self._hash = self._key = None
+        self._ntt_bits = self._hash_bits = 0
+        self._key_off = 0
+
+    def Init(self, device, config: Optional[OaPqcPoolConfig] = None) -> OaStatus:
+        c = config or OaPqcPoolConfig()
+        if not (0 < c.MaxConcurrentSigns <= 64 and 0 < c.MaxConcurrentHashes <= 64) or c.NttSlotSize <= 0 or c.HashSlotSize <= 0:
+            return OaStatus(OaStatusCode.InvalidArgument, "between 1 and 64 slots of a positive size are required")
+        self._cfg = c
+        self._ntt = torch.zeros(c.MaxConcurrentSigns, c.NttSlotSize, dtype=torch.uint8, device=device)
+        self._hash = torch.zeros(c.MaxConcurrentHashes, c.HashSlotSize, dtype=torch.uint8, device=device)
+        self._key = torch.zeros(c.KeyCapacity, dtype=torch.uint8, device=device)
+        self._ntt_bits = self._hash_bits = self._key_off = 0
+        return OaStatus.Ok()
+
+    def Destroy(self) -> None:
+        if self._key is not None:
+            self._key.zero_()
+        self._ntt = self._hash = self._key = self._cfg = None
+
+    @staticmethod
+    def _take(bits: int, limit: int):
+        for i in range(limit):
+            if not (bits >> i) & 1:
+                return i, bits | (1 << i)
+        return -1, bits
+
+    def AllocNttSlot(self) -> Optional[torch.Tensor]:
+        if self._cfg is None:
+            return None
+        i, self._ntt_bits = self._take(self._ntt_bits, self._cfg.MaxConcurrentSigns)
+        return None if i < 0 else self._ntt[i]
+
+    def AllocHashSlot(self) -> Optional[torch.Tensor]:
+        if self._cfg is None:
+            return None
+        i, self._hash_bits = self._take(self._hash_bits, self._cfg.MaxConcurrentHashes)
+        return None if i < 0 else self._hash[i]
+
+    def _slot_of(self, arena: torch.Tensor, slot: torch.Tensor) -> int:
+        off = slot.data_ptr() - arena.data_ptr()
+        stride = arena.shape[1]
+        return off // stride if 0 <= off < arena.numel() and off % stride == 0 else -1
+
+    def FreeNttSlot(self, slot: torch.Tensor) -> None:
+        i = self._slot_of(self._ntt, slot)
+        if i >= 0:
+            self._ntt_bits &= ~(1 << i)
+
+    def FreeHashSlot(self, slot: torch.Tensor) -> None:
+        i = self._slot_of(self._hash, slot)
+        if i >= 0:
+            self._hash[i].zero_()
+            self._hash_bits &= ~(1 << i)
+
+    def AllocKeyBuffer(self, size: int) -> OaSecureBuffer:
+        size_al = (size + 15) & ~15
+        if self._key is None or size <= 0 or self._key_off + size_al > self._key.numel():
+            return OaSecureBuffer(None)
+        view = self._key[self._key_off:self._key_off + size]
+        self._key_off += size_al
+        return OaSecureBuffer(view)
+
+    def NttSlotsUsed(self) -> int: return bin(self._ntt_bits).count("1")
+    def HashSlotsUsed(self) -> int: return bin(self._hash_bits).count("1")

@@ -118,3 +118,23 @@ def test_precision_policy():
     assert OaPrecisionDtype(OaPrecisionTag.Bf16, OaPrecision.FP32) == 0
     assert OaLoadStoreStrideBytes(OaPrecisionTag.Bf16, OaPrecision.BF16) == 2 and OaLoadStoreStrideBytes(OaPrecisionTag.Fp32, OaPrecision.BF16) == 4
     assert OaPipelineNameIsF32Variant("Gemm_f32") and not OaPipelineNameIsF32Variant("f32") and not OaPipelineNameIsF32Variant("Gemm_bf16")
+
+
+def test_pqc_pool_slots_and_secure_buffers():
+    from oa_b200.runtime.stream import OaPqcPool, OaPqcPoolConfig
+    pool = OaPqcPool()
+    assert pool.AllocNttSlot() is None and not pool.Init("cpu", OaPqcPoolConfig(MaxConcurrentSigns=65)).IsOk()
+    assert pool.Init("cpu", OaPqcPoolConfig(MaxConcurrentSigns=2, MaxConcurrentHashes=3, KeyCapacity=64)).IsOk()
+    a, b = pool.AllocNttSlot(), pool.AllocNttSlot()
+    assert a.numel() == 1024 and a.data_ptr() != b.data_ptr() and pool.AllocNttSlot() is None and pool.NttSlotsUsed() == 2
+    pool.FreeNttSlot(a)
+    assert pool.NttSlotsUsed() == 1 and pool.AllocNttSlot().data_ptr() == a.data_ptr()
+    h = pool.AllocHashSlot(); h.fill_(7)
+    pool.FreeHashSlot(h)
+    assert pool.HashSlotsUsed() == 0 and int(pool.AllocHashSlot().sum()) == 0         # a freed state is wiped
+    k1, k2 = pool.AllocKeyBuffer(20), pool.AllocKeyBuffer(30)
+    assert k1.IsValid() and k1.Size() == 20 and k2.Tensor().data_ptr() - k1.Tensor().data_ptr() == 32 and not pool.AllocKeyBuffer(10).IsValid()
+    view = k1.Tensor(); view.fill_(9); k1.Release()
+    assert int(view.sum()) == 0 and not k1.IsValid()
+    pool.Destroy()
+    assert pool.AllocHashSlot() is None
