@@ -249,7 +249,7 @@ int oa_accuracy_count(const void* logits, const void* targets, const void* mask,
 int oa_sr_round_bf16(const void* x, void* out, long long n, unsigned seed_lo, unsigned seed_hi, void* stream);
 int oa_gemm_int8(const void* a, const void* b, void* c_i32, void* c_f32, const void* row_scale, const void* col_scale, int M, int N, int K,
                  void* stream);
-// LunarLander3d (lunar.cu).  cfg_f: 75 host floats, cfg_n: 6 host ints, spawn8: 8 host floats; the rest is device memory.
+// LunarLander3d (lunar.cu).  cfg_f: 77 host floats, cfg_n: 6 host ints, spawn8: 8 host floats; the rest is device memory.
 int oa_rl_lunar_step(const float* cfg_f, const int* cfg_n, const void* terrain, const void* action, const void* external_stop, void* state_f,
                      void* state_u, void* trans_obs, void* obs, void* reward, void* terminated, void* truncated, void* end_reason, int envs,
                      void* stream);

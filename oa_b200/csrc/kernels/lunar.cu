@@ -18,14 +18,17 @@ enum : int {
   C_DT = 0, C_GRAVITY, C_MASS, C_IX, C_IY, C_IZ, C_THRUST, C_TORQUE, C_FUEL_CAP, C_MAIN_RATE, C_ATT_RATE, C_RESTITUTION, C_FRICTION,
   C_SLOP, C_CORR_FRAC, C_MAX_CORR, C_MAX_IMPULSE, C_MAX_BIAS, C_MIN_Y, C_MAX_Y, C_SAFE_LIN, C_SAFE_ANG, C_SAFE_TILT, C_HARD_FOOT,
   C_POS_SCALE, C_VEL_SCALE, C_ANG_SCALE, C_TERRAIN_SCALE, C_FOOT_SCALE, C_PROBE, C_GAMMA, C_W_POS, C_W_VEL, C_W_TILT, C_W_ANG,
-  C_W_MAIN_FUEL, C_W_ATT_FUEL, C_R_SOFT, C_R_DWELL, C_R_SUCCESS, C_R_FAIL, C_CELL, C_MIN_X, C_MAX_X, C_MIN_Z, C_MAX_Z, C_PAD, C_SUPPORT
+  C_W_MAIN_FUEL, C_W_ATT_FUEL, C_R_SOFT, C_R_DWELL, C_R_SUCCESS, C_R_FAIL, C_CELL, C_MIN_X, C_MAX_X, C_MIN_Z, C_MAX_Z, C_PAD, C_SUPPORT,
+  C_TERRAIN_TOP = C_SUPPORT + 28,   // no terrain vertex lies above this height
+  C_REACH,                          // largest |support offset| + radius: no support sphere reaches further from the centre
+  C_COUNT
 };
 enum : int { N_SUBSTEPS = 0, N_ITERATIONS, N_DWELL, N_MAX_STEPS, N_CELLS_X, N_CELLS_Z };
 enum : int { S_POS = 0, S_VEL = 3, S_QUAT = 6, S_ANG = 10, S_FUEL = 13, S_THROTTLE = 14, S_ATT = 15, S_BODY_IMP = 18, S_FOOT_IMP = 21, S_RETURN = 25 };
 enum : int { U_ACTION = 0, U_BODY, U_FOOT, U_PAD, U_REWARDED, U_STEP, U_DWELL, U_TERM, U_TRUNC, U_REASON, U_EPISODE };
 enum : int { END_SAFE = 1, END_BODY = 2, END_HARD_FOOT = 3, END_OOB = 4, END_NUMERIC = 5, END_TIME = 6, END_STOP = 7, END_BAD_ACTION = 8 };
 
-struct Config { float f[75]; int n[6]; };
+struct Config { float f[C_COUNT]; int n[6]; };
 
 struct V3 { float x, y, z; };
 __device__ __forceinline__ V3 v3(float x, float y, float z) { return V3{x, y, z}; }
@@ -280,7 +283,9 @@ lunar_step_kernel(const Config c, const float* __restrict__ terrain, const int* 
     const float norm = sqrtf(n.w * n.w + n.x * n.x + n.y * n.y + n.z * n.z);
     b.q = Quat{n.w / norm, n.x / norm, n.y / norm, n.z / norm};
     valid = finite_body(b);
-    for (int it = 0; it < iterations && valid; ++it) {
+    // a lander whose lowest possible point is above the highest terrain vertex touches nothing: skip the contact pass
+    const bool airborne = b.pos.y - c.f[C_REACH] > c.f[C_TERRAIN_TOP];
+    for (int it = 0; it < iterations && valid && !airborne; ++it) {
       for (int k = 0; k < 7; ++k) resolve_support(c, terrain, b, k, h, d);
       valid = finite_body(b) && isfinite(d.foot_speed);
     }
@@ -368,14 +373,14 @@ lunar_reset_kernel(const Config c, const Spawn sp, const float* __restrict__ ter
 
 static Config make_config(const float* cfg_f, const int* cfg_n) {
   Config c;
-  for (int i = 0; i < 75; ++i) c.f[i] = cfg_f[i];
+  for (int i = 0; i < C_COUNT; ++i) c.f[i] = cfg_f[i];
   for (int i = 0; i < 6; ++i) c.n[i] = cfg_n[i];
   return c;
 }
 
 extern "C" {
 
-// cfg_f: 75 host floats, cfg_n: 6 host ints (see the enums above); everything else is device memory.
+// cfg_f: 77 host floats, cfg_n: 6 host ints (see the enums above); everything else is device memory.
 int oa_rl_lunar_step(const float* cfg_f, const int* cfg_n, const void* terrain, const void* action, const void* external_stop, void* state_f,
                      void* state_u, void* trans_obs, void* obs, void* reward, void* terminated, void* truncated, void* end_reason, int envs,
                      void* stream) {

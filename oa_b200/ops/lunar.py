@@ -93,7 +93,7 @@ class LunarParams:
         return -0.5 * self.CellsX * self.CellSize, -0.5 * self.CellsZ * self.CellSize
 
     def Floats(self) -> List[float]:
-        """The 75-entry float table in the kernel's index order (47 scalars, then 7 x 4 support entries)."""
+        """The 77-entry float table in the kernel's index order (47 scalars, 7 x 4 support entries, two bounds)."""
         mnx, mnz = self.TerrainMin()
         f = [self.PolicyDt, self.Gravity, self.Mass, *self.Inertia, self.MainThrust, self.AttitudeTorque, self.FuelCapacity,
              self.MainFuelRate, self.AttitudeFuelRate, self.Restitution, self.Friction, self.ContactSlop, self.CorrectionFraction,
@@ -106,6 +106,10 @@ class LunarParams:
         assert len(f) == 47
         for s in self.Supports:
             f.extend(s)
+        # bounds that let a lane far above the ground skip its contact pass: the highest terrain vertex (terrain heights
+        # must stay within +-MaxAbsHeight) and the largest distance of any support sphere's surface from the centre
+        f.append(self.MaxAbsHeight)
+        f.append(max(math.sqrt(s[0] ** 2 + s[1] ** 2 + s[2] ** 2) + s[3] for s in self.Supports))
         return [float(v) for v in f]
 
     def Ints(self) -> List[int]:
@@ -452,6 +456,9 @@ def _uniform(seed: int, env: torch.Tensor, episode: torch.Tensor, comp: int) -> 
     return (v >> 8).to(torch.float32) * (1.0 / 16777216.0)
 
 
+_checked_terrains: set = set()
+
+
 def _host_tables(p: LunarParams):
     f, n = p.Floats(), p.Ints()
     return (ctypes.c_float * len(f))(*f), (ctypes.c_int * len(n))(*n)
@@ -465,6 +472,13 @@ def _check(p: LunarParams, terrain, sf, su, obs) -> None:
         raise ValueError("state must be [E, 32] fp32 and [E, 16] int32, observation [E, 33] fp32")
     if len(p.Supports) != 7 or p.Substeps <= 0 or p.ContactIterations < 0:
         raise ValueError("seven supports and a positive substep count are required")
+    key = (terrain.data_ptr(), terrain._version)
+    if key not in _checked_terrains:                       # once per terrain: one device read
+        if float(terrain.abs().max()) > p.MaxAbsHeight + 1e-6:
+            raise ValueError("terrain heights must lie within +-MaxAbsHeight")
+        if len(_checked_terrains) > 64:
+            _checked_terrains.clear()
+        _checked_terrains.add(key)
 
 
 def reset(p: LunarParams, terrain, sf, su, obs, seed: int, only_done: bool, spawn=SPAWN_DEFAULT) -> None:
