@@ -1,12 +1,14 @@
 #!/usr/bin/env python
 """Flagship benchmark: training throughput (tokens/s) of the dense GPT-style Transformer LM, data parallel.
 
-Config (BASELINE.json config 2): vocab 32000, d_model 1024, 24 layers, 16 heads (head_dim 64), FFN 4096 GELU,
+Config: vocab 32000, d_model 1024, 24 layers, 16 heads (head_dim 64), FFN 4096 GELU,
 RMSNorm, RoPE, seq 2048, micro-batch 8 per GPU, bf16 compute with fp32 master weights and AdamW, token ids
 uniform over the vocabulary from a seed, weights N(0, 0.02).  Weak scaling: per-GPU work is fixed.
 
   python bench.py --gpus N --steps K --warmup W            (N>1: launched by torchrun, one rank per GPU)
-  python bench.py --impl reference ...                      (the reference arm)
+  python bench.py --impl reference ...                      (the reference arm: the unmodified reference through its own public API; it is a
+                                                            Vulkan-only library and does not install on an image without a Vulkan SDK, in which
+                                                            case this prints one line saying why it is unavailable and exits 0)
 
 Prints ONE JSON line on rank 0.  `value` is timed on the device with CUDA events around exactly K steps
 (barrier + synchronize on both sides, max over ranks); `e2e` is the same metric through the public
