@@ -197,6 +197,10 @@ from oa_b200.utils.log import (OA_LOG_DEBUG, OA_LOG_ERROR, OA_LOG_INFO, OA_LOG_T
 from oa_b200.utils.perf import OaNvtxRange, OaPerfRecord, OaPerfStat, OaPerfStore
 
 
+# ---- rank health and host-side fault injection
+from oa_b200.parallel.health import OaFault, OaFaultInjector, OaFaultKind, OaRankFailure, OaRankMonitor, OaRankState
+
+
 class Context:
     """Executes and synchronises the default context on scope exit."""
 
