@@ -208,6 +208,14 @@ class OaItTraining:
         """One step in two phases: `prepare` refills the (static) input buffers, `record` launches zero-grad, forward,
         loss and backward and returns the loss.  With a program configured, `record` + the optimizer step are captured
         at step 2 and replayed afterwards; only `prepare` runs on the host on replay steps."""
+        monitor = getattr(self, "_rank_monitor", None)
+        if monitor is not None:                      # between steps: nothing of this rank is in flight yet
+            monitor.Beat(self._index)
+            st = monitor.Check()
+            if not st:
+                self.LastStatus = st
+                self._stop = True
+                return float("nan")
         if self._program is not None and self._program.IsCaptured():
             if prepare is not None:
                 prepare()
@@ -239,6 +247,11 @@ class OaItTraining:
             loss = record()
         self.Phase.BodyMs = (time.perf_counter() - t0) * 1e3
         return self.Next(loss)
+
+    def SetRankMonitor(self, monitor) -> None:
+        """Check the peers' heartbeats before every `Step`: a rank that failed or fell silent stops this loop with an
+        `Unavailable` status before the next launch (see `oa_b200.parallel.health.OaRankMonitor`)."""
+        self._rank_monitor = monitor
 
     def _range(self, name: str):
         """Profiler range around a phase of the step when OA_NVTX is set (a system profiler then shows the phases)."""

@@ -120,3 +120,40 @@ def test_survivors_stop_between_steps(kind, tmp_path):
         assert "rank 2 raised: injected failure" in outs[2] and "rank 2 done 3" in outs[2]
     else:
         assert procs[2].returncode == 0 and "rank 2" in outs[2]
+
+
+def test_training_loop_stops_when_a_peer_falls_silent():
+    import torch
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.core.matrix import OaMatrix
+    from oa_b200.ml import autograd as AG
+    from oa_b200.ml import fn_loss as L
+    from oa_b200.ml.nn.layers import OaLinear
+    from oa_b200.ml.optim import OaAdamW
+    from oa_b200.ml.training import OaItTraining, OaItTrainingConfig
+    store, now = DictStore(), [0.0]
+    clock = lambda: now[0]
+    me, peer = OaRankMonitor(store, 0, 2, timeout_s=2.0, clock=clock), OaRankMonitor(store, 1, 2, timeout_s=2.0, clock=clock)
+    model = OaLinear(4, 3)
+    opt = OaAdamW(model.AllParameterPtrs(), 1e-2)
+    training = OaItTraining(opt, OaItTrainingConfig(TotalSteps=10, BatchSize=5, SequenceLength=1, Program=False))
+    training.SetRankMonitor(me)
+    x, y = OaMatrix(torch.randn(5, 4)), OaMatrix(torch.randint(0, 3, (5,), dtype=torch.int32))
+
+    def record():
+        opt.ZeroGrad()
+        with AG.OaGradientTape() as tape:
+            loss = L.CrossEntropy(model.Forward(x), y)
+        tape.Backward(loss)
+        return loss
+
+    steps = 0
+    while not training.IsDone():
+        if steps < 3:
+            peer.Beat(steps)                    # the peer is alive for three steps, then falls silent
+        now[0] += 1.0
+        training.Step(None, record)
+        steps += 1
+    training.Finish()
+    assert training.StepCount() == 4 and not training.LastStatus.IsOk() and "[1]" in training.LastStatus.message
+    assert training.LastStatus.code == OaStatusCode.Unavailable
