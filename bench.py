@@ -1,22 +1,34 @@
 #!/usr/bin/env python
-"""Flagship benchmark: training throughput (tokens/s) of the dense GPT-style Transformer LM, data parallel.
+"""Training-throughput benchmark (tokens/s) of the five benchmark configurations, on 1..8 GPUs of one node.
 
-Config: vocab 32000, d_model 1024, 24 layers, 16 heads (head_dim 64), FFN 4096 GELU,
-RMSNorm, RoPE, seq 2048, micro-batch 8 per GPU, bf16 compute with fp32 master weights and AdamW, token ids
-uniform over the vocabulary from a seed, weights N(0, 0.02).  Weak scaling: per-GPU work is fixed.
+  python bench.py --gpus N --steps K --warmup W [--config 1|2|3|4|5]   (N>1: launched by torchrun, one rank per GPU)
 
-  python bench.py --gpus N --steps K --warmup W            (N>1: launched by torchrun, one rank per GPU)
-  python bench.py --impl reference ...                      (the reference arm: the unmodified reference through its own public API; it is a
-                                                            Vulkan-only library and does not install on an image without a Vulkan SDK, in which
-                                                            case this prints one line saying why it is unavailable and exits 0)
+  --config 1  char-level Transformer LM, FP32: vocab 256, d 128, 4 layers, 4 heads, FFN 512 GELU, pre-LayerNorm, learned
+              positions, seq 128, batch 16 (after the timed steps: `.oam` save / reload and 64-token greedy generation)
+  --config 2  (default, the flagship) dense GPT 24x1024, 16 heads, FFN 4096 GELU, RMSNorm, RoPE, vocab 32000, seq 2048,
+              micro-batch 8 per GPU, data parallel (fused reduce-scatter + AdamW + all-gather kernel)
+  --config 3  sparse MoE 16x2048, 64 experts top-2 + 1 shared, SwiGLU 1408, seq 2048, micro-batch 4 per GPU; one GPU holds all
+              experts, N GPUs shard them (expert parallel = N) with every other parameter data parallel
+  --config 4  Mamba-3 32x1536, state 128, seq 4096, micro-batch 4 per GPU, data parallel
+  --config 5  7B-class Transformer 32x4096, SwiGLU 11008, seq 4096, micro-batch 1 accumulated to 32 sequences per optimizer
+              step, tensor parallel = N with sequence parallelism; `--decode` adds batch-32 greedy decoding of 256 tokens
+              after a 2048-token prompt as a second key
 
-Prints ONE JSON line on rank 0.  `value` is timed on the device with CUDA events around exactly K steps
-(barrier + synchronize on both sides, max over ranks); `e2e` is the same metric through the public
-OaItTraining API including the per-step pinned-host -> device input copy and the loss readback.
+  --impl oa_b200   (default) this framework; it first runs the PyTorch arm in the same process group and reports
+                   `vs_baseline` = {value, ratio, e2e_value, e2e_ratio} against it (skip with --no-baseline)
+  --impl torch     the same model in plain PyTorch (cuBLAS, SDPA, fused AdamW over fp32 masters, DDP / NCCL TP / NCCL EP):
+                   `baseline/torch_arm.py`
+  --impl reference the unmodified reference through its own public API; it is a Vulkan-only library and does not install
+                   on an image without a Vulkan SDK, so this prints one line saying why it is unavailable and exits 0
+
+Prints ONE JSON line on rank 0.  `value` is timed on the device with CUDA events around exactly K steps (barrier +
+synchronize on both sides, max over ranks, inputs resident); `e2e` is the same metric through the public training API with
+the per-step pinned-host -> device input copy and the loss readback inside the timed region.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -26,6 +38,17 @@ import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
+
+NAMES = {
+    1: "char-level Transformer LM, FP32: vocab 256, d 128, 4 layers, 4 heads, FFN 512 GELU, pre-LayerNorm, learned positions",
+    2: "dense GPT 24x1024, 16 heads, FFN 4096 GELU, RMSNorm, RoPE, vocab 32000",
+    3: "sparse MoE 16x2048, 64 experts top-2, SwiGLU 1408, 1 shared expert, vocab 32000",
+    4: "Mamba-3 32x1536, state 128, expand 2, head dim 64, scan chunk 128, vocab 32000",
+    5: "7B-class Transformer 32x4096, 32 heads, SwiGLU 11008, RMSNorm, RoPE, vocab 32000",
+}
+MICRO_BATCH = {1: 16, 2: 8, 3: 4, 4: 4, 5: 1}
+ACCUM = {1: 1, 2: 1, 3: 1, 4: 1, 5: 32}
+MODEL_TO_CONFIG = {"char": 1, "gpt350m": 2, "moe": 3, "mamba3": 4, "llama7b": 5}
 
 
 def reference_arm(args) -> int:
@@ -90,20 +113,372 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
 
 
+class HostBatches:
+    """Synthetic token ids (uniform over the vocabulary, seeded) in pinned host memory, copied to static device buffers."""
+
+    def __init__(self, torch, vocab: int, batch: int, seq: int, seed: int, ids_dev, tgt_dev, n: int = 8):
+        gen = torch.Generator().manual_seed(seed)
+        self.host = [torch.randint(0, vocab, (batch, seq + 1), generator=gen, dtype=torch.int32).pin_memory() for _ in range(n)]
+        self.ids, self.tgt, self.seq, self.i = ids_dev, tgt_dev, seq, 0
+        self.bytes_per_copy = 2 * batch * seq * 4
+
+    def feed(self, *_):
+        t = self.host[self.i % len(self.host)]
+        self.i += 1
+        self.ids.copy_(t[:, :self.seq], non_blocking=True)
+        self.tgt.copy_(t[:, 1:], non_blocking=True)
+
+
+# ------------------------------------------------------------------------------------------------ jobs
+class TorchJob:
+    """The PyTorch arm (baseline/torch_arm.py)."""
+
+    impl = "torch"
+
+    def __init__(self, args, torch, world, rank, dev):
+        from baseline.torch_arm import TorchTrainer
+        k = args.config
+        self.accum = args.accum or ACCUM[k]
+        self.tr = TorchTrainer(k, world, dev, args.micro_batch, self.accum, fp32=(k == 1), layers=args.layers, seq=args.seq,
+                               graph=not args.no_graph)
+        c = self.tr.cfg
+        self.seq = c.seq_len
+        data_rank = 0 if k == 5 else rank                    # tensor-parallel ranks see the same batch
+        self.batches = HostBatches(torch, c.vocab, args.micro_batch, self.seq, 1234 + data_rank, self.tr.ids, self.tr.tgt)
+        self.tokens_per_step = args.micro_batch * self.seq * self.accum * (1 if k == 5 else world)
+        self.h2d = self.batches.bytes_per_copy * self.accum
+        self.launches_per_step = 0
+        self.torch = torch
+
+    def warm(self, n):
+        self.batches.feed()
+        self.tr.warm(n)
+
+    def timed_step(self):
+        self.tr.step()
+
+    def e2e_step(self) -> float:
+        if self.accum > 1:
+            self.tr.micro_feed = self.batches.feed
+            self.tr.step()
+            self.tr.micro_feed = None
+        else:
+            self.batches.feed()
+            self.tr.step()
+        return float(self.tr.loss.item())
+
+    def info(self) -> dict:
+        return {"executor": self.tr.executor(), "optimizer": "torch.optim.AdamW(fused) over fp32 masters",
+                "attention": "F.scaled_dot_product_attention", "layers": getattr(self.tr.cfg, "n_layers", None)}
+
+    def close(self):
+        self.tr = None
+
+
+class OaJob:
+    """This framework: configurations 1, 2, 4 (and 3 on one GPU) through OaItTraining with the step captured as a CUDA
+    graph; expert-parallel 3 and configuration 5 through an explicit step with gradient accumulation."""
+
+    impl = "oa_b200"
+
+    def __init__(self, args, torch, world, rank, dev):
+        import torch.distributed as dist
+        from oa_b200 import _native
+        from oa_b200.core import fn_matrix as F
+        from oa_b200.core.types import OaPrecision
+        from oa_b200.ml.autograd import OaGradientTape
+        from oa_b200.ml.optim import OaAdam, OaAdamW
+        from oa_b200.ml.training import OaItTraining, OaItTrainingConfig
+        from oa_b200.models import OaGptConfig, OaGptModel, OaMamba3Config, OaMamba3LmModel
+        from oa_b200.ops import kernels as K
+        from oa_b200.runtime.engine import OaContextGetDefault, OaEngineConfig, OaInitComputeEngine
+
+        k = args.config
+        self.k, self.world, self.torch, self.native, self.K = k, world, torch, _native, K
+        self.accum = args.accum or ACCUM[k]
+        assert OaInitComputeEngine(OaEngineConfig(Precision=OaPrecision.FP32 if k == 1 else OaPrecision.BF16, DeviceIndex=dev.index))
+        self.ctx = OaContextGetDefault()
+        F.SetRngSeed(20260714)                      # same weights on every rank
+        self.mesh = self.dp = self.training = None
+        self.after_backward = lambda: None
+        B = args.micro_batch
+        if k == 4:
+            cfg = OaMamba3Config.Mamba3_32x1536()
+        else:
+            cfg = {1: OaGptConfig.CharLm, 2: OaGptConfig.Gpt350M, 3: OaGptConfig.Moe16x2048, 5: OaGptConfig.Llama7B}[k]()
+        if args.layers:
+            cfg.NLayers = args.layers
+        if args.seq:
+            cfg.SeqLen = args.seq
+        self.cfg, self.seq = cfg, cfg.SeqLen
+        self.parallelism = f"dp{world}"
+        self.dp_mode = args.dp_mode if world > 1 else "none"
+        if k == 5 and world > 1:
+            from oa_b200.parallel.mesh import OaDeviceMesh
+            from oa_b200.parallel.tp_model import OaTpGptModel
+            self.mesh = OaDeviceMesh()
+            self.model = OaTpGptModel(cfg, self.mesh, B)
+            self.opts = [OaAdamW(self.model.AllParameterPtrs(), 3e-4, weight_decay=0.1)]
+            self.after_backward = self.model.SyncReplicatedGrads
+            self.parallelism = f"tp{world} + sequence parallel (fused all-gather -> GEMM, GEMM -> reduce-scatter)"
+        elif k == 3 and world > 1:
+            from oa_b200.parallel.dp import OaDataParallel
+            from oa_b200.parallel.ep import OaExpertParallel
+            from oa_b200.parallel.mesh import OaDeviceMesh
+            self.mesh = OaDeviceMesh()
+            self.model = OaGptModel(cfg)
+            self.ep = OaExpertParallel(self.model, self.mesh, tokens_per_rank=B * self.seq)
+            ex = self.ep.ExpertParameters()
+            ex_ids = {id(p) for p in ex}
+            dense = [p for p in self.model.AllParameterPtrs() if id(p) not in ex_ids]
+            opt_dense, opt_exp = OaAdamW(dense, 3e-4, weight_decay=0.1), OaAdamW(ex, 3e-4, weight_decay=0.1)
+            self.dp = OaDataParallel(self.model, opt_dense, mode="fused", mesh=self.mesh)
+            opt_exp.SetGradScale(1.0 / world)
+            self.opts = [opt_dense, opt_exp]
+            self.parallelism = f"ep{world} (experts, peer-memory dispatch / combine) x dp{world} (rest)"
+        else:
+            self.model = OaMamba3LmModel(cfg) if k == 4 else OaGptModel(cfg)
+            params = self.model.AllParameterPtrs()
+            opt = OaAdam(params, 3e-4) if k == 1 else OaAdamW(params, 3e-4, weight_decay=0.1)
+            self.opts = [opt]
+            if world > 1:
+                from oa_b200.parallel.dp import OaDataParallel
+                self.dp = OaDataParallel(self.model, opt, mode=args.dp_mode)
+        if self.accum > 1:
+            for o in self.opts:
+                o.SetGradScale((1.0 / self.accum) * (1.0 / world if (k == 3 and world > 1 and o is self.opts[-1]) else 1.0))
+        self.ids = F.FromTensor(torch.empty((B, self.seq), dtype=torch.int32, device=dev))
+        self.tgt = F.FromTensor(torch.empty((B, self.seq), dtype=torch.int32, device=dev))
+        data_rank = 0 if (k == 5 and world > 1) else rank
+        self.batches = HostBatches(torch, cfg.Vocab, B, self.seq, 1234 + data_rank, self.ids.Tensor(), self.tgt.Tensor())
+        self.tokens_per_step = B * self.seq * self.accum * (1 if (k == 5 and world > 1) else world)
+        self.h2d = self.batches.bytes_per_copy * self.accum
+        self.Tape = OaGradientTape
+        self.explicit = self.accum > 1 or len(self.opts) > 1 or (k == 5 and world > 1)
+        if not self.explicit:
+            tcfg = OaItTrainingConfig(TotalSteps=10 ** 9, BatchSize=B * world, SequenceLength=self.seq, Program=not args.no_graph)
+            self.training = OaItTraining(self.opts[0], tcfg)
+        self.launches_per_step = 0
+        self.loss = None
+
+    # one forward + backward on the resident batch
+    def _record(self):
+        self.opts[0].ZeroGrad()
+        with self.Tape() as tape:
+            loss = self.model.Loss(self.ids, self.tgt)
+            tape.Backward(loss)
+        return loss
+
+    def _explicit_step(self, feed):
+        for o in self.opts:
+            o.ZeroGrad()
+        loss = None
+        for m in range(self.accum):
+            if feed is not None:
+                feed()
+            with self.Tape() as tape:
+                loss = self.model.Loss(self.ids, self.tgt)
+                tape.Backward(loss)
+        self.after_backward()
+        for o in self.opts:
+            o.Step()
+        self.loss = loss
+
+    def warm(self, n):
+        if self.explicit:
+            self.batches.feed()
+            n0 = self.native.launches()
+            for _ in range(n):
+                self._explicit_step(None)
+            self.launches_per_step = (self.native.launches() - n0) // n
+            return
+        for w in range(n):
+            self.training.IsDone()
+            n0 = self.native.launches()
+            self.training.Step(self.batches.feed, self._record)
+            if w == 1 or self.training.Program() is None:
+                self.launches_per_step = self.native.launches() - n0
+
+    def timed_step(self):
+        if self.explicit:
+            self._explicit_step(None)
+            return
+        prog = self.training.Program()
+        if prog is not None and prog.IsCaptured():
+            prog.Replay()
+            self.opts[0].NotifyProgramReplay()
+        else:
+            self._record()
+            self.opts[0].Step()
+
+    def e2e_step(self) -> float:
+        if self.explicit:
+            self._explicit_step(self.batches.feed)
+            return self.loss.Item()
+        self.training.IsDone()
+        self.training.Step(self.batches.feed, self._record)
+        return self.training.LastLoss()
+
+    def info(self) -> dict:
+        prog = self.training.Program() if self.training is not None else None
+        return {"executor": "cuda graph replay" if (prog is not None and prog.IsCaptured()) else "eager stream",
+                "optimizer": "AdamW fp32 master" if self.k != 1 else "Adam fp32", "dp": self.dp_mode, "layers": self.cfg.NLayers,
+                "status": "ok" if self.ctx.Sync() else "error"}
+
+    def flops_per_token(self) -> float:
+        return self.model.FlopsPerToken() if hasattr(self.model, "FlopsPerToken") else 0.0
+
+    def after_timing(self, out: dict):
+        """Configuration 1 ends with a checkpoint round trip and greedy generation, as its description asks."""
+        if self.k != 1:
+            return
+        import tempfile
+        from oa_b200.core import fn_matrix as F
+        from oa_b200.ml.optim import OaAdam
+        from oa_b200.models import OaGptModel
+        torch = self.torch
+
+        def greedy(model, n=64):
+            ctx = torch.zeros((1, self.seq), dtype=torch.int32, device=self.ids.Tensor().device)
+            ctx[0, -2:] = torch.tensor([116, 111], dtype=torch.int32)       # "to"
+            outs = []
+            for _ in range(n):
+                logits = model.Forward(F.FromTensor(ctx)).Tensor()
+                nxt = int(logits[-1].float().argmax())
+                outs.append(nxt)
+                ctx = torch.cat((ctx[:, 1:], torch.tensor([[nxt]], dtype=torch.int32, device=ctx.device)), 1)
+            return outs
+
+        t0 = time.perf_counter()
+        with tempfile.TemporaryDirectory() as d:
+            path = os.path.join(d, "char.oam")
+            st = self.model.Save(path, self.opts[0])
+            fresh = OaGptModel(self.cfg)
+            fresh_opt = OaAdam(fresh.AllParameterPtrs(), 3e-4)
+            st2 = fresh.Load(path, fresh_opt)
+        a, b = greedy(self.model), greedy(fresh)
+        out["checkpoint"] = {"saved": bool(st), "loaded": bool(st2), "generation_identical": a == b, "generated_tokens": len(a),
+                             "seconds": round(time.perf_counter() - t0, 3)}
+
+    def close(self):
+        self.K.check_status()
+        if self.dp is not None:
+            self.dp.Close()
+        elif self.mesh is not None:
+            self.mesh.Close()
+
+
+def run_protocol(job, args, torch, dist, world, dev, local_rank):
+    """W untimed steps, K device-timed steps (inputs resident), K end-to-end steps (H2D + loss readback each step)."""
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    job.warm(args.warmup)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        job.timed_step()
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    t0 = time.perf_counter()
+    loss = float("nan")
+    for _ in range(args.steps):
+        loss = job.e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3)
+    if world > 1:
+        t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = float(t[0]), float(t[1])
+    tokens = job.tokens_per_step * args.steps
+    return {"value": tokens / (dev_ms / 1e3), "ms_per_step": dev_ms / args.steps, "e2e_value": tokens / (e2e_ms / 1e3),
+            "e2e_ms_per_step": e2e_ms / args.steps, "clocks": clocks, "final_loss": loss}
+
+
+def decode_key(args, torch, dist, world, rank, dev) -> dict:
+    """Configuration 5's second key: batch-32 greedy decoding of 256 tokens after a 2048-token prompt."""
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.models import OaGptConfig, OaGptModel
+    cfg = OaGptConfig.Llama7B()
+    if args.layers:
+        cfg.NLayers = args.layers
+    Bd, prompt_len, new = 32, 2048, 256
+    gen = torch.Generator().manual_seed(99)
+    prompt = torch.randint(0, cfg.Vocab, (Bd, prompt_len), generator=gen, dtype=torch.int32).to(dev)
+    mesh = None
+    if world > 1:
+        from oa_b200.parallel.mesh import OaDeviceMesh
+        from oa_b200.parallel.tp_model import OaTpGptModel
+        from oa_b200.serve.tp_decoder import OaTpGptDecoder
+        mesh = OaDeviceMesh()
+        dec = OaTpGptDecoder(OaTpGptModel(cfg, mesh, 1), Bd, prompt_len + new)
+    else:
+        from oa_b200.serve.decoder import OaGptDecoder
+        dec = OaGptDecoder(OaGptModel(cfg), Bd, prompt_len + new)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    dec.Generate(prompt[:, :256], 8)                       # warm-up
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev[0].record()
+    logits = dec.Prefill(prompt)
+    ev[1].record()
+    for _ in range(new):
+        logits = dec.Step(logits.float().argmax(-1).to(torch.int32))
+    ev[2].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2])], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = {"metric": "greedy decode tokens/s (device-timed, max over ranks)", "value": Bd * new / (float(t[1]) / 1e3),
+           "ms_per_token": float(t[1]) / new, "prefill_tokens_per_s": Bd * prompt_len / (float(t[0]) / 1e3), "batch": Bd,
+           "prompt": prompt_len, "new_tokens": new, "layers": cfg.NLayers}
+    if mesh is not None:
+        mesh.Close()
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=0, help="0 = the configuration's default (10; 2 for configuration 5)")
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="oa_b200")
-    ap.add_argument("--model", default="gpt350m", choices=["gpt350m", "tiny", "mamba3", "mamba3-tiny", "moe", "char"])
-    ap.add_argument("--micro-batch", type=int, default=0, help="sequences per GPU; 0 = the configuration's own (8 GPT, 4 Mamba-3 / MoE, 16 char LM)")
+    ap.add_argument("--impl", default="oa_b200", choices=["oa_b200", "torch", "reference"])
+    ap.add_argument("--config", type=int, default=0, choices=[0, 1, 2, 3, 4, 5])
+    ap.add_argument("--model", default="", choices=["", *MODEL_TO_CONFIG], help="older spelling of --config")
+    ap.add_argument("--micro-batch", type=int, default=0, help="sequences per GPU; 0 = the configuration's own")
+    ap.add_argument("--accum", type=int, default=0, help="micro-steps per optimizer step; 0 = the configuration's own")
     ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the configuration's own; a reduced model is not a valid headline)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the PyTorch arm that fills vs_baseline")
+    ap.add_argument("--decode", action="store_true", help="configuration 5: also run the batch-32 greedy decode")
     ap.add_argument("--dp-mode", default="fused", choices=["fused", "nccl"])
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if not args.config:
+        args.config = MODEL_TO_CONFIG.get(args.model, 2)
+    k = args.config
+    if not args.steps:
+        args.steps = 2 if k == 5 else 10
+    args.warmup = max(args.warmup, 3)
+    if not args.micro_batch:
+        args.micro_batch = MICRO_BATCH[k]
 
     import torch
     import torch.distributed as dist
@@ -111,166 +486,78 @@ def main() -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus != world:
-        if world == 1 and args.gpus > 1:
-            print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks", file=sys.stderr)
-            return 2
-    args.warmup = max(args.warmup, 3)
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        print(f"bench.py: --gpus {args.gpus} needs torchrun with {args.gpus} ranks", file=sys.stderr)
+        return 2
     torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        if k in (3, 5):
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=dev)
 
-    import oa_b200 as oa
-    from oa_b200 import _native
-    from oa_b200.core import fn_matrix as F
-    from oa_b200.core.types import OaPrecision
-    from oa_b200.ml.autograd import OaGradientTape
-    from oa_b200.ml.optim import OaAdamW
-    from oa_b200.ml.training import OaItTraining, OaItTrainingConfig
-    from oa_b200.models import OaGptConfig, OaGptModel
-    from oa_b200.runtime.engine import OaContextGetDefault, OaEngineConfig, OaInitComputeEngine
+    baseline = None
+    if args.impl == "oa_b200" and not args.no_baseline:
+        try:
+            tj = TorchJob(args, torch, world, rank, dev)
+            baseline = run_protocol(tj, args, torch, dist, world, dev, local_rank)
+            baseline["info"] = tj.info()
+            tj.close()
+        except Exception as e:
+            baseline = {"error": repr(e)[:300]}
+        tj = None
+        gc.collect()
+        torch.cuda.empty_cache()
 
-    if args.micro_batch <= 0:
-        args.micro_batch = {"mamba3": 4, "moe": 4, "char": 16}.get(args.model, 8)
-    cfg_e = OaEngineConfig(Precision=OaPrecision.FP32 if args.model == "char" else OaPrecision.BF16, DeviceIndex=local_rank)
-    assert OaInitComputeEngine(cfg_e)
-    from oa_b200.models import OaMamba3Config, OaMamba3LmModel
-    names = {"gpt350m": "dense GPT 24x1024, 16 heads, FFN 4096 GELU, RMSNorm, RoPE, vocab 32000", "tiny": "tiny",
-             "mamba3": "Mamba-3 32x1536, state 128, expand 2, head dim 64, chunk 256, vocab 32000", "mamba3-tiny": "mamba3-tiny",
-             "char": "char-level Transformer LM, FP32: vocab 256, d 128, 4 layers, 4 heads, FFN 512 GELU, pre-LayerNorm, learned positions",
-             "moe": "sparse MoE 16x2048, 64 experts top-2, SwiGLU 1408, 1 shared expert, vocab 32000 (single-GPU experts)"}
-    if args.model in ("mamba3", "mamba3-tiny"):
-        mcfg = OaMamba3Config.Mamba3_32x1536() if args.model == "mamba3" else OaMamba3Config(1024, 256, 2, 32, 2, 16, 256, 64)
-    elif args.model == "moe":
-        mcfg = OaGptConfig.Moe16x2048()
-    elif args.model == "char":
-        mcfg = OaGptConfig.CharLm()
-    else:
-        mcfg = OaGptConfig.Gpt350M() if args.model == "gpt350m" else OaGptConfig(1024, 256, 2, 4, 1024, 256, "rms", "gelu", 10000.0, False, 1e-5, 0.02)
-    if args.seq:
-        mcfg.SeqLen = args.seq
-    B, S = args.micro_batch, mcfg.SeqLen
-    F.SetRngSeed(20260714)                      # same weights on every rank
-    model = OaMamba3LmModel(mcfg) if args.model.startswith("mamba3") else OaGptModel(mcfg)
-    params = model.AllParameterPtrs()
-    opt = OaAdamW(params, 3e-4, weight_decay=0.1)
-    dp = None
-    if world > 1:
-        from oa_b200.parallel.dp import OaDataParallel
-        dp = OaDataParallel(model, opt, mode=args.dp_mode)
-    dev = torch.device("cuda", local_rank)
-    gen = torch.Generator().manual_seed(1234 + rank)
-    n_host = 8
-    host_tokens = [torch.randint(0, mcfg.Vocab, (B, S + 1), generator=gen, dtype=torch.int32).pin_memory() for _ in range(n_host)]
-    ids = F.FromTensor(torch.empty((B, S), dtype=torch.int32, device=dev))
-    tgt = F.FromTensor(torch.empty((B, S), dtype=torch.int32, device=dev))
-    h2d_bytes = 2 * B * S * 4
-    step_counter = {"i": 0}
-
-    def prepare():
-        t = host_tokens[step_counter["i"] % n_host]
-        step_counter["i"] += 1
-        ids.Tensor().copy_(t[:, :S], non_blocking=True)
-        tgt.Tensor().copy_(t[:, 1:], non_blocking=True)
-
-    def record():
-        opt.ZeroGrad()
-        with OaGradientTape() as tape:
-            loss = model.Loss(ids, tgt)
-            tape.Backward(loss)
-        return loss
-
-    tcfg = OaItTrainingConfig(TotalSteps=10 ** 9, BatchSize=B * world, SequenceLength=S, Program=not args.no_graph)
-    training = OaItTraining(opt, tcfg)
-    ctx = OaContextGetDefault()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # ---- warm-up through the public API (step 1 eager, step 2 captures the program)
-    launches_before_capture = None
-    for w in range(args.warmup):
-        training.IsDone()
-        n0 = _native.launches()
-        training.Step(prepare, record)
-        if w == 1 or args.no_graph:
-            launches_before_capture = _native.launches() - n0
-    launches_per_step = launches_before_capture or 0
-    loss_warm = training.LastLoss()
-
-    # ---- device-timed region: exactly K steps, inputs resident, no host sync inside
-    sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    prog = training.Program()
-    for _ in range(args.steps):
-        if prog is not None and prog.IsCaptured():
-            prog.Replay()
-            opt.NotifyProgramReplay()
-        else:
-            record()
-            opt.Step()
-    e1.record()
-    barrier()
-    dev_ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
-
-    # ---- end-to-end region: public API, H2D of the inputs and D2H of the loss every step
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        training.IsDone()
-        training.Step(prepare, record)
-    f1.record()
-    barrier()
-    e2e_ms = max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3)
-    final_loss = training.LastLoss()
-    st = ctx.Sync()
-
-    if world > 1:
-        t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, e2e_ms = float(t[0]), float(t[1])
-    tokens = B * S * world * args.steps
-    value = tokens / (dev_ms / 1e3)
-    e2e_value = tokens / (e2e_ms / 1e3)
-    flops_per_token = model.FlopsPerToken()
+    job = (TorchJob if args.impl == "torch" else OaJob)(args, torch, world, rank, dev)
+    res = run_protocol(job, args, torch, dist, world, dev, local_rank)
+    info = job.info()
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(REPO, "MEASURED_PEAKS.json")))
     except Exception:
         pass
     peak_tf = peaks.get("bf16_tflops_sustained", 1400.0)
+    vs = None
+    if baseline is not None and "value" in baseline:
+        vs = {"value": baseline["value"], "ratio": res["value"] / baseline["value"], "e2e_value": baseline["e2e_value"],
+              "e2e_ratio": res["e2e_value"] / baseline["e2e_value"], "ms_per_step": baseline["ms_per_step"],
+              "what": "the same model in plain PyTorch on the same GPUs in the same process group (cuBLAS, SDPA, fused AdamW over fp32 "
+                      "masters, NCCL): baseline/torch_arm.py", "executor": baseline["info"]["executor"], "final_loss": baseline["final_loss"]}
+    elif baseline is not None:
+        vs = baseline
+    parallelism = getattr(job, "parallelism", None) or {1: f"dp{world}", 2: f"dp{world}", 4: f"dp{world}", 3: f"ep{world} x dp{world}",
+                                                         5: f"tp{world}"}[k]
     out = {
-        "metric": "train tokens/s (device-timed, max over ranks)", "value": value, "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp32" if args.model == "char" else "bf16", "data": "synthetic (uniform token ids, random-init N(0,0.02) weights)",
-        "config": {"model": names[args.model],
-                   "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}", "optimizer": "AdamW fp32 master",
-                   "l2": "inputs larger than L2 (activations and weights >> 126 MB per step)",
-                   "executor": "cuda graph replay" if (prog is not None and prog.IsCaptured()) else "eager stream",
-                   "dp": (args.dp_mode if world > 1 else "none")},
-        "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4,
-                "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": launches_per_step * args.steps,
-        "launches_per_step": launches_per_step,
-        "model_tflops_per_gpu": value / world * flops_per_token / 1e12,
-        "frac_of_measured_bf16_sustained": (value / world * flops_per_token / 1e12) / peak_tf,
-        "loss_after_warmup": loss_warm, "final_loss": final_loss, "status": "ok" if st else repr(st),
+        "metric": "train tokens/s (device-timed, max over ranks)", "value": res["value"], "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms_per_step"], "higher_is_better": True, "scaling": "weak" if k != 5 else "strong",
+        "vs_baseline": vs, "impl": job.impl, "dtype": "fp32" if k == 1 else "bf16",
+        "data": "synthetic (uniform token ids, random-init N(0,0.02) weights)",
+        "config": {"number": k, "model": NAMES[k], "global_batch": args.micro_batch * (1 if k == 5 else world) * job.accum, "seq_len": job.seq,
+                   "micro_batch": args.micro_batch, "micro_steps": job.accum, "parallelism": parallelism,
+                   "l2": "inputs larger than L2 (activations and weights >> 126 MB per step)" if k != 1 else
+                         "working set smaller than L2: 64 MB of scratch is rewritten by the optimizer state and activations each step; not flushed",
+                   **info},
+        "clocks": res["clocks"],
+        "e2e": {"value": res["e2e_value"], "unit": "tokens/s", "h2d_bytes_per_step": job.h2d, "d2h_bytes_per_step": 4,
+                "ms_per_step": res["e2e_ms_per_step"]},
+        "gpu_launches": job.launches_per_step * args.steps, "launches_per_step": job.launches_per_step,
+        "final_loss": res["final_loss"],
     }
+    if args.impl == "oa_b200":
+        fpt = job.flops_per_token()
+        out["model_tflops_per_gpu"] = res["value"] / world * fpt / 1e12
+        out["frac_of_measured_bf16_sustained"] = out["model_tflops_per_gpu"] / peak_tf
+        job.after_timing(out)
+    job.close()
+    if args.decode and k == 5 and args.impl == "oa_b200":
+        job = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        out["decode"] = decode_key(args, torch, dist, world, rank, dev)
     if rank == 0:
         print(json.dumps(out))
-    if dp is not None:
-        dp.Close()
     if world > 1:
         dist.destroy_process_group()
     return 0

@@ -19,6 +19,7 @@
 // exp latency.  Every wait is bounded and reports to a status word.
 #include "common.cuh"
 #include "api.h"
+#include <stdlib.h>
 
 namespace oa {
 
@@ -319,6 +320,280 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
+}
+
+// ===================================================================================== forward, two query tiles per CTA
+// One CTA owns two adjacent 128-query tiles of one (batch, head) and walks the key blocks once for both.  The tensor pipe
+// alternates between the tiles (S_t = Q_t K^T, O_t += P_t V), so the products of one tile run while the other tile's
+// softmax occupies the SFU / FMA pipes:
+//   warps 0-3  softmax of tile 0, warps 4-7 softmax of tile 1: ONE thread per query row (TMEM lane = row), the whole
+//              128-column score row is read from TMEM once, the row maximum and sum stay in registers (no shuffles, no
+//              exchange through shared memory), probabilities go back to TMEM as packed bf16 over the columns of S;
+//   warp 8     MMA issuer: P is the A operand straight from TMEM, V the B operand from shared memory, O accumulates in
+//              TMEM over all key blocks and is read once at the end;
+//   warp 9     TMA producer (Q tiles once, K / V rings).
+// The running maximum is updated lazily: while the new row maximum exceeds the one in use by less than 2^8 the old one
+// is kept (probabilities then stay below 256, exact in fp32 / safe in bf16), so O in TMEM is rescaled only in the
+// rare iterations where some row of a warp jumps by more than that; the final 1/l uses the same maxima, so the result is
+// the exact softmax.  TMEM: S0 | S1 | O0 | O1 = 128 + 128 + 2 * head_dim columns.
+template <int HD>
+struct Fwd2Cfg {
+  static constexpr int NS = (HD == 64) ? 3 : 2;           // K / V ring depth
+  static constexpr int Q_BYTES = FA_BM * HD * 2;          // one query tile
+  static constexpr int KV_BYTES = FA_BN * HD * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + 2 * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NS * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_V + NS * KV_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int TM_S = 0;                           // + 128 * tile
+  static constexpr int TM_O = 256;                         // + HD * tile
+};
+
+constexpr float FA_RESCALE_THRESHOLD = 8.f;                // log2 units
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+  using Cfg = Fwd2Cfg<HD>;
+  constexpr int NS = Cfg::NS;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;             // [NS]
+  uint64_t* v_full = bars + 1 + NS;        // [NS]
+  uint64_t* k_empty = bars + 1 + 2 * NS;   // [NS]
+  uint64_t* v_empty = bars + 1 + 3 * NS;   // [NS]
+  uint64_t* s_full = bars + 1 + 4 * NS;    // [2]  S_t holds Q_t K_j^T
+  uint64_t* p_full = s_full + 2;           // [2]  P_t written (and O_t rescaled if needed)
+  uint64_t* o_done = s_full + 4;           // [2]  O_t += P_t V_j finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 6);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = (p.seq + FA_BM - 1) / FA_BM;
+  const int npair = (nblk + 1) >> 1;
+  const int pr = npair - 1 - blockIdx.x;   // heaviest causal pairs first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int row0 = b * p.seq;
+  const int nkv0 = p.causal ? (2 * pr + 1) : nblk;                                  // key blocks of tile 0 (query block 2 pr)
+  const int nkv1 = (2 * pr + 1 < nblk) ? (p.causal ? (2 * pr + 2) : nblk) : 0;      // tile 1 (query block 2 pr + 1), 0 = absent
+  const int n_it = max(nkv0, nkv1);
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_error(p.status, OA_KERR_BAD_ARG);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    mbar_init(q_full, 1);
+    for (int s = 0; s < NS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1); }
+    mbar_fence_init();
+  }
+  if (warp == 8) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 9) {
+    // ------------- producer: the whole warp walks the loop and waits together; one lane issues the copies
+    if (lane == 0) {
+      mbar_expect_tx(q_full, (nkv1 > 0 ? 2 : 1) * Cfg::Q_BYTES);
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (t == 0 || nkv1 > 0)
+#pragma unroll
+          for (int x = 0; x < HD / 64; ++x)
+            tma_load_2d(smem + Cfg::OFF_Q + t * Cfg::Q_BYTES + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + (2 * pr + t) * FA_BM);
+    }
+    for (int j = 0; j < n_it; ++j) {
+      const int st = j % NS;
+      const uint32_t ph = (j / NS) & 1;
+      if (!warp_wait(&k_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+      if (lane == 0) {
+        mbar_expect_tx(&k_full[st], Cfg::KV_BYTES);
+#pragma unroll
+        for (int x = 0; x < HD / 64; ++x)
+          tma_load_2d(smem + Cfg::OFF_K + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmK, &k_full[st], h * HD + x * 64, row0 + j * FA_BN);
+      }
+      if (!warp_wait(&v_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+      if (lane == 0) {
+        mbar_expect_tx(&v_full[st], Cfg::KV_BYTES);
+#pragma unroll
+        for (int x = 0; x < HD / 64; ++x)
+          tma_load_2d(smem + Cfg::OFF_V + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmV, &v_full[st], h * HD + x * 64, row0 + j * FA_BN);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 8) {
+    // ------------- MMA issuer (warp-uniform waits, lane 0 issues)
+    constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_BM, HD, 0, 1);
+    const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q);
+    auto issue_qk = [&](int t, int st) {
+      if (lane == 0) {
+        const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+          umma_f16(tmem_base + Cfg::TM_S + t * FA_BN, umma_smem_desc_sw128(q_addr + t * Cfg::Q_BYTES + off, 16, 1024),
+                   umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+      }
+      __syncwarp();
+    };
+    bool ok = warp_wait(q_full, 0);
+    if (ok) ok = warp_wait(&k_full[0], 0);
+    if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
+    if (ok) {
+      tc_fence_after();
+      issue_qk(0, 0);
+      if (nkv1 > 0) issue_qk(1, 0);
+      if (lane == 0) umma_commit(&k_empty[0]);
+      __syncwarp();
+    }
+    for (int j = 0; j < n_it && ok; ++j) {
+      const int st = j % NS;
+      const int stn = (j + 1) % NS;
+      const bool has_next = j + 1 < n_it;
+      if (!warp_wait(&v_full[st], (j / NS) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      if (has_next && !warp_wait(&k_full[stn], ((j + 1) / NS) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        const int n_t = t == 0 ? nkv0 : nkv1;
+        if (j >= n_t) continue;
+        if (!warp_wait(&p_full[t], j & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::KV_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < FA_BN / 16; ++ks)
+            umma_f16_ts(tmem_base + Cfg::TM_O + t * HD, tmem_base + Cfg::TM_S + t * FA_BN + ks * 8,
+                        umma_smem_desc_sw128(v_addr + ks * 2048, FA_BN * 128, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&o_done[t]);
+        }
+        __syncwarp();
+        if (j + 1 < n_t) issue_qk(t, stn);
+      }
+      if (!ok) break;
+      if (lane == 0) {
+        umma_commit(&v_empty[st]);
+        if (has_next) umma_commit(&k_empty[stn]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------- softmax + output: one thread per query row
+    const int t = warp >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int qbt = 2 * pr + t;                   // this tile's query block
+    const int qi = qbt * FA_BM + r;               // query index inside the sequence
+    const int n = t == 0 ? nkv0 : nkv1;
+    const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
+    const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + t * FA_BN;
+    const uint32_t o_addr = tmem_base + t_lane + Cfg::TM_O + t * HD;
+    const float sl2 = p.scale * LOG2E;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      ok = warp_wait(&s_full[t], j & 1);
+      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+      tc_fence_after();
+      uint32_t sv[FA_BN];
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c) tmem_ld32(s_addr + c * 32, sv + c * 32);
+      tmem_ld_wait();
+      const bool need_mask = (p.causal && j == qbt) || (j * FA_BN + FA_BN > p.seq);
+      if (need_mask) {
+        const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - j * FA_BN;   // columns i <= lim are alive
+#pragma unroll
+        for (int i = 0; i < FA_BN; ++i) sv[i] = (i <= lim) ? sv[i] : 0xff800000u;  // -inf
+      }
+      float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]), m3 = __uint_as_float(sv[3]);
+#pragma unroll
+      for (int i = 4; i < FA_BN; i += 4) {
+        m0 = fmaxf(m0, __uint_as_float(sv[i])); m1 = fmaxf(m1, __uint_as_float(sv[i + 1]));
+        m2 = fmaxf(m2, __uint_as_float(sv[i + 2])); m3 = fmaxf(m3, __uint_as_float(sv[i + 3]));
+      }
+      const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * sl2;
+      const float m_new = fmaxf(m_run, mx);
+      const bool grow = (m_new - m_run) > FA_RESCALE_THRESHOLD;           // first block: m_run = -inf -> true
+      const float m_cand = grow ? m_new : m_run;
+      const float m_use = (m_cand == -INFINITY) ? 0.f : m_cand;           // row fully masked so far
+      const float alpha = grow ? fast_exp2(m_run - m_use) : 1.f;           // m_run = -inf -> 0
+      const float neg_m = -m_use;
+      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, neg_m));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, neg_m));
+          const float e2 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 2]), sl2, neg_m));
+          const float e3 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 3]), sl2, neg_m));
+          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+          pk[i >> 1] = pack_bf16x2(e0, e1);
+          pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
+        }
+        tmem_st16(s_addr + c * 16, pk);          // P over the first 64 columns of S (two keys per column)
+      }
+      l_run = l_run * alpha + ((l0 + l1) + (l2 + l3));
+      m_run = m_cand;
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // some row of this warp moved its maximum: rescale O (needs the previous P*V finished)
+        ok = warp_wait(&o_done[t], (j - 1) & 1);
+        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(o_addr + c * 32, o);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    if (ok && n > 0) {
+      ok = warp_wait(&o_done[t], (n - 1) & 1);
+      if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL);
+    }
+    if (ok && n > 0) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* op = p.o + (long long)(row0 + qi) * p.o_stride + h * HD;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + c * 32, o);
+        tmem_ld_wait();
+        if (qi < p.seq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(op + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(o[g * 8]) * inv, __uint_as_float(o[g * 8 + 1]) * inv),
+                pack_bf16x2(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv),
+                pack_bf16x2(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv),
+                pack_bf16x2(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv));
+        }
+      }
+      if (p.lse && qi < p.seq) p.lse[((long long)b * p.heads + h) * p.seq + qi] = (m_run + log2f(l_run)) / LOG2E;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
 }
 
 // ===================================================================================== backward
@@ -811,8 +1086,23 @@ extern "C" int oa_flash_fwd(const void* q, const void* k, const void* v, void* o
   FlashParams p;
   p.batch = batch; p.heads = heads; p.seq = seq; p.head_dim = head_dim; p.scale = scale; p.causal = causal;
   p.o = (__nv_bfloat16*)o; p.o_stride = o_row_stride; p.lse = lse; p.status = status;
-  dim3 grid((seq + FA_BM - 1) / FA_BM, heads, batch);
   cudaStream_t st = (cudaStream_t)stream;
+  static const int version = [] { const char* e = getenv("OA_FLASH_FWD"); return (e && e[0] == '1') ? 1 : 2; }();
+  if (version == 2) {
+    const int nblk = (seq + FA_BM - 1) / FA_BM;
+    dim3 grid2((nblk + 1) / 2, heads, batch);
+    if (head_dim == 64) {
+      static bool set = false;
+      if (!set) { if (cudaFuncSetAttribute(flash_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<64>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
+      flash_fwd2_kernel<64><<<grid2, FA_THREADS, Fwd2Cfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    } else {
+      static bool set = false;
+      if (!set) { if (cudaFuncSetAttribute(flash_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<128>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
+      flash_fwd2_kernel<128><<<grid2, FA_THREADS, Fwd2Cfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    }
+    return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+  }
+  dim3 grid((seq + FA_BM - 1) / FA_BM, heads, batch);
   if (head_dim == 64) {
     static bool set = false;
     if (!set) { if (cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
