@@ -376,6 +376,17 @@ int oa_peer_reduce(int dtype, const void* const* in_peers, void* out, long long 
 int oa_peer_allreduce_oneshot(const void* const* slots_peers, const void* const* counters_peers, const void* src,
                               const void* residual, void* out, void* sync2, long long n, long long slot_elems, int world,
                               int rank, int max_ctas, int* status, void* stream);
+// Bound (milliseconds of wall time) of every device-side wait on a peer flag; the default is 2000.
+int oa_set_peer_wait_ms(long long ms);
+// Gradient-norm clipping under the fused data-parallel step: sum of squares of this rank's shard of the summed gradient
+// (block partials, `oa_dp_sumsq_blocks()` floats, accumulated over calls), publication of the total into slot `rank`
+// (16-byte slots) of every rank, and the clip coefficient from the `world` slots (+ `extra[0]`, may be null);
+// coef[0] = coefficient, coef[1] = norm.
+int oa_dp_sumsq_blocks(void);
+int oa_dp_shard_sumsq(const void* const* grad_peers, long long shard_lo, long long shard_n, int rank, int world, float* partial,
+                      int accumulate, void* stream);
+int oa_dp_sumsq_publish(const float* partial, const void* const* slot_peers, int rank, int world, void* stream);
+int oa_dp_clip_finalize(const float* slots, int world, const float* extra, float max_norm, float* coef, void* stream);
 int oa_peer_push(const void* const* dst_peers, long long dst_off_bytes, const void* src, long long nbytes, int world,
                  void* stream);
 

@@ -20,17 +20,23 @@
 
 namespace oa {
 
-#ifndef OA_PEER_WAIT_LIMIT
-#define OA_PEER_WAIT_LIMIT (1u << 21)
-#endif
+// Upper bound of every wait on a peer, in nanoseconds of wall time (set from the host with oa_set_peer_wait_ms).  Ranks
+// drift apart by whole host phases (a data-loader stall, a checkpoint write), so the bound is wall time, not iterations.
+__device__ unsigned long long g_peer_wait_ns = OA_WAIT_LIMIT_NS;
 
-// Waits until every slot in `flags[0..world)` has reached `target`.  Returns false when the limit runs out.
+// Waits until every slot in `flags[0..world)` has reached `target`.  Returns false when the time limit runs out.
 __device__ __forceinline__ bool wait_flags(const unsigned long long* flags, int world, unsigned long long target) {
+  uint64_t t0 = 0;
+  const unsigned long long limit = g_peer_wait_ns;
   for (int r = 0; r < world; ++r) {
     uint32_t it = 0;
     while (ld_acquire_sys(flags + r) < target) {
-      if (++it >= OA_PEER_WAIT_LIMIT) return false;
-      if (it > 32) __nanosleep(it > 2048 ? 512 : 64);
+      if ((++it & 0x3f) == 0) {
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > limit) return false;
+        __nanosleep(it > 2048 ? 512 : 64);
+      }
     }
   }
   return true;
@@ -136,6 +142,57 @@ dp_reduce_adam_gather_kernel(const DpParams p) {
       }
     }
   }
+}
+
+// ---- gradient-norm clipping under the fused step.  The norm is that of the SUMMED gradient, so each rank sums its shard over
+// the peers once more (sum of squares only, nothing written back), publishes the scalar to every rank, and the clip
+// coefficient is computed from the `world` scalars in rank order: the same value, bit for bit, on every rank.
+constexpr int DP_SUMSQ_BLOCKS = 296;
+__global__ void __launch_bounds__(256)
+dp_shard_sumsq_kernel(PeerTable grads, long long shard_lo, long long shard_n, int rank, int world, float* partial, int accumulate) {
+  __shared__ float s_w[8];
+  const long long nvec = shard_n / 8;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  float acc = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const long long e = shard_lo + i * 8;
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int rr = 0; rr < MAX_RANKS; ++rr) {
+      if (rr < world) {
+        const int r = (rank + rr) % world;
+        const uint4 x = ld_peer_v4(reinterpret_cast<const __nv_bfloat16*>(grads.ptr[r]) + e);
+        const float2 a = unpack_bf16x2(x.x), b = unpack_bf16x2(x.y), c = unpack_bf16x2(x.z), d = unpack_bf16x2(x.w);
+        g[0] += a.x; g[1] += a.y; g[2] += b.x; g[3] += b.y; g[4] += c.x; g[5] += c.y; g[6] += d.x; g[7] += d.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc = fmaf(g[j], g[j], acc);
+  }
+  acc = warp_sum(acc);
+  if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += s_w[w];
+    partial[blockIdx.x] = accumulate ? partial[blockIdx.x] + t : t;
+  }
+}
+// One warp: sum of the block partials in a fixed order, written into slot `rank` (16-byte slots) of every rank.
+__global__ void dp_sumsq_publish_kernel(const float* partial, int n_partial, PeerTable slots, int rank, int world) {
+  float t = 0.f;
+  for (int i = threadIdx.x; i < n_partial; i += 32) t += partial[i];
+  t = warp_sum(t);
+  if (threadIdx.x < world)
+    *reinterpret_cast<volatile float*>(reinterpret_cast<float*>(slots.ptr[threadIdx.x]) + rank * 4) = t;
+  __threadfence_system();
+}
+__global__ void dp_clip_finalize_kernel(const float* slots, int world, const float* extra, float max_norm, float* coef) {
+  float t = extra ? extra[0] : 0.f;
+  for (int r = 0; r < world; ++r) t += *reinterpret_cast<const volatile float*>(slots + r * 4);
+  const float nrm = sqrtf(t);
+  coef[0] = nrm > max_norm ? max_norm / (nrm + 1e-6f) : 1.f;
+  coef[1] = nrm;
 }
 
 // Generic peer collectives on fp32 / bf16 buffers (OaCollective verbs), pull-based, bounded by the caller's
@@ -305,6 +362,29 @@ extern "C" int oa_dp_reduce_adam_gather(const void* const* grad_peers, const voi
   long long cap = max_blocks > 0 ? max_blocks : 148 * 4;
   if (blocks > cap) blocks = cap;
   dp_reduce_adam_gather_kernel<<<(int)blocks, 256, 0, ST>>>(p);
+  return CHECK_LAUNCH();
+}
+extern "C" int oa_set_peer_wait_ms(long long ms) {
+  if (ms <= 0) return OA_ERR_ARG;
+  const unsigned long long ns = (unsigned long long)ms * 1000000ull;
+  return cudaMemcpyToSymbol(g_peer_wait_ns, &ns, sizeof(ns)) == cudaSuccess ? OA_OK : OA_ERR_DRIVER;
+}
+extern "C" int oa_dp_sumsq_blocks(void) { return DP_SUMSQ_BLOCKS; }
+extern "C" int oa_dp_shard_sumsq(const void* const* grad_peers, long long shard_lo, long long shard_n, int rank, int world,
+                                 float* partial, int accumulate, void* stream) {
+  if (world < 1 || world > MAX_RANKS) return OA_ERR_ARG;
+  if ((shard_lo & 7) || (shard_n & 7)) return OA_ERR_ALIGN;
+  dp_shard_sumsq_kernel<<<DP_SUMSQ_BLOCKS, 256, 0, ST>>>(make_table(grad_peers, world), shard_lo, shard_n, rank, world, partial, accumulate);
+  return CHECK_LAUNCH();
+}
+extern "C" int oa_dp_sumsq_publish(const float* partial, const void* const* slot_peers, int rank, int world, void* stream) {
+  if (world < 1 || world > MAX_RANKS) return OA_ERR_ARG;
+  dp_sumsq_publish_kernel<<<1, 32, 0, ST>>>(partial, DP_SUMSQ_BLOCKS, make_table(slot_peers, world), rank, world);
+  return CHECK_LAUNCH();
+}
+extern "C" int oa_dp_clip_finalize(const float* slots, int world, const float* extra, float max_norm, float* coef, void* stream) {
+  if (world < 1 || world > MAX_RANKS) return OA_ERR_ARG;
+  dp_clip_finalize_kernel<<<1, 1, 0, ST>>>(slots, world, extra, max_norm, coef);
   return CHECK_LAUNCH();
 }
 extern "C" int oa_peer_reduce(int dtype, const void* const* in_peers, void* out, long long lo, long long n, int world, int op,

@@ -322,64 +322,84 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
 }
 
-// ===================================================================================== forward, two query tiles per CTA
-// One CTA owns two adjacent 128-query tiles of one (batch, head) and walks the key blocks once for both.  The tensor pipe
-// alternates between the tiles (S_t = Q_t K^T, O_t += P_t V), so the products of one tile run while the other tile's
-// softmax occupies the SFU / FMA pipes:
-//   warps 0-3  softmax of tile 0, warps 4-7 softmax of tile 1: ONE thread per query row (TMEM lane = row), the whole
-//              128-column score row is read from TMEM once, the row maximum and sum stay in registers (no shuffles, no
-//              exchange through shared memory), probabilities go back to TMEM as packed bf16 over the columns of S;
+// ===================================================================================== forward, S double-buffered in TMEM
+// One CTA owns one 128-query tile of one (batch, head).  S = Q K_j^T alternates between two TMEM buffers, and the MMA warp
+// always runs two key blocks ahead of the softmax (Q K_{j+2}^T is issued right after P_j V_j), so the softmax warps never
+// wait for the tensor pipe: they go from block j straight to block j+1 and the SFU stays busy.
+//   warps 0-7  softmax: two threads per query row (warp w: TMEM lane quadrant w % 4, key columns [64 * (w / 4), +64)), the
+//              64 scores of a thread are read from TMEM once, the row maximum is exchanged with the partner thread through
+//              a parity-double-buffered slot, probabilities go back to TMEM as packed bf16 over the columns of S_j;
 //   warp 8     MMA issuer: P is the A operand straight from TMEM, V the B operand from shared memory, O accumulates in
 //              TMEM over all key blocks and is read once at the end;
-//   warp 9     TMA producer (Q tiles once, K / V rings).
-// The running maximum is updated lazily: while the new row maximum exceeds the one in use by less than 2^8 the old one
-// is kept (probabilities then stay below 256, exact in fp32 / safe in bf16), so O in TMEM is rescaled only in the
-// rare iterations where some row of a warp jumps by more than that; the final 1/l uses the same maxima, so the result is
-// the exact softmax.  TMEM: S0 | S1 | O0 | O1 = 128 + 128 + 2 * head_dim columns.
+//   warp 9     TMA producer (Q once, K / V rings).
+// The running maximum is updated lazily: while the new row maximum exceeds the one in use by less than 2^8 the old one is
+// kept (probabilities then stay below 256), so O in TMEM is rescaled only in the rare iterations where some row of a warp
+// jumps by more than that; the final 1/l uses the same maxima, so the result is the exact softmax.  A share of the
+// exponentials (POLY of every 8) is evaluated as a degree-3 polynomial on the FMA pipe instead of the SFU.
+// TMEM: S0 | S1 | O = 128 + 128 + head_dim columns.
 template <int HD>
 struct Fwd2Cfg {
-  static constexpr int NS = (HD == 64) ? 3 : 2;           // K / V ring depth
-  static constexpr int Q_BYTES = FA_BM * HD * 2;          // one query tile
+  static constexpr int NSK = 3;                            // K ring depth (K runs two blocks ahead of V)
+  static constexpr int NSV = (HD == 64) ? 3 : 2;           // V ring depth
+  static constexpr int Q_BYTES = FA_BM * HD * 2;
   static constexpr int KV_BYTES = FA_BN * HD * 2;
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + 2 * Q_BYTES;
-  static constexpr int OFF_V = OFF_K + NS * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_V + NS * KV_BYTES;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NSK * KV_BYTES;
+  static constexpr int OFF_X = OFF_V + NSV * KV_BYTES;     // float[2 parities][2 halves][128 rows]: row-maximum exchange
+  static constexpr int OFF_BAR = OFF_X + 2 * 2 * FA_BM * 4;
   static constexpr int SMEM_BYTES = OFF_BAR + 256;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int TM_S = 0;                           // + 128 * tile
-  static constexpr int TM_O = 256;                         // + HD * tile
+  static constexpr int TM_S = 0;                           // + 128 * (j & 1)
+  static constexpr int TM_O = 256;
 };
 
 constexpr float FA_RESCALE_THRESHOLD = 8.f;                // log2 units
 
-template <int HD>
+#ifdef OA_FA_PROF
+// Development aid (compiled only with -DOA_FA_PROF): cycle stamps of one CTA's softmax warp 0 and MMA warp.
+__device__ long long g_fa_prof[8192];
+#define FA_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (slot) < 8192) g_fa_prof[(slot)] = clock64(); } while (0)
+#else
+#define FA_STAMP(slot) do { } while (0)
+#endif
+
+// 2^x for x <= 0 on the FMA pipe: floor by a round-down add of 1.5 * 2^23, cubic for 2^frac, exponent added as an integer.
+__device__ __forceinline__ float exp2_poly3(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = __fadd_rd(x, 12582912.f);
+  const float f = x - (t - 12582912.f);
+  float q = fmaf(f, 0.07711909f, 0.22756439f);
+  q = fmaf(q, f, 0.69514614f);
+  q = fmaf(q, f, 1.0f);
+  return __int_as_float(__float_as_int(q) + (__float_as_int(t) << 23));
+}
+
+template <int HD, int POLY>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   using Cfg = Fwd2Cfg<HD>;
-  constexpr int NS = Cfg::NS;
+  constexpr int NSK = Cfg::NSK, NSV = Cfg::NSV;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;             // [NS]
-  uint64_t* v_full = bars + 1 + NS;        // [NS]
-  uint64_t* k_empty = bars + 1 + 2 * NS;   // [NS]
-  uint64_t* v_empty = bars + 1 + 3 * NS;   // [NS]
-  uint64_t* s_full = bars + 1 + 4 * NS;    // [2]  S_t holds Q_t K_j^T
-  uint64_t* p_full = s_full + 2;           // [2]  P_t written (and O_t rescaled if needed)
-  uint64_t* o_done = s_full + 4;           // [2]  O_t += P_t V_j finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 6);
+  uint64_t* k_full = bars + 1;                 // [NSK]
+  uint64_t* k_empty = k_full + NSK;            // [NSK]
+  uint64_t* v_full = k_empty + NSK;            // [NSV]
+  uint64_t* v_empty = v_full + NSV;            // [NSV]
+  uint64_t* s_full = v_empty + NSV;            // [2]  S buffer holds Q K_j^T
+  uint64_t* p_full = s_full + 2;               // [2]  P_j written over S buffer (and O rescaled if needed)
+  uint64_t* o_done = s_full + 4;               //      O += P_j V_j finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 5);
+  float* xch = reinterpret_cast<float*>(smem + Cfg::OFF_X);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = (p.seq + FA_BM - 1) / FA_BM;
-  const int npair = (nblk + 1) >> 1;
-  const int pr = npair - 1 - blockIdx.x;   // heaviest causal pairs first
+  const int qb = nblk - 1 - blockIdx.x;        // heaviest causal tiles first
   const int h = blockIdx.y, b = blockIdx.z;
+  const int n_kv = p.causal ? (qb + 1) : nblk;
   const int row0 = b * p.seq;
-  const int nkv0 = p.causal ? (2 * pr + 1) : nblk;                                  // key blocks of tile 0 (query block 2 pr)
-  const int nkv1 = (2 * pr + 1 < nblk) ? (p.causal ? (2 * pr + 2) : nblk) : 0;      // tile 1 (query block 2 pr + 1), 0 = absent
-  const int n_it = max(nkv0, nkv1);
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) report_error(p.status, OA_KERR_BAD_ARG);
@@ -388,8 +408,10 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
     mbar_init(q_full, 1);
-    for (int s = 0; s < NS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1); }
+    for (int s = 0; s < NSK; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < NSV; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 8); }
+    mbar_init(o_done, 1);
     mbar_fence_init();
   }
   if (warp == 8) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
@@ -399,32 +421,35 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 9) {
-    // ------------- producer: the whole warp walks the loop and waits together; one lane issues the copies
+    // ------------- producer: the whole warp walks the loop and waits together; one lane issues the copies.  K block i is
+    // loaded two iterations before V block i - 2... both rings are simply filled in order, K first.
     if (lane == 0) {
-      mbar_expect_tx(q_full, (nkv1 > 0 ? 2 : 1) * Cfg::Q_BYTES);
+      mbar_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
-      for (int t = 0; t < 2; ++t)
-        if (t == 0 || nkv1 > 0)
+      for (int x = 0; x < HD / 64; ++x)
+        tma_load_2d(smem + Cfg::OFF_Q + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + qb * FA_BM);
+    }
+    for (int i = 0; i < n_kv + 2; ++i) {
+      if (i < n_kv) {
+        const int st = i % NSK;
+        if (!warp_wait(&k_empty[st], ((i / NSK) & 1) ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+        if (lane == 0) {
+          mbar_expect_tx(&k_full[st], Cfg::KV_BYTES);
 #pragma unroll
           for (int x = 0; x < HD / 64; ++x)
-            tma_load_2d(smem + Cfg::OFF_Q + t * Cfg::Q_BYTES + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + (2 * pr + t) * FA_BM);
-    }
-    for (int j = 0; j < n_it; ++j) {
-      const int st = j % NS;
-      const uint32_t ph = (j / NS) & 1;
-      if (!warp_wait(&k_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
-      if (lane == 0) {
-        mbar_expect_tx(&k_full[st], Cfg::KV_BYTES);
-#pragma unroll
-        for (int x = 0; x < HD / 64; ++x)
-          tma_load_2d(smem + Cfg::OFF_K + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmK, &k_full[st], h * HD + x * 64, row0 + j * FA_BN);
+            tma_load_2d(smem + Cfg::OFF_K + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmK, &k_full[st], h * HD + x * 64, row0 + i * FA_BN);
+        }
       }
-      if (!warp_wait(&v_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
-      if (lane == 0) {
-        mbar_expect_tx(&v_full[st], Cfg::KV_BYTES);
+      const int jv = i - 2;                    // V lags K by two blocks, like its consumer
+      if (jv >= 0) {
+        const int st = jv % NSV;
+        if (!warp_wait(&v_empty[st], ((jv / NSV) & 1) ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+        if (lane == 0) {
+          mbar_expect_tx(&v_full[st], Cfg::KV_BYTES);
 #pragma unroll
-        for (int x = 0; x < HD / 64; ++x)
-          tma_load_2d(smem + Cfg::OFF_V + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmV, &v_full[st], h * HD + x * 64, row0 + j * FA_BN);
+          for (int x = 0; x < HD / 64; ++x)
+            tma_load_2d(smem + Cfg::OFF_V + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmV, &v_full[st], h * HD + x * 64, row0 + jv * FA_BN);
+        }
       }
       __syncwarp();
     }
@@ -433,94 +458,94 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
     constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_BM, HD, 0, 1);
     const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q);
-    auto issue_qk = [&](int t, int st) {
+    auto issue_qk = [&](int i) -> bool {       // S[i & 1] = Q K_i^T
+      const int st = i % NSK;
+      if (!warp_wait(&k_full[st], (i / NSK) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); return false; }
+      tc_fence_after();
       if (lane == 0) {
         const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_S + t * FA_BN, umma_smem_desc_sw128(q_addr + t * Cfg::Q_BYTES + off, 16, 1024),
+          umma_f16(tmem_base + Cfg::TM_S + (i & 1) * FA_BN, umma_smem_desc_sw128(q_addr + off, 16, 1024),
                    umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[t]);
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[i & 1]);
       }
       __syncwarp();
+      return true;
     };
     bool ok = warp_wait(q_full, 0);
-    if (ok) ok = warp_wait(&k_full[0], 0);
     if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
-    if (ok) {
+    if (ok) ok = issue_qk(0);
+    if (ok && n_kv > 1) ok = issue_qk(1);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int st = j % NSV;
+      if (!warp_wait(&v_full[st], (j / NSV) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      FA_STAMP(j * 16 + 8);
+      if (!warp_wait(&p_full[j & 1], (j >> 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); break; }
       tc_fence_after();
-      issue_qk(0, 0);
-      if (nkv1 > 0) issue_qk(1, 0);
-      if (lane == 0) umma_commit(&k_empty[0]);
-      __syncwarp();
-    }
-    for (int j = 0; j < n_it && ok; ++j) {
-      const int st = j % NS;
-      const int stn = (j + 1) % NS;
-      const bool has_next = j + 1 < n_it;
-      if (!warp_wait(&v_full[st], (j / NS) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
-      if (has_next && !warp_wait(&k_full[stn], ((j + 1) / NS) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const int n_t = t == 0 ? nkv0 : nkv1;
-        if (j >= n_t) continue;
-        if (!warp_wait(&p_full[t], j & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::KV_BYTES);
-#pragma unroll
-          for (int ks = 0; ks < FA_BN / 16; ++ks)
-            umma_f16_ts(tmem_base + Cfg::TM_O + t * HD, tmem_base + Cfg::TM_S + t * FA_BN + ks * 8,
-                        umma_smem_desc_sw128(v_addr + ks * 2048, FA_BN * 128, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-          umma_commit(&o_done[t]);
-        }
-        __syncwarp();
-        if (j + 1 < n_t) issue_qk(t, stn);
-      }
-      if (!ok) break;
+      FA_STAMP(j * 16 + 9);
       if (lane == 0) {
+        const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < FA_BN / 16; ++ks)
+          umma_f16_ts(tmem_base + Cfg::TM_O, tmem_base + Cfg::TM_S + (j & 1) * FA_BN + ks * 8,
+                      umma_smem_desc_sw128(v_addr + ks * 2048, FA_BN * 128, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         umma_commit(&v_empty[st]);
-        if (has_next) umma_commit(&k_empty[stn]);
+        umma_commit(o_done);
       }
       __syncwarp();
+      FA_STAMP(j * 16 + 10);
+      if (j + 2 < n_kv) ok = issue_qk(j + 2);  // overwrites S[j & 1] = P_j: ordered after P_j V_j by the pipe
+      FA_STAMP(j * 16 + 11);
     }
   } else {
-    // ------------- softmax + output: one thread per query row
-    const int t = warp >> 2;
+    // ------------- softmax + output: two threads per query row (key columns split in halves)
+    constexpr int OC = HD / 2;                   // output columns owned by this thread
     const int quad = warp & 3;
+    const int half = warp >> 2;
     const int r = quad * 32 + lane;
-    const int qbt = 2 * pr + t;                   // this tile's query block
-    const int qi = qbt * FA_BM + r;               // query index inside the sequence
-    const int n = t == 0 ? nkv0 : nkv1;
+    const int qi = qb * FA_BM + r;               // query index inside the sequence
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
-    const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + t * FA_BN;
-    const uint32_t o_addr = tmem_base + t_lane + Cfg::TM_O + t * HD;
+    const uint32_t o_addr = tmem_base + t_lane + Cfg::TM_O + half * OC;
     const float sl2 = p.scale * LOG2E;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n; ++j) {
-      ok = warp_wait(&s_full[t], j & 1);
+    for (int j = 0; j < n_kv; ++j) {
+      if (warp == 0) FA_STAMP(j * 16 + 0);
+      ok = warp_wait(&s_full[j & 1], (j >> 1) & 1);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
-      uint32_t sv[FA_BN];
-#pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c) tmem_ld32(s_addr + c * 32, sv + c * 32);
+      if (warp == 0) FA_STAMP(j * 16 + 1);
+      const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + (j & 1) * FA_BN;
+      uint32_t sv[64];
+      tmem_ld32(s_addr + half * 64, sv);
+      tmem_ld32(s_addr + half * 64 + 32, sv + 32);
       tmem_ld_wait();
-      const bool need_mask = (p.causal && j == qbt) || (j * FA_BN + FA_BN > p.seq);
+      if (warp == 0) FA_STAMP(j * 16 + 2);
+      const bool need_mask = (p.causal && j == qb) || (j * FA_BN + FA_BN > p.seq);
       if (need_mask) {
-        const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - j * FA_BN;   // columns i <= lim are alive
+        const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - j * FA_BN - half * 64;   // columns i <= lim are alive
 #pragma unroll
-        for (int i = 0; i < FA_BN; ++i) sv[i] = (i <= lim) ? sv[i] : 0xff800000u;  // -inf
+        for (int i = 0; i < 64; ++i) sv[i] = (i <= lim) ? sv[i] : 0xff800000u;                 // -inf
       }
       float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]), m3 = __uint_as_float(sv[3]);
 #pragma unroll
-      for (int i = 4; i < FA_BN; i += 4) {
+      for (int i = 4; i < 64; i += 4) {
         m0 = fmaxf(m0, __uint_as_float(sv[i])); m1 = fmaxf(m1, __uint_as_float(sv[i + 1]));
         m2 = fmaxf(m2, __uint_as_float(sv[i + 2])); m3 = fmaxf(m3, __uint_as_float(sv[i + 3]));
       }
-      const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * sl2;
+      float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      // Exchange with the partner thread of this row.  Both threads now hold their scores in registers, so after this
+      // barrier the S buffer may be overwritten by either of them.
+      float* slots = xch + (j & 1) * (2 * FA_BM);
+      slots[(half ^ 1) * FA_BM + r] = mx;
+      if (warp == 0) FA_STAMP(j * 16 + 3);
+      pair_sync(quad);
+      mx = fmaxf(mx, slots[half * FA_BM + r]) * sl2;
+      if (warp == 0) FA_STAMP(j * 16 + 4);
       const float m_new = fmaxf(m_run, mx);
       const bool grow = (m_new - m_run) > FA_RESCALE_THRESHOLD;           // first block: m_run = -inf -> true
       const float m_cand = grow ? m_new : m_run;
@@ -528,30 +553,43 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float alpha = grow ? fast_exp2(m_run - m_use) : 1.f;           // m_run = -inf -> 0
       const float neg_m = -m_use;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+      uint32_t pk[32];
+      if (POLY == 0 || need_mask) {
 #pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, neg_m));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, neg_m));
-          const float e2 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 2]), sl2, neg_m));
-          const float e3 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 3]), sl2, neg_m));
+        for (int i = 0; i < 64; i += 4) {
+          const float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, neg_m));
+          const float e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_m));
+          const float e2 = fast_exp2(fmaf(__uint_as_float(sv[i + 2]), sl2, neg_m));
+          const float e3 = fast_exp2(fmaf(__uint_as_float(sv[i + 3]), sl2, neg_m));
           l0 += e0; l1 += e1; l2 += e2; l3 += e3;
           pk[i >> 1] = pack_bf16x2(e0, e1);
           pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
         }
-        tmem_st16(s_addr + c * 16, pk);          // P over the first 64 columns of S (two keys per column)
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {
+          float e[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const float x = fmaf(__uint_as_float(sv[i + u]), sl2, neg_m);
+            e[u] = (u < POLY) ? exp2_poly3(x) : fast_exp2(x);
+          }
+          l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) pk[(i >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
+        }
       }
+      if (warp == 0) FA_STAMP(j * 16 + 5);
+      tmem_st32(s_addr + half * 32, pk);          // P over the first 64 columns of S (two keys per column)
       l_run = l_run * alpha + ((l0 + l1) + (l2 + l3));
       m_run = m_cand;
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
         // some row of this warp moved its maximum: rescale O (needs the previous P*V finished)
-        ok = warp_wait(&o_done[t], (j - 1) & 1);
+        ok = warp_wait(o_done, (j - 1) & 1);
         if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t o[32];
           tmem_ld32(o_addr + c * 32, o);
           tmem_ld_wait();
@@ -561,15 +599,341 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       tmem_st_wait();
+      if (warp == 0) FA_STAMP(j * 16 + 6);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[t]);
+      if (lane == 0) mbar_arrive(&p_full[j & 1]);
+      if (warp == 0) FA_STAMP(j * 16 + 7);
     }
-    if (ok && n > 0) {
-      ok = warp_wait(&o_done[t], (n - 1) & 1);
+    // combine the two partial row sums (parity slot of an iteration that is two behind any reader)
+    {
+      float* slots = xch + (n_kv & 1) * (2 * FA_BM);
+      slots[(half ^ 1) * FA_BM + r] = l_run;
+      pair_sync(quad);
+      l_run += slots[half * FA_BM + r];
+    }
+    if (ok) {
+      ok = warp_wait(o_done, (n_kv - 1) & 1);
       if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL);
     }
-    if (ok && n > 0) {
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* op = p.o + (long long)(row0 + qi) * p.o_stride + h * HD + half * OC;
+#pragma unroll
+      for (int c = 0; c < OC / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld32(o_addr + c * 32, o);
+        tmem_ld_wait();
+        if (qi < p.seq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(op + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(o[g * 8]) * inv, __uint_as_float(o[g * 8 + 1]) * inv),
+                pack_bf16x2(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv),
+                pack_bf16x2(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv),
+                pack_bf16x2(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv));
+        }
+      }
+      if (p.lse && half == 0 && qi < p.seq) p.lse[((long long)b * p.heads + h) * p.seq + qi] = (m_run + log2f(l_run)) / LOG2E;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
+}
+
+// ===================================================================================== forward, head_dim 64: two tiles per CTA
+// Two adjacent 128-query tiles of one (batch, head) share a CTA and the K / V rings but are otherwise independent pipelines
+// (softmax warps 0-3 + MMA warp 8 for tile 0, warps 4-7 + MMA warp 9 for tile 1), so their phases drift apart and the
+// exponentials of one tile cover the TMEM traffic, row maxima and barrier hand-offs of the other.  One thread owns one query
+// row (all 128 key columns: no partner exchange).  The score tile is copied to registers and RELEASED at once, so
+// Q K_{j+1}^T is issued while the exponentials of block j run; probabilities have their own TMEM columns:
+// S0 | S1 | P0 | P1 | O0 | O1 = 128 + 128 + 64 + 64 + 64 + 64.
+struct FwdPairCfg {
+  static constexpr int HD = 64;
+  static constexpr int NS = 3;
+  static constexpr int Q_BYTES = FA_BM * HD * 2;
+  static constexpr int KV_BYTES = FA_BN * HD * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + 2 * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NS * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_V + NS * KV_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int TM_S = 0, TM_P = 256, TM_O = 384;   // + 128 / 64 / 64 * tile
+  static constexpr int THREADS = 352;                        // 8 softmax warps, 2 MMA warps, 1 TMA warp
+};
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Persistent: one CTA per SM walks the work items (tile pair, head, batch) it owns, heaviest causal pairs first and items
+// dealt in snake order (round r: CTA c takes item r G + c, or r G + G-1-c when r is odd; within 3 % of the greedy optimum), so TMEM, barriers and the K / V rings live across items, the producer and the MMA warps run ahead
+// into the next item while the softmax warps write the previous output, and no SM pays a CTA launch per item.  Every
+// barrier phase is derived from a running count kept identically by its producers and consumers.
+__global__ void __launch_bounds__(FwdPairCfg::THREADS, 1)
+flash_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+  using Cfg = FwdPairCfg;
+  constexpr int NS = Cfg::NS, HD = Cfg::HD;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  uint64_t* q_full = bars + 0;
+  uint64_t* q_empty = bars + 1;            // both MMA warps are done with the Q tiles of the item
+  uint64_t* k_full = bars + 2;             // [NS]
+  uint64_t* k_empty = k_full + NS;         // [NS]  one arrival per MMA warp
+  uint64_t* v_full = k_empty + NS;         // [NS]
+  uint64_t* v_empty = v_full + NS;         // [NS]  one arrival per MMA warp
+  uint64_t* s_full = v_empty + NS;         // [2]   S_t holds Q_t K_j^T
+  uint64_t* s_empty = s_full + 2;          // [2]   ... and is in registers (4 warps)
+  uint64_t* p_full = s_full + 4;           // [2]   P_t written (and O_t rescaled if needed) (4 warps)
+  uint64_t* o_done = s_full + 6;           // [2]   O_t += P_t V_j finished: P_t may be overwritten, O_t may be rescaled
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = (p.seq + FA_BM - 1) / FA_BM;
+  const int npair = (nblk + 1) >> 1;
+  const int hb = p.heads * p.batch;
+  const int n_items = npair * hb;
+  const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto item_of = [&](int round) -> int {     // snake order; >= n_items: this CTA sits the round out
+    return round * (int)gridDim.x + ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  };
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) report_error(p.status, OA_KERR_BAD_ARG);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 2);
+    for (int s = 0; s < NS; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&k_empty[s], 2); mbar_init(&v_empty[s], 2); }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&s_empty[t], 4); mbar_init(&p_full[t], 4); mbar_init(&o_done[t], 1); }
+    mbar_fence_init();
+  }
+  if (warp == 8) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // item -> (pair, head, batch) and the block counts of its two tiles (tile 1 absent: 0)
+  auto decode = [&](int item, int& pr, int& h, int& b, int& nkv0, int& nkv1) {
+    pr = npair - 1 - item / hb;
+    const int rem = item % hb;
+    h = rem % p.heads;
+    b = rem / p.heads;
+    nkv0 = p.causal ? (2 * pr + 1) : nblk;
+    nkv1 = (2 * pr + 1 < nblk) ? (p.causal ? (2 * pr + 2) : nblk) : 0;
+  };
+
+  if (warp == 10) {
+    // ------------- producer
+    uint32_t blk = 0, itc = 0;   // K / V blocks and items loaded so far
+    bool ok = true;
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int pr, h, b, nkv0, nkv1;
+      decode(item, pr, h, b, nkv0, nkv1);
+      const int n_it = max(nkv0, nkv1), row0 = b * p.seq;
+      if (!warp_wait(q_empty, (itc & 1) ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+      if (lane == 0) {
+        const int tiles = nkv1 > 0 ? 2 : 1;
+        mbar_expect_tx(q_full, tiles * Cfg::Q_BYTES);
+        for (int t = 0; t < tiles; ++t)
+          tma_load_2d(smem + Cfg::OFF_Q + t * Cfg::Q_BYTES, &tmQ, q_full, h * HD, row0 + (2 * pr + t) * FA_BM);
+      }
+      for (int j = 0; j < n_it; ++j, ++blk) {
+        const int st = blk % NS;
+        const uint32_t ph = (blk / NS) & 1;
+        if (!warp_wait(&k_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(&k_full[st], Cfg::KV_BYTES);
+          tma_load_2d(smem + Cfg::OFF_K + st * Cfg::KV_BYTES, &tmK, &k_full[st], h * HD, row0 + j * FA_BN);
+        }
+        if (!warp_wait(&v_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(&v_full[st], Cfg::KV_BYTES);
+          tma_load_2d(smem + Cfg::OFF_V + st * Cfg::KV_BYTES, &tmV, &v_full[st], h * HD, row0 + j * FA_BN);
+        }
+        __syncwarp();
+      }
+      ++itc;
+    }
+  } else if (warp == 8 || warp == 9) {
+    // ------------- MMA issuer of tile t (warp-uniform waits, lane 0 issues)
+    const int t = warp - 8;
+    constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_BM, HD, 0, 1);
+    const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q + t * Cfg::Q_BYTES);
+    const uint32_t s_tm = tmem_base + Cfg::TM_S + t * FA_BN, p_tm = tmem_base + Cfg::TM_P + t * 64, o_tm = tmem_base + Cfg::TM_O + t * HD;
+    uint32_t base = 0, itc = 0, sc = 0, pc = 0;   // K / V blocks before this item, items, S products and P V products of this tile so far
+    bool ok = true;
+    auto issue_qk = [&](uint32_t blk, bool last) -> bool {       // S_t = Q_t K^T of ring block `blk`
+      const int st = blk % NS;
+      if (!warp_wait(&k_full[st], (blk / NS) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); return false; }
+      if (sc > 0 && !warp_wait(&s_empty[t], (sc - 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); return false; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks)
+          umma_f16(s_tm, umma_smem_desc_sw128(q_addr + ks * 32, 16, 1024), umma_smem_desc_sw128(k_addr + ks * 32, 16, 1024),
+                   idesc_qk, ks > 0 ? 1u : 0u);
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[t]);
+        if (last) umma_commit(q_empty);
+      }
+      __syncwarp();
+      ++sc;
+      return true;
+    };
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int pr, h, b, nkv0, nkv1;
+      decode(item, pr, h, b, nkv0, nkv1);
+      const int n_it = max(nkv0, nkv1);
+      const int n = t == 0 ? nkv0 : nkv1;
+      if (!warp_wait(q_full, itc & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      if (n > 0) ok = issue_qk(base, n == 1);
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) { ok = issue_qk(base + j + 1, j + 2 == n); if (!ok) break; }
+        const int st = (base + j) % NS;
+        if (!warp_wait(&v_full[st], ((base + j) / NS) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+        if (!warp_wait(&p_full[t], pc & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::KV_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < FA_BN / 16; ++ks)
+            umma_f16_ts(o_tm, p_tm + ks * 8, umma_smem_desc_sw128(v_addr + ks * 2048, FA_BN * 128, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&v_empty[st]);
+          umma_commit(&o_done[t]);
+        }
+        __syncwarp();
+        ++pc;
+      }
+      // blocks of this item that this tile does not use (the last one of the pair's shorter tile, or all of an absent tile):
+      // the rings still expect one arrival per MMA warp, given once the block has landed
+      for (int j = n; j < n_it && ok; ++j) {
+        const int st = (base + j) % NS;
+        const uint32_t ph = ((base + j) / NS) & 1;
+        if (!warp_wait(&k_full[st], ph)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+        if (lane == 0) mbar_arrive(&k_empty[st]);
+        if (!warp_wait(&v_full[st], ph)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+        if (lane == 0) mbar_arrive(&v_empty[st]);
+        __syncwarp();
+      }
+      if (n == 0 && ok && lane == 0) mbar_arrive(q_empty);
+      __syncwarp();
+      base += n_it;
+      ++itc;
+    }
+  } else {
+    // ------------- softmax + output of tile t: one thread per query row
+    const int t = warp >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
+    const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + t * FA_BN;
+    const uint32_t p_addr = tmem_base + t_lane + Cfg::TM_P + t * 64;
+    const uint32_t o_addr = tmem_base + t_lane + Cfg::TM_O + t * HD;
+    const float sl2 = p.scale * LOG2E;
+    uint32_t sc = 0, pc = 0;     // score tiles consumed and P V completions awaited so far
+    bool ok = true;
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int pr, h, b, nkv0, nkv1;
+      decode(item, pr, h, b, nkv0, nkv1);
+      const int n = t == 0 ? nkv0 : nkv1;
+      if (n == 0) continue;
+      const int row0 = b * p.seq;
+      const int qbt = 2 * pr + t;
+      const int qi = qbt * FA_BM + r;               // query index inside the sequence
+      float m_run = -INFINITY, l_run = 0.f;
+      for (int j = 0; j < n; ++j, ++sc) {
+        ok = warp_wait(&s_full[t], sc & 1);
+        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+        tc_fence_after();
+        uint32_t sv[FA_BN];
+#pragma unroll
+        for (int c = 0; c < FA_BN / 32; ++c) tmem_ld32(s_addr + c * 32, sv + c * 32);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_empty[t]);   // the next block's scores may overwrite S_t now
+        const bool need_mask = (p.causal && j == qbt) || (j * FA_BN + FA_BN > p.seq);
+        if (need_mask) {
+          const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - j * FA_BN;   // columns i <= lim are alive
+#pragma unroll
+          for (int i = 0; i < FA_BN; ++i) sv[i] = (i <= lim) ? sv[i] : 0xff800000u;  // -inf
+        }
+        float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]);
+#pragma unroll
+        for (int i = 2; i < FA_BN - 2; i += 4) {
+          m0 = fmax3(m0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+          m1 = fmax3(m1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+        }
+        const float mx = fmax3(m0, m1, fmaxf(__uint_as_float(sv[FA_BN - 2]), __uint_as_float(sv[FA_BN - 1]))) * sl2;
+        const float m_new = fmaxf(m_run, mx);
+        const bool grow = (m_new - m_run) > FA_RESCALE_THRESHOLD;           // first block: m_run = -inf -> true
+        const float m_cand = grow ? m_new : m_run;
+        const float m_use = (m_cand == -INFINITY) ? 0.f : m_cand;           // row fully masked so far
+        const float alpha = grow ? fast_exp2(m_run - m_use) : 1.f;           // m_run = -inf -> 0
+        const float neg_m = -m_use;
+        if (j > 0) {                               // P_t is free and O_t is complete once the previous P V has finished
+          ok = warp_wait(&o_done[t], pc & 1);
+          if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+          ++pc;
+          tc_fence_after();
+        }
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+        for (int c = 0; c < FA_BN / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float e0 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i]), sl2, neg_m));
+            const float e1 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 1]), sl2, neg_m));
+            const float e2 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 2]), sl2, neg_m));
+            const float e3 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + i + 3]), sl2, neg_m));
+            l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+            pk[i >> 1] = pack_bf16x2(e0, e1);
+            pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
+          }
+          tmem_st16(p_addr + c * 16, pk);
+        }
+        l_run = l_run * alpha + ((l0 + l1) + (l2 + l3));
+        m_run = m_cand;
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
+          // some row of this warp moved its maximum: rescale O
+#pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_addr + c * 32, o);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[t]);
+      }
+      if (!ok) break;
+      ok = warp_wait(&o_done[t], pc & 1);
+      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+      ++pc;
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* op = p.o + (long long)(row0 + qi) * p.o_stride + h * HD;
@@ -589,11 +953,23 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       if (p.lse && qi < p.seq) p.lse[((long long)b * p.heads + h) * p.seq + qi] = (m_run + log2f(l_run)) / LOG2E;
+      tc_fence_before();   // the O reads above complete before this warp's next p_full arrival lets the next item's first P V overwrite O
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
+}
+
+template <int HD, int POLY>
+static int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashParams& p, dim3 grid, cudaStream_t st) {
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(flash_fwd2_kernel<HD, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<HD>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
+    set = true;
+  }
+  flash_fwd2_kernel<HD, POLY><<<grid, FA_THREADS, Fwd2Cfg<HD>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
 // ===================================================================================== backward
@@ -636,40 +1012,57 @@ flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __r
   }
 }
 
+constexpr int FA_BWD_THREADS = 384;   // 8 softmax warps + 3 MMA issuer warps (the dQ kernel uses 2) + 1 TMA warp
+
+// Backward pipeline (both kernels).  The score products of a tile land in TMEM; the eight softmax warps (two threads
+// per TMEM lane) copy them to registers and release the buffers at once, so the first MMA warp issues the score products
+// of the NEXT tile while this tile's exponentials run.  The bf16 results (P^T and dS^T in the dK/dV kernel, dS in the dQ
+// kernel) are written back to TMEM and are the A operands of the gradient products, which the second MMA warp issues:
+// nothing passes through shared memory.  One tcgen05.mma costs about 50 cycles to issue from a thread and the
+// N = head_dim products are issue bound, hence two issuing warps.
+//
+// The dK/dV kernel works on the TRANSPOSED tile, S^T = K Q^T with keys on the TMEM lanes, because dV = P^T dO and
+// dK = dS^T Q need P^T / dS^T with keys as the M dimension.  Per-query statistics (log-sum-exp, delta) are then per
+// COLUMN: the softmax warps stage them in shared memory (double buffered by iteration parity) and read them as broadcasts.
 template <int HD>
 struct BwdKvCfg {
-  static constexpr int NST = (HD == 64) ? 2 : 1;
+  static constexpr int NST = (HD == 64) ? 3 : 2;       // Q / dO ring: a stage is held from the score products to the end of dK
+  static constexpr bool ALIAS = HD != 64;               // head_dim 128: P^T / dS^T overwrite S^T / dP^T (no spare TMEM columns)
   static constexpr int T_BYTES = FA_BM * HD * 2;        // one [128 x HD] tile
-  static constexpr int P_BYTES = FA_BM * FA_BN * 2;
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = OFF_K + T_BYTES;
   static constexpr int OFF_Q = OFF_V + T_BYTES;
   static constexpr int OFF_DO = OFF_Q + NST * T_BYTES;
-  static constexpr int OFF_P = OFF_DO + NST * T_BYTES;
-  static constexpr int OFF_DS = OFF_P + P_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + P_BYTES;
+  static constexpr int OFF_STAT = OFF_DO + NST * T_BYTES;   // float[NST][256]: -lse*log2e | -delta*scale of the query block
+  static constexpr int OFF_BAR = OFF_STAT + NST * 256 * 4;
   static constexpr int SMEM_BYTES = OFF_BAR + 128;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 256 + HD;
+  static constexpr int TM_S = 0, TM_DP = 128;
+  static constexpr int TM_P = ALIAS ? 0 : 256, TM_DS = ALIAS ? 128 : 320;
+  static constexpr int TM_DV = ALIAS ? 256 : 384, TM_DK = TM_DV + HD;
 };
 
 // One CTA per (key block, head, batch): dK, dV accumulate in TMEM over the query blocks.
 template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const FlashBwdParams p) {
   using Cfg = BwdKvCfg<HD>;
   constexpr int NST = Cfg::NST;
+  constexpr bool ALIAS = Cfg::ALIAS;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;   // [2]
-  uint64_t* qdo_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* pds_full = bars + 6;
-  uint64_t* fin_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* qdo_full = bars + 1;   // [3]
+  uint64_t* qdo_empty = bars + 4;  // [3]  (dV and dK issuers both arrive)
+  uint64_t* s_full = bars + 7;     // S^T, dP^T of this tile are in TMEM
+  uint64_t* s_empty = bars + 8;    // ... and have been copied to registers (8 warps)
+  uint64_t* pds_full = bars + 9;   // P^T, dS^T of this tile are in TMEM (8 warps)
+  uint64_t* pds_empty = bars + 10; // ... and have been consumed by the gradient products (dV and dK issuers both arrive)
+  uint64_t* fin_full = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  float* stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = (p.seq + FA_BM - 1) / FA_BM;
@@ -686,19 +1079,23 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&qdo_full[s], 1); mbar_init(&qdo_empty[s], 1); }
+    for (int s = 0; s < NST; ++s) { mbar_init(&qdo_full[s], 2); mbar_init(&qdo_empty[s], 2); }   // full: TMA bytes + the statistics
     mbar_init(s_full, 1);
+    mbar_init(s_empty, 8);
     mbar_init(pds_full, 8);
-    mbar_init(fin_full, 1);
+    mbar_init(pds_empty, 2);
+    mbar_init(fin_full, 2);
     mbar_fence_init();
   }
-  if (warp == 1) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
+  if (warp == 8) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 11) {
+    // ------------- TMA producer (also stages the per-query statistics of each block)
+    const long long stat_base = ((long long)b * p.heads + h) * p.seq;
     if (lane == 0) {
       mbar_expect_tx(kv_full, 2 * Cfg::T_BYTES);
 #pragma unroll
@@ -706,126 +1103,180 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tma_load_2d(smem + Cfg::OFF_K + x * (FA_BN * 128), &tmK, kv_full, h * HD + x * 64, row0 + jb * FA_BN);
         tma_load_2d(smem + Cfg::OFF_V + x * (FA_BN * 128), &tmV, kv_full, h * HD + x * 64, row0 + jb * FA_BN);
       }
-      for (int it = 0; it < n_it; ++it) {
-        int st = it % NST;
-        uint32_t ph = (it / NST) & 1;
-        if (!mbar_wait(&qdo_empty[st], ph ^ 1)) { report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it % NST;
+      const uint32_t ph = (it / NST) & 1;
+      if (!warp_wait(&qdo_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+      if (lane == 0) {
         mbar_expect_tx(&qdo_full[st], 2 * Cfg::T_BYTES);
-        int qrow = row0 + (i0 + it) * FA_BM;
+        const int qrow = row0 + (i0 + it) * FA_BM;
 #pragma unroll
         for (int x = 0; x < HD / 64; ++x) {
           tma_load_2d(smem + Cfg::OFF_Q + st * Cfg::T_BYTES + x * (FA_BM * 128), &tmQ, &qdo_full[st], h * HD + x * 64, qrow);
           tma_load_2d(smem + Cfg::OFF_DO + st * Cfg::T_BYTES + x * (FA_BM * 128), &tmDO, &qdo_full[st], h * HD + x * 64, qrow);
         }
       }
+      // per-query statistics of this block, negated and pre-scaled: lane l stages queries 4l .. 4l+3
+      {
+        float4 nl, nd;
+        float* nlp = reinterpret_cast<float*>(&nl);
+        float* ndp = reinterpret_cast<float*>(&nd);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int qi = (i0 + it) * FA_BM + lane * 4 + u;
+          const bool okq = qi < p.seq;
+          nlp[u] = okq ? -p.lse[stat_base + qi] * LOG2E : -INFINITY;
+          ndp[u] = okq ? -p.delta[stat_base + qi] * p.scale : 0.f;
+        }
+        float* dst = stat + st * 256;
+        reinterpret_cast<float4*>(dst)[lane] = nl;
+        reinterpret_cast<float4*>(dst + 128)[lane] = nd;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&qdo_full[st]);
+      __syncwarp();
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
-      constexpr uint32_t idesc_g = umma_idesc_bf16(FA_BN, HD, 1, 1);   // [keys x HD] += X^T[keys x q] * Y[q x HD]
-      const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K), v_addr = smem_u32(smem + Cfg::OFF_V);
-      const uint32_t p_addr = smem_u32(smem + Cfg::OFF_P), ds_addr = smem_u32(smem + Cfg::OFF_DS);
-      bool ok = mbar_wait(kv_full, 0);
-      if (!ok) report_error(p.status, OA_KERR_WAIT_FULL);
-      for (int it = 0; it < n_it && ok; ++it) {
-        int st = it % NST;
-        if (!mbar_wait(&qdo_full[st], (it / NST) & 1)) { report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
-        tc_fence_after();
+  } else if (warp == 8) {
+    // ------------- MMA issuer A: transposed score products S^T = K Q^T, dP^T = V dO^T
+    constexpr uint32_t idesc_s = umma_idesc_bf16(FA_BN, FA_BM, 0, 0);
+    const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K), v_addr = smem_u32(smem + Cfg::OFF_V);
+    bool ok = warp_wait(kv_full, 0);
+    if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int st = it % NST;
+      FA_STAMP(it * 16 + 8);
+      if (!warp_wait(&qdo_full[st], (it / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      // S^T / dP^T may be overwritten once the softmax warps hold the previous tile in registers; when P^T / dS^T share
+      // those columns, only once the previous gradient products have consumed them
+      if (it > 0 && !warp_wait(ALIAS ? pds_empty : s_empty, (it - 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
+      tc_fence_after();
+      FA_STAMP(it * 16 + 9);
+      if (lane == 0) {
         const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q + st * Cfg::T_BYTES);
         const uint32_t do_addr = smem_u32(smem + Cfg::OFF_DO + st * Cfg::T_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(q_addr + off, 16, 1024),
-                   umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+          umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(k_addr + off, 16, 1024),
+                   umma_smem_desc_sw128(q_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_DP, umma_smem_desc_sw128(do_addr + off, 16, 1024),
-                   umma_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+          umma_f16(tmem_base + Cfg::TM_DP, umma_smem_desc_sw128(v_addr + off, 16, 1024),
+                   umma_smem_desc_sw128(do_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(s_full);
-        if (!mbar_wait(pds_full, it & 1)) { report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < FA_BM / 16; ++ks) {   // reduction over the 128 queries of this block
-          umma_f16(tmem_base + Cfg::TM_DV, umma_smem_desc_sw128(p_addr + ks * 2048, FA_BM * 128, 1024),
-                   umma_smem_desc_sw128(do_addr + ks * 2048, FA_BM * 128, 1024), idesc_g, (it > 0 || ks > 0) ? 1u : 0u);
-        }
-#pragma unroll
-        for (int ks = 0; ks < FA_BM / 16; ++ks) {
-          umma_f16(tmem_base + Cfg::TM_DK, umma_smem_desc_sw128(ds_addr + ks * 2048, FA_BM * 128, 1024),
-                   umma_smem_desc_sw128(q_addr + ks * 2048, FA_BM * 128, 1024), idesc_g, (it > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(&qdo_empty[st]);
       }
-      if (ok) umma_commit(fin_full);
+      __syncwarp();
+      FA_STAMP(it * 16 + 10);
     }
+  } else if (warp == 9 || warp == 10) {
+    // ------------- MMA issuers B (warp 9: dV += P^T dO) and C (warp 10: dK += dS^T Q), A operands from TMEM
+    constexpr uint32_t idesc_g = umma_idesc_bf16(FA_BN, HD, 0, 1);   // [keys x HD] += X^T[keys x q] (TMEM) * Y[q x HD]
+    const bool is_dv = warp == 9;
+    const uint32_t acc_addr = tmem_base + (is_dv ? Cfg::TM_DV : Cfg::TM_DK);
+    const uint32_t a_addr = tmem_base + (is_dv ? Cfg::TM_P : Cfg::TM_DS);
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it % NST;
+      if (!warp_wait(&qdo_full[st], (it / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+      if (!warp_wait(pds_full, it & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t b_addr = smem_u32(smem + (is_dv ? Cfg::OFF_DO : Cfg::OFF_Q) + st * Cfg::T_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < FA_BM / 16; ++ks)    // reduction over the 128 queries of this block
+          umma_f16_ts(acc_addr, a_addr + ks * 8, umma_smem_desc_sw128(b_addr + ks * 2048, FA_BM * 128, 1024), idesc_g,
+                      (it > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&qdo_empty[st]);
+        umma_commit(pds_empty);
+      }
+      __syncwarp();
+    }
+    if (ok && lane == 0) umma_commit(fin_full);
+    __syncwarp();
   } else {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;            // this thread owns key columns [64*half, 64*half+64)
-    const int r = quad * 32 + lane;
+    const int half = warp >> 2;                  // this thread owns query columns [64*half, 64*half+64) of the tile
+    const int r = quad * 32 + lane;              // key row inside the block = TMEM lane
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    uint8_t* sP = smem + Cfg::OFF_P;
-    uint8_t* sDS = smem + Cfg::OFF_DS;
-    const long long stat_base = ((long long)b * p.heads + h) * p.seq;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const int ib = i0 + it;
-      const int qi = ib * FA_BM + r;
-      const bool q_ok = qi < p.seq;
-      const float lse2 = q_ok ? p.lse[stat_base + qi] * LOG2E : INFINITY;
-      const float dlt = q_ok ? p.delta[stat_base + qi] : 0.f;
-      ok = mbar_wait(s_full, it & 1);
-      ok = __all_sync(0xffffffffu, ok);
+      const float* st_cur = stat + (it % NST) * 256;
+      if (warp == 0) FA_STAMP(it * 16 + 0);
+      ok = warp_wait(&qdo_full[it % NST], (it / NST) & 1);   // statistics of this block are staged
+      if (warp == 0) FA_STAMP(it * 16 + 1);
+      if (ok) ok = warp_wait(s_full, it & 1);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
-      const int k0 = jb * FA_BN;
-      const bool need_mask = (p.causal && ib == jb) || (k0 + FA_BN > p.seq) || !q_ok;
+      if (warp == 0) FA_STAMP(it * 16 + 2);
+      uint32_t s[64], dp[64];
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64, s);
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64 + 32, s + 32);
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64, dp);
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64 + 32, dp + 32);
+      tmem_ld_wait();
+      if (ALIAS) {
+        pair_sync(quad);                         // both threads of the lane hold their columns before either overwrites them
+      } else {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty);     // the next tile's score products may overwrite S^T, dP^T now
+      }
+      if (warp == 0) FA_STAMP(it * 16 + 3);
+      const float4* nl4 = reinterpret_cast<const float4*>(st_cur + half * 64);
+      const float4* nd4 = reinterpret_cast<const float4*>(st_cur + 128 + half * 64);
+      const bool diag = p.causal && ib == jb;    // alive iff key <= query: column >= row
+      const int first = r - half * 64;           // first alive column of this thread on the diagonal tile
+      uint32_t pw[32], dw[32];
+      if (diag) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
-        uint32_t s[32], dp[32];
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + c * 32, s);
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + c * 32, dp);
-        tmem_ld_wait();
-        uint32_t pw[16], dw[16];
-        const float nlse = -lse2, ndlt = -dlt * p.scale;
-        if (need_mask) {
-          const int lim = q_ok ? (min(p.causal ? qi : 0x7fffffff, p.seq - 1) - (k0 + c * 32)) : -1;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse)) : 0.f;
-            float p1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse)) : 0.f;
-            pw[i >> 1] = pack_bf16x2(p0, p1);
-            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse));
-            float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse));
-            pw[i >> 1] = pack_bf16x2(p0, p1);
-            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
-          }
+        for (int i = 0; i < 64; i += 4) {
+          const float4 nl = nl4[i >> 2], nd = nd4[i >> 2];
+          const float p0 = (i >= first) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nl.x)) : 0.f;
+          const float p1 = (i + 1 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nl.y)) : 0.f;
+          const float p2 = (i + 2 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 2]), sl2, nl.z)) : 0.f;
+          const float p3 = (i + 3 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 3]), sl2, nl.w)) : 0.f;
+          pw[i >> 1] = pack_bf16x2(p0, p1);
+          pw[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, nd.x), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, nd.y));
+          dw[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(dp[i + 2]), p.scale, nd.z), p3 * fmaf(__uint_as_float(dp[i + 3]), p.scale, nd.w));
         }
+      } else {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint32_t off = half * (FA_BM * 128) + r * 128 + ((((cc * 4 + g) ^ (r & 7))) << 4);
-          *reinterpret_cast<uint4*>(sP + off) = make_uint4(pw[g * 4], pw[g * 4 + 1], pw[g * 4 + 2], pw[g * 4 + 3]);
-          *reinterpret_cast<uint4*>(sDS + off) = make_uint4(dw[g * 4], dw[g * 4 + 1], dw[g * 4 + 2], dw[g * 4 + 3]);
+        for (int i = 0; i < 64; i += 4) {
+          const float4 nl = nl4[i >> 2], nd = nd4[i >> 2];
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nl.x));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nl.y));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), sl2, nl.z));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), sl2, nl.w));
+          pw[i >> 1] = pack_bf16x2(p0, p1);
+          pw[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, nd.x), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, nd.y));
+          dw[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(dp[i + 2]), p.scale, nd.z), p3 * fmaf(__uint_as_float(dp[i + 3]), p.scale, nd.w));
         }
       }
+      if (warp == 0) FA_STAMP(it * 16 + 4);
+      if (!ALIAS && it > 0) {                     // the previous tile's gradient products still read P^T, dS^T
+        ok = warp_wait(pds_empty, (it - 1) & 1);
+        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+        tc_fence_after();
+      }
+      if (warp == 0) FA_STAMP(it * 16 + 5);
+      tmem_st32(tmem_base + t_lane + Cfg::TM_P + half * 32, pw);
+      tmem_st32(tmem_base + t_lane + Cfg::TM_DS + half * 32, dw);
+      tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if (warp == 0) FA_STAMP(it * 16 + 6);
     }
     if (ok) {
-      ok = mbar_wait(fin_full, 0);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = warp_wait(fin_full, 0);
       if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL);
     }
     if (ok) {
@@ -856,28 +1307,26 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
+  if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
 }
 
 template <int HD>
 struct BwdQCfg {
-  static constexpr int NST = (HD == 64) ? 2 : 1;
+  static constexpr int NST = (HD == 64) ? 3 : 2;       // K / V ring
   static constexpr int T_BYTES = FA_BM * HD * 2;
-  static constexpr int P_BYTES = FA_BM * FA_BN * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = OFF_Q + T_BYTES;
   static constexpr int OFF_K = OFF_DO + T_BYTES;
   static constexpr int OFF_V = OFF_K + NST * T_BYTES;
-  static constexpr int OFF_DS = OFF_V + NST * T_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + P_BYTES;
+  static constexpr int OFF_BAR = OFF_V + NST * T_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 128;
   static constexpr int TMEM_COLS = 512;
-  static constexpr int TM_S = 0, TM_DP = 128, TM_DQ = 256;
+  static constexpr int TM_S = 0, TM_DP = 128, TM_DS = 256, TM_DQ = 320;
 };
 
 // One CTA per (query block, head, batch): dQ accumulates in TMEM over the key blocks.
 template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const FlashBwdParams p) {
@@ -886,12 +1335,14 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* ds_full = bars + 6;
-  uint64_t* fin_full = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* s_full = bars + 7;
+  uint64_t* s_empty = bars + 8;
+  uint64_t* ds_full = bars + 9;
+  uint64_t* ds_empty = bars + 10;
+  uint64_t* fin_full = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = (p.seq + FA_BM - 1) / FA_BM;
@@ -907,19 +1358,21 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < NST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
+    mbar_init(s_empty, 8);
     mbar_init(ds_full, 8);
+    mbar_init(ds_empty, 1);
     mbar_init(fin_full, 1);
     mbar_fence_init();
   }
-  if (warp == 1) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
+  if (warp == 8) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 10) {
     if (lane == 0) {
       mbar_expect_tx(q_full, 2 * Cfg::T_BYTES);
 #pragma unroll
@@ -927,10 +1380,12 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         tma_load_2d(smem + Cfg::OFF_Q + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + ib * FA_BM);
         tma_load_2d(smem + Cfg::OFF_DO + x * (FA_BM * 128), &tmDO, q_full, h * HD + x * 64, row0 + ib * FA_BM);
       }
-      for (int j = 0; j < n_kv; ++j) {
-        int st = j % NST;
-        uint32_t ph = (j / NST) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1)) { report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+    }
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j % NST;
+      const uint32_t ph = (j / NST) & 1;
+      if (!warp_wait(&kv_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+      if (lane == 0) {
         mbar_expect_tx(&kv_full[st], 2 * Cfg::T_BYTES);
 #pragma unroll
         for (int x = 0; x < HD / 64; ++x) {
@@ -938,104 +1393,130 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tma_load_2d(smem + Cfg::OFF_V + st * Cfg::T_BYTES + x * (FA_BN * 128), &tmV, &kv_full[st], h * HD + x * 64, row0 + j * FA_BN);
         }
       }
+      __syncwarp();
     }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
-      constexpr uint32_t idesc_q = umma_idesc_bf16(FA_BM, HD, 0, 1);   // dQ[q x HD] += dS[q x keys] * K[keys x HD]
-      const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q), do_addr = smem_u32(smem + Cfg::OFF_DO);
-      const uint32_t ds_addr = smem_u32(smem + Cfg::OFF_DS);
-      bool ok = mbar_wait(q_full, 0);
-      if (!ok) report_error(p.status, OA_KERR_WAIT_FULL);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        int st = j % NST;
-        if (!mbar_wait(&kv_full[st], (j / NST) & 1)) { report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
-        tc_fence_after();
+  } else if (warp == 8) {
+    // ------------- MMA issuer A: S = Q K_j^T, dP = dO V_j^T
+    constexpr uint32_t idesc_s = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
+    const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q), do_addr = smem_u32(smem + Cfg::OFF_DO);
+    bool ok = warp_wait(q_full, 0);
+    if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int st = j % NST;
+      FA_STAMP(4096 + j * 16 + 8);
+      if (!warp_wait(&kv_full[st], (j / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      FA_STAMP(4096 + j * 16 + 9);
+      if (j > 0 && !warp_wait(s_empty, (j - 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
+      tc_fence_after();
+      if (lane == 0) {
         const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::T_BYTES);
         const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::T_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
           umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(q_addr + off, 16, 1024),
                    umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-          uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
           umma_f16(tmem_base + Cfg::TM_DP, umma_smem_desc_sw128(do_addr + off, 16, 1024),
                    umma_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
         }
         umma_commit(s_full);
-        if (!mbar_wait(ds_full, j & 1)) { report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < FA_BN / 16; ++ks) {
-          uint32_t a_off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_DQ, umma_smem_desc_sw128(ds_addr + a_off, 16, 1024),
-                   umma_smem_desc_sw128(k_addr + ks * 2048, FA_BN * 128, 1024), idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(&kv_empty[st]);
       }
-      if (ok) umma_commit(fin_full);
+      __syncwarp();
+      FA_STAMP(4096 + j * 16 + 10);
     }
-  } else {
+  } else if (warp == 9) {
+    // ------------- MMA issuer B: dQ += dS K_j (dS from TMEM)
+    constexpr uint32_t idesc_q = umma_idesc_bf16(FA_BM, HD, 0, 1);   // dQ[q x HD] += dS[q x keys] * K[keys x HD]
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j % NST;
+      if (!warp_wait(&kv_full[st], (j / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+      FA_STAMP(4096 + j * 16 + 11);
+      if (!warp_wait(ds_full, j & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
+      tc_fence_after();
+      FA_STAMP(4096 + j * 16 + 12);
+      if (lane == 0) {
+        const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::T_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < FA_BN / 16; ++ks)
+          umma_f16_ts(tmem_base + Cfg::TM_DQ, tmem_base + Cfg::TM_DS + ks * 8,
+                      umma_smem_desc_sw128(k_addr + ks * 2048, FA_BN * 128, 1024), idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(&kv_empty[st]);
+        umma_commit(ds_empty);
+      }
+      __syncwarp();
+      FA_STAMP(4096 + j * 16 + 13);
+    }
+    if (ok && lane == 0) umma_commit(fin_full);
+    __syncwarp();
+  } else if (warp < 8) {
     const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = warp >> 2;
     const int r = quad * 32 + lane;
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    uint8_t* sDS = smem + Cfg::OFF_DS;
     const long long stat_base = ((long long)b * p.heads + h) * p.seq;
     const int qi = ib * FA_BM + r;
     const bool q_ok = qi < p.seq;
     const float lse2 = q_ok ? p.lse[stat_base + qi] * LOG2E : INFINITY;
     const float dlt = q_ok ? p.delta[stat_base + qi] : 0.f;
+    const float nlse = -lse2, ndlt = -dlt * p.scale;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      ok = mbar_wait(s_full, j & 1);
-      ok = __all_sync(0xffffffffu, ok);
+      if (warp == 0) FA_STAMP(4096 + j * 16 + 0);
+      ok = warp_wait(s_full, j & 1);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
+      if (warp == 0) FA_STAMP(4096 + j * 16 + 1);
+      uint32_t s[64], dp[64];
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64, s);
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64 + 32, s + 32);
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64, dp);
+      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64 + 32, dp + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty);
+      if (warp == 0) FA_STAMP(4096 + j * 16 + 2);
       const int k0 = j * FA_BN;
       const bool need_mask = (p.causal && j == ib) || (k0 + FA_BN > p.seq) || !q_ok;
+      uint32_t dw[32];
+      if (need_mask) {
+        const int lim = q_ok ? (min(p.causal ? qi : 0x7fffffff, p.seq - 1) - (k0 + half * 64)) : -1;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
-        uint32_t s[32], dp[32];
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + c * 32, s);
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + c * 32, dp);
-        tmem_ld_wait();
-        uint32_t dw[16];
-        const float nlse = -lse2, ndlt = -dlt * p.scale;
-        if (need_mask) {
-          const int lim = q_ok ? (min(p.causal ? qi : 0x7fffffff, p.seq - 1) - (k0 + c * 32)) : -1;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse)) : 0.f;
-            float p1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse)) : 0.f;
-            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse));
-            float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse));
-            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
-          }
+        for (int i = 0; i < 64; i += 2) {
+          const float p0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse)) : 0.f;
+          const float p1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse)) : 0.f;
+          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
         }
+      } else {
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(sDS + half * (FA_BM * 128) + r * 128 + ((((cc * 4 + g) ^ (r & 7))) << 4)) =
-              make_uint4(dw[g * 4], dw[g * 4 + 1], dw[g * 4 + 2], dw[g * 4 + 3]);
+        for (int i = 0; i < 64; i += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse));
+          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
+        }
       }
+      if (warp == 0) FA_STAMP(4096 + j * 16 + 3);
+      if (j > 0) {
+        ok = warp_wait(ds_empty, (j - 1) & 1);
+        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+        tc_fence_after();
+      }
+      if (warp == 0) FA_STAMP(4096 + j * 16 + 4);
+      tmem_st32(tmem_base + t_lane + Cfg::TM_DS + half * 32, dw);
+      tmem_st_wait();
       tc_fence_before();
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
+      if (warp == 0) FA_STAMP(4096 + j * 16 + 5);
     }
     if (ok) {
-      ok = mbar_wait(fin_full, 0);
-      ok = __all_sync(0xffffffffu, ok);
+      ok = warp_wait(fin_full, 0);
       if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL);
     }
     if (ok) {
@@ -1061,7 +1542,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
+  if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
 }
 
 int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
@@ -1089,18 +1570,31 @@ extern "C" int oa_flash_fwd(const void* q, const void* k, const void* v, void* o
   cudaStream_t st = (cudaStream_t)stream;
   static const int version = [] { const char* e = getenv("OA_FLASH_FWD"); return (e && e[0] == '1') ? 1 : 2; }();
   if (version == 2) {
-    const int nblk = (seq + FA_BM - 1) / FA_BM;
-    dim3 grid2((nblk + 1) / 2, heads, batch);
-    if (head_dim == 64) {
-      static bool set = false;
-      if (!set) { if (cudaFuncSetAttribute(flash_fwd2_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<64>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
-      flash_fwd2_kernel<64><<<grid2, FA_THREADS, Fwd2Cfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, p);
-    } else {
-      static bool set = false;
-      if (!set) { if (cudaFuncSetAttribute(flash_fwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<128>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
-      flash_fwd2_kernel<128><<<grid2, FA_THREADS, Fwd2Cfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    static const int poly = [] { const char* e = getenv("OA_FLASH_POLY"); return e ? atoi(e) : 0; }();
+    dim3 grid2((seq + FA_BM - 1) / FA_BM, heads, batch);
+    static const bool single = [] { const char* e = getenv("OA_FLASH_FWD"); return e && e[0] == '3'; }();
+    if (head_dim == 64 && !single) {
+      static int sms = 0;
+      if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return OA_ERR_DRIVER;
+        if (cudaFuncSetAttribute(flash_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdPairCfg::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
+      }
+      const int nblk = (seq + FA_BM - 1) / FA_BM;
+      const long long items = (long long)((nblk + 1) / 2) * heads * batch;
+      const int ctas = (int)(items < sms ? items : sms);
+      flash_fwd_pair_kernel<<<ctas, FwdPairCfg::THREADS, FwdPairCfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+      return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
     }
-    return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+    if (head_dim == 64) {
+      if (poly == 2) return launch_fwd2<64, 2>(tq, tk, tv, p, grid2, st);
+      if (poly == 3) return launch_fwd2<64, 3>(tq, tk, tv, p, grid2, st);
+      if (poly == 4) return launch_fwd2<64, 4>(tq, tk, tv, p, grid2, st);
+      return launch_fwd2<64, 0>(tq, tk, tv, p, grid2, st);
+    }
+    if (poly == 2) return launch_fwd2<128, 2>(tq, tk, tv, p, grid2, st);
+    if (poly == 3) return launch_fwd2<128, 3>(tq, tk, tv, p, grid2, st);
+    return launch_fwd2<128, 0>(tq, tk, tv, p, grid2, st);
   }
   dim3 grid((seq + FA_BM - 1) / FA_BM, heads, batch);
   if (head_dim == 64) {
@@ -1114,6 +1608,12 @@ extern "C" int oa_flash_fwd(const void* q, const void* k, const void* v, void* o
   }
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
+
+#ifdef OA_FA_PROF
+extern "C" int oa_flash_prof_read(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_fa_prof, sizeof(long long) * (size_t)n) == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+}
+#endif
 
 // scratch: float[B*H*S] for delta
 extern "C" size_t oa_flash_bwd_scratch_bytes(int batch, int heads, int seq, int head_dim) {
@@ -1164,8 +1664,8 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
       if ((rc = set_max_smem(flash_bwd_q_kernel<64>, BwdQCfg<64>::SMEM_BYTES))) return rc;
       set = true;
     }
-    flash_bwd_kv_kernel<64><<<grid, FA_THREADS, BwdKvCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    flash_bwd_q_kernel<64><<<grid, FA_THREADS, BwdQCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_kv_kernel<64><<<grid, FA_BWD_THREADS, BwdKvCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_q_kernel<64><<<grid, FA_BWD_THREADS, BwdQCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
   } else {
     static bool set = false;
     if (!set) {
@@ -1173,8 +1673,8 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
       if ((rc = set_max_smem(flash_bwd_q_kernel<128>, BwdQCfg<128>::SMEM_BYTES))) return rc;
       set = true;
     }
-    flash_bwd_kv_kernel<128><<<grid, FA_THREADS, BwdKvCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    flash_bwd_q_kernel<128><<<grid, FA_THREADS, BwdQCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_kv_kernel<128><<<grid, FA_BWD_THREADS, BwdKvCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    flash_bwd_q_kernel<128><<<grid, FA_BWD_THREADS, BwdQCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
   }
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }

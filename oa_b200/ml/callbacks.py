@@ -105,14 +105,15 @@ class OaCbCheckpoint(OaCallback):
         return self.Status
 
     def _metric(self, training) -> float:
-        return float(self.Metric.Value()) if self.Metric is not None else float(training.EpochMeanLoss())
+        value = float(self.Metric.Value()) if self.Metric is not None else float(training.EpochMeanLoss())
+        return OaCheckpointManager._agreed(self.Opt, value)      # the same number on every rank
 
     def OnStepEnd(self, training, step, loss):
         if not self.Status or self.SaveEvery <= 0 or training.IsEpochBoundary() or step % self.SaveEvery:
             return None
         if self.Verbose:
             print(f"\nStep {step}: loss = {loss:.6f} - saving resumable checkpoint", flush=True)
-        self.Status = self.Mgr.SaveIncremental(self.Model, self.Opt, step, float(loss), "loss")
+        self.Status = self.Mgr.SaveIncremental(self.Model, self.Opt, step, float(loss), "loss")   # agrees on the loss itself
         return self.Status
 
     def OnEpochEnd(self, training, epoch):
@@ -122,7 +123,7 @@ class OaCbCheckpoint(OaCallback):
         if self.Mgr.IsBetter(metric):
             if self.Verbose:
                 print(f"\nEpoch {epoch + 1}: {self.Mgr.MetricName()} improved {self.Mgr.GetBestMetric():.6f} -> {metric:.6f}, saving best", flush=True)
-            self.Status = self.Mgr.MaybeSave(self.Model, self.Opt, training.StepCount(), metric)
+            self.Status = self.Mgr.MaybeSave(self.Model, self.Opt, training.StepCount(), metric, agreed=True)
             self._saved_best = bool(self.Status)
         return self.Status
 

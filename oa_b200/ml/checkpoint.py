@@ -57,8 +57,16 @@ class OaCheckpointManager:
         return self.Config.MetricName
 
     # ---- saving
+    @staticmethod
+    def _agreed(opt, metric: float) -> float:
+        """The metric as every rank sees it (mean over the ranks under data parallelism): the decision to save must be
+        collective, because the optimizer's SaveTo gathers sharded state with a collective call."""
+        return float(opt.ReduceMetric(metric)) if opt is not None and hasattr(opt, "ReduceMetric") else float(metric)
+
     def _write(self, path: str, model, opt, step: int, metric: float, metric_name: str) -> OaStatus:
-        os.makedirs(os.path.dirname(path), exist_ok=True)
+        primary = opt.IsPrimaryWriter() if opt is not None and hasattr(opt, "IsPrimaryWriter") else True
+        if primary:
+            os.makedirs(os.path.dirname(path), exist_ok=True)
         oam = OamModel()
         st = model.SaveTo(oam)
         if not st:
@@ -72,10 +80,13 @@ class OaCheckpointManager:
         if opt is not None:
             pr.Lr = float(opt.Lr())
         oam.SetProgress(pr)
-        return oam.Save(path)
+        return oam.Save(path) if primary else OaStatus.Ok()     # every rank took part in the gather; one rank writes
 
-    def MaybeSave(self, model, opt, step: int, metric: float, force: bool = False) -> OaStatus:
-        """Writes the best-model file when the metric improved (or when forced)."""
+    def MaybeSave(self, model, opt, step: int, metric: float, force: bool = False, agreed: bool = False) -> OaStatus:
+        """Writes the best-model file when the metric improved (or when forced).  `agreed`: the metric is already the
+        value every rank holds."""
+        if not agreed:
+            metric = self._agreed(opt, metric)
         if not (force or self.IsBetter(metric)):
             return OaStatus.Ok()
         if self.Config.SaveBest or force:
@@ -86,14 +97,17 @@ class OaCheckpointManager:
             self.BestMetric = float(metric)
         return OaStatus.Ok()
 
-    def SaveIncremental(self, model, opt, step: int, metric: float, metric_name: str = "") -> OaStatus:
+    def SaveIncremental(self, model, opt, step: int, metric: float, metric_name: str = "", agreed: bool = False) -> OaStatus:
+        if not agreed:
+            metric = self._agreed(opt, metric)
         name = metric_name or self.Config.MetricName
         path = os.path.join(self.GetIncrementalDir(), self.BuildFilename(step, metric, name))
         st = self._write(path, model, opt, step, metric, name)
         if not st:
             return st
-        self._saved.append((path, float(metric), int(step)))
-        self._rotate()
+        if opt is None or not hasattr(opt, "IsPrimaryWriter") or opt.IsPrimaryWriter():
+            self._saved.append((path, float(metric), int(step)))
+            self._rotate()
         return OaStatus.Ok()
 
     def _rotate(self) -> None:

@@ -215,6 +215,8 @@ class OaModule:
             st = optimizer.SaveTo(oam)
         if not st:
             return st
+        if optimizer is not None and hasattr(optimizer, "IsPrimaryWriter") and not optimizer.IsPrimaryWriter():
+            return OaStatus.Ok()      # took part in the optimizer's gather; rank 0 writes the file
         return oam.Save(path)
 
     def Load(self, path, optimizer=None) -> OaStatus:

@@ -141,6 +141,15 @@ class OaOptimizer:
 
     StepCount = GetStep
 
+    def ReduceMetric(self, value: float) -> float:
+        """A host scalar as every rank should see it.  One process: the value itself; a data-parallel wrapper replaces
+        this with the mean over its ranks so that metric-driven decisions (save the best model) agree everywhere."""
+        return float(value)
+
+    def IsPrimaryWriter(self) -> bool:
+        """Whether this process writes checkpoint files (rank 0 under data parallelism)."""
+        return True
+
     def NotifyProgramReplay(self, count: int = 1) -> None:
         self.Step_ += count
 

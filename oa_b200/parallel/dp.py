@@ -47,9 +47,17 @@ class OaDataParallel:
         # identical initial weights on every rank
         for a in self.arenas:
             dist.broadcast(a.flat, src=0, group=self.mesh.group)
+        optimizer.ReduceMetric = self.ReduceMetric
+        optimizer.IsPrimaryWriter = lambda: self.rank == 0
         if mode == "fused":
             self.ch_grads = self.mesh.NewChannel()
             self.ch_params = self.mesh.NewChannel()
+            self.ch_norm = self.mesh.NewChannel()
+            lib = N.require()
+            self._norm_partial = torch.zeros(int(lib.oa_dp_sumsq_blocks()), dtype=torch.float32, device=self.mesh.device)
+            self._norm_slots = self.mesh.AllocSymmetric(16 * 8)          # one 16-byte slot per rank
+            self._norm_extra = torch.zeros(1, dtype=torch.float32, device=self.mesh.device)
+            self._coef = torch.ones(2, dtype=torch.float32, device=self.mesh.device)
             self._shards = []
             for i, a in enumerate(self.arenas):
                 if a.dtype != torch.bfloat16:
@@ -87,6 +95,39 @@ class OaDataParallel:
         return t
 
     # ---- steps
+    def _clip_coef(self, replicated) -> Optional[torch.Tensor]:
+        """Clip coefficient from the norm of the gradient summed over the ranks (every rank gets the same bits): each
+        rank takes the sum of squares of its shard, the scalars are exchanged through peer memory."""
+        opt = self.opt
+        if opt._clip_norm is None:
+            return None
+        lib = N.require()
+        ctx = RT.OaContext.GetDefault()
+        for k, i in enumerate(replicated):
+            K.sumsq(self._summed[i], self._norm_extra[0:1], accumulate=k > 0)
+        first = True
+        for a, sh in zip(self.arenas, self._shards):
+            if sh is None:
+                continue
+            lo, sn = sh[0], sh[1]
+            ctx.Add("DpShardSumSq")
+            N.check(lib.oa_dp_shard_sumsq(self._sym[a.grad.data_ptr()].ptr_array, lo, sn, self.rank, self.world,
+                                          self._norm_partial.data_ptr(), 0 if first else 1, N.stream()), "oa_dp_shard_sumsq")
+            N.count_launch()
+            first = False
+        if first:
+            self._norm_partial.zero_()
+        N.check(lib.oa_dp_sumsq_publish(self._norm_partial.data_ptr(), self._norm_slots.ptr_array, self.rank, self.world, N.stream()),
+                "oa_dp_sumsq_publish")
+        N.count_launch()
+        self.ch_norm.Signal()
+        self.ch_norm.Wait()
+        N.check(lib.oa_dp_clip_finalize(self._norm_slots.local_ptr, self.world, self._norm_extra.data_ptr() if replicated else None,
+                                        float(opt._clip_norm) / max(opt.GradScale_, 1e-30), self._coef.data_ptr(), N.stream()),
+                "oa_dp_clip_finalize")
+        N.count_launch()
+        return self._coef
+
     def _fused_step(self) -> None:
         opt = self.opt
         ctx = RT.OaContext.GetDefault()
@@ -96,17 +137,21 @@ class OaDataParallel:
         self.ch_grads.Signal()
         status = K.status_word(self.mesh.device)
         replicated = [i for i, sh in enumerate(self._shards) if sh is None]
-        if replicated:
+        clip = opt._clip_norm is not None
+        if replicated or clip:
             self.ch_grads.Wait()                       # every rank's gradients are complete
-            for i in replicated:
-                a = self.arenas[i]
-                ctx.Add("DpPeerReduceAdam")
-                gbuf = self._sym[a.grad.data_ptr()]
-                summed = self._summed.setdefault(i, torch.empty(a.numel, dtype=a.dtype, device=a.device))
-                N.check(lib.oa_peer_reduce(K.dt(a.grad), gbuf.ptr_array, summed.data_ptr(), 0, a.numel, self.world, 0, N.stream()),
-                        "oa_peer_reduce")
-                N.count_launch()
-                K.adam_step(a.flat, summed, a.master, opt._m[i], opt._v[i], opt._state, decoupled=opt.Decoupled)
+        for i in replicated:
+            a = self.arenas[i]
+            ctx.Add("DpPeerReduce")
+            gbuf = self._sym[a.grad.data_ptr()]
+            summed = self._summed.setdefault(i, torch.empty(a.numel, dtype=a.dtype, device=a.device))
+            N.check(lib.oa_peer_reduce(K.dt(a.grad), gbuf.ptr_array, summed.data_ptr(), 0, a.numel, self.world, 0, N.stream()),
+                    "oa_peer_reduce")
+            N.count_launch()
+        coef = self._clip_coef(replicated)
+        for i in replicated:
+            a = self.arenas[i]
+            K.adam_step(a.flat, self._summed[i], a.master, opt._m[i], opt._v[i], opt._state, decoupled=opt.Decoupled, inv_clip=coef)
         for a, sh in zip(self.arenas, self._shards):
             if sh is None:
                 continue
@@ -114,7 +159,8 @@ class OaDataParallel:
             ctx.Add("DpReduceScatterAdamAllGather")
             gbuf, pbuf = self._sym[a.grad.data_ptr()], self._sym[a.flat.data_ptr()]
             N.check(lib.oa_dp_reduce_adam_gather(gbuf.ptr_array, pbuf.ptr_array, master.data_ptr(), m.data_ptr(), v.data_ptr(), lo, sn,
-                                                 opt._state.data_ptr(), None, int(opt.Decoupled), self.rank, self.world,
+                                                 opt._state.data_ptr(), coef.data_ptr() if coef is not None else None,
+                                                 int(opt.Decoupled), self.rank, self.world,
                                                  self.ch_grads.flags.local_ptr, self.ch_grads.epoch.data_ptr(), status.data_ptr(),
                                                  self.max_blocks, N.stream()), "oa_dp_reduce_adam_gather")
             N.count_launch()
@@ -122,6 +168,13 @@ class OaDataParallel:
         self.ch_params.Signal()
         self.ch_params.Wait()
         opt.Step_ += 1
+
+    def ReduceMetric(self, value: float) -> float:
+        """Mean of a host scalar over the ranks: checkpoint decisions (is this the best loss so far?) must be the same on
+        every rank, because saving gathers the sharded optimizer state with a collective."""
+        t = torch.tensor([float(value)], dtype=torch.float64, device=self.mesh.device)
+        dist.all_reduce(t, group=self.mesh.group)
+        return float(t[0]) / self.world
 
     def _nccl_step(self) -> None:
         for a in self.arenas:
