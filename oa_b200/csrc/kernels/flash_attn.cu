@@ -2,31 +2,33 @@
 //
 // The reference's FlashCausal kernels (Source/Private/Oa/Ml/Shader/Compute/Nn/Attention/FlashCausal*.slang)
 // run one work-group per query row with all scores of the row in shared memory (S <= 1024, fp32 only, no
-// tensor cores).  Here the work is tiled 128 queries x 128 keys, both matrix products of a tile run on
-// tcgen05 with accumulators in TMEM, tiles arrive through TMA, and softmax runs one thread per query row on
-// values read straight from TMEM (no shuffles).  Q, K, V are read in place from a packed projection output
-// ([B*S, row_stride] with head h at column h*head_dim), and O is written merged ([B*S, H*head_dim]), so there
-// are no SplitHeads / MergeHeads passes.
+// tensor cores).  Here the work is tiled 128 queries x 128 keys, every matrix product of a tile runs on
+// tcgen05 with accumulators in TMEM, tiles arrive through TMA, and the probabilities (and their gradients) are
+// written back to TMEM as bf16 and read from there as the A operand of the next product: nothing but Q, K, V, dO
+// passes through shared memory.  Q, K, V are read in place from a packed projection output ([B*S, row_stride] with
+// head h at column h*head_dim), and O is written merged ([B*S, H*head_dim]), so there are no SplitHeads / MergeHeads
+// passes.
+//
+// Measured facts that shape the kernels: one tcgen05.mma costs about 50 cycles to issue from a thread (the N = 64
+// products are issue bound), an MUFU exponential occupies its pipe for 8 cycles per warp (1024 cycles per 128 x 128
+// tile), and a warp that waits for the tensor pipe between key blocks idles the SFU.  Hence: score tiles are copied
+// to registers and released at once so the next score product is issued under this block's exponentials, products are
+// issued by two or three warps, and every kernel but the head_dim 128 forward is persistent (one CTA per SM walks its
+// work items in snake order, heaviest causal items first), so TMEM, barriers and the operand rings live across items.
 //
 // Backward is two kernels, both deterministic (single writer per output element, like the reference's
-// FlashCausalBwdQ / FlashCausalBwdKV): one CTA per key block accumulates dK, dV in TMEM over the query blocks,
-// one CTA per query block accumulates dQ in TMEM over the key blocks.  Probabilities are recomputed from the
-// saved log-sum-exp.
-//
-// CTA = 320 threads: warp 0 = TMA producer, warp 1 = MMA issuer (+ TMEM owner), warps 2..9 = softmax /
-// epilogue.  Two threads share a query row: warp w works on TMEM lane quadrant w % 4 and on key columns
-// [64*half, 64*half+64) with half = (w-2)/4, which doubles the warps available to hide TMEM-load and
-// exp latency.  Every wait is bounded and reports to a status word.
+// FlashCausalBwdQ / FlashCausalBwdKV): one accumulates dK, dV in TMEM over the query blocks of a key block, the other dQ
+// over the key blocks of a query block.  Probabilities are recomputed from the saved log-sum-exp.
+// Every wait is bounded and reports to a status word.
 #include "common.cuh"
 #include "api.h"
-#include <stdlib.h>
 
 namespace oa {
 
 constexpr int FA_BM = 128;   // queries per tile
 constexpr int FA_BN = 128;   // keys per tile
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int FA_THREADS = 320;   // 2 service warps + 8 softmax warps
+constexpr int FA_THREADS = 320;   // head_dim 128 forward: 8 softmax warps + MMA warp + TMA warp
 
 // 64-thread named barrier shared by the two warps that own the same 32 query rows.
 __device__ __forceinline__ void pair_sync(int quad) {
@@ -43,285 +45,6 @@ struct FlashParams {
   int* status;
 };
 
-// Byte offset of element (row, col) in a [rows x 64] bf16 box stored with the 128-byte swizzle
-// (16-byte chunk index XOR (row % 8)); boxes of 64 columns are `box_bytes` apart.
-__device__ __forceinline__ uint32_t sw128_offset(int row, int col, int box_bytes) {
-  int box = col >> 6, c = col & 63;
-  return box * box_bytes + row * 128 + ((((c >> 3) ^ (row & 7)) << 4) | ((c & 7) << 1));
-}
-
-template <int HD>
-struct FwdCfg {
-  static constexpr int Q_BYTES = FA_BM * HD * 2;
-  static constexpr int KV_BYTES = FA_BN * HD * 2;
-  static constexpr int P_BYTES = FA_BM * FA_BN * 2;
-  static constexpr int STAGES = 2;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + Q_BYTES;
-  static constexpr int OFF_V = OFF_K + STAGES * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + STAGES * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BAR + 128;
-  static constexpr int TMEM_COLS = 256;
-  static constexpr int TM_S = 0;
-  static constexpr int TM_O = 128;
-};
-
-template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, HD == 64 ? 2 : 1)
-flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                 const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
-  using Cfg = FwdCfg<HD>;
-  extern __shared__ __align__(1024) uint8_t smem[];
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-  uint64_t* q_full = bars + 0;
-  uint64_t* k_full = bars + 1;   // [2]
-  uint64_t* v_full = bars + 3;   // [2]
-  uint64_t* kv_empty = bars + 5; // [2]  V stage free (P*V done)
-  uint64_t* k_empty = bars + 11; // [2]  K stage free (Q*K^T done): lets the next K load start one iteration earlier
-  uint64_t* s_full = bars + 7;
-  uint64_t* p_full = bars + 8;
-  uint64_t* o_full = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nblk = (p.seq + FA_BM - 1) / FA_BM;
-  const int qb = nblk - 1 - blockIdx.x;  // heaviest causal tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int n_kv = p.causal ? (qb + 1) : nblk;
-  const int row0 = b * p.seq;            // first row of this batch element in the [B*S, .] matrices
-
-  if ((smem_u32(smem) & 1023u) != 0) {   // the swizzled tiles need a 1024-byte aligned base
-    if (threadIdx.x == 0) report_error(p.status, OA_KERR_BAD_ARG);
-    return;
-  }
-  if (threadIdx.x == 0) {
-    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
-    mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&k_full[s], 1); mbar_init(&v_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&k_empty[s], 1); }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 8);
-    mbar_init(o_full, 1);
-    mbar_fence_init();
-  }
-  if (warp == 1) { tmem_alloc<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish(); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    // ------------- producer.  The whole warp walks the loop and waits together; one lane issues the copies.
-    // (A warp split between a spinning lane and 31 lanes parked at the final barrier hands off very slowly.)
-    if (lane == 0) {
-      mbar_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-      for (int x = 0; x < HD / 64; ++x)
-        tma_load_2d(smem + Cfg::OFF_Q + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + qb * FA_BM);
-    }
-    for (int j = 0; j < n_kv; ++j) {
-      const int st = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      if (!warp_wait(&k_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
-      if (lane == 0) {
-        mbar_expect_tx(&k_full[st], Cfg::KV_BYTES);
-#pragma unroll
-        for (int x = 0; x < HD / 64; ++x)
-          tma_load_2d(smem + Cfg::OFF_K + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmK, &k_full[st], h * HD + x * 64, row0 + j * FA_BN);
-      }
-      if (!warp_wait(&kv_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
-      if (lane == 0) {
-        mbar_expect_tx(&v_full[st], Cfg::KV_BYTES);
-#pragma unroll
-        for (int x = 0; x < HD / 64; ++x)
-          tma_load_2d(smem + Cfg::OFF_V + st * Cfg::KV_BYTES + x * (FA_BN * 128), &tmV, &v_full[st], h * HD + x * 64, row0 + j * FA_BN);
-      }
-      __syncwarp();
-    }
-  } else if (warp == 1) {
-    // ------------- MMA issuer (warp-uniform waits, lane 0 issues)
-    constexpr uint32_t idesc_qk = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
-    constexpr uint32_t idesc_pv = umma_idesc_bf16(FA_BM, HD, 0, 1);
-    const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q);
-    const uint32_t p_addr = smem_u32(smem + Cfg::OFF_P);
-    bool ok = warp_wait(q_full, 0);
-    if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
-    auto issue_qk = [&](int j) -> bool {
-      const int st = j & 1;
-      if (!warp_wait(&k_full[st], (j >> 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); return false; }
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::KV_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(q_addr + off, 16, 1024),
-                   umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_qk, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(&k_empty[st]);
-        umma_commit(s_full);
-      }
-      __syncwarp();
-      return true;
-    };
-    if (ok) ok = issue_qk(0);
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int st = j & 1;
-      if (!warp_wait(p_full, j & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); break; }
-      if (!warp_wait(&v_full[st], (j >> 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::KV_BYTES);
-#pragma unroll
-        for (int ks = 0; ks < FA_BN / 16; ++ks) {
-          uint32_t a_off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_O, umma_smem_desc_sw128(p_addr + a_off, 16, 1024),
-                   umma_smem_desc_sw128(v_addr + ks * 2048, FA_BN * 128, 1024), idesc_pv, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(&kv_empty[st]);
-        umma_commit(o_full);
-      }
-      __syncwarp();
-      if (j + 1 < n_kv) ok = issue_qk(j + 1);
-    }
-  } else {
-    // ------------- softmax + output: two threads per query row (key columns split in halves)
-    constexpr int OC = HD / 2;                   // output columns owned by this thread
-    const int quad = warp & 3;
-    const int half = (warp - 2) >> 2;
-    const int r = quad * 32 + lane;
-    const int qi = qb * FA_BM + r;               // query index inside the sequence
-    const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
-    const float sl2 = p.scale * LOG2E;
-    float m_run = -INFINITY, l_run = 0.f;
-    float acc[OC];
-#pragma unroll
-    for (int d = 0; d < OC; ++d) acc[d] = 0.f;
-    uint8_t* sP = smem + Cfg::OFF_P;
-    bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      ok = warp_wait(s_full, j & 1);
-      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
-      tc_fence_after();
-      const int k0 = j * FA_BN + half * 64;
-      const bool need_mask = (p.causal && j == qb) || (j * FA_BN + FA_BN > p.seq);
-      const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + half * 64;
-      // pass 1: maximum over this thread's 64 key columns.  Masked tiles (the diagonal one and the sequence tail)
-      // take a separate loop so that the common loop carries no per-element predicate.
-      float mx = -INFINITY;
-      if (need_mask) {
-        const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - k0;   // columns i <= lim are alive
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t sv[32];
-          tmem_ld32(s_addr + c * 32, sv);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, (c * 32 + i <= lim) ? __uint_as_float(sv[i]) : -INFINITY);
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t sv[32];
-          tmem_ld32(s_addr + c * 32, sv);
-          tmem_ld_wait();
-          float m0 = __uint_as_float(sv[0]), m1 = __uint_as_float(sv[1]), m2 = __uint_as_float(sv[2]), m3 = __uint_as_float(sv[3]);
-#pragma unroll
-          for (int i = 4; i < 32; i += 4) {
-            m0 = fmaxf(m0, __uint_as_float(sv[i])); m1 = fmaxf(m1, __uint_as_float(sv[i + 1]));
-            m2 = fmaxf(m2, __uint_as_float(sv[i + 2])); m3 = fmaxf(m3, __uint_as_float(sv[i + 3]));
-          }
-          mx = fmaxf(mx, fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)));
-        }
-      }
-      // Exchange with the partner thread.  The slot is the first word of the PARTNER's own row of the P tile: the
-      // P tile is idle here (the previous P*V has completed before s_full fires) and only the slot's reader
-      // overwrites it later.
-      float* slot_mine = reinterpret_cast<float*>(sP + half * (FA_BM * 128) + r * 128);
-      float* slot_partner = reinterpret_cast<float*>(sP + (half ^ 1) * (FA_BM * 128) + r * 128);
-      *slot_partner = mx;
-      pair_sync(quad);
-      mx = fmaxf(mx, *slot_mine);
-      const float m_new = fmaxf(m_run, mx * sl2);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // fully masked row so far
-      const float alpha = fast_exp2(m_run - m_use);             // m_run = -inf -> 0
-      const float neg_m = -m_use;
-      float l0 = 0.f, l1 = 0.f;
-      uint8_t* prow = sP + half * (FA_BM * 128) + r * 128;       // this thread's 128-byte row of box `half`
-      const int rx = r & 7;
-      // pass 2: probabilities -> bf16 -> swizzled smem tile (A operand of P*V)
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32];
-        tmem_ld32(s_addr + c * 32, sv);
-        tmem_ld_wait();
-        uint32_t pk[16];
-        if (need_mask) {
-          const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - k0 - c * 32;
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float e0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, neg_m)) : 0.f;
-            float e1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_m)) : 0.f;
-            l0 += e0; l1 += e1;
-            pk[i >> 1] = pack_bf16x2(e0, e1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, neg_m));
-            float e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_m));
-            l0 += e0; l1 += e1;
-            pk[i >> 1] = pack_bf16x2(e0, e1);
-          }
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(prow + (((c * 4 + g) ^ rx) << 4)) = make_uint4(pk[g * 4], pk[g * 4 + 1], pk[g * 4 + 2], pk[g * 4 + 3]);
-      }
-      l_run = l_run * alpha + (l0 + l1);
-      m_run = m_new;
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-      // accumulate the partial output of this key block (this thread's half of the head dimension)
-      ok = warp_wait(o_full, j & 1);
-      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < OC / 32; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tmem_base + t_lane + Cfg::TM_O + half * OC + c * 32, o);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(acc[c * 32 + i], alpha, __uint_as_float(o[i]));
-      }
-      tc_fence_before();
-    }
-    // combine the two partial row sums (same exchange slots; the last P*V has completed)
-    {
-      float* slot_mine = reinterpret_cast<float*>(sP + half * (FA_BM * 128) + r * 128);
-      float* slot_partner = reinterpret_cast<float*>(sP + (half ^ 1) * (FA_BM * 128) + r * 128);
-      *slot_partner = l_run;
-      pair_sync(quad);
-      l_run += *slot_mine;
-    }
-    if (ok && qi < p.seq) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* op = p.o + (long long)(row0 + qi) * p.o_stride + h * HD + half * OC;
-#pragma unroll
-      for (int g = 0; g < OC / 8; ++g)
-        *reinterpret_cast<uint4*>(op + g * 8) =
-            make_uint4(pack_bf16x2(acc[g * 8] * inv, acc[g * 8 + 1] * inv), pack_bf16x2(acc[g * 8 + 2] * inv, acc[g * 8 + 3] * inv),
-                       pack_bf16x2(acc[g * 8 + 4] * inv, acc[g * 8 + 5] * inv), pack_bf16x2(acc[g * 8 + 6] * inv, acc[g * 8 + 7] * inv));
-      if (p.lse && half == 0) p.lse[((long long)b * p.heads + h) * p.seq + qi] = (m_run + log2f(l_run)) / LOG2E;
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
-}
-
 // ===================================================================================== forward, S double-buffered in TMEM
 // One CTA owns one 128-query tile of one (batch, head).  S = Q K_j^T alternates between two TMEM buffers, and the MMA warp
 // always runs two key blocks ahead of the softmax (Q K_{j+2}^T is issued right after P_j V_j), so the softmax warps never
@@ -334,8 +57,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 //   warp 9     TMA producer (Q once, K / V rings).
 // The running maximum is updated lazily: while the new row maximum exceeds the one in use by less than 2^8 the old one is
 // kept (probabilities then stay below 256), so O in TMEM is rescaled only in the rare iterations where some row of a warp
-// jumps by more than that; the final 1/l uses the same maxima, so the result is the exact softmax.  A share of the
-// exponentials (POLY of every 8) is evaluated as a degree-3 polynomial on the FMA pipe instead of the SFU.
+// jumps by more than that; the final 1/l uses the same maxima, so the result is the exact softmax.
 // TMEM: S0 | S1 | O = 128 + 128 + head_dim columns.
 template <int HD>
 struct Fwd2Cfg {
@@ -356,26 +78,8 @@ struct Fwd2Cfg {
 
 constexpr float FA_RESCALE_THRESHOLD = 8.f;                // log2 units
 
-#ifdef OA_FA_PROF
-// Development aid (compiled only with -DOA_FA_PROF): cycle stamps of one CTA's softmax warp 0 and MMA warp.
-__device__ long long g_fa_prof[8192];
-#define FA_STAMP(slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && (slot) < 8192) g_fa_prof[(slot)] = clock64(); } while (0)
-#else
-#define FA_STAMP(slot) do { } while (0)
-#endif
 
-// 2^x for x <= 0 on the FMA pipe: floor by a round-down add of 1.5 * 2^23, cubic for 2^frac, exponent added as an integer.
-__device__ __forceinline__ float exp2_poly3(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = __fadd_rd(x, 12582912.f);
-  const float f = x - (t - 12582912.f);
-  float q = fmaf(f, 0.07711909f, 0.22756439f);
-  q = fmaf(q, f, 0.69514614f);
-  q = fmaf(q, f, 1.0f);
-  return __int_as_float(__float_as_int(q) + (__float_as_int(t) << 23));
-}
-
-template <int HD, int POLY>
+template <int HD>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
@@ -483,10 +187,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     for (int j = 0; j < n_kv && ok; ++j) {
       const int st = j % NSV;
       if (!warp_wait(&v_full[st], (j / NSV) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
-      FA_STAMP(j * 16 + 8);
       if (!warp_wait(&p_full[j & 1], (j >> 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); break; }
       tc_fence_after();
-      FA_STAMP(j * 16 + 9);
       if (lane == 0) {
         const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::KV_BYTES);
 #pragma unroll
@@ -497,9 +199,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         umma_commit(o_done);
       }
       __syncwarp();
-      FA_STAMP(j * 16 + 10);
       if (j + 2 < n_kv) ok = issue_qk(j + 2);  // overwrites S[j & 1] = P_j: ordered after P_j V_j by the pipe
-      FA_STAMP(j * 16 + 11);
     }
   } else {
     // ------------- softmax + output: two threads per query row (key columns split in halves)
@@ -514,17 +214,14 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      if (warp == 0) FA_STAMP(j * 16 + 0);
       ok = warp_wait(&s_full[j & 1], (j >> 1) & 1);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
-      if (warp == 0) FA_STAMP(j * 16 + 1);
       const uint32_t s_addr = tmem_base + t_lane + Cfg::TM_S + (j & 1) * FA_BN;
       uint32_t sv[64];
       tmem_ld32(s_addr + half * 64, sv);
       tmem_ld32(s_addr + half * 64 + 32, sv + 32);
       tmem_ld_wait();
-      if (warp == 0) FA_STAMP(j * 16 + 2);
       const bool need_mask = (p.causal && j == qb) || (j * FA_BN + FA_BN > p.seq);
       if (need_mask) {
         const int lim = min(p.causal ? qi : 0x7fffffff, p.seq - 1) - j * FA_BN - half * 64;   // columns i <= lim are alive
@@ -542,10 +239,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // barrier the S buffer may be overwritten by either of them.
       float* slots = xch + (j & 1) * (2 * FA_BM);
       slots[(half ^ 1) * FA_BM + r] = mx;
-      if (warp == 0) FA_STAMP(j * 16 + 3);
       pair_sync(quad);
       mx = fmaxf(mx, slots[half * FA_BM + r]) * sl2;
-      if (warp == 0) FA_STAMP(j * 16 + 4);
       const float m_new = fmaxf(m_run, mx);
       const bool grow = (m_new - m_run) > FA_RESCALE_THRESHOLD;           // first block: m_run = -inf -> true
       const float m_cand = grow ? m_new : m_run;
@@ -554,32 +249,16 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const float neg_m = -m_use;
       float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
       uint32_t pk[32];
-      if (POLY == 0 || need_mask) {
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, neg_m));
-          const float e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_m));
-          const float e2 = fast_exp2(fmaf(__uint_as_float(sv[i + 2]), sl2, neg_m));
-          const float e3 = fast_exp2(fmaf(__uint_as_float(sv[i + 3]), sl2, neg_m));
-          l0 += e0; l1 += e1; l2 += e2; l3 += e3;
-          pk[i >> 1] = pack_bf16x2(e0, e1);
-          pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; i += 8) {
-          float e[8];
-#pragma unroll
-          for (int u = 0; u < 8; ++u) {
-            const float x = fmaf(__uint_as_float(sv[i + u]), sl2, neg_m);
-            e[u] = (u < POLY) ? exp2_poly3(x) : fast_exp2(x);
-          }
-          l0 += e[0] + e[4]; l1 += e[1] + e[5]; l2 += e[2] + e[6]; l3 += e[3] + e[7];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) pk[(i >> 1) + u] = pack_bf16x2(e[2 * u], e[2 * u + 1]);
-        }
+      for (int i = 0; i < 64; i += 4) {
+        const float e0 = fast_exp2(fmaf(__uint_as_float(sv[i]), sl2, neg_m));
+        const float e1 = fast_exp2(fmaf(__uint_as_float(sv[i + 1]), sl2, neg_m));
+        const float e2 = fast_exp2(fmaf(__uint_as_float(sv[i + 2]), sl2, neg_m));
+        const float e3 = fast_exp2(fmaf(__uint_as_float(sv[i + 3]), sl2, neg_m));
+        l0 += e0; l1 += e1; l2 += e2; l3 += e3;
+        pk[i >> 1] = pack_bf16x2(e0, e1);
+        pk[(i >> 1) + 1] = pack_bf16x2(e2, e3);
       }
-      if (warp == 0) FA_STAMP(j * 16 + 5);
       tmem_st32(s_addr + half * 32, pk);          // P over the first 64 columns of S (two keys per column)
       l_run = l_run * alpha + ((l0 + l1) + (l2 + l3));
       m_run = m_cand;
@@ -599,11 +278,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
       }
       tmem_st_wait();
-      if (warp == 0) FA_STAMP(j * 16 + 6);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[j & 1]);
-      if (warp == 0) FA_STAMP(j * 16 + 7);
     }
     // combine the two partial row sums (parity slot of an iteration that is two behind any reader)
     {
@@ -961,14 +638,14 @@ flash_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
 }
 
-template <int HD, int POLY>
+template <int HD>
 static int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashParams& p, dim3 grid, cudaStream_t st) {
   static bool set = false;
   if (!set) {
-    if (cudaFuncSetAttribute(flash_fwd2_kernel<HD, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<HD>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(flash_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<HD>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
     set = true;
   }
-  flash_fwd2_kernel<HD, POLY><<<grid, FA_THREADS, Fwd2Cfg<HD>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  flash_fwd2_kernel<HD><<<grid, FA_THREADS, Fwd2Cfg<HD>::SMEM_BYTES, st>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
@@ -1042,7 +719,8 @@ struct BwdKvCfg {
   static constexpr int TM_DV = ALIAS ? 256 : 384, TM_DK = TM_DV + HD;
 };
 
-// One CTA per (key block, head, batch): dK, dV accumulate in TMEM over the query blocks.
+// Persistent: one CTA per SM walks the work items (key block, head, batch) it owns, heaviest causal key blocks first, items
+// dealt in snake order; dK, dV of an item accumulate in TMEM over its query blocks.  Barrier phases come from running counts.
 template <int HD>
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -1054,23 +732,31 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;   // [3]
-  uint64_t* qdo_empty = bars + 4;  // [3]  (dV and dK issuers both arrive)
-  uint64_t* s_full = bars + 7;     // S^T, dP^T of this tile are in TMEM
-  uint64_t* s_empty = bars + 8;    // ... and have been copied to registers (8 warps)
-  uint64_t* pds_full = bars + 9;   // P^T, dS^T of this tile are in TMEM (8 warps)
-  uint64_t* pds_empty = bars + 10; // ... and have been consumed by the gradient products (dV and dK issuers both arrive)
-  uint64_t* fin_full = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* kv_empty = bars + 1;   // the item's last score products have read K, V
+  uint64_t* qdo_full = bars + 2;   // [3]
+  uint64_t* qdo_empty = bars + 5;  // [3]  (dV and dK issuers both arrive)
+  uint64_t* s_full = bars + 8;     // S^T, dP^T of this tile are in TMEM
+  uint64_t* s_empty = bars + 9;    // ... and have been copied to registers (8 warps)
+  uint64_t* pds_full = bars + 10;  // P^T, dS^T of this tile are in TMEM (8 warps)
+  uint64_t* pds_empty = bars + 11; // ... and have been consumed by the gradient products (dV and dK issuers both arrive)
+  uint64_t* fin_full = bars + 12;  // dV, dK of the item are complete (both issuers arrive)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   float* stat = reinterpret_cast<float*>(smem + Cfg::OFF_STAT);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = (p.seq + FA_BM - 1) / FA_BM;
-  const int jb = blockIdx.x;                     // key block (light causal tiles are the high jb: launched last)
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int i0 = p.causal ? jb : 0;
-  const int n_it = nblk - i0;
-  const int row0 = b * p.seq;
+  const int hb = p.heads * p.batch;
+  const int n_items = nblk * hb;
+  const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto item_of = [&](int round) -> int {     // snake order; >= n_items: this CTA sits the round out
+    return round * (int)gridDim.x + ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  };
+  auto decode = [&](int item, int& jb, int& h, int& b) {   // key block 0 has the most query blocks under the causal mask
+    jb = item / hb;
+    const int rem = item % hb;
+    h = rem % p.heads;
+    b = rem / p.heads;
+  };
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) report_error(p.status, OA_KERR_BAD_ARG);
@@ -1079,6 +765,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
     mbar_init(kv_full, 1);
+    mbar_init(kv_empty, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&qdo_full[s], 2); mbar_init(&qdo_empty[s], 2); }   // full: TMA bytes + the statistics
     mbar_init(s_full, 1);
     mbar_init(s_empty, 8);
@@ -1095,82 +782,100 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (warp == 11) {
     // ------------- TMA producer (also stages the per-query statistics of each block)
-    const long long stat_base = ((long long)b * p.heads + h) * p.seq;
-    if (lane == 0) {
-      mbar_expect_tx(kv_full, 2 * Cfg::T_BYTES);
-#pragma unroll
-      for (int x = 0; x < HD / 64; ++x) {
-        tma_load_2d(smem + Cfg::OFF_K + x * (FA_BN * 128), &tmK, kv_full, h * HD + x * 64, row0 + jb * FA_BN);
-        tma_load_2d(smem + Cfg::OFF_V + x * (FA_BN * 128), &tmV, kv_full, h * HD + x * 64, row0 + jb * FA_BN);
-      }
-    }
-    for (int it = 0; it < n_it; ++it) {
-      const int st = it % NST;
-      const uint32_t ph = (it / NST) & 1;
-      if (!warp_wait(&qdo_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+    uint32_t itc = 0, qc = 0;       // items and Q / dO blocks loaded so far
+    bool ok = true;
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int jb, h, b;
+      decode(item, jb, h, b);
+      const int i0 = p.causal ? jb : 0, n_it = nblk - i0, row0 = b * p.seq;
+      const long long stat_base = ((long long)b * p.heads + h) * p.seq;
+      if (!warp_wait(kv_empty, (itc & 1) ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
       if (lane == 0) {
-        mbar_expect_tx(&qdo_full[st], 2 * Cfg::T_BYTES);
-        const int qrow = row0 + (i0 + it) * FA_BM;
+        mbar_expect_tx(kv_full, 2 * Cfg::T_BYTES);
 #pragma unroll
         for (int x = 0; x < HD / 64; ++x) {
-          tma_load_2d(smem + Cfg::OFF_Q + st * Cfg::T_BYTES + x * (FA_BM * 128), &tmQ, &qdo_full[st], h * HD + x * 64, qrow);
-          tma_load_2d(smem + Cfg::OFF_DO + st * Cfg::T_BYTES + x * (FA_BM * 128), &tmDO, &qdo_full[st], h * HD + x * 64, qrow);
+          tma_load_2d(smem + Cfg::OFF_K + x * (FA_BN * 128), &tmK, kv_full, h * HD + x * 64, row0 + jb * FA_BN);
+          tma_load_2d(smem + Cfg::OFF_V + x * (FA_BN * 128), &tmV, kv_full, h * HD + x * 64, row0 + jb * FA_BN);
         }
       }
-      // per-query statistics of this block, negated and pre-scaled: lane l stages queries 4l .. 4l+3
-      {
-        float4 nl, nd;
-        float* nlp = reinterpret_cast<float*>(&nl);
-        float* ndp = reinterpret_cast<float*>(&nd);
+      for (int it = 0; it < n_it; ++it, ++qc) {
+        const int st = qc % NST;
+        const uint32_t ph = (qc / NST) & 1;
+        if (!warp_wait(&qdo_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(&qdo_full[st], 2 * Cfg::T_BYTES);
+          const int qrow = row0 + (i0 + it) * FA_BM;
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int qi = (i0 + it) * FA_BM + lane * 4 + u;
-          const bool okq = qi < p.seq;
-          nlp[u] = okq ? -p.lse[stat_base + qi] * LOG2E : -INFINITY;
-          ndp[u] = okq ? -p.delta[stat_base + qi] * p.scale : 0.f;
+          for (int x = 0; x < HD / 64; ++x) {
+            tma_load_2d(smem + Cfg::OFF_Q + st * Cfg::T_BYTES + x * (FA_BM * 128), &tmQ, &qdo_full[st], h * HD + x * 64, qrow);
+            tma_load_2d(smem + Cfg::OFF_DO + st * Cfg::T_BYTES + x * (FA_BM * 128), &tmDO, &qdo_full[st], h * HD + x * 64, qrow);
+          }
         }
-        float* dst = stat + st * 256;
-        reinterpret_cast<float4*>(dst)[lane] = nl;
-        reinterpret_cast<float4*>(dst + 128)[lane] = nd;
+        // per-query statistics of this block, negated and pre-scaled: lane l stages queries 4l .. 4l+3
+        {
+          float4 nl, nd;
+          float* nlp = reinterpret_cast<float*>(&nl);
+          float* ndp = reinterpret_cast<float*>(&nd);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int qi = (i0 + it) * FA_BM + lane * 4 + u;
+            const bool okq = qi < p.seq;
+            nlp[u] = okq ? -p.lse[stat_base + qi] * LOG2E : -INFINITY;
+            ndp[u] = okq ? -p.delta[stat_base + qi] * p.scale : 0.f;
+          }
+          float* dst = stat + st * 256;
+          reinterpret_cast<float4*>(dst)[lane] = nl;
+          reinterpret_cast<float4*>(dst + 128)[lane] = nd;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&qdo_full[st]);
+        __syncwarp();
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&qdo_full[st]);
-      __syncwarp();
+      ++itc;
     }
   } else if (warp == 8) {
     // ------------- MMA issuer A: transposed score products S^T = K Q^T, dP^T = V dO^T
     constexpr uint32_t idesc_s = umma_idesc_bf16(FA_BN, FA_BM, 0, 0);
     const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K), v_addr = smem_u32(smem + Cfg::OFF_V);
-    bool ok = warp_wait(kv_full, 0);
-    if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int st = it % NST;
-      FA_STAMP(it * 16 + 8);
-      if (!warp_wait(&qdo_full[st], (it / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
-      // S^T / dP^T may be overwritten once the softmax warps hold the previous tile in registers; when P^T / dS^T share
-      // those columns, only once the previous gradient products have consumed them
-      if (it > 0 && !warp_wait(ALIAS ? pds_empty : s_empty, (it - 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
-      tc_fence_after();
-      FA_STAMP(it * 16 + 9);
-      if (lane == 0) {
-        const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q + st * Cfg::T_BYTES);
-        const uint32_t do_addr = smem_u32(smem + Cfg::OFF_DO + st * Cfg::T_BYTES);
+    uint32_t itc = 0, qc = 0;
+    bool ok = true;
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int jb, h, b;
+      decode(item, jb, h, b);
+      const int n_it = nblk - (p.causal ? jb : 0);
+      if (!warp_wait(kv_full, itc & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      for (int it = 0; it < n_it; ++it, ++qc) {
+        const int st = qc % NST;
+        if (!warp_wait(&qdo_full[st], (qc / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+        // S^T / dP^T may be overwritten once the softmax warps hold the previous tile in registers; when P^T / dS^T share
+        // those columns, only once the previous gradient products have consumed them
+        if (qc > 0 && !warp_wait(ALIAS ? pds_empty : s_empty, (qc - 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q + st * Cfg::T_BYTES);
+          const uint32_t do_addr = smem_u32(smem + Cfg::OFF_DO + st * Cfg::T_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(k_addr + off, 16, 1024),
-                   umma_smem_desc_sw128(q_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-        }
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+            umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(k_addr + off, 16, 1024),
+                     umma_smem_desc_sw128(q_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          }
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_DP, umma_smem_desc_sw128(v_addr + off, 16, 1024),
-                   umma_smem_desc_sw128(do_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+            umma_f16(tmem_base + Cfg::TM_DP, umma_smem_desc_sw128(v_addr + off, 16, 1024),
+                     umma_smem_desc_sw128(do_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(s_full);
+          if (it + 1 == n_it) umma_commit(kv_empty);
         }
-        umma_commit(s_full);
+        __syncwarp();
       }
-      __syncwarp();
-      FA_STAMP(it * 16 + 10);
+      ++itc;
     }
   } else if (warp == 9 || warp == 10) {
     // ------------- MMA issuers B (warp 9: dV += P^T dO) and C (warp 10: dK += dS^T Q), A operands from TMEM
@@ -1178,108 +883,116 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool is_dv = warp == 9;
     const uint32_t acc_addr = tmem_base + (is_dv ? Cfg::TM_DV : Cfg::TM_DK);
     const uint32_t a_addr = tmem_base + (is_dv ? Cfg::TM_P : Cfg::TM_DS);
+    uint32_t qc = 0;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int st = it % NST;
-      if (!warp_wait(&qdo_full[st], (it / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
-      if (!warp_wait(pds_full, it & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t b_addr = smem_u32(smem + (is_dv ? Cfg::OFF_DO : Cfg::OFF_Q) + st * Cfg::T_BYTES);
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int jb, h, b;
+      decode(item, jb, h, b);
+      const int n_it = nblk - (p.causal ? jb : 0);
+      // the previous item's dV / dK were read by the softmax warps before they produced this item's first P^T, dS^T
+      for (int it = 0; it < n_it; ++it, ++qc) {
+        const int st = qc % NST;
+        if (!warp_wait(&qdo_full[st], (qc / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+        if (!warp_wait(pds_full, qc & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t b_addr = smem_u32(smem + (is_dv ? Cfg::OFF_DO : Cfg::OFF_Q) + st * Cfg::T_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < FA_BM / 16; ++ks)    // reduction over the 128 queries of this block
-          umma_f16_ts(acc_addr, a_addr + ks * 8, umma_smem_desc_sw128(b_addr + ks * 2048, FA_BM * 128, 1024), idesc_g,
-                      (it > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&qdo_empty[st]);
-        umma_commit(pds_empty);
+          for (int ks = 0; ks < FA_BM / 16; ++ks)    // reduction over the 128 queries of this block
+            umma_f16_ts(acc_addr, a_addr + ks * 8, umma_smem_desc_sw128(b_addr + ks * 2048, FA_BM * 128, 1024), idesc_g,
+                        (it > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&qdo_empty[st]);
+          umma_commit(pds_empty);
+          if (it + 1 == n_it) umma_commit(fin_full);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
-    if (ok && lane == 0) umma_commit(fin_full);
-    __syncwarp();
   } else {
     const int quad = warp & 3;
     const int half = warp >> 2;                  // this thread owns query columns [64*half, 64*half+64) of the tile
     const int r = quad * 32 + lane;              // key row inside the block = TMEM lane
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
+    uint32_t itc = 0, qc = 0;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int ib = i0 + it;
-      const float* st_cur = stat + (it % NST) * 256;
-      if (warp == 0) FA_STAMP(it * 16 + 0);
-      ok = warp_wait(&qdo_full[it % NST], (it / NST) & 1);   // statistics of this block are staged
-      if (warp == 0) FA_STAMP(it * 16 + 1);
-      if (ok) ok = warp_wait(s_full, it & 1);
-      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
-      tc_fence_after();
-      if (warp == 0) FA_STAMP(it * 16 + 2);
-      uint32_t s[64], dp[64];
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64, s);
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64 + 32, s + 32);
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64, dp);
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64 + 32, dp + 32);
-      tmem_ld_wait();
-      if (ALIAS) {
-        pair_sync(quad);                         // both threads of the lane hold their columns before either overwrites them
-      } else {
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int jb, h, b;
+      decode(item, jb, h, b);
+      const int i0 = p.causal ? jb : 0, n_it = nblk - i0, row0 = b * p.seq;
+      for (int it = 0; it < n_it; ++it, ++qc) {
+        const int ib = i0 + it;
+        const int st = qc % NST;
+        const float* st_cur = stat + st * 256;
+        ok = warp_wait(&qdo_full[st], (qc / NST) & 1);   // statistics of this block are staged
+        if (ok) ok = warp_wait(s_full, qc & 1);
+        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+        tc_fence_after();
+        uint32_t s[64], dp[64];
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64, s);
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64 + 32, s + 32);
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64, dp);
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64 + 32, dp + 32);
+        tmem_ld_wait();
+        if (ALIAS) {
+          pair_sync(quad);                         // both threads of the lane hold their columns before either overwrites them
+        } else {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(s_empty);     // the next tile's score products may overwrite S^T, dP^T now
+        }
+        const float4* nl4 = reinterpret_cast<const float4*>(st_cur + half * 64);
+        const float4* nd4 = reinterpret_cast<const float4*>(st_cur + 128 + half * 64);
+        const bool diag = p.causal && ib == jb;    // alive iff key <= query: column >= row
+        const int first = r - half * 64;           // first alive column of this thread on the diagonal tile
+        uint32_t pw[32], dw[32];
+        if (diag) {
+#pragma unroll
+          for (int i = 0; i < 64; i += 4) {
+            const float4 nl = nl4[i >> 2], nd = nd4[i >> 2];
+            const float p0 = (i >= first) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nl.x)) : 0.f;
+            const float p1 = (i + 1 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nl.y)) : 0.f;
+            const float p2 = (i + 2 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 2]), sl2, nl.z)) : 0.f;
+            const float p3 = (i + 3 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 3]), sl2, nl.w)) : 0.f;
+            pw[i >> 1] = pack_bf16x2(p0, p1);
+            pw[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, nd.x), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, nd.y));
+            dw[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(dp[i + 2]), p.scale, nd.z), p3 * fmaf(__uint_as_float(dp[i + 3]), p.scale, nd.w));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; i += 4) {
+            const float4 nl = nl4[i >> 2], nd = nd4[i >> 2];
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nl.x));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nl.y));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), sl2, nl.z));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), sl2, nl.w));
+            pw[i >> 1] = pack_bf16x2(p0, p1);
+            pw[(i >> 1) + 1] = pack_bf16x2(p2, p3);
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, nd.x), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, nd.y));
+            dw[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(dp[i + 2]), p.scale, nd.z), p3 * fmaf(__uint_as_float(dp[i + 3]), p.scale, nd.w));
+          }
+        }
+        if (!ALIAS && qc > 0) {                     // the previous tile's gradient products still read P^T, dS^T
+          ok = warp_wait(pds_empty, (qc - 1) & 1);
+          if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+          tc_fence_after();
+        }
+        tmem_st32(tmem_base + t_lane + Cfg::TM_P + half * 32, pw);
+        tmem_st32(tmem_base + t_lane + Cfg::TM_DS + half * 32, dw);
+        tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(s_empty);     // the next tile's score products may overwrite S^T, dP^T now
+        if (lane == 0) mbar_arrive(pds_full);
       }
-      if (warp == 0) FA_STAMP(it * 16 + 3);
-      const float4* nl4 = reinterpret_cast<const float4*>(st_cur + half * 64);
-      const float4* nd4 = reinterpret_cast<const float4*>(st_cur + 128 + half * 64);
-      const bool diag = p.causal && ib == jb;    // alive iff key <= query: column >= row
-      const int first = r - half * 64;           // first alive column of this thread on the diagonal tile
-      uint32_t pw[32], dw[32];
-      if (diag) {
-#pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float4 nl = nl4[i >> 2], nd = nd4[i >> 2];
-          const float p0 = (i >= first) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nl.x)) : 0.f;
-          const float p1 = (i + 1 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nl.y)) : 0.f;
-          const float p2 = (i + 2 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 2]), sl2, nl.z)) : 0.f;
-          const float p3 = (i + 3 >= first) ? fast_exp2(fmaf(__uint_as_float(s[i + 3]), sl2, nl.w)) : 0.f;
-          pw[i >> 1] = pack_bf16x2(p0, p1);
-          pw[(i >> 1) + 1] = pack_bf16x2(p2, p3);
-          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, nd.x), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, nd.y));
-          dw[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(dp[i + 2]), p.scale, nd.z), p3 * fmaf(__uint_as_float(dp[i + 3]), p.scale, nd.w));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float4 nl = nl4[i >> 2], nd = nd4[i >> 2];
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nl.x));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nl.y));
-          const float p2 = fast_exp2(fmaf(__uint_as_float(s[i + 2]), sl2, nl.z));
-          const float p3 = fast_exp2(fmaf(__uint_as_float(s[i + 3]), sl2, nl.w));
-          pw[i >> 1] = pack_bf16x2(p0, p1);
-          pw[(i >> 1) + 1] = pack_bf16x2(p2, p3);
-          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, nd.x), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, nd.y));
-          dw[(i >> 1) + 1] = pack_bf16x2(p2 * fmaf(__uint_as_float(dp[i + 2]), p.scale, nd.z), p3 * fmaf(__uint_as_float(dp[i + 3]), p.scale, nd.w));
-        }
-      }
-      if (warp == 0) FA_STAMP(it * 16 + 4);
-      if (!ALIAS && it > 0) {                     // the previous tile's gradient products still read P^T, dS^T
-        ok = warp_wait(pds_empty, (it - 1) & 1);
-        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
-        tc_fence_after();
-      }
-      if (warp == 0) FA_STAMP(it * 16 + 5);
-      tmem_st32(tmem_base + t_lane + Cfg::TM_P + half * 32, pw);
-      tmem_st32(tmem_base + t_lane + Cfg::TM_DS + half * 32, dw);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pds_full);
-      if (warp == 0) FA_STAMP(it * 16 + 6);
-    }
-    if (ok) {
-      ok = warp_wait(fin_full, 0);
-      if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL);
-    }
-    if (ok) {
+      if (!ok) break;
+      ok = warp_wait(fin_full, itc & 1);
+      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+      ++itc;
       tc_fence_after();
       const int kj = jb * FA_BN + r;   // accumulator rows are keys
 #pragma unroll 1
@@ -1303,6 +1016,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
       }
+      tc_fence_before();   // dV / dK are read before this warp's next pds_full arrival lets the next item's products overwrite them
     }
   }
   tc_fence_before();
@@ -1324,7 +1038,8 @@ struct BwdQCfg {
   static constexpr int TM_S = 0, TM_DP = 128, TM_DS = 256, TM_DQ = 320;
 };
 
-// One CTA per (query block, head, batch): dQ accumulates in TMEM over the key blocks.
+// Persistent, like the dK / dV kernel: items are (query block, head, batch), heaviest causal query blocks first; dQ of an item
+// accumulates in TMEM over its key blocks.
 template <int HD>
 __global__ void __launch_bounds__(FA_BWD_THREADS, 1)
 flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -1335,21 +1050,30 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;    // [3]
-  uint64_t* kv_empty = bars + 4;   // [3]
-  uint64_t* s_full = bars + 7;
-  uint64_t* s_empty = bars + 8;
-  uint64_t* ds_full = bars + 9;
-  uint64_t* ds_empty = bars + 10;
-  uint64_t* fin_full = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* q_empty = bars + 1;    // the item's last score products have read Q, dO
+  uint64_t* kv_full = bars + 2;    // [3]
+  uint64_t* kv_empty = bars + 5;   // [3]
+  uint64_t* s_full = bars + 8;
+  uint64_t* s_empty = bars + 9;
+  uint64_t* ds_full = bars + 10;
+  uint64_t* ds_empty = bars + 11;
+  uint64_t* fin_full = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nblk = (p.seq + FA_BM - 1) / FA_BM;
-  const int ib = nblk - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
-  const int n_kv = p.causal ? (ib + 1) : nblk;
-  const int row0 = b * p.seq;
+  const int hb = p.heads * p.batch;
+  const int n_items = nblk * hb;
+  const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  auto item_of = [&](int round) -> int {
+    return round * (int)gridDim.x + ((round & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  };
+  auto decode = [&](int item, int& ib, int& h, int& b) {   // the last query block has the most key blocks under the causal mask
+    ib = nblk - 1 - item / hb;
+    const int rem = item % hb;
+    h = rem % p.heads;
+    b = rem / p.heads;
+  };
 
   if ((smem_u32(smem) & 1023u) != 0) {
     if (threadIdx.x == 0) report_error(p.status, OA_KERR_BAD_ARG);
@@ -1358,6 +1082,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int s = 0; s < NST; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     mbar_init(s_full, 1);
     mbar_init(s_empty, 8);
@@ -1373,153 +1098,175 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 10) {
-    if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * Cfg::T_BYTES);
-#pragma unroll
-      for (int x = 0; x < HD / 64; ++x) {
-        tma_load_2d(smem + Cfg::OFF_Q + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + ib * FA_BM);
-        tma_load_2d(smem + Cfg::OFF_DO + x * (FA_BM * 128), &tmDO, q_full, h * HD + x * 64, row0 + ib * FA_BM);
-      }
-    }
-    for (int j = 0; j < n_kv; ++j) {
-      const int st = j % NST;
-      const uint32_t ph = (j / NST) & 1;
-      if (!warp_wait(&kv_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+    uint32_t itc = 0, kc = 0;
+    bool ok = true;
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int ib, h, b;
+      decode(item, ib, h, b);
+      const int n_kv = p.causal ? (ib + 1) : nblk, row0 = b * p.seq;
+      if (!warp_wait(q_empty, (itc & 1) ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
       if (lane == 0) {
-        mbar_expect_tx(&kv_full[st], 2 * Cfg::T_BYTES);
+        mbar_expect_tx(q_full, 2 * Cfg::T_BYTES);
 #pragma unroll
         for (int x = 0; x < HD / 64; ++x) {
-          tma_load_2d(smem + Cfg::OFF_K + st * Cfg::T_BYTES + x * (FA_BN * 128), &tmK, &kv_full[st], h * HD + x * 64, row0 + j * FA_BN);
-          tma_load_2d(smem + Cfg::OFF_V + st * Cfg::T_BYTES + x * (FA_BN * 128), &tmV, &kv_full[st], h * HD + x * 64, row0 + j * FA_BN);
+          tma_load_2d(smem + Cfg::OFF_Q + x * (FA_BM * 128), &tmQ, q_full, h * HD + x * 64, row0 + ib * FA_BM);
+          tma_load_2d(smem + Cfg::OFF_DO + x * (FA_BM * 128), &tmDO, q_full, h * HD + x * 64, row0 + ib * FA_BM);
         }
       }
-      __syncwarp();
+      for (int j = 0; j < n_kv; ++j, ++kc) {
+        const int st = kc % NST;
+        const uint32_t ph = (kc / NST) & 1;
+        if (!warp_wait(&kv_empty[st], ph ^ 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
+        if (lane == 0) {
+          mbar_expect_tx(&kv_full[st], 2 * Cfg::T_BYTES);
+#pragma unroll
+          for (int x = 0; x < HD / 64; ++x) {
+            tma_load_2d(smem + Cfg::OFF_K + st * Cfg::T_BYTES + x * (FA_BN * 128), &tmK, &kv_full[st], h * HD + x * 64, row0 + j * FA_BN);
+            tma_load_2d(smem + Cfg::OFF_V + st * Cfg::T_BYTES + x * (FA_BN * 128), &tmV, &kv_full[st], h * HD + x * 64, row0 + j * FA_BN);
+          }
+        }
+        __syncwarp();
+      }
+      ++itc;
     }
   } else if (warp == 8) {
     // ------------- MMA issuer A: S = Q K_j^T, dP = dO V_j^T
     constexpr uint32_t idesc_s = umma_idesc_bf16(FA_BM, FA_BN, 0, 0);
     const uint32_t q_addr = smem_u32(smem + Cfg::OFF_Q), do_addr = smem_u32(smem + Cfg::OFF_DO);
-    bool ok = warp_wait(q_full, 0);
-    if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_FULL);
-    for (int j = 0; j < n_kv && ok; ++j) {
-      const int st = j % NST;
-      FA_STAMP(4096 + j * 16 + 8);
-      if (!warp_wait(&kv_full[st], (j / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
-      FA_STAMP(4096 + j * 16 + 9);
-      if (j > 0 && !warp_wait(s_empty, (j - 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::T_BYTES);
-        const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::T_BYTES);
+    uint32_t itc = 0, kc = 0;
+    bool ok = true;
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int ib, h, b;
+      decode(item, ib, h, b);
+      const int n_kv = p.causal ? (ib + 1) : nblk;
+      if (!warp_wait(q_full, itc & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); break; }
+      for (int j = 0; j < n_kv; ++j, ++kc) {
+        const int st = kc % NST;
+        if (!warp_wait(&kv_full[st], (kc / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+        if (kc > 0 && !warp_wait(s_empty, (kc - 1) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::T_BYTES);
+          const uint32_t v_addr = smem_u32(smem + Cfg::OFF_V + st * Cfg::T_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(q_addr + off, 16, 1024),
-                   umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
-        }
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+            umma_f16(tmem_base + Cfg::TM_S, umma_smem_desc_sw128(q_addr + off, 16, 1024),
+                     umma_smem_desc_sw128(k_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          }
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
-          umma_f16(tmem_base + Cfg::TM_DP, umma_smem_desc_sw128(do_addr + off, 16, 1024),
-                   umma_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            const uint32_t off = (ks >> 2) * (FA_BM * 128) + (ks & 3) * 32;
+            umma_f16(tmem_base + Cfg::TM_DP, umma_smem_desc_sw128(do_addr + off, 16, 1024),
+                     umma_smem_desc_sw128(v_addr + off, 16, 1024), idesc_s, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(s_full);
+          if (j + 1 == n_kv) umma_commit(q_empty);
         }
-        umma_commit(s_full);
+        __syncwarp();
       }
-      __syncwarp();
-      FA_STAMP(4096 + j * 16 + 10);
+      ++itc;
     }
   } else if (warp == 9) {
     // ------------- MMA issuer B: dQ += dS K_j (dS from TMEM)
     constexpr uint32_t idesc_q = umma_idesc_bf16(FA_BM, HD, 0, 1);   // dQ[q x HD] += dS[q x keys] * K[keys x HD]
+    uint32_t kc = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      const int st = j % NST;
-      if (!warp_wait(&kv_full[st], (j / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
-      FA_STAMP(4096 + j * 16 + 11);
-      if (!warp_wait(ds_full, j & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
-      tc_fence_after();
-      FA_STAMP(4096 + j * 16 + 12);
-      if (lane == 0) {
-        const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::T_BYTES);
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int ib, h, b;
+      decode(item, ib, h, b);
+      const int n_kv = p.causal ? (ib + 1) : nblk;
+      for (int j = 0; j < n_kv; ++j, ++kc) {
+        const int st = kc % NST;
+        if (!warp_wait(&kv_full[st], (kc / NST) & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+        if (!warp_wait(ds_full, kc & 1)) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_SOFTMAX); ok = false; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t k_addr = smem_u32(smem + Cfg::OFF_K + st * Cfg::T_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < FA_BN / 16; ++ks)
-          umma_f16_ts(tmem_base + Cfg::TM_DQ, tmem_base + Cfg::TM_DS + ks * 8,
-                      umma_smem_desc_sw128(k_addr + ks * 2048, FA_BN * 128, 1024), idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
-        umma_commit(&kv_empty[st]);
-        umma_commit(ds_empty);
+          for (int ks = 0; ks < FA_BN / 16; ++ks)
+            umma_f16_ts(tmem_base + Cfg::TM_DQ, tmem_base + Cfg::TM_DS + ks * 8,
+                        umma_smem_desc_sw128(k_addr + ks * 2048, FA_BN * 128, 1024), idesc_q, (j > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(&kv_empty[st]);
+          umma_commit(ds_empty);
+          if (j + 1 == n_kv) umma_commit(fin_full);
+        }
+        __syncwarp();
       }
-      __syncwarp();
-      FA_STAMP(4096 + j * 16 + 13);
     }
-    if (ok && lane == 0) umma_commit(fin_full);
-    __syncwarp();
   } else if (warp < 8) {
     const int quad = warp & 3;
     const int half = warp >> 2;
     const int r = quad * 32 + lane;
     const uint32_t t_lane = (uint32_t)(quad * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    const long long stat_base = ((long long)b * p.heads + h) * p.seq;
-    const int qi = ib * FA_BM + r;
-    const bool q_ok = qi < p.seq;
-    const float lse2 = q_ok ? p.lse[stat_base + qi] * LOG2E : INFINITY;
-    const float dlt = q_ok ? p.delta[stat_base + qi] : 0.f;
-    const float nlse = -lse2, ndlt = -dlt * p.scale;
+    uint32_t itc = 0, kc = 0;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (warp == 0) FA_STAMP(4096 + j * 16 + 0);
-      ok = warp_wait(s_full, j & 1);
-      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
-      tc_fence_after();
-      if (warp == 0) FA_STAMP(4096 + j * 16 + 1);
-      uint32_t s[64], dp[64];
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64, s);
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64 + 32, s + 32);
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64, dp);
-      tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64 + 32, dp + 32);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty);
-      if (warp == 0) FA_STAMP(4096 + j * 16 + 2);
-      const int k0 = j * FA_BN;
-      const bool need_mask = (p.causal && j == ib) || (k0 + FA_BN > p.seq) || !q_ok;
-      uint32_t dw[32];
-      if (need_mask) {
-        const int lim = q_ok ? (min(p.causal ? qi : 0x7fffffff, p.seq - 1) - (k0 + half * 64)) : -1;
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float p0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse)) : 0.f;
-          const float p1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse)) : 0.f;
-          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse));
-          dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
-        }
-      }
-      if (warp == 0) FA_STAMP(4096 + j * 16 + 3);
-      if (j > 0) {
-        ok = warp_wait(ds_empty, (j - 1) & 1);
-        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+    for (int round = 0; round < n_rounds && ok; ++round) {
+      const int item = item_of(round);
+      if (item >= n_items) continue;
+      int ib, h, b;
+      decode(item, ib, h, b);
+      const int n_kv = p.causal ? (ib + 1) : nblk, row0 = b * p.seq;
+      const long long stat_base = ((long long)b * p.heads + h) * p.seq;
+      const int qi = ib * FA_BM + r;
+      const bool q_ok = qi < p.seq;
+      const float lse2 = q_ok ? p.lse[stat_base + qi] * LOG2E : INFINITY;
+      const float dlt = q_ok ? p.delta[stat_base + qi] : 0.f;
+      const float nlse = -lse2, ndlt = -dlt * p.scale;
+      for (int j = 0; j < n_kv; ++j, ++kc) {
+        ok = warp_wait(s_full, kc & 1);
+        if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
         tc_fence_after();
+        uint32_t s[64], dp[64];
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64, s);
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_S + half * 64 + 32, s + 32);
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64, dp);
+        tmem_ld32(tmem_base + t_lane + Cfg::TM_DP + half * 64 + 32, dp + 32);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_empty);
+        const int k0 = j * FA_BN;
+        const bool need_mask = (p.causal && j == ib) || (k0 + FA_BN > p.seq) || !q_ok;
+        uint32_t dw[32];
+        if (need_mask) {
+          const int lim = q_ok ? (min(p.causal ? qi : 0x7fffffff, p.seq - 1) - (k0 + half * 64)) : -1;
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            const float p0 = (i <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse)) : 0.f;
+            const float p1 = (i + 1 <= lim) ? fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse)) : 0.f;
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(s[i]), sl2, nlse));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(s[i + 1]), sl2, nlse));
+            dw[i >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(dp[i]), p.scale, ndlt), p1 * fmaf(__uint_as_float(dp[i + 1]), p.scale, ndlt));
+          }
+        }
+        if (kc > 0) {
+          ok = warp_wait(ds_empty, (kc - 1) & 1);
+          if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_EMPTY); break; }
+          tc_fence_after();
+        }
+        tmem_st32(tmem_base + t_lane + Cfg::TM_DS + half * 32, dw);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_full);
       }
-      if (warp == 0) FA_STAMP(4096 + j * 16 + 4);
-      tmem_st32(tmem_base + t_lane + Cfg::TM_DS + half * 32, dw);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ds_full);
-      if (warp == 0) FA_STAMP(4096 + j * 16 + 5);
-    }
-    if (ok) {
-      ok = warp_wait(fin_full, 0);
-      if (!ok && lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL);
-    }
-    if (ok) {
+      if (!ok) break;
+      ok = warp_wait(fin_full, itc & 1);
+      if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
+      ++itc;
       tc_fence_after();
       __nv_bfloat16* base = p.dq + (long long)(row0 + qi) * p.dq_stride + h * HD;
 #pragma unroll 1
@@ -1538,6 +1285,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 pack_bf16x2(__uint_as_float(a[g * 8 + 6]), __uint_as_float(a[g * 8 + 7])));
         }
       }
+      tc_fence_before();   // dQ is read before this warp's next ds_full arrival lets the next item's products overwrite it
     }
   }
   tc_fence_before();
@@ -1568,52 +1316,22 @@ extern "C" int oa_flash_fwd(const void* q, const void* k, const void* v, void* o
   p.batch = batch; p.heads = heads; p.seq = seq; p.head_dim = head_dim; p.scale = scale; p.causal = causal;
   p.o = (__nv_bfloat16*)o; p.o_stride = o_row_stride; p.lse = lse; p.status = status;
   cudaStream_t st = (cudaStream_t)stream;
-  static const int version = [] { const char* e = getenv("OA_FLASH_FWD"); return (e && e[0] == '1') ? 1 : 2; }();
-  if (version == 2) {
-    static const int poly = [] { const char* e = getenv("OA_FLASH_POLY"); return e ? atoi(e) : 0; }();
-    dim3 grid2((seq + FA_BM - 1) / FA_BM, heads, batch);
-    static const bool single = [] { const char* e = getenv("OA_FLASH_FWD"); return e && e[0] == '3'; }();
-    if (head_dim == 64 && !single) {
-      static int sms = 0;
-      if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return OA_ERR_DRIVER;
-        if (cudaFuncSetAttribute(flash_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdPairCfg::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
-      }
-      const int nblk = (seq + FA_BM - 1) / FA_BM;
-      const long long items = (long long)((nblk + 1) / 2) * heads * batch;
-      const int ctas = (int)(items < sms ? items : sms);
-      flash_fwd_pair_kernel<<<ctas, FwdPairCfg::THREADS, FwdPairCfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
-      return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
-    }
-    if (head_dim == 64) {
-      if (poly == 2) return launch_fwd2<64, 2>(tq, tk, tv, p, grid2, st);
-      if (poly == 3) return launch_fwd2<64, 3>(tq, tk, tv, p, grid2, st);
-      if (poly == 4) return launch_fwd2<64, 4>(tq, tk, tv, p, grid2, st);
-      return launch_fwd2<64, 0>(tq, tk, tv, p, grid2, st);
-    }
-    if (poly == 2) return launch_fwd2<128, 2>(tq, tk, tv, p, grid2, st);
-    if (poly == 3) return launch_fwd2<128, 3>(tq, tk, tv, p, grid2, st);
-    return launch_fwd2<128, 0>(tq, tk, tv, p, grid2, st);
-  }
-  dim3 grid((seq + FA_BM - 1) / FA_BM, heads, batch);
   if (head_dim == 64) {
-    static bool set = false;
-    if (!set) { if (cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
-    flash_fwd_kernel<64><<<grid, FA_THREADS, FwdCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, p);
-  } else {
-    static bool set = false;
-    if (!set) { if (cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<128>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH; set = true; }
-    flash_fwd_kernel<128><<<grid, FA_THREADS, FwdCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    // persistent kernel, two query tiles per work item
+    static int sms = 0;
+    if (sms == 0) {
+      int dev = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return OA_ERR_DRIVER;
+      if (cudaFuncSetAttribute(flash_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdPairCfg::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
+    }
+    const int nblk = (seq + FA_BM - 1) / FA_BM;
+    const long long items = (long long)((nblk + 1) / 2) * heads * batch;
+    const int ctas = (int)(items < sms ? items : sms);
+    flash_fwd_pair_kernel<<<ctas, FwdPairCfg::THREADS, FwdPairCfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
   }
-  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+  return launch_fwd2<128>(tq, tk, tv, p, dim3((seq + FA_BM - 1) / FA_BM, heads, batch), st);
 }
-
-#ifdef OA_FA_PROF
-extern "C" int oa_flash_prof_read(long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, g_fa_prof, sizeof(long long) * (size_t)n) == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
-}
-#endif
 
 // scratch: float[B*H*S] for delta
 extern "C" size_t oa_flash_bwd_scratch_bytes(int batch, int heads, int seq, int head_dim) {
@@ -1656,7 +1374,13 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
   p.dq = (__nv_bfloat16*)dq; p.dq_stride = dq_row_stride;
   p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv; p.dkv_stride = dkv_row_stride;
   p.status = status;
-  dim3 grid((seq + FA_BM - 1) / FA_BM, heads, batch);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return OA_ERR_DRIVER;
+  }
+  const long long items = (long long)((seq + FA_BM - 1) / FA_BM) * heads * batch;
+  const dim3 grid((unsigned)(items < sms ? items : sms));     // persistent: one CTA per SM walks its items
   if (head_dim == 64) {
     static bool set = false;
     if (!set) {
@@ -1678,4 +1402,3 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
   }
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
-
