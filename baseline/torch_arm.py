@@ -475,7 +475,10 @@ class TorchTrainer:
         self.fp32 = fp32
         self.params = [p for p in self.model.parameters()]
         self.masters = self.params if fp32 else [p.detach().float().clone() for p in self.params]
-        if not fp32:
+        # The two largest models on ONE GPU (64 experts resident, or all of the 7B model) leave no room for a second fp32
+        # copy of every gradient: there the update walks the parameters one at a time, each with its own fused AdamW.
+        self.low_mem = (not fp32) and world == 1 and config in (3, 5) and not layers
+        if not fp32 and not self.low_mem:
             for m in self.masters:
                 m.grad = torch.zeros_like(m)
         self.run = self.model
@@ -490,9 +493,12 @@ class TorchTrainer:
             ex = {id(p) for p in self.model.expert_parameters()}
             self.sync_lists = [([p for p in self.params if id(p) not in ex], 1.0 / world)]
             self.expert_scale = 1.0 / world
-        self.use_graph = graph and world == 1 and config != 3
-        self.opt = torch.optim.AdamW(self.masters, lr=3e-4, weight_decay=0.0 if config == 1 else 0.1,
-                                     fused=True, capturable=self.use_graph)
+        self.use_graph = graph and world == 1 and config != 3 and not self.low_mem
+        wd = 0.0 if config == 1 else 0.1
+        if self.low_mem:
+            self.opts = [torch.optim.AdamW([m], lr=3e-4, weight_decay=wd, fused=True) for m in self.masters]
+        else:
+            self.opt = torch.optim.AdamW(self.masters, lr=3e-4, weight_decay=wd, fused=True, capturable=self.use_graph)
         self.ids = torch.zeros((micro_batch, c.seq_len), dtype=torch.int32, device=device)
         self.tgt = torch.zeros((micro_batch, c.seq_len), dtype=torch.int32, device=device)
         self.loss = torch.zeros((), device=device)
@@ -520,6 +526,13 @@ class TorchTrainer:
             if self.config == 3:
                 for p in self.model.expert_parameters():
                     p.grad *= self.expert_scale
+        if self.low_mem:
+            for p, m, o in zip(self.params, self.masters, self.opts):
+                m.grad = p.grad.float()
+                o.step()
+                p.copy_(m)
+                m.grad = None
+            return
         if not self.fp32:
             torch._foreach_copy_([m.grad for m in self.masters], [p.grad for p in self.params])
         self.opt.step()

@@ -3,9 +3,10 @@
 // precision) and the finite-difference gradient checks, where TF32/bf16 rounding is not acceptable.
 // The bf16 path uses gemm_tcgen05.cu instead.
 //   C[b][m,n] = act(alpha * sum_k A[b][m*sam + k*sak] * B[b][n*sbn + k*sbk] + bias[n]) (+ C)
-// 64x64x16 tiles, 256 threads, 4x4 outputs per thread: the same tiling class as the reference's
-// GemmTiled (Source/Private/Oa/Core/Shader/Compute/Blas/Gemm/GemmTiled.slang:1-110), here with
-// runtime strides so that NT / NN / TN products and Bmm need no transposed copies.
+// 64x64x16 tiles, 256 threads, 4x4 outputs per thread with 16-byte shared-memory reads and the next
+// K tile prefetched into registers (the reference's GemmTiled,
+// Source/Private/Oa/Core/Shader/Compute/Blas/Gemm/GemmTiled.slang:1-110, is the same tiling class), here
+// with runtime strides so that NT / NN / TN products and Bmm need no transposed copies.
 #include "common.cuh"
 #include "api.h"
 
@@ -18,8 +19,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
                 long long sam, long long sak, long long sbn, long long sbk, int ldc, long long batch_a,
                 long long batch_b, long long batch_c, const float* __restrict__ bias, int act, int accumulate,
                 float alpha, int k_chunk) {
-  __shared__ float sA[FK][FT + 1];
-  __shared__ float sB[FK][FT + 1];
+  __shared__ __align__(16) float sA[FK][FT + 4];
+  __shared__ __align__(16) float sB[FK][FT + 4];
   const int b = blockIdx.z;
   // k_chunk > 0: split-K mode - blockIdx.z is the K slice (batch 1) and C is the slice's own [M, ldc] partial buffer
   const int k_lo = k_chunk > 0 ? b * k_chunk : 0;
@@ -33,28 +34,38 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
   }
   const int m0 = blockIdx.y * FT, n0 = blockIdx.x * FT;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  float acc[4][4] = {};
-  for (int k0 = k_lo; k0 < k_hi; k0 += FK) {
-    // 64x16 elements per operand, 256 threads -> 4 loads each
+  // 64x16 elements per operand, 256 threads -> 4 loads each; the faster-varying index follows the contiguous dimension
+  int ar[4], ak[4], br[4], bk[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int idx = threadIdx.x + i * 256;
+    if (sak == 1) { ak[i] = idx & 15; ar[i] = idx >> 4; } else { ar[i] = idx & 63; ak[i] = idx >> 6; }
+    if (sbk == 1) { bk[i] = idx & 15; br[i] = idx >> 4; } else { br[i] = idx & 63; bk[i] = idx >> 6; }
+  }
+  float ra[4], rb[4];
+  auto fetch = [&](int k0) {       // global -> registers (the next tile is in flight while this one is multiplied)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      int idx = threadIdx.x + i * 256;
-      int r, kk;
-      // choose the faster-varying index to follow the contiguous dimension of each operand
-      if (sak == 1) { kk = idx & 15; r = idx >> 4; } else { r = idx & 63; kk = idx >> 6; }
-      int gm = m0 + r, gk = k0 + kk;
-      sA[kk][r] = (gm < M && gk < k_hi) ? A[gm * sam + gk * sak] : 0.f;
-      if (sbk == 1) { kk = idx & 15; r = idx >> 4; } else { r = idx & 63; kk = idx >> 6; }
-      int gn = n0 + r;
-      gk = k0 + kk;
-      sB[kk][r] = (gn < N && gk < k_hi) ? B[gn * sbn + gk * sbk] : 0.f;
+      const int gm = m0 + ar[i], gka = k0 + ak[i], gn = n0 + br[i], gkb = k0 + bk[i];
+      ra[i] = (gm < M && gka < k_hi) ? A[gm * sam + gka * sak] : 0.f;
+      rb[i] = (gn < N && gkb < k_hi) ? B[gn * sbn + gkb * sbk] : 0.f;
     }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { sA[ak[i]][ar[i]] = ra[i]; sB[bk[i]][br[i]] = rb[i]; }
+  };
+  float acc[4][4] = {};
+  if (k_lo < k_hi) fetch(k_lo);
+  for (int k0 = k_lo; k0 < k_hi; k0 += FK) {
+    stash();
     __syncthreads();
+    if (k0 + FK < k_hi) fetch(k0 + FK);
 #pragma unroll
     for (int kk = 0; kk < FK; ++kk) {
-      float a[4], bb[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { a[i] = sA[kk][ty * 4 + i]; bb[i] = sB[kk][tx * 4 + i]; }
+      const float4 a4 = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
+      const float4 b4 = *reinterpret_cast<const float4*>(&sB[kk][tx * 4]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll

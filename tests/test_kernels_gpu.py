@@ -279,19 +279,20 @@ def test_flash_fwd_bwd(hd, heads, seq, batch, causal):
     _close(dq, dqr, 3e-2, what="flash dq")
 
 
-def test_attn_f32():
+@pytest.mark.parametrize("hd,seq,causal", [(32, 70, True), (16, 33, False), (64, 200, True), (128, 130, True), (48, 64, False)])
+def test_attn_f32(hd, seq, causal):
     torch.manual_seed(10)
-    batch, seq, heads, hd = 2, 70, 4, 32
+    batch, heads = 2, 4
     D = heads * hd
     qkv = torch.randn(batch * seq, 3 * D, device=DEV)
     q, k, v = qkv[:, :D], qkv[:, D:2 * D], qkv[:, 2 * D:]
-    o, lse = K.flash_fwd(q, k, v, batch, seq, heads, hd, causal=True)
-    orf, lser = K.flash_fwd(q.cpu(), k.cpu(), v.cpu(), batch, seq, heads, hd, causal=True)
+    o, lse = K.flash_fwd(q, k, v, batch, seq, heads, hd, causal=causal)
+    orf, lser = K.flash_fwd(q.cpu(), k.cpu(), v.cpu(), batch, seq, heads, hd, causal=causal)
     _close(o, orf, 1e-5)
     _close(lse, lser, 1e-5)
     do = torch.randn(batch * seq, D, device=DEV)
-    got = K.flash_bwd(q, k, v, o, do, lse, batch, seq, heads, hd, causal=True)
-    ref = K.flash_bwd(q.cpu(), k.cpu(), v.cpu(), orf, do.cpu(), lser, batch, seq, heads, hd, causal=True)
+    got = K.flash_bwd(q, k, v, o, do, lse, batch, seq, heads, hd, causal=causal)
+    ref = K.flash_bwd(q.cpu(), k.cpu(), v.cpu(), orf, do.cpu(), lser, batch, seq, heads, hd, causal=causal)
     for g, r, nm in zip(got, ref, "qkv"):
         _close(g, r, 1e-4, what="attn_f32 d" + nm)
 
