@@ -117,6 +117,10 @@ OaFnLoss.__all__ = OaFnLoss.__all__ + ("PpoClippedPolicy", "PpoClippedPolicyBwd"
 for _n in ("MaskedMse", "SmoothL1Mean", "VelSmoothL1"):
     setattr(OaFnLoss, _n, getattr(_F, _n))
 OaFnLoss.__all__ = OaFnLoss.__all__ + ("MaskedMse", "SmoothL1Mean", "VelSmoothL1")
+from oa_b200.ml import fn_optim as _FO
+OaFnOptim = _namespace("OaFnOptim", "Stateless optimizer steps (AdamW, SGD, Muon, gradient-norm clipping).", _FO,
+                       ["OaAdamWParamSet", "MakeAdamWState", "AdamWAdvanceGraphState", "AdamWStep", "AdamWStepGraph", "AdamWStepMany",
+                        "AdamWStepManyGraph", "SgdStep", "MuonStep", "ClipGradNorm"])
 OaFnRl = _namespace("OaFnRl", "Advantage estimation, policy distributions, transforms and evaluation.", _RL.OaFnRl,
                     ["Gae", "GaeInto", "NormalizeAdvantages", "SampleCategoricalPolicy", "EvaluateCategoricalPolicy", "SampleTanhNormalPolicy",
                      "EvaluateTanhNormalPolicy", "NormalizeObservation", "ScaleAction", "ClipReward", "SampleLogits", "EvaluateCategorical"])

@@ -80,10 +80,60 @@ def _next_offset(n: int) -> int:
     return off
 
 
+# ---- random numbers inside a captured training program.  A launch argument is frozen in a CUDA graph, so a captured
+# Dropout with host-side (seed, offset) would repeat the same mask on every replay.  While a program is being captured the
+# random ops read (seed, base offset) from a device word pair instead and pass only the offset RELATIVE to the start of
+# the step; the program closes the step with a one-thread kernel that adds the counters the step consumed to the base
+# (the reference rewrites Philox nodes the same way: Source/Private/Oa/Ml/TrainingProgram.cpp:245-324).  Eager step k and
+# replayed step k therefore draw the same counters.
+_rng_capture = {"state": None, "base": 0}
+
+
+def BeginProgramRng():
+    """Called by OaTrainingProgram right before capture: device state := host (seed, offset)."""
+    dev = _dev()
+    if dev.type != "cuda":
+        return None
+    st = _rng_capture["state"]
+    if st is None or st.device != dev:
+        st = torch.zeros(2, dtype=torch.int64, device=dev)
+    seed, off = _rng["seed"], _rng["offset"]
+    st.copy_(torch.tensor([seed - (1 << 64) if seed >= (1 << 63) else seed, off], dtype=torch.int64))
+    _rng_capture["state"], _rng_capture["base"] = st, off
+    _rng_capture["active"] = True
+    return st
+
+
+def EndProgramRng() -> int:
+    """Called at the end of the captured body: appends the advance launch; returns the counters one step consumes.  The
+    host offset goes back to its value before the capture (the capture pass itself executed nothing)."""
+    st = _rng_capture["state"]
+    used = _rng["offset"] - _rng_capture["base"]
+    if st is not None and used > 0:
+        K.philox_state_advance(st, used)
+    _rng["offset"] = _rng_capture["base"]
+    _rng_capture["active"] = False
+    return used
+
+
+def AdvanceHostRng(counters: int) -> None:
+    """A replayed step consumed `counters` Philox counters on the device: keep the host offset in step."""
+    _rng["offset"] += int(counters)
+
+
+def _rng_args(n: int):
+    """(seed, offset, state) for one random launch of n values."""
+    off = _next_offset(n)
+    if _rng_capture.get("active"):
+        return 0, off - _rng_capture["base"], _rng_capture["state"]
+    return _rng["seed"], off, None
+
+
 def _philox(shape, dtype, normal: bool, a: float, b: float) -> OaMatrix:
     dt = _dtype(dtype)
     t = torch.empty(tuple(shape), dtype=torch.float32 if dt not in (torch.float32, torch.bfloat16) else dt, device=_dev())
-    K.philox_(t, _rng["seed"], _next_offset(t.numel()), normal=normal, a=a, b=b)
+    seed, off, state = _rng_args(t.numel())
+    K.philox_(t, seed, off, normal=normal, a=a, b=b, state=state)
     return _w(t if t.dtype == dt else t.to(dt))
 
 
@@ -414,9 +464,9 @@ def Dropout(m: OaMatrix, p: float, training: bool = True) -> OaMatrix:
         return m
     _ctx_add("Dropout")
     x = _c(m.Tensor())
-    seed, off = _rng["seed"], _next_offset(x.numel())
-    out = _w(K.dropout(x, p, seed, off))
-    return AG.attach("Dropout", out, [m], lambda g: (K.dropout(_c(g), p, seed, off),))
+    seed, off, state = _rng_args(x.numel())
+    out = _w(K.dropout(x, p, seed, off, state))
+    return AG.attach("Dropout", out, [m], lambda g: (K.dropout(_c(g), p, seed, off, state),))
 
 
 # ======================================================================= shape ops

@@ -87,10 +87,13 @@ int oa_softmax(int dtype, const void* x, void* y, long long rows, int cols, int 
                const void* mask, long long mask_rows, void* stream);
 int oa_softmax_bwd(int dtype, const void* y, const void* dy, void* dx, long long rows, int cols, int log_mode,
                    float scale, void* stream);
+// `state` (may be null): device u64[2] = {seed, base offset}; when given, the seed comes from it and `offset` is relative to
+// its base, so a captured launch draws fresh counters on every replay once oa_philox_state_advance closes the step.
 int oa_philox(int dtype, void* y, long long n, unsigned long long seed, unsigned long long offset, int normal,
-              float a, float b, void* stream);
+              float a, float b, const unsigned long long* state, void* stream);
 int oa_dropout(int dtype, const void* x, void* y, long long n, float p, unsigned long long seed,
-               unsigned long long offset, void* stream);
+               unsigned long long offset, const unsigned long long* state, void* stream);
+int oa_philox_state_advance(unsigned long long* state, unsigned long long delta, void* stream);
 int oa_copy_strided(int dtype, const void* x, void* y, int rank, const long long* shape, const long long* src_strides,
                     void* stream);
 
@@ -376,6 +379,7 @@ int oa_peer_reduce(int dtype, const void* const* in_peers, void* out, long long 
 int oa_peer_allreduce_oneshot(const void* const* slots_peers, const void* const* counters_peers, const void* src,
                               const void* residual, void* out, void* sync2, long long n, long long slot_elems, int world,
                               int rank, int max_ctas, int* status, void* stream);
+int oa_p2p_attributes(int src, int dst, int* out);
 // Bound (milliseconds of wall time) of every device-side wait on a peer flag; the default is 2000.
 int oa_set_peer_wait_ms(long long ms);
 // Gradient-norm clipping under the fused data-parallel step: sum of squares of this rank's shard of the summed gradient

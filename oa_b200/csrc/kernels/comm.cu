@@ -364,6 +364,19 @@ extern "C" int oa_dp_reduce_adam_gather(const void* const* grad_peers, const voi
   dp_reduce_adam_gather_kernel<<<(int)blocks, 256, 0, ST>>>(p);
   return CHECK_LAUNCH();
 }
+// Peer-to-peer attributes of the link from device `src` to device `dst` as the driver reports them:
+// out[0] = access supported, out[1] = native atomics supported (true over NVLink, false over plain PCIe), out[2] = performance rank.
+extern "C" int oa_p2p_attributes(int src, int dst, int* out) {
+  if (!out) return OA_ERR_ARG;
+  int v = 0;
+  if (cudaDeviceGetP2PAttribute(&v, cudaDevP2PAttrAccessSupported, src, dst) != cudaSuccess) { cudaGetLastError(); return OA_ERR_DRIVER; }
+  out[0] = v;
+  if (cudaDeviceGetP2PAttribute(&v, cudaDevP2PAttrNativeAtomicSupported, src, dst) != cudaSuccess) { cudaGetLastError(); return OA_ERR_DRIVER; }
+  out[1] = v;
+  if (cudaDeviceGetP2PAttribute(&v, cudaDevP2PAttrPerformanceRank, src, dst) != cudaSuccess) { cudaGetLastError(); return OA_ERR_DRIVER; }
+  out[2] = v;
+  return OA_OK;
+}
 extern "C" int oa_set_peer_wait_ms(long long ms) {
   if (ms <= 0) return OA_ERR_ARG;
   const unsigned long long ns = (unsigned long long)ms * 1000000ull;

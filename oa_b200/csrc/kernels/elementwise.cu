@@ -315,16 +315,31 @@ __global__ void embedding_bwd_kernel(const T* __restrict__ dout, const int* __re
 }
 
 // Column sums (bias gradient): stage 1 writes per-block partials, stage 2 reduces them in a fixed order.
+// Block = 128 columns x 4 row lanes; a lane walks every fourth row of the block's slab with four independent partial sums
+// (16 loads in flight per column), the lanes are then added in a fixed order, so the result does not depend on scheduling.
 template <typename T>
-__global__ void col_sum_partial_kernel(const T* __restrict__ x, float* __restrict__ partial, long long rows, int cols,
-                                       int rows_per_block) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  long long r0 = (long long)blockIdx.y * rows_per_block;
-  long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
-  float s = 0.f;
-  for (long long r = r0; r < r1; ++r) s += IO<T>::ld1(x + r * cols + c);
-  partial[(long long)blockIdx.y * cols + c] = s;
+__global__ void __launch_bounds__(512)
+col_sum_partial_kernel(const T* __restrict__ x, float* __restrict__ partial, long long rows, int cols, int rows_per_block) {
+  __shared__ float sm[4][128];
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int lane = threadIdx.y;
+  const long long r0 = (long long)blockIdx.y * rows_per_block;
+  const long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < cols) {
+    long long r = r0 + lane;
+    for (; r + 12 < r1; r += 16) {
+      s0 += IO<T>::ld1(x + r * cols + c);
+      s1 += IO<T>::ld1(x + (r + 4) * cols + c);
+      s2 += IO<T>::ld1(x + (r + 8) * cols + c);
+      s3 += IO<T>::ld1(x + (r + 12) * cols + c);
+    }
+    for (; r < r1; r += 4) s0 += IO<T>::ld1(x + r * cols + c);
+  }
+  sm[lane][threadIdx.x] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (lane == 0 && c < cols)
+    partial[(long long)blockIdx.y * cols + c] = (sm[0][threadIdx.x] + sm[1][threadIdx.x]) + (sm[2][threadIdx.x] + sm[3][threadIdx.x]);
 }
 template <typename D>
 __global__ void col_sum_final_kernel(const float* __restrict__ partial, D* __restrict__ out, int nparts, int cols,
@@ -454,7 +469,8 @@ __device__ __forceinline__ float u01(uint32_t x) { return (float)(x >> 8) * (1.0
 
 template <typename T>
 __global__ void philox_kernel(T* y, long long n, unsigned long long seed, unsigned long long offset, int normal, float a,
-                              float b) {
+                              float b, const unsigned long long* __restrict__ state) {
+  if (state) { seed = state[0]; offset += state[1]; }     // device-resident (seed, base offset): replay-safe inside a graph
   long long stride = (long long)gridDim.x * blockDim.x;
   long long groups = (n + 3) / 4;
   for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < groups; g += stride) {
@@ -483,7 +499,8 @@ __global__ void philox_kernel(T* y, long long n, unsigned long long seed, unsign
 }
 template <typename T>
 __global__ void dropout_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, float p, unsigned long long seed,
-                               unsigned long long offset) {
+                               unsigned long long offset, const unsigned long long* __restrict__ state) {
+  if (state) { seed = state[0]; offset += state[1]; }     // device-resident (seed, base offset): replay-safe inside a graph
   long long stride = (long long)gridDim.x * blockDim.x;
   long long groups = (n + 3) / 4;
   float keep_scale = 1.f / (1.f - p);
@@ -604,7 +621,7 @@ extern "C" int oa_col_sum(int dtype, const void* x, void* out, int out_dtype, lo
   const int RPB = 256;
   int nparts = (int)((rows + RPB - 1) / RPB);
   dim3 g1((cols + 127) / 128, nparts);
-  DISPATCH_T(dtype, col_sum_partial_kernel<T><<<g1, 128, 0, ST>>>((const T*)x, scratch, rows, cols, RPB));
+  DISPATCH_T(dtype, col_sum_partial_kernel<T><<<g1, dim3(128, 4), 0, ST>>>((const T*)x, scratch, rows, cols, RPB));
   if (out_dtype == OA_F32) col_sum_final_kernel<float><<<(cols + 127) / 128, 128, 0, ST>>>(scratch, (float*)out, nparts, cols, accumulate);
   else col_sum_final_kernel<__nv_bfloat16><<<(cols + 127) / 128, 128, 0, ST>>>(scratch, (__nv_bfloat16*)out, nparts, cols, accumulate);
   return CHECK_LAUNCH();
@@ -636,15 +653,24 @@ extern "C" int oa_softmax_bwd(int dtype, const void* y, const void* dy, void* dx
   return CHECK_LAUNCH();
 }
 extern "C" int oa_philox(int dtype, void* y, long long n, unsigned long long seed, unsigned long long offset,
-                         int normal, float a, float b, void* stream) {
+                         int normal, float a, float b, const unsigned long long* state, void* stream) {
   if (n <= 0) return OA_OK;
-  DISPATCH_T(dtype, philox_kernel<T><<<grid_for((n + 3) / 4, 256), 256, 0, ST>>>((T*)y, n, seed, offset, normal, a, b));
+  DISPATCH_T(dtype, philox_kernel<T><<<grid_for((n + 3) / 4, 256), 256, 0, ST>>>((T*)y, n, seed, offset, normal, a, b, state));
   return CHECK_LAUNCH();
 }
 extern "C" int oa_dropout(int dtype, const void* x, void* y, long long n, float p, unsigned long long seed,
-                          unsigned long long offset, void* stream) {
+                          unsigned long long offset, const unsigned long long* state, void* stream) {
   if (n <= 0) return OA_OK;
-  DISPATCH_T(dtype, dropout_kernel<T><<<grid_for((n + 3) / 4, 256), 256, 0, ST>>>((const T*)x, (T*)y, n, p, seed, offset));
+  DISPATCH_T(dtype, dropout_kernel<T><<<grid_for((n + 3) / 4, 256), 256, 0, ST>>>((const T*)x, (T*)y, n, p, seed, offset, state));
+  return CHECK_LAUNCH();
+}
+// state[1] += delta: closes a captured step, so that every replay draws the counters the eager step would have drawn
+// (the reference's PhiloxGraphAdvance, Source/Private/Oa/Core/Shader/Compute/Rng/PhiloxGraphAdvance.slang).
+__global__ void philox_state_advance_kernel(unsigned long long* state, unsigned long long delta) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) state[1] += delta;
+}
+extern "C" int oa_philox_state_advance(unsigned long long* state, unsigned long long delta, void* stream) {
+  philox_state_advance_kernel<<<1, 32, 0, ST>>>(state, delta);
   return CHECK_LAUNCH();
 }
 extern "C" int oa_copy_strided(int dtype, const void* x, void* y, int rank, const long long* shape,

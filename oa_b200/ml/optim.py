@@ -314,6 +314,8 @@ class OaSGD(OaOptimizer):
 
     def Step(self) -> None:
         self._build()
+        RT.OaContext.GetDefault().MarkReplayUnsafe("OaSGD.Step passes the learning rate, momentum and weight decay as launch "
+                                                   "arguments: a replay would ignore SetLr")
         for a, mom in zip(self._arenas, self._mom):
             RT.OaContext.GetDefault().Add("SgdMomentum" if mom is not None else "Sgd")
             K.sgd_step(a.flat, a.grad, a.master, mom, lr=self.Lr_, momentum=self.Momentum_, weight_decay=self.WeightDecay_)
@@ -392,6 +394,7 @@ class OaMuon(OaOptimizer):
     def Step(self) -> None:
         self._build()
         ctx = RT.OaContext.GetDefault()
+        ctx.MarkReplayUnsafe("OaMuon.Step applies host-side learning rate and momentum scalars: a replay would ignore SetLr")
         for a, mom in zip(self._arenas, self._mom):
             w_all = a.master if a.master is not None else a.flat
             for p, o in zip(a.params, a.offsets):

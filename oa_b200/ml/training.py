@@ -36,6 +36,8 @@ class OaItTrainingConfig:
     TimerName: str = "train"
     StepsPerEpoch: int = 0
     Program: bool = False            # capture the step into a CUDA graph from step 2 on
+    ValidateEvery: int = 0           # with a program: every N steps run the step eagerly, compare its node structure with
+                                     # the captured one and drop the program when it changed (0: only on request)
     SyncEveryStep: bool = True       # exact per-step loss readback (the reference always does)
     LogEvery: int = 0
 
@@ -61,10 +63,23 @@ class OaTrainingPhaseStats:
 
 
 class OaTrainingProgram:
-    """A captured training step.  `Capture(fn)` records everything `fn` launches into a CUDA graph and keeps the
-    tensors it returns alive as static outputs; `Replay()` launches the graph, `Wait()` blocks until it finished."""
+    """A captured training step.  `Capture(fn)` records everything `fn` launches into a CUDA graph and keeps the tensors it
+    returns alive as static outputs; `Replay()` launches the graph, `Wait()` blocks until it finished.
 
-    Stages = ("collect", "rng-rewrite", "validate", "alias", "instantiate", "ready")
+    Stages of a capture (`StageLog` lists the ones that ran, with their milliseconds):
+      collect      `fn` runs under stream capture while the context collects its nodes and the marks of ops that freeze
+                   host values into their launches;
+      rng-rewrite  random ops inside `fn` read (seed, base offset) from device memory and the step is closed by a launch
+                   that advances the base by the counters the step consumed, so every replay draws fresh numbers, the
+                   same ones the eager step would have drawn;
+      validate     replay-unsafe marks refuse the capture; the collected nodes go through the native compute graph
+                   (hazards, levels) and their structure hash is stored;
+      instantiate  the CUDA graph is instantiated (by the end of the capture);
+      ready.
+    `Verify(nodes)` compares the structure hash of a freshly recorded step with the captured one: OaItTraining re-records
+    a step eagerly every `ValidateEvery` steps and drops a program whose step has changed shape instead of replaying it."""
+
+    Stages = ("collect", "rng-rewrite", "validate", "instantiate", "ready")
 
     def __init__(self):
         self._graph: Optional[torch.cuda.CUDAGraph] = None
@@ -74,11 +89,18 @@ class OaTrainingProgram:
         self.NodeCount = 0
         self.Replays = 0
         self.StageLog: list = []
+        self.StructureHash = 0
+        self.GraphHash = 0
+        self.Levels = 0
+        self.Barriers = 0
+        self.RngCountersPerStep = 0
+        self.Unsafe: list = []
 
     def IsCaptured(self) -> bool:
         return self._graph is not None
 
     def Capture(self, fn: Callable[[], object]) -> OaStatus:
+        from ..core import fn_matrix as F
         eng = RT.get_engine()
         if not eng.IsCuda():
             return OaStatus.Error(OaStatusCode.FailedPrecondition, "program capture needs a CUDA engine")
@@ -87,25 +109,55 @@ class OaTrainingProgram:
         torch.cuda.synchronize()
         n0 = ctx.NodeCount()
         g = torch.cuda.CUDAGraph()
-        self.StageLog = [("collect", 0.0)]
+        self.StageLog = []
+        F.BeginProgramRng()
+        ctx.BeginCollect()
         try:
             # thread-local capture mode: a communication watchdog thread may query events while we capture
             with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self._outputs = fn()
+                self.RngCountersPerStep = F.EndProgramRng()
         except Exception as e:  # leave no half-captured graph behind
+            F.EndProgramRng()
+            ctx.EndCollect()
             self._graph = None
             return OaStatus.Error(OaStatusCode.Internal, f"capture failed: {e}")
+        t1 = time.perf_counter()
+        self.StageLog.append(("collect", (t1 - t0) * 1e3))
+        if self.RngCountersPerStep:
+            self.StageLog.append(("rng-rewrite", 0.0))
+        nodes, self.Unsafe = ctx.EndCollect()
+        if self.Unsafe:
+            self._outputs = None
+            return OaStatus.Error(OaStatusCode.FailedPrecondition,
+                                  "the step cannot be replayed: " + "; ".join(sorted(set(self.Unsafe))))
+        graph, self.StructureHash = RT.OaContext.Compile(nodes)
+        self.GraphHash, self.Levels, self.Barriers = graph.Hash(), graph.NumLevels(), graph.NumBarriers()
         self.NodeCount = ctx.NodeCount() - n0
+        t2 = time.perf_counter()
+        self.StageLog.append(("validate", (t2 - t1) * 1e3))
         self._graph = g
         self.CaptureMs = (time.perf_counter() - t0) * 1e3
-        self.StageLog += [("instantiate", self.CaptureMs), ("ready", self.CaptureMs)]
+        self.StageLog += [("instantiate", 0.0), ("ready", self.CaptureMs)]
+        return OaStatus.Ok()
+
+    def Verify(self, nodes) -> OaStatus:
+        """Does a freshly recorded step still have the structure that was captured?"""
+        _, h = RT.OaContext.Compile(nodes)
+        if h != self.StructureHash or len(nodes) != self.NodeCount:
+            return OaStatus.Error(OaStatusCode.FailedPrecondition,
+                                  f"the recorded step changed ({len(nodes)} nodes, hash {h:016x}) since it was captured "
+                                  f"({self.NodeCount} nodes, hash {self.StructureHash:016x})")
         return OaStatus.Ok()
 
     def Outputs(self):
         return self._outputs
 
     def Replay(self) -> None:
+        from ..core import fn_matrix as F
         self._graph.replay()
+        if self.RngCountersPerStep:
+            F.AdvanceHostRng(self.RngCountersPerStep)
         self.Replays += 1
 
     def Wait(self) -> OaStatus:
@@ -113,7 +165,9 @@ class OaTrainingProgram:
 
     def DebugReport(self) -> dict:
         return {"captured": self.IsCaptured(), "nodes": self.NodeCount, "capture_ms": self.CaptureMs, "replays": self.Replays,
-                "stages": [s for s, _ in self.StageLog]}
+                "stages": [s for s, _ in self.StageLog], "structure_hash": f"{self.StructureHash:016x}",
+                "graph_hash": f"{self.GraphHash:016x}", "levels": self.Levels, "barriers": self.Barriers,
+                "rng_counters_per_step": self.RngCountersPerStep}
 
 
 class OaCallback:
@@ -216,6 +270,10 @@ class OaItTraining:
                 self.LastStatus = st
                 self._stop = True
                 return float("nan")
+        if self._program is not None and self._program.IsCaptured() and (
+                getattr(self, "_verify_next", False)
+                or (self.Config.ValidateEvery > 0 and self._index > 0 and self._index % self.Config.ValidateEvery == 0)):
+            return self._verified_eager_step(prepare, record)
         if self._program is not None and self._program.IsCaptured():
             if prepare is not None:
                 prepare()
@@ -247,6 +305,27 @@ class OaItTraining:
             loss = record()
         self.Phase.BodyMs = (time.perf_counter() - t0) * 1e3
         return self.Next(loss)
+
+    def RequestVerify(self) -> None:
+        """The next step runs eagerly and its recorded structure is compared with the captured program."""
+        self._verify_next = True
+
+    def _verified_eager_step(self, prepare, record) -> float:
+        """One eager step whose node sequence is checked against the captured program.  The step does the real work of
+        this iteration; on a mismatch the program is dropped (the following steps re-capture) and the status says why."""
+        self._verify_next = False
+        if prepare is not None:
+            prepare()
+        ctx = RT.OaContext.GetDefault()
+        ctx.BeginCollect()
+        loss = record()
+        self.Opt_.Step()
+        nodes, _ = ctx.EndCollect()
+        st = self._program.Verify(nodes)
+        self.LastVerify = st
+        if not st:
+            self.RequestRecapture()
+        return self._finish_step(loss, stepped=True)
 
     def SetRankMonitor(self, monitor) -> None:
         """Check the peers' heartbeats before every `Step`: a rank that failed or fell silent stops this loop with an

@@ -504,8 +504,10 @@ def softmax_bwd(y: torch.Tensor, dy: torch.Tensor, *, log: bool = False, scale: 
     return dx
 
 
-def philox_(x: torch.Tensor, seed: int, offset: int, *, normal: bool, a: float, b: float) -> torch.Tensor:
-    """Fills x with U[a,b) or N(a, b^2) from Philox4x32-10 (4 values per counter)."""
+def philox_(x: torch.Tensor, seed: int, offset: int, *, normal: bool, a: float, b: float,
+            state: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fills x with U[a,b) or N(a, b^2) from Philox4x32-10 (4 values per counter).  `state`: device int64[2] {seed, base
+    offset}; when given the seed is read from it and `offset` counts from its base (replay-safe inside a captured step)."""
     if not x.is_cuda:
         g = torch.Generator().manual_seed((seed * 1000003 + offset) & 0x7FFFFFFFFFFFFFFF)
         if normal:
@@ -513,12 +515,17 @@ def philox_(x: torch.Tensor, seed: int, offset: int, *, normal: bool, a: float, 
         else:
             x.copy_(torch.rand(x.shape, generator=g) * (b - a) + a)
         return x
-    _launch(N.require().oa_philox(dt(x), x.data_ptr(), x.numel(), seed, offset, int(normal), float(a), float(b), N.stream()),
-            "oa_philox")
+    _launch(N.require().oa_philox(dt(x), x.data_ptr(), x.numel(), seed, offset, int(normal), float(a), float(b), N.ptr(state),
+                                  N.stream()), "oa_philox")
     return x
 
 
-def dropout(x: torch.Tensor, p: float, seed: int, offset: int) -> torch.Tensor:
+def philox_state_advance(state: torch.Tensor, delta: int) -> None:
+    """state[1] += delta on the device (one thread): the last launch of a captured step that drew random numbers."""
+    _launch(N.require().oa_philox_state_advance(state.data_ptr(), int(delta), N.stream()), "oa_philox_state_advance")
+
+
+def dropout(x: torch.Tensor, p: float, seed: int, offset: int, state: Optional[torch.Tensor] = None) -> torch.Tensor:
     out = torch.empty_like(x)
     if not x.is_cuda:
         g = torch.Generator().manual_seed((seed * 1000003 + offset) & 0x7FFFFFFFFFFFFFFF)
@@ -526,7 +533,7 @@ def dropout(x: torch.Tensor, p: float, seed: int, offset: int) -> torch.Tensor:
         out.copy_(x.float() * keep)
         return out
     _launch(N.require().oa_dropout(dt(x), x.contiguous().data_ptr(), out.data_ptr(), x.numel(), float(p), seed, offset,
-                                   N.stream()), "oa_dropout")
+                                   N.ptr(state), N.stream()), "oa_dropout")
     return out
 
 

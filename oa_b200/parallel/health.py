@@ -111,6 +111,7 @@ class OaRankMonitor:
             silent = (now - s.Stamp) if s.Seen else (now - self._start)
             if s.State == FAILED or silent > self.TimeoutS:
                 bad.append(s.Rank)
+        self.LastBad = bad                       # the ranks this pass found gone (Guard reports exactly these)
         if bad:
             return OaStatus(OaStatusCode.Unavailable, f"rank(s) {bad} failed or stopped responding (timeout {self.TimeoutS:.1f} s)")
         return OaStatus.Ok()
@@ -120,8 +121,7 @@ class OaRankMonitor:
         self.Beat(step)
         st = self.Check()
         if not st.IsOk():
-            silent = [s.Rank for s in self.Peers() if s.Rank != self.Rank and s.State != LEFT and (s.State == FAILED or s.Age(self._clock()) > self.TimeoutS)]
-            raise OaRankFailure(silent, st.message)
+            raise OaRankFailure(list(self.LastBad), st.message)     # one pass over the store: list and message agree
 
     def SlowestPeer(self) -> Optional[OaRankState]:
         alive = [s for s in self.Peers() if s.Seen and s.State == ALIVE]
@@ -153,9 +153,20 @@ class OaFaultInjector:
     @staticmethod
     def FromEnv(name: str = "OA_FAULT") -> "OaFaultInjector":
         out = []
-        for item in filter(None, os.environ.get(name, "").split(",")):
+        kinds = (OaFaultKind.Raise, OaFaultKind.Exit, OaFaultKind.Silence, OaFaultKind.Delay)
+        for item in filter(None, (x.strip() for x in os.environ.get(name, "").split(","))):
             p = item.split(":")
-            out.append(OaFault(int(p[0]), int(p[1]), p[2] if len(p) > 2 else OaFaultKind.Raise, float(p[3]) if len(p) > 3 else 0.0))
+            try:
+                if not 2 <= len(p) <= 4:
+                    raise ValueError("expected rank:step[:kind[:seconds]]")
+                fault = OaFault(int(p[0]), int(p[1]), p[2] if len(p) > 2 else OaFaultKind.Raise, float(p[3]) if len(p) > 3 else 0.0)
+                if fault.Kind not in kinds:
+                    raise ValueError(f"unknown kind {fault.Kind!r} (one of {', '.join(kinds)})")
+                if fault.Rank < 0 or fault.Seconds < 0:
+                    raise ValueError("rank and seconds must not be negative")
+            except ValueError as e:
+                raise ValueError(f"{name}: bad item {item!r}: {e}") from None
+            out.append(fault)
         return OaFaultInjector(out)
 
     def AtStep(self, rank: int, step: int, monitor: Optional[OaRankMonitor] = None) -> None:

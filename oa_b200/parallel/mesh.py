@@ -134,9 +134,22 @@ class OaDeviceMesh:
         return self.world
 
     def LinkType(self, a: int, b: int) -> OaInterconnect:
+        """What the driver says about the link between the devices of ranks a and b (one node: rank r runs on device r of
+        the visible set): peer access with native atomics is NVLink / NVSwitch, peer access without them is PCIe, no peer
+        access means staging through the host."""
         if self.device.type != "cuda":
             return OaInterconnect.Host
-        return OaInterconnect.NvLink if a != b else OaInterconnect.Unknown
+        if a == b:
+            return OaInterconnect.Unknown
+        n = torch.cuda.device_count()
+        if a >= n or b >= n:
+            return OaInterconnect.Unknown         # the other rank's device is not visible from this process
+        out = (ctypes.c_int * 3)()
+        if N.require().oa_p2p_attributes(int(a), int(b), out) != 0:
+            return OaInterconnect.Unknown
+        if not out[0]:
+            return OaInterconnect.Host
+        return OaInterconnect.NvLink if out[1] else OaInterconnect.PciE
 
     def CanAccessPeers(self) -> bool:
         if self.device.type != "cuda":

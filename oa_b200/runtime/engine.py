@@ -169,11 +169,52 @@ class OaContext:
     def Add(self, kernel: str, reads=(), writes=()) -> None:
         """Notes one recorded kernel node. Buffers are identified by their storage address."""
         self._interval_nodes += 1
-        if self._recording:
-            self._nodes.append((kernel, tuple(_buf_id(t) for t in reads), tuple(_buf_id(t) for t in writes)))
+        collecting = getattr(self, "_collect", None) is not None
+        if self._recording or collecting:
+            node = (kernel, tuple(_buf_id(t) for t in reads), tuple(_buf_id(t) for t in writes))
+            if self._recording:
+                self._nodes.append(node)
+            if collecting:
+                self._collect.append(node)
 
     def SetRecording(self, on: bool) -> None:
         self._recording = bool(on)
+
+    # -- collection of one step for a training program (validate stage) ---------
+    def BeginCollect(self) -> None:
+        """Starts collecting the nodes of one recorded step (whatever the recording flag says) together with the marks
+        of ops that cannot be replayed."""
+        self._collect = []
+        self._unsafe: list = []
+
+    def EndCollect(self):
+        """Returns (nodes, unsafe marks) of the step collected since BeginCollect."""
+        nodes, unsafe = getattr(self, "_collect", None) or [], getattr(self, "_unsafe", [])
+        self._collect = None
+        return nodes, unsafe
+
+    def IsCollecting(self) -> bool:
+        return getattr(self, "_collect", None) is not None
+
+    def MarkReplayUnsafe(self, reason: str) -> None:
+        """An op calls this when it freezes a host-side value into its launch (a learning rate passed by value, a random
+        offset, a host-computed count): a captured program that contains it would replay stale values, so capture is
+        refused (Source/Private/Oa/Ml/TrainingProgram.cpp:167-252 rejects the same classes of node)."""
+        if getattr(self, "_collect", None) is not None:
+            self._unsafe.append(str(reason))
+
+    @staticmethod
+    def Compile(nodes):
+        """Builds the native compute graph of a node list: hazards, dependency levels, alias groups, structural hash.
+        Returns (OaComputeGraph, structure hash): the structure hash covers the kernel sequence only (buffer addresses
+        differ between an eager step and a captured one), the graph's own hash covers buffers too."""
+        from ..io.oam import OamHash
+        from .graph import OaAccess, OaComputeGraph
+        g = OaComputeGraph()
+        for kernel, reads, writes in nodes:
+            bufs = [(b, 0, OaAccess.Read) for b in reads] + [(b, 0, OaAccess.Write) for b in writes]
+            g.AddNode(kernel, bufs)
+        return g, OamHash("\n".join(n[0] for n in nodes).encode())
 
     def RecordFailure(self, status: OaStatus) -> None:
         """Sticky recording failure: surfaces at the next Execute and clears the interval (rollback)."""
@@ -194,6 +235,10 @@ class OaContext:
         self._stats.LastExecuteNodes = self._interval_nodes
         if self._recording:
             self._last_graph = self._nodes
+            # the interval as the native compute graph sees it: hazards, dependency levels, structural hash
+            graph, structure = OaContext.Compile(self._nodes)
+            self._last_compiled = {"nodes": len(self._nodes), "levels": graph.NumLevels(), "barriers": graph.NumBarriers(),
+                                   "hash": graph.Hash(), "structure_hash": structure}
         self._nodes = []
         self._interval_nodes = 0
         return OaStatus.Ok()
@@ -251,6 +296,10 @@ class OaContext:
 
     def LastGraph(self) -> list:
         return list(self._last_graph)
+
+    def LastCompiled(self) -> dict:
+        """Report of the native compute graph of the last executed interval (recording must be on)."""
+        return dict(getattr(self, "_last_compiled", {}))
 
     def MaxAsyncSubmissions(self) -> int:
         return 1

@@ -31,3 +31,11 @@ def test_tensor_parallel_kernels_and_model():
 
 def test_tensor_parallel_decoding():
     assert "TP_DECODE_CHECK_OK" in _run("tp_decode_check.py")
+
+
+def test_collective_verbs_match_nccl():
+    assert "COLLECTIVE_CHECK_OK" in _run("collective_check.py")
+
+
+def test_data_parallel_fused_step_clipping_and_checkpoint():
+    assert "DP_CHECK_OK" in _run("dp_check.py", timeout=400)

@@ -42,6 +42,17 @@ def test_monitor_on_a_manual_clock():
     late = OaRankMonitor(DictStore(), 0, 2, timeout_s=1.0, clock=clock)
     now[0] += 2
     assert late.Check().code == OaStatusCode.Unavailable      # a peer that never showed up within the timeout
+    with pytest.raises(OaRankFailure) as e:                   # Guard names exactly the ranks Check found, also a never-seen one
+        late.Guard(0)
+    assert e.value.Ranks == [1] and "[1]" in str(e.value)
+
+
+@pytest.mark.parametrize("bad", ["1", "a:2", "1:2:explode", "1:2:delay:-1", "1:2:raise:0:9"])
+def test_fault_injector_rejects_malformed_items(monkeypatch, bad):
+    monkeypatch.setenv("OA_FAULT", "0:1:raise," + bad)
+    with pytest.raises(ValueError) as e:
+        OaFaultInjector.FromEnv()
+    assert "OA_FAULT" in str(e.value) and bad in str(e.value)
 
 
 def test_fault_injector_schedule(monkeypatch):

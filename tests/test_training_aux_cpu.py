@@ -169,3 +169,42 @@ def test_training_session_commands_apply_at_step_boundaries():
 def OaStatus_ok():
     from oa_b200.core.types import OaStatus
     return OaStatus.Ok()
+
+
+def test_context_collects_nodes_and_compiles_them():
+    """The nodes of a recorded step go through the native compute graph: the structure hash follows the kernel sequence,
+    replay-unsafe marks are collected only while a step is being collected, and a recording context compiles every
+    executed interval."""
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.runtime import engine as RT
+    ctx = RT.OaContext.GetDefault()
+    ctx.MarkReplayUnsafe("ignored outside a collection")
+    ctx.BeginCollect()
+    a = F.Ones([4, 4])
+    b = F.Add(F.Scale(a, 2.0), a)
+    ctx.MarkReplayUnsafe("host scalar")
+    nodes, unsafe = ctx.EndCollect()
+    assert unsafe == ["host scalar"] and len(nodes) >= 2
+    g1, h1 = RT.OaContext.Compile(nodes)
+    g2, h2 = RT.OaContext.Compile(nodes)
+    g3, h3 = RT.OaContext.Compile(nodes + [("Extra", (), ())])
+    assert h1 == h2 != h3 and g1.NumNodes() == len(nodes) and g3.NumNodes() == len(nodes) + 1
+    assert not ctx.IsCollecting()
+    ctx.SetRecording(True)
+    try:
+        ctx.Execute()
+        F.Add(b, a)
+        assert ctx.Execute()
+        rep = ctx.LastCompiled()
+        assert rep["nodes"] >= 1 and rep["levels"] >= 1 and rep["structure_hash"] != 0
+    finally:
+        ctx.SetRecording(False)
+
+
+def test_program_rng_bookkeeping_on_cpu():
+    """Without CUDA there is no device state: BeginProgramRng answers None and the host offset is untouched."""
+    from oa_b200.core import fn_matrix as F
+    F.SetRngSeed(5)
+    assert F.BeginProgramRng() is None
+    F.AdvanceHostRng(12)
+    assert F._rng["offset"] == 12
