@@ -30,6 +30,19 @@ def NextSeq() -> int:
     return n
 
 
+# A data-parallel wrapper overlaps its gradient reduction with the rest of the backward pass: it registers a hook that is
+# called (a) when a backward pass starts and (b) each time a leaf has received its LAST gradient contribution of the pass.
+_leaf_ready_hook = None
+_backward_begin_hook = None
+
+
+def SetLeafReadyHooks(on_begin, on_leaf_ready) -> None:
+    """on_begin() at the start of every Backward; on_leaf_ready(matrix) when no node of the pass still writes to the leaf's
+    gradient.  Pass (None, None) to remove them."""
+    global _leaf_ready_hook, _backward_begin_hook
+    _backward_begin_hook, _leaf_ready_hook = on_begin, on_leaf_ready
+
+
 class OaGradNode:
     """One recorded differentiable operation.
 
@@ -108,6 +121,20 @@ class OaGradientTape:
                 if child is not None and id(child) not in seen:
                     stack.append(child)
         topo.sort(key=lambda n: n.seq)
+        hook = _leaf_ready_hook
+        pending = None
+        if hook is not None:
+            if _backward_begin_hook is not None:
+                _backward_begin_hook()
+            pending = {}
+            for fn in topo:
+                for inp in fn.inputs:
+                    if inp is not None and inp.IsLeaf() and inp.RequiresGrad():
+                        e = pending.get(id(inp))
+                        if e is None:
+                            pending[id(inp)] = [1, inp]
+                        else:
+                            e[0] += 1
         if grad is None:
             grad = torch.ones_like(root.Tensor())
             grad._oa_root_seed = True   # lets scalar losses skip the multiply by 1 without reading the device
@@ -116,6 +143,8 @@ class OaGradientTape:
             for fn in reversed(topo):
                 up = grad_map.pop(id(fn), None)
                 if up is None:
+                    if pending is not None:
+                        _count_down(fn, pending, hook)
                     continue
                 if tuple(up.shape) != fn.out_shape and up.numel() == _numel(fn.out_shape):
                     up = up.reshape(fn.out_shape)
@@ -138,7 +167,23 @@ class OaGradientTape:
                         if tuple(d.shape) != tuple(prev.shape):
                             d = d.reshape(prev.shape)
                         grad_map[id(child)] = K.binary("add", prev, d if d.dtype == prev.dtype else d.to(prev.dtype))
+                if pending is not None:
+                    _count_down(fn, pending, hook)
                 fn.ClearTensors()
+
+
+def _count_down(fn, pending, hook) -> None:
+    """`fn` has run (or was skipped): every leaf it feeds has one contribution less to wait for."""
+    for inp in fn.inputs:
+        if inp is None:
+            continue
+        e = pending.get(id(inp))
+        if e is None:
+            continue
+        e[0] -= 1
+        if e[0] == 0:
+            del pending[id(inp)]
+            hook(e[1])
 
 
 def _numel(shape) -> int:

@@ -34,13 +34,13 @@ def main() -> int:
     gen = torch.Generator().manual_seed(500 + rank)                 # every rank its own data
     data = [torch.randint(0, cfg.Vocab, (B, S + 1), generator=gen, dtype=torch.int32).to(dev) for _ in range(8)]
 
-    def build(mode, clip):
+    def build(mode, clip, overlap=False):
         F.SetRngSeed(99)
         model = OaGptModel(cfg)
         opt = OaAdamW(model.AllParameterPtrs(), 1e-3, weight_decay=0.1)
         if clip:
             opt.SetClipGradNorm(0.05)
-        dp = OaDataParallel(model, opt, mode=mode)
+        dp = OaDataParallel(model, opt, mode=mode, overlap=overlap, buckets=4)
         return model, opt, dp
 
     def step(model, opt, k):
@@ -58,14 +58,15 @@ def main() -> int:
 
     for clip in (False, True):
         results = {}
-        for mode in ("fused", "nccl"):
-            model, opt, dp = build(mode, clip)
+        for mode in ("fused", "overlap", "nccl"):
+            model, opt, dp = build("fused" if mode == "overlap" else mode, clip, overlap=mode == "overlap")
             losses = [step(model, opt, k) for k in range(5)]
             torch.cuda.synchronize()
             K.check_status()
             results[mode] = (weights(model), losses)
             if mode == "fused" and not clip:
                 keep = (model, opt, dp)
+        assert torch.equal(results["fused"][0], results["overlap"][0]), "buckets reduced under the backward pass must give the same bits"
         wf, wn = results["fused"][0], results["nccl"][0]
         err = (wf - wn).abs().max().item()
         assert err <= 2e-2 * wn.abs().max().item(), f"rank {rank} clip={clip}: fused vs nccl parameters differ by {err}"
