@@ -341,6 +341,8 @@ class TorchMamba3Config:
     seq_len: int = 4096
     chunk: int = 128
     eps: float = 1e-5
+    conv_width: int = 4
+    a_log: bool = True
 
 
 def _softplus_inv(y):
@@ -367,16 +369,26 @@ class Mamba3Mixer(nn.Module):
         self.C_bias = nn.Parameter(torch.ones(self.heads, c.d_state))
         self.D = nn.Parameter(torch.ones(self.heads))
         self.norm_weight = nn.Parameter(torch.ones(self.d_inner))
+        cw = self.d_inner + 2 * c.d_state
+        self.conv = nn.Conv1d(cw, cw, c.conv_width, groups=cw, padding=c.conv_width - 1, bias=False) if c.conv_width else None
+        self.A_log = nn.Parameter(torch.log(1.0 + 15.0 * torch.rand(self.heads))) if c.a_log else None
 
     def forward(self, u, batch, seq):
         c, H, P, N, A, Q = self.c, self.heads, self.c.headdim, self.c.d_state, self.angles, self.c.chunk
         proj = self.in_proj(u).view(batch, seq, self.d_in_proj)
         z, x, Bn, Cn, dd_dt, dd_a, trap, ang = proj.split([self.d_inner, self.d_inner, N, N, H, H, H, A], -1)
+        if self.conv is not None:
+            xbc = torch.cat((x, Bn, Cn), -1).transpose(1, 2)
+            xbc = F.silu(self.conv(xbc)[..., :seq]).transpose(1, 2)
+            x, Bn, Cn = xbc.split([self.d_inner, N, N], -1)
         f32 = torch.float32
         dt = F.softplus(dd_dt.to(f32) + self.dt_bias.to(f32)).clamp(1e-3, 0.1)
-        da = dd_a.to(f32)
-        heavy = torch.where(da >= 0, 1.0 + da, 1.0 / (1.0 - da.clamp(max=0.0)))
-        adt = torch.minimum(-heavy, torch.full_like(heavy, -1e-4)) * dt
+        if self.A_log is not None:
+            adt = -torch.exp(self.A_log.to(f32)) * dt
+        else:
+            da = dd_a.to(f32)
+            heavy = torch.where(da >= 0, 1.0 + da, 1.0 / (1.0 - da.clamp(max=0.0)))
+            adt = torch.minimum(-heavy, torch.full_like(heavy, -1e-4)) * dt
         Bn = F.rms_norm(Bn.to(f32), (N,), eps=c.eps)
         Cn = F.rms_norm(Cn.to(f32), (N,), eps=c.eps)
         tr = torch.sigmoid(trap.to(f32))
@@ -394,7 +406,7 @@ class Mamba3Mixer(nn.Module):
         Bt = rot(Bn[:, :, None, :] + self.B_bias.to(f32))
         nC = seq // Q
         ch = lambda t: t.reshape(batch, nC, Q, H, *t.shape[3:]).transpose(2, 3)      # [B, nC, H, Q, ...]
-        xh = x.view(batch, seq, H, P)
+        xh = x.reshape(batch, seq, H, P)
         cum = torch.cumsum(ch(adt), -1)                             # [B, nC, H, Q]
         Cc, Bc, Xc = ch(Ct).to(u.dtype), ch(Bt).to(u.dtype), ch(xh)
         G = torch.matmul(Cc, Bc.transpose(-1, -2)).float()           # [B, nC, H, Q, Q]

@@ -43,7 +43,7 @@ NAMES = {
     1: "char-level Transformer LM, FP32: vocab 256, d 128, 4 layers, 4 heads, FFN 512 GELU, pre-LayerNorm, learned positions",
     2: "dense GPT 24x1024, 16 heads, FFN 4096 GELU, RMSNorm, RoPE, vocab 32000",
     3: "sparse MoE 16x2048, 64 experts top-2, SwiGLU 1408, 1 shared expert, vocab 32000",
-    4: "Mamba-3 32x1536, state 128, expand 2, head dim 64, scan chunk 128, vocab 32000",
+    4: "Mamba-3 32x1536, state 128, expand 2, head dim 64, conv width 4, learned A_log, scan chunk 128, vocab 32000",
     5: "7B-class Transformer 32x4096, 32 heads, SwiGLU 11008, RMSNorm, RoPE, vocab 32000",
 }
 MICRO_BATCH = {1: 16, 2: 8, 3: 4, 4: 4, 5: 1}

@@ -314,6 +314,21 @@ int oa_ssd_theta_bwd(const void* dtheta, const void* angle, int lda, const void*
                      int H, int A, void* stream);
 int oa_ssd_dx_out(const void* dX, const void* dXw, const void* X, const void* w, void* dx, long long lddx, void* dw, int B, int L, int H,
                   int P, void* stream);
+// Benchmark-variant options of the Mamba-3 block (mamba3_conv.cu): causal depthwise convolution (width Kw <= 8) + SiLU over
+// columns [col0, col0 + C) of x [B*L, ld], in place (`saved` [B*L, C] receives the inputs); its backward overwrites the same
+// columns of dy with dx and writes weight-gradient partials float[B * ceil(L/64)][Kw][C]; and the learned-decay fill
+// x[row, col0 + h] = exp(a_log[h]) - 1.
+int oa_mamba3_conv_fwd(int dtype, void* x, long long ld, int col0, void* saved, const float* w, int B, int L, int C, int Kw,
+                       void* stream);
+int oa_mamba3_conv_bwd(int dtype, void* dy, long long ld, int col0, const void* saved, const float* w, float* dw_part, void* gbuf,
+                       int B, int L, int C, int Kw, void* stream);
+int oa_mamba3_alog_fill(int dtype, void* x, long long ld, int col0, const float* a_log, long long rows, int H, void* stream);
+// Scalar tail of the chunked-scan backward (three small kernels): [G, Q] inputs -> dadt, ddt, dtrap [B*L, H] and dD [H] (may
+// be null); ddt_theta may be null; scratch: float[2 * B*L*H + B*H*L/128].
+int oa_ssd_tail(const void* dw, const void* w, const void* col_ge, const void* row_mm, const void* col_mm, const void* dcum_ce,
+                const void* diag, const void* qk, const void* cum, const void* dcumQ, const void* dt, const void* trap,
+                const void* ddt_theta, void* dadt, void* ddt, void* dtrap, void* dD, void* scratch, int B, int L, int H,
+                void* stream);
 
 // ---- audio DSP (audio.cu)
 int oa_audio_stft_frame(const void* x, void* frames, int channels, long long samples, int n_frames, int fft, int hop, int win, int kind,

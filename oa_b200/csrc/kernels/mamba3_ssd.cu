@@ -489,6 +489,78 @@ __global__ void __launch_bounds__(256) ssd_theta_bwd_kernel(const float* __restr
   }
 }
 
+// ---- the per-token scalar tail of the backward pass, three small kernels over [G, Q] / [B, L, H] sized tensors.
+// (1) per chunk: gradient of the decay prefix sums (a suffix sum inside the chunk), of gamma and of scale, written in token
+//     order [B, L, H]; (2) per token: dt and trap gradients (scale_l looks one token ahead, so token l also receives from
+//     token l - 1); (3) per head: the skip gradient, summed over batch and chunks in a fixed order.
+__global__ void __launch_bounds__(SQ)
+ssd_tail_chunk_kernel(const float* __restrict__ dw, const float* __restrict__ w, const float* __restrict__ col_ge,
+                      const float* __restrict__ row_mm, const float* __restrict__ col_mm, const float* __restrict__ dcum_ce,
+                      const float* __restrict__ diag, const float* __restrict__ qk, const float* __restrict__ cum,
+                      const float* __restrict__ dcumQ, float* __restrict__ dadt, float* __restrict__ dgam, float* __restrict__ dscale_l,
+                      float* __restrict__ dpart, int B, int L, int H, int nC) {
+  __shared__ float sm[SQ];
+  __shared__ float s_tot[2];
+  const int g = blockIdx.x, q = threadIdx.x;
+  const long long i = (long long)g * SQ + q;
+  const float cq = cum[i], cQ = cum[(long long)g * SQ + SQ - 1];
+  const float dww = dw[i] * w[i];
+  const float dsc = col_ge[i] + dw[i] * __expf(cQ - cq);
+  float dc = row_mm[i] - col_mm[i] + dcum_ce[i] - dww;
+  const float dg = diag[i];
+  // block sums of dww and of diag (fixed tree order)
+  float a = warp_sum(dww), b = warp_sum(dg);
+  if ((q & 31) == 0) { sm[q >> 5] = a; sm[4 + (q >> 5)] = b; }
+  __syncthreads();
+  if (q == 0) { s_tot[0] = (sm[0] + sm[1]) + (sm[2] + sm[3]); s_tot[1] = (sm[4] + sm[5]) + (sm[6] + sm[7]); }
+  __syncthreads();
+  if (q == SQ - 1) dc += dcumQ[g] + s_tot[0];
+  // inclusive suffix sum over the chunk: cum is an inclusive prefix sum of a * dt
+  __syncthreads();
+  sm[q] = dc;
+  __syncthreads();
+  for (int off = 1; off < SQ; off <<= 1) {
+    const float add = (q + off < SQ) ? sm[q + off] : 0.f;
+    __syncthreads();
+    sm[q] += add;
+    __syncthreads();
+  }
+  const int c = g % nC, h = (g / nC) % H, bb = g / (nC * H);
+  const long long o = ((long long)bb * L + c * SQ + q) * H + h;
+  dadt[o] = sm[q];
+  dgam[o] = dg * qk[i] + dsc;
+  dscale_l[o] = dsc;
+  if (q == 0 && dpart) dpart[g] = s_tot[1];
+}
+
+__global__ void ssd_tail_token_kernel(const float* __restrict__ dgam, const float* __restrict__ dscale_l, const float* __restrict__ dt,
+                                      const float* __restrict__ trap, const float* __restrict__ ddt_theta, float* __restrict__ ddt,
+                                      float* __restrict__ dtrap, int B, int L, int H) {
+  const long long total = (long long)B * L * H;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int l = (int)((i / H) % L);
+    const float tr = sigmoid_f(trap[i]), dti = dt[i];
+    float a = (ddt_theta ? ddt_theta[i] : 0.f) + dgam[i] * tr;
+    float t = dgam[i] * dti;
+    if (l > 0) {
+      const float prev = dscale_l[i - H];
+      a += prev * (1.f - tr);
+      t -= prev * dti;
+    }
+    ddt[i] = a;
+    dtrap[i] = t * tr * (1.f - tr);
+  }
+}
+
+__global__ void ssd_tail_skip_kernel(const float* __restrict__ dpart, float* __restrict__ dD, int B, int H, int nC) {
+  const int h = blockIdx.x;
+  float s = 0.f;
+  for (int k = threadIdx.x; k < B * nC; k += 32) s += dpart[((long long)(k / nC) * H + h) * nC + (k % nC)];
+  s = warp_sum(s);
+  if (threadIdx.x == 0) dD[h] = s;
+}
+
 inline bool ssd_dims_ok(const SsdDims& d) {
   return d.B > 0 && d.L > 0 && d.H > 0 && d.P > 0 && d.N > 0 && d.A >= 0 && d.L % SQ == 0 && d.nC == d.L / SQ && d.N % 4 == 0 && d.P % 2 == 0 &&
          2 * d.A <= d.N;
@@ -607,6 +679,32 @@ int oa_ssd_theta_bwd(const void* dtheta, const void* angle, int lda, const void*
                                                               (float*)tot, (float*)dangle, (float*)ddt, d, 0);
   ssd_theta_bwd_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)dtheta, (const float*)angle, lda, (const float*)dt,
                                                               (float*)tot, (float*)dangle, (float*)ddt, d, 1);
+  return ssd_status();
+}
+
+// Scalar tail of the chunked-scan backward: [G, Q] inputs (G = B*H*nC chunks of 128 tokens) -> dadt, dt and trap gradients
+// [B*L, H] and the skip gradient dD [H] (null: skipped); ddt_theta [B*L, H] (may be null) is the dt gradient that came through
+// the rotary phases; scratch: float[2 * B*L*H + G].
+int oa_ssd_tail(const void* dw, const void* w, const void* col_ge, const void* row_mm, const void* col_mm, const void* dcum_ce,
+                const void* diag, const void* qk, const void* cum, const void* dcumQ, const void* dt, const void* trap,
+                const void* ddt_theta, void* dadt, void* ddt, void* dtrap, void* dD, void* scratch, int B, int L, int H,
+                void* stream) {
+  if (B <= 0 || L <= 0 || H <= 0 || L % SQ) return OA_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int nC = L / SQ, G = B * H * nC;
+  const long long n = (long long)B * L * H;
+  float* dgam = (float*)scratch;
+  float* dscale_l = dgam + n;
+  float* dpart = dscale_l + n;
+  ssd_tail_chunk_kernel<<<G, SQ, 0, st>>>((const float*)dw, (const float*)w, (const float*)col_ge, (const float*)row_mm,
+                                         (const float*)col_mm, (const float*)dcum_ce, (const float*)diag, (const float*)qk,
+                                         (const float*)cum, (const float*)dcumQ, (float*)dadt, dgam, dscale_l, dD ? dpart : nullptr,
+                                         B, L, H, nC);
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  ssd_tail_token_kernel<<<(int)blocks, 256, 0, st>>>(dgam, dscale_l, (const float*)dt, (const float*)trap, (const float*)ddt_theta,
+                                                    (float*)ddt, (float*)dtrap, B, L, H);
+  if (dD) ssd_tail_skip_kernel<<<H, 32, 0, st>>>(dpart, (float*)dD, B, H, nC);
   return ssd_status();
 }
 

@@ -32,11 +32,14 @@ class OaMamba3Config:
     OutprojNorm: bool = True
     Eps: float = 1e-5
     InitStd: Optional[float] = 0.02
+    ConvWidth: int = 0            # > 0: causal depthwise convolution + SiLU over x | B | C before the scan
+    ALog: bool = False            # learned per-head decay A = -exp(A_log), A_log ~ log U(1, 16), instead of the data-dependent one
 
     @staticmethod
     def Mamba3_32x1536() -> "OaMamba3Config":
-        """vocab 32000, d 1536, 32 layers, state 128, expand 2, head dim 64, chunk 256, seq 4096."""
-        return OaMamba3Config()
+        """vocab 32000, d 1536, 32 layers, state 128, expand 2, head dim 64, conv width 4, A_log ~ log U(1, 16),
+        dt log-uniform in [1e-3, 1e-1], seq 4096."""
+        return OaMamba3Config(ConvWidth=4, ALog=True)
 
     @staticmethod
     def Tiny() -> "OaMamba3Config":
@@ -48,7 +51,8 @@ class OaMamba3Block(OaModule):
         super().__init__()
         self.Norm = self.RegisterModule("norm", OaRmsNorm(cfg.DModel, cfg.Eps))
         self.Mixer = self.RegisterModule("mixer", OaMamba3Module(cfg.DModel, cfg.DState, cfg.Expand, cfg.HeadDim,
-                                                                 is_outproj_norm=cfg.OutprojNorm, chunk=cfg.Chunk))
+                                                                 is_outproj_norm=cfg.OutprojNorm, chunk=cfg.Chunk,
+                                                                 conv_width=cfg.ConvWidth, a_log=cfg.ALog))
 
     def Forward(self, x: OaMatrix) -> OaMatrix:
         return F.Add(x, self.Mixer.Forward(self.Norm.Forward(x)))

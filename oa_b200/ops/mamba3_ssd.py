@@ -335,7 +335,7 @@ def ssd_bwd_cuda(s: SsdSavedCuda, proj: torch.Tensor, dy: torch.Tensor, dproj: t
     del dM, Gm
     dCt = K.bgemm(dG, s.Bt, b_mn=True, out_dtype=torch.float32)
     K.bgemm(dG, s.Ct, a_mn=True, b_mn=True, out=dBt, accumulate=True)
-    dqk = diag * s.gamma
+    dqk = K.binary("mul", diag, s.gamma)
     dCn, dBn, dCb, dBb = f32(rows, Nn), f32(rows, Nn), z32(H, Nn), z32(H, Nn)
     dtheta = f32(B, L, H, A) if A else None
     dcum_ce = f32(G, Q)
@@ -346,32 +346,23 @@ def ssd_bwd_cuda(s: SsdSavedCuda, proj: torch.Tensor, dy: torch.Tensor, dproj: t
     dw = f32(G, Q)
     K._launch(lib.oa_ssd_dx_out(dX.data_ptr(), dXw.data_ptr(), s.X.data_ptr(), s.w.data_ptr(), dproj.data_ptr() + o[1] * es, d.d_in_proj,
                                 dw.data_ptr(), B, L, H, P, st), "oa_ssd_dx_out")
-    # ---- per-token scalar tail ([G, Q] / [B, L, H] sized tensors)
-    cumQ = s.cum[:, -1:]
-    dww = dw * s.w
-    dscale = col_ge + dw * torch.exp(cumQ - s.cum)
-    dcum = row_mm - col_mm + dcum_ce - dww
-    dcum[:, -1:] += dcumQ[:, None] + dww.sum(1, keepdim=True)
-    dadt = _unchunk_small(torch.flip(torch.cumsum(torch.flip(dcum, [1]), 1), [1]), B, L, H)
-    dgamma_l, dscale_l = _unchunk_small(diag * s.qk, B, L, H), _unchunk_small(dscale, B, L, H)
-    out = {"Bn": dBn, "Cn": dCn, "Bb": dBb, "Cb": dCb, "adt": dadt.reshape(rows, H).contiguous()}
-    out["D"] = diag.reshape(B, H, nC * Q).sum((0, 2)) if s.Dh is not None else None
-    dt3, trap3 = s.dt.reshape(B, L, H), s.trap.reshape(B, L, H)
-    tr = torch.sigmoid(trap3)
+    # ---- per-token scalar tail ([G, Q] / [B, L, H] sized tensors): three small kernels
+    out = {"Bn": dBn, "Cn": dCn, "Bb": dBb, "Cb": dCb}
+    ddt_theta = None
     if A:
         lda = s.angle.shape[-1]
-        dangle, ddt, tot = z32(rows, lda), f32(B, L, H), f32(B, nC, H, A)
+        dangle, ddt_theta, tot = z32(rows, lda), f32(B, L, H), f32(B, nC, H, A)
         K._launch(lib.oa_ssd_theta_bwd(dtheta.data_ptr(), s.angle.data_ptr(), lda, s.dt.data_ptr(), tot.data_ptr(), dangle.data_ptr(),
-                                       ddt.data_ptr(), B, L, H, A, st), "oa_ssd_theta_bwd", 2)
+                                       ddt_theta.data_ptr(), B, L, H, A, st), "oa_ssd_theta_bwd", 2)
         out["angle"] = dangle
     else:
-        ddt = torch.zeros_like(dt3)
-        out["angle"] = torch.zeros(rows, 1, dtype=torch.float32, device=dev)
-    dgam = dgamma_l + dscale_l
-    ddt = ddt + dgam * tr
-    dtr = dgam * dt3
-    ddt[:, 1:] += dscale_l[:, :-1] * (1 - tr[:, 1:])
-    dtr[:, 1:] -= dscale_l[:, :-1] * dt3[:, 1:]
-    out["dt"] = ddt.reshape(rows, H).contiguous()
-    out["trap"] = (dtr * tr * (1 - tr)).reshape(rows, H).contiguous()
+        out["angle"] = z32(rows, 1)
+    dadt, ddt, dtrap = f32(rows, H), f32(rows, H), f32(rows, H)
+    dD = f32(H) if s.Dh is not None else None
+    scratch = K.scratch(dev, (2 * rows * H + G) * 4, "ssd_tail")
+    K._launch(lib.oa_ssd_tail(dw.data_ptr(), s.w.data_ptr(), col_ge.data_ptr(), row_mm.data_ptr(), col_mm.data_ptr(), dcum_ce.data_ptr(),
+                              diag.data_ptr(), s.qk.data_ptr(), s.cum.data_ptr(), dcumQ.data_ptr(), s.dt.data_ptr(), s.trap.data_ptr(),
+                              N.ptr(ddt_theta), dadt.data_ptr(), ddt.data_ptr(), dtrap.data_ptr(), N.ptr(dD), scratch.data_ptr(), B, L, H, st),
+              "oa_ssd_tail", 3 if dD is not None else 2)
+    out["adt"], out["dt"], out["trap"], out["D"] = dadt, ddt, dtrap, dD
     return out

@@ -341,3 +341,46 @@ def test_empyrealm_core_modes_cpu():
     custom = OaEmpyrealmCore(Pose(5, 16), 16, d_state=8, headdim=8)
     assert tuple(custom.Forward(OaMatrix(torch.randn(3, 4, 5))).Tensor().shape) == (12, 16)
     custom.ResetState(3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_benchmark_variant_kernels_match_the_composed_ops(dtype):
+    """Causal depthwise convolution + SiLU and the learned-decay fill (mamba3_conv.cu) against the same options composed from
+    differentiable tensor ops on the CPU: forward values and every gradient."""
+    from oa_b200.core import fn_matrix as F
+    from oa_b200.core.matrix import OaMatrix
+    from oa_b200.core.types import OaPrecision
+    from oa_b200.ml.autograd import OaGradientTape
+    from oa_b200.ml.nn.mamba3 import OaMamba3Module
+    from oa_b200.runtime import engine as RT
+    B, L = 2, 150
+
+    def run(device):
+        cfg = RT.OaEngineConfig(Precision=OaPrecision.FP32 if dtype == torch.float32 else OaPrecision.BF16)
+        if device == "cpu":
+            cfg.DevicePreference = RT.OaDevicePreference.Cpu
+            cfg.Precision = OaPrecision.FP32
+        eng = RT.OaEngine.Create(cfg)
+        eng.SetAsGlobal()
+        F.SetRngSeed(4)
+        m = OaMamba3Module(32, d_state=16, expand=2, headdim=16, conv_width=4, a_log=True)
+        g = torch.Generator().manual_seed(9)
+        wref = {n.Name: torch.randn(n.Param.Tensor().shape, generator=g) * 0.3 for n in m.AllNamedParameterPtrs()}
+        for n in m.AllNamedParameterPtrs():
+            n.Param.Tensor().copy_(wref[n.Name].to(n.Param.Tensor().dtype))
+        x = torch.randn(B * L, m.DInProj, generator=g)
+        up = torch.randn(B * L, m.DInProj, generator=g)
+        dev = eng.Device()
+        proj = OaMatrix(x.to(device=dev, dtype=dtype if device != "cpu" else torch.float32)).SetRequiresGrad(True)
+        with OaGradientTape() as tape:
+            out = m._prepare(proj, B, L)
+            tape.Backward(out, grad=up.to(device=dev, dtype=out.Tensor().dtype))
+        return (out.Tensor().float().cpu(), proj.GradTensor().float().cpu(), m.ConvWeight.Data.GradTensor().float().cpu(),
+                m.ALog.Data.GradTensor().float().cpu())
+
+    got, ref = run("cuda"), run("cpu")
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    for a, b, what in zip(got, ref, ("forward", "dproj", "dconv_weight", "dA_log")):
+        scale = b.abs().max().item() + 1e-9
+        assert (a - b).abs().max().item() <= tol * scale, (what, (a - b).abs().max().item(), scale)
