@@ -23,6 +23,26 @@ def _close(got, ref, rtol, atol=None, what=""):
     assert math.isfinite(err) and err <= tol, f"{what}: max err {err:.4g} > tol {tol:.4g} (ref scale {scale:.4g})"
 
 
+BF16_EPS = 2.0 ** -8          # half an ulp of a bf16 result, relative
+
+
+def _close_elem(got, ref, atol, rtol, what=""):
+    """Every element on its own: |got - ref| <= atol + rtol * |ref| (a max-norm bound alone hides relative errors on
+    small entries)."""
+    got, ref = got.float().cpu(), ref.float().cpu()
+    err = (got - ref).abs()
+    bound = atol + rtol * ref.abs()
+    bad = err > bound
+    assert torch.isfinite(got).all() and not bad.any(), \
+        f"{what}: {int(bad.sum())} of {bad.numel()} elements out of tolerance, worst {float((err - bound).max()):.4g} over the bound"
+
+
+def _close_gemm_bf16(got, ref, k_total, what="", out_bf16=True):
+    """The reference's GEMM tier (Test/OaTest.h:118-127): absolute bound 2e-2 * sqrt(K / 16) for unit-variance bf16 operands
+    accumulated in fp32, plus the rounding of a bf16 result; checked per element."""
+    _close_elem(got, ref, 2.0e-2 * math.sqrt(k_total / 16.0), BF16_EPS if out_bf16 else 1e-6, what)
+
+
 @pytest.fixture(autouse=True)
 def _status():
     yield
@@ -45,6 +65,7 @@ def test_gemm_bf16_layouts(a_mn, b_mn, M, N, K_):
     out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
     ref = K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn)
     _close(out, ref, 1e-2, what=f"gemm a_mn={a_mn} b_mn={b_mn} {M}x{N}x{K_}")
+    _close_gemm_bf16(out, ref, K_, what=f"gemm (per element) a_mn={a_mn} b_mn={b_mn} {M}x{N}x{K_}")
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
@@ -61,7 +82,9 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
     out32 = torch.zeros(M, N, dtype=torch.float32, device=DEV)
     K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out32)
     K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out32, accumulate=True)
-    _close(out32, 2 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn), 1e-2, what="pair gemm fp32 accumulate")
+    ref32 = 2 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn)
+    _close(out32, ref32, 1e-2, what="pair gemm fp32 accumulate")
+    _close_gemm_bf16(out32, ref32, K_, what="pair gemm fp32 accumulate (per element)", out_bf16=False)
 
 
 @pytest.mark.parametrize("bn", [128, 256])
@@ -136,6 +159,9 @@ def test_elementwise(dtype):
     tol = 1e-5 if dtype == torch.float32 else 1e-2
     for op in ["neg", "abs", "exp", "sin", "cos", "relu", "gelu", "silu", "tanh", "sigmoid", "softplus", "mish", "square"]:
         _close(K.unary(op, x), K.unary(op, x.cpu().float()), tol, what=op)
+        # the reference's elementwise tier (Test/OaTest.h:108-110: 5e-4 absolute) plus the rounding of the stored result
+        _close_elem(K.unary(op, x), K.unary(op, x.cpu().float()), 5e-4 if dtype == torch.bfloat16 else 2e-6,
+                    BF16_EPS if dtype == torch.bfloat16 else 2e-6, what=op + " (per element)")
     xp = x.abs() + 0.5
     for op in ["log", "sqrt", "recip"]:
         _close(K.unary(op, xp), K.unary(op, xp.cpu().float()), tol, what=op)
