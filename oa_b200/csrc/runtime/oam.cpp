@@ -143,9 +143,27 @@ int write_all(int fd, const void* data, size_t n) {
   return 0;
 }
 
+// A writer never produces a file that the loader refuses: an entry whose byte count disagrees with its shape and data
+// type is caught here, not at the next load.
+bool entries_consistent(const std::vector<TensorEntry>& idx, std::string& err) {
+  for (const TensorEntry& e : idx) {
+    if (e.rank > kMaxRank) { err = std::string("tensor rank above the format's limit: ") + e.name; return false; }
+    const size_t eb = dtype_bytes(e.dtype);
+    if (!eb) continue;
+    uint64_t n = 1;
+    for (int r = 0; r < e.rank; ++r) {
+      if (e.shape[r] != 0 && n > UINT64_MAX / e.shape[r]) { err = std::string("tensor element count overflow: ") + e.name; return false; }
+      n *= e.shape[r];
+    }
+    if (n * eb != e.num_bytes) { err = std::string("tensor byte count does not match shape/dtype: ") + e.name; return false; }
+  }
+  return true;
+}
+
 int save_model(const Model& m, const char* path, std::string& err) {
   struct Payload { uint32_t type; std::vector<uint8_t> data; };
   std::vector<Payload> pl;
+  if (!entries_consistent(m.weight_index, err) || !entries_consistent(m.state_index, err)) return 4;
   {
     std::vector<uint8_t> raw(sizeof(Config) + m.arch_config.size());
     Config c = m.config;

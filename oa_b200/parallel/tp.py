@@ -42,9 +42,24 @@ class OaTpArena:
         self.buf = mesh.AllocSymmetric(nbytes)
         self.buf.tensor.zero_()
         self.used = 0
+        self._last_site = None
+        self._fence_ch = None
         torch.cuda.synchronize()
         if mesh.world > 1:
             dist.barrier(group=mesh.group)          # nobody pushes into a buffer that is still being zeroed
+
+    def enter_site(self, site) -> None:
+        """Orders two uses of one call site.  A peer may push the next use's rows into this rank's staging buffer as soon as
+        it has finished its own kernel of this use, which only proves that this rank's PUSHES arrived, not that this rank
+        has finished reading.  With another site's kernel in between the order holds by itself (that kernel completes on a
+        peer only after this rank's kernel of it started, hence after this rank's earlier kernel ended); a site that
+        runs twice in a row gets a ready/ack round over a channel first."""
+        if self._last_site is site and self.mesh.world > 1:
+            if self._fence_ch is None:
+                self._fence_ch = self.mesh.NewChannel()
+            self._fence_ch.Signal()
+            self._fence_ch.Wait()
+        self._last_site = site
 
     def take(self, nbytes: int) -> int:
         off = self.used
@@ -114,6 +129,7 @@ def ag_gemm(site: OaTpAgSite, x_shard: torch.Tensor, w: torch.Tensor, *, b_mn: b
     if x_shard.data_ptr() != own.data_ptr():
         K.unary("copy", x_shard, out=own)      # a producer that writes into site.own_rows() directly skips this copy
     x_shard = own
+    site.arena.enter_site(site)
     K._launch(N.require().oa_gemm_bf16_tp(1, stage.data_ptr(), w.data_ptr(), out.data_ptr(), site.M, Nn, site.K, site.K, w.shape[1], Nn,
                                           int(b_mn), None, 0, 0, 1.0, x_shard.data_ptr(), site.K, site.bufs, site.flags,
                                           site.sync.data_ptr(), m.world, m.rank, comm_ctas, K.status_word(m.device).data_ptr(),
@@ -129,6 +145,7 @@ def gemm_rs(site: OaTpRsSite, a: torch.Tensor, w: torch.Tensor, *, b_mn: bool = 
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
     assert a.shape[0] == site.M and Nn == site.N
     out = torch.empty((site.M // m.world, Nn), dtype=torch.bfloat16, device=a.device)
+    site.arena.enter_site(site)
     K._launch(N.require().oa_gemm_bf16_tp(2, a.data_ptr(), w.data_ptr(), out.data_ptr(), site.M, Nn, Kk, Kk, w.shape[1], Nn, int(b_mn),
                                           N.ptr(residual), Nn if residual is not None else 0, 0, 1.0, None, 0, site.bufs, site.flags,
                                           site.sync.data_ptr(), m.world, m.rank, 0, K.status_word(m.device).data_ptr(), N.stream()),
