@@ -173,8 +173,8 @@ int oa_moe_gather_bwd(const void* dpacked, const int* inverse, const void* base,
 
 // expert parallelism over peer memory (moe.cu): layout from the exchanged counts, dispatch (push), combine (pull)
 int oa_ep_layout(const int* counts_all, const int* topk_idx, const int* inverse, const int* offsets_local, int* route_rank,
-                 int* route_row, int* loc_offsets, int* loc_counts, int* counts_global, long long routes, int E, int world,
-                 int rank, void* stream);
+                 int* route_row, int* loc_offsets, int* loc_counts, int* counts_global, int* need, long long routes, int E,
+                 int world, int rank, void* stream);
 int oa_ep_push_rows(const void* x, const void* const* dst_peers, const int* route_rank, const int* route_row, const float* gate,
                     long long routes, int K, int dim, int world, int cap_rows, int* status, void* stream);
 int oa_ep_pull_rows(const void* const* src_peers, const int* route_rank, const int* route_row, const float* gate, const void* base,

@@ -418,11 +418,12 @@ struct PeerPtrs { void* ptr[8]; };
 __global__ void ep_layout_kernel(const int* __restrict__ counts_all, const int* __restrict__ topk_idx, const int* __restrict__ inverse,
                                  const int* __restrict__ offsets_local, int* __restrict__ route_rank, int* __restrict__ route_row,
                                  int* __restrict__ loc_offsets, int* __restrict__ loc_counts, int* __restrict__ counts_global,
-                                 long long routes, int E, int world, int rank) {
+                                 int* __restrict__ need, long long routes, int E, int world, int rank) {
   __shared__ int seg_off[MOE_MAX_E];     // owner-local padded segment start of every global expert
   __shared__ int src_off[MOE_MAX_E];     // rows of earlier sources inside the segment
   const int E_loc = E / world;
   if (threadIdx.x == 0) {
+    int most = 0;
     for (int d = 0; d < world; ++d) {
       int off = 0;
       for (int le = 0; le < E_loc; ++le) {
@@ -440,8 +441,12 @@ __global__ void ep_layout_kernel(const int* __restrict__ counts_all, const int* 
         }
         off += (tot + MOE_SEG_ALIGN - 1) / MOE_SEG_ALIGN * MOE_SEG_ALIGN;
       }
-      if (blockIdx.x == 0 && d == rank) loc_offsets[E_loc] = off;
+      if (blockIdx.x == 0 && d == rank) { loc_offsets[E_loc] = off; if (need) need[0] = off; }
+      most = max(most, off);
     }
+    // rows (padded per expert) that the busiest owner receives: the same number on every rank, computed from the same table,
+    // so that all ranks size their peer-mapped buffers alike before any row moves
+    if (blockIdx.x == 0 && need) need[1] = most;
   }
   __syncthreads();
   long long stride = (long long)gridDim.x * blockDim.x;
@@ -553,11 +558,11 @@ static PeerPtrs make_peers(const void* const* ptrs, int world) {
 }
 
 extern "C" int oa_ep_layout(const int* counts_all, const int* topk_idx, const int* inverse, const int* offsets_local,
-                            int* route_rank, int* route_row, int* loc_offsets, int* loc_counts, int* counts_global,
+                            int* route_rank, int* route_row, int* loc_offsets, int* loc_counts, int* counts_global, int* need,
                             long long routes, int E, int world, int rank, void* stream) {
   if (E > MOE_MAX_E || world < 1 || world > 8 || E % world) return OA_ERR_ARG;
   ep_layout_kernel<<<mgrid(routes), 256, 0, ST>>>(counts_all, topk_idx, inverse, offsets_local, route_rank, route_row, loc_offsets,
-                                                  loc_counts, counts_global, routes, E, world, rank);
+                                                  loc_counts, counts_global, need, routes, E, world, rank);
   return CHECK_LAUNCH();
 }
 extern "C" int oa_ep_push_rows(const void* x, const void* const* dst_peers, const int* route_rank, const int* route_row,

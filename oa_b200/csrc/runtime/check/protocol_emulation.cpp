@@ -16,6 +16,8 @@
 //             counters grow by `slabs` per call) and mode 2 (partial tiles stored into the owner's slots, four counted
 //             releases per tile, the owner's reduce waits per row block), the per-site epoch word that advances when the
 //             last CTA leaves, and the ready/ack round that separates two consecutive uses of one site
+//   ep        expert-parallel dispatch / combine: three rounds per layer forward, two backward, per-layer row buffers, one
+//             shared pair of gradient staging buffers with no round after a layer's last pull
 //   timeout   a rank that never signals: the others' bounded waits run out, set the status word and return
 // Negative controls (`dp-no-ack`, `tp-no-fence`) drop one ordering edge on purpose; the detector must report them, which
 // shows that the harness can see the hazards the protocols are there to prevent.
@@ -428,6 +430,83 @@ void run_tp(int W, const std::vector<int>& order, bool fence, uint64_t seed, boo
 
 }  // namespace
 
+// ------------------------------------------------------------------------------------------- expert-parallel dispatch
+namespace {
+
+// parallel/ep.py: three ready/ack rounds per layer forward (counts, rows landed, outputs ready), two backward (output
+// gradients landed, token gradients ready).  Row buffers px / po are per layer; the gradient staging pair is shared by all
+// layers and there is NO round after the last pull of a layer.
+struct EpWorld {
+  int W, layers, R;                                   // R rows from every source to every owner
+  std::vector<std::vector<std::vector<float>>> px, po; // [layer][rank][W * R]
+  std::vector<std::vector<float>> dpo, dpx, counts;    // [rank][W * R], [rank][W]
+  std::vector<Channel> ch;                             // 5 per layer
+  EpWorld(int W_, int layers_, int R_) : W(W_), layers(layers_), R(R_) {
+    for (int l = 0; l < layers; ++l) {
+      px.emplace_back(W, std::vector<float>(W * R, -1.f));
+      po.emplace_back(W, std::vector<float>(W * R, -1.f));
+      for (int c = 0; c < 5; ++c) ch.emplace_back(W);
+    }
+    dpo.assign(W, std::vector<float>(W * R, -1.f));
+    dpx.assign(W, std::vector<float>(W * R, -1.f));
+    counts.assign(W, std::vector<float>(W, 0.f));
+  }
+};
+
+float ep_value(int rank, int step, int layer, int owner, int j) { return float((rank * 7 + step * 5 + layer * 3 + owner * 11 + j) % 31) - 15.f; }
+
+void run_ep(int W, int layers, uint64_t seed) {
+  EpWorld w(W, layers, 6);
+  std::atomic<int> wrong{0};
+  std::vector<int> status(W, 0);
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < W; ++r)
+    ranks.emplace_back([&, r] {
+      Rng rng(seed * 53 + r);
+      int& st = status[r];
+      auto round = [&](int layer, int c) { Channel& ch = w.ch[layer * 5 + c]; ch.signal(r); return ch.wait(r, &st); };
+      for (int step = 0; step < 5 && !st; ++step) {
+        for (int l = 0; l < layers && !st; ++l) {                       // forward
+          jitter(rng);
+          for (int p = 0; p < W; ++p) w.counts[p][r] = float(w.R);        // counts into every peer's table row
+          if (!round(l, 0)) break;
+          for (int p = 0; p < W; ++p) if (w.counts[r][p] != float(w.R)) wrong.fetch_add(1);
+          for (int o = 0; o < W; ++o)                                     // dispatch: rows into the owners' buffers
+            for (int j = 0; j < w.R; ++j) w.px[l][o][r * w.R + j] = ep_value(r, step, l, o, j);
+          jitter(rng);
+          if (!round(l, 1)) break;
+          for (int i = 0; i < W * w.R; ++i) w.po[l][r][i] = 2.f * w.px[l][r][i];   // this owner's experts
+          jitter(rng);
+          if (!round(l, 2)) break;
+          for (int o = 0; o < W; ++o)                                     // combine: pull from the owners
+            for (int j = 0; j < w.R; ++j)
+              if (w.po[l][o][r * w.R + j] != 2.f * ep_value(r, step, l, o, j)) wrong.fetch_add(1);
+        }
+        for (int l = layers - 1; l >= 0 && !st; --l) {                  // backward
+          jitter(rng);
+          for (int o = 0; o < W; ++o)                                     // dgate: pulled dot products with the saved outputs
+            for (int j = 0; j < w.R; ++j)
+              if (w.po[l][o][r * w.R + j] != 2.f * ep_value(r, step, l, o, j)) wrong.fetch_add(1);
+          for (int o = 0; o < W; ++o)
+            for (int j = 0; j < w.R; ++j) w.dpo[o][r * w.R + j] = 3.f * ep_value(r, step, l, o, j);
+          jitter(rng);
+          if (!round(l, 3)) break;
+          for (int i = 0; i < W * w.R; ++i) w.dpx[r][i] = w.dpo[r][i] + w.px[l][r][i];   // dX (and dW from the saved rows)
+          jitter(rng);
+          if (!round(l, 4)) break;
+          for (int o = 0; o < W; ++o)
+            for (int j = 0; j < w.R; ++j)
+              if (w.dpx[o][r * w.R + j] != 4.f * ep_value(r, step, l, o, j)) wrong.fetch_add(1);
+        }
+      }
+    });
+  for (auto& t : ranks) t.join();
+  for (int r = 0; r < W; ++r) EXPECT(status[r] == 0);
+  EXPECT(wrong.load() == 0);
+}
+
+}  // namespace
+
 int main(int argc, char** argv) {
   const std::string what = argc > 1 ? argv[1] : "all";
   const uint64_t seed = argc > 2 ? std::strtoull(argv[2], nullptr, 10) : 1;
@@ -444,6 +523,11 @@ int main(int argc, char** argv) {
       run_tp(W, {0, 1, 2, 1}, true, seed + 1, true);
       run_tp(W, {0, 0, 1, 1}, true, seed + 2, true);  // the same site twice in a row: separated by the ready/ack round
       run_tp(W, {2}, true, seed + 3, true);
+    }
+  if (what == "ep" || what == "all")
+    for (int W = 2; W <= 4; ++W) {
+      run_ep(W, 1, seed);                               // one layer: the shared gradient buffers are reused by the very next use
+      run_ep(W, 3, seed + 1);
     }
   if (what == "timeout" || what == "all") run_timeout(3);
   // negative controls: the detector must report these

@@ -163,6 +163,25 @@ class OaDeviceMesh:
         self._buffers.append(b)
         return b
 
+    def Release(self, buf: OaSymmetricBuffer) -> None:
+        """Frees one symmetric buffer on every rank (a host collective: all ranks call it for the same buffer).  The caller
+        has made sure that no kernel of any rank still touches it; the barrier keeps a rank from freeing memory that a
+        peer still has mapped."""
+        if buf in self._buffers:
+            self._buffers.remove(buf)
+        lib = N.lib()
+        if lib is None or buf.local_ptr is None:
+            return
+        torch.cuda.synchronize()
+        buf.tensor = None
+        for q in buf._opened:
+            lib.oa_ipc_close(q)
+        buf._opened = []
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)
+        lib.oa_ipc_free(buf.local_ptr)
+        buf.local_ptr = None
+
     def NewChannel(self) -> OaPeerChannel:
         c = OaPeerChannel(self)
         self._channels.append(c)

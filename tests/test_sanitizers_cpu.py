@@ -5,7 +5,7 @@ under the race detector.
   -fsanitize=thread: the driver walks the C API of the compute graph, plan cache, pool / channel / locks, .oam writer and
   loader (with truncated and bit-flipped files), asynchronous reader and allocation session.
 * `check/protocol_emulation.cpp` built with -fsanitize=thread: the flag / epoch protocols of the data-parallel fused step
-  and of the tensor-parallel call sites, several seeds; two negative controls (one ordering edge removed) must be
+  of the tensor-parallel call sites and of the expert-parallel dispatch, several seeds; two negative controls (one ordering edge removed) must be
   REPORTED by the detector.
 
 Reference strategy: the upstream project's host validation profile builds everything with -fsanitize=address,undefined
@@ -88,7 +88,7 @@ def emulation(workdir):
     return _build(workdir, "proto_tsan", ["-fsanitize=thread"], [CHECK / "protocol_emulation.cpp"])
 
 
-@pytest.mark.parametrize("what", ["dp", "tp", "timeout"])
+@pytest.mark.parametrize("what", ["dp", "tp", "ep", "timeout"])
 def test_protocols_are_race_free_over_random_interleavings(emulation, what):
     for seed in (1, 2, 3, 4, 5, 6):
         r = subprocess.run([str(emulation), what, str(seed)], capture_output=True, text=True, timeout=300,
