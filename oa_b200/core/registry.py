@@ -124,16 +124,21 @@ def Populate() -> None:
     if _populated:
         return
     L = _lib()
+    # kernel rows come from the generated table; a table that is older than the header is ignored and the header is read
+    import hashlib
     api = (Path(__file__).resolve().parent.parent / "csrc" / "kernels" / "api.h").read_text()
-    category, provider = "core", "api.h"
-    for line in api.splitlines():
-        m = re.match(r"//\s*-+\s*(.+?)\s*\(([\w.]+\.cu)[^)]*\)", line)
-        if m:
-            category, provider = m.group(1).strip(), m.group(2)
-            continue
-        m = re.match(r"\s*(?:int|size_t|void)\s+(oa_\w+)\s*\(", line)
-        if m:
-            L.oa_registry_add_kernel(m.group(1).encode(), category.encode(), provider.encode())
+    rows = None
+    try:
+        from .._generated import kernel_table as KT
+        if KT.API_SHA256 == hashlib.sha256(api.encode()).hexdigest():
+            rows = [(name, section, file) for name, section, file, _, _, _ in KT.KERNELS]
+    except ImportError:
+        pass
+    if rows is None:
+        from ..utils.api_header import parse_api
+        rows = [(r["name"], r["section"], r["file"]) for r in parse_api(api)[0]]
+    for name, category, provider in rows:
+        L.oa_registry_add_kernel(name.encode(), category.encode(), provider.encode())
     from . import fn_matrix as F
     from ..ml import fn_loss as FL
     for ns, mod in (("", F), ("Loss.", FL)):

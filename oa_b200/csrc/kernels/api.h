@@ -239,25 +239,13 @@ int oa_rl_cartpole_reset(void* state, void* done, void* steps, void* episode, in
 int oa_rl_cartpole_step(const void* action, void* state, void* trans_obs, void* reward, void* terminated, void* truncated,
                         void* done, void* steps, int envs, int max_steps, float gravity, float cart_mass, float pole_mass,
                         float half_len, float force, float dt, float x_limit, float angle_limit, void* stream);
-// ---- rows.cu: row compaction / scatter with a device-resident count, accuracy counters, stochastic rounding, int8 GEMM
-size_t oa_rows_scan_scratch_ints(int rows);
-int oa_rows_scan(const void* mask, void* position, void* count, void* scratch, int rows, void* stream);
-int oa_rows_compact(const void* x, const void* mask, const void* position, void* packed, void* index, int rows, int width, int elem_bytes,
-                    void* stream);
-int oa_rows_scatter(const void* packed, const void* index, const void* count, void* out, int capacity, int out_rows, int width, int dtype, int add,
-                    void* stream);
-int oa_rows_gather(const void* src, const void* index, const void* count, void* packed, int capacity, int src_rows, int width, int elem_bytes,
-                   void* stream);
-int oa_accuracy_count(const void* logits, const void* targets, const void* mask, void* out2, int rows, int vocab, int dtype, void* stream);
-int oa_sr_round_bf16(const void* x, void* out, long long n, unsigned seed_lo, unsigned seed_hi, void* stream);
-int oa_gemm_int8(const void* a, const void* b, void* c_i32, void* c_f32, const void* row_scale, const void* col_scale, int M, int N, int K,
-                 void* stream);
-// LunarLander3d (lunar.cu).  cfg_f: 77 host floats, cfg_n: 6 host ints, spawn8: 8 host floats; the rest is device memory.
+// ---- LunarLander3d (lunar.cu):  cfg_f: 77 host floats, cfg_n: 6 host ints, spawn8: 8 host floats; the rest is device memory.
 int oa_rl_lunar_step(const float* cfg_f, const int* cfg_n, const void* terrain, const void* action, const void* external_stop, void* state_f,
                      void* state_u, void* trans_obs, void* obs, void* reward, void* terminated, void* truncated, void* end_reason, int envs,
                      void* stream);
 int oa_rl_lunar_reset(const float* cfg_f, const int* cfg_n, const float* spawn8, const void* terrain, void* state_f, void* state_u, void* obs,
                       int envs, unsigned seed_lo, unsigned seed_hi, int only_done, void* stream);
+// ---- reinforcement learning, continued (rl.cu)
 int oa_rl_gae(const void* reward, const void* value, const void* next_value, const void* terminated, const void* truncated,
               void* adv, void* ret, int T, int E, float gamma, float lambda, void* stream);
 int oa_rl_rollout_append(const void* obs, const void* action, const void* reward, const void* value, const void* next_value,
@@ -276,6 +264,19 @@ int oa_rl_sac_target(const void* reward, const void* q1, const void* q2, const v
                      int batch, float discount, float alpha, void* stream);
 int oa_rl_sample_categorical(const void* logits, void* action, int rows, int actions, float temperature, unsigned seed_lo,
                              unsigned seed_hi, int greedy, void* stream);
+// ---- rows.cu: row compaction / scatter with a device-resident count, accuracy counters, stochastic rounding, int8 GEMM
+size_t oa_rows_scan_scratch_ints(int rows);
+int oa_rows_scan(const void* mask, void* position, void* count, void* scratch, int rows, void* stream);
+int oa_rows_compact(const void* x, const void* mask, const void* position, void* packed, void* index, int rows, int width, int elem_bytes,
+                    void* stream);
+int oa_rows_scatter(const void* packed, const void* index, const void* count, void* out, int capacity, int out_rows, int width, int dtype, int add,
+                    void* stream);
+int oa_rows_gather(const void* src, const void* index, const void* count, void* packed, int capacity, int src_rows, int width, int elem_bytes,
+                   void* stream);
+int oa_accuracy_count(const void* logits, const void* targets, const void* mask, void* out2, int rows, int vocab, int dtype, void* stream);
+int oa_sr_round_bf16(const void* x, void* out, long long n, unsigned seed_lo, unsigned seed_hi, void* stream);
+int oa_gemm_int8(const void* a, const void* b, void* c_i32, void* c_f32, const void* row_scale, const void* col_scale, int M, int N, int K,
+                 void* stream);
 
 // ---- vector quantisation (vq.cu)
 int oa_vq_code_norm(const void* codebook, void* enorm, int K, int D, void* stream);

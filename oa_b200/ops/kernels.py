@@ -14,6 +14,7 @@ from typing import Optional
 import torch
 
 from .. import _native as N
+from ..core import validation as V
 
 C = N.CONST
 ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU = C["OA_ACT_NONE"], C["OA_ACT_GELU"], C["OA_ACT_RELU"], C["OA_ACT_SILU"]
@@ -54,6 +55,26 @@ def check_status(device: Optional[torch.device] = None) -> None:
             raise N.OaKernelError(f"a device-side wait ran out on cuda:{i} (kernel status {v})")
 
 
+_STATUS_NAMES = {0: "none", 1: "wait for a TMA stage ran out", 2: "wait for a free stage ran out", 3: "wait for the accumulator ran out",
+                 4: "wait for a free accumulator ran out", 5: "wait for a peer's flag ran out", 6: "wait for the softmax warps ran out",
+                 7: "bad argument or index"}
+
+
+def status_name(code: int) -> str:
+    return _STATUS_NAMES.get(int(code), "unknown")
+
+
+def peek_status(device: Optional[torch.device] = None) -> int:
+    """The kernels' error word of the device (synchronises; does not clear it)."""
+    for i, t in list(_status.items()):
+        if device is not None and device.index is not None and device.index != i:
+            continue
+        v = int(t[0].item())
+        if v != 0:
+            return v
+    return 0
+
+
 def workspace(device: torch.device) -> torch.Tensor:
     i = device.index if device.index is not None else torch.cuda.current_device()
     if i not in _workspace:
@@ -75,9 +96,11 @@ def scratch(device: torch.device, nbytes: int, tag: str = "") -> torch.Tensor:
     return cur
 
 
-def _launch(rc: int, what: str, n: int = 1) -> None:
+def _launch(rc: int, what: str, n: int = 1, outputs=()) -> None:
     N.check(rc, what)
     N.count_launch(n)
+    if V.OaValidation._enabled:
+        V.AfterLaunch(what, outputs)
 
 
 def _gelu_ref(x: torch.Tensor) -> torch.Tensor:
@@ -142,6 +165,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         ws = workspace(a.device)
         status = status_word(a.device)
         plain = bias is None and residual is None and aux_out is None and aux_in is None and act == ACT_NONE
+        if V.OaValidation._enabled:
+            for nm, t in (("gemm.a", a), ("gemm.b", b), ("gemm.out", out), ("gemm.residual", residual), ("gemm.aux_out", aux_out),
+                          ("gemm.aux_in", aux_in)):
+                V.ValidateTensor(nm, t, cuda=True, contiguous=False, align=16)
+                if t is not None:      # TMA wants rows that start on 16-byte boundaries
+                    V.OA_VALIDATE(t.stride(0) * t.element_size() % 16 == 0, V.OaValidationSeverity.Error, "Kernel",
+                                  "%s: row pitch %d bytes is not a multiple of 16", nm, t.stride(0) * t.element_size())
+            V.ValidateTensor("gemm.bias", bias, dtype=torch.bfloat16, cuda=True)
+            V.OA_VALIDATE(Nn % 8 == 0 and K % 8 == 0, V.OaValidationSeverity.Error, "Kernel", "gemm: N=%d and K=%d must be multiples of 8", Nn, K)
+            if force_bn == 0 and (M < 128 or Nn < 128):
+                V.OaValidation.Report(V.OaValidationSeverity.Info, "Kernel", "gemm M=%d N=%d K=%d: tile larger than the problem", M, Nn, K)
         rc = lib.oa_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, Nn, K, a.stride(0), b.stride(0),
                               out.stride(0), int(a_mn), int(b_mn), N.ptr(bias), N.ptr(residual),
                               residual.stride(0) if residual is not None else 0, N.ptr(aux_out), N.ptr(aux_in),
@@ -149,7 +183,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
                               act, int(out.dtype == torch.float32), int(accumulate), float(alpha),
                               ws.data_ptr() if plain else None, ws.numel() if plain else 0, force_bn,
                               status.data_ptr(), st)
-        _launch(rc, f"oa_gemm_bf16 M={M} N={Nn} K={K}")
+        _launch(rc, f"oa_gemm_bf16 M={M} N={Nn} K={K}", outputs=(out,))
         return out
     if a.dtype == torch.float32:
         assert b.dtype == torch.float32 and out.dtype == torch.float32

@@ -187,6 +187,12 @@ class OaDeviceMesh:
         self._channels.append(c)
         return c
 
+    def SetPeerWaitMs(self, ms: int) -> None:
+        """Upper bound of every device-side wait on a peer's flag (wall time).  Ranks drift apart by whole host phases (a
+        data-loader stall, a checkpoint write): choose it above the longest such phase; a wait that runs out sets the kernel
+        status word instead of hanging the stream."""
+        N.check(N.require().oa_set_peer_wait_ms(int(ms)), "oa_set_peer_wait_ms")
+
     def Barrier(self) -> None:
         """Device-side barrier on the current stream: every rank signals, then waits for all (bounded)."""
         if self._barrier is None:
