@@ -6,6 +6,25 @@ import re
 from typing import Dict, List, Tuple
 
 
+def _const_expr(text: str) -> int:
+    """Value of an integer constant expression of a C enum (literals, + - * << >> | & and parentheses)."""
+    import ast
+    import operator as op
+    ops = {ast.Add: op.add, ast.Sub: op.sub, ast.Mult: op.mul, ast.LShift: op.lshift, ast.RShift: op.rshift, ast.BitOr: op.or_,
+           ast.BitAnd: op.and_}
+
+    def ev(n):
+        if isinstance(n, ast.Constant) and isinstance(n.value, int):
+            return n.value
+        if isinstance(n, ast.BinOp) and type(n.op) in ops:
+            return ops[type(n.op)](ev(n.left), ev(n.right))
+        if isinstance(n, ast.UnaryOp) and isinstance(n.op, ast.USub):
+            return -ev(n.operand)
+        raise ValueError(f"unsupported constant expression: {text!r}")
+
+    return ev(ast.parse(re.sub(r"(?<=[0-9a-fA-F])[uUlL]+\b", "", text), mode="eval").body)
+
+
 def fnv1a32(s: str) -> int:
     h = 0x811C9DC5
     for b in s.encode():
@@ -26,7 +45,7 @@ def parse_api(text: str) -> Tuple[List[dict], Dict[str, int]]:
                 continue
             if "=" in item:
                 name, v = item.split("=")
-                val = int(v.strip(), 0)
+                val = _const_expr(v.strip())
                 consts[name.strip()] = val
             else:
                 val += 1
