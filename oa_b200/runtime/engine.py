@@ -447,6 +447,8 @@ def OaInitComputeEngine(config: Optional[OaEngineConfig] = None) -> bool:
     except OaError:
         return False
     eng.SetAsGlobal()
+    from .gemm_tuner import InstallFromEnv
+    InstallFromEnv()                      # OA_GEMM_TUNE / OA_GEMM_PLANS: launch plans of the GEMM family from the native plan cache
     return True
 
 

@@ -152,3 +152,29 @@ def test_kernel_registry_and_operation_contracts():
     assert R.OaOperationRegistry.Find("Dropout").Effects == R.OaEffects.Random
     assert R.OaOperationRegistry.Find("Loss.CrossEntropy").Kind == R.OaOperationKind.Loss
     assert R.OaOperationRegistry.Find("Tanh").Differentiation == R.OaDifferentiation.Analytic
+
+
+def test_gemm_tuner_times_unknown_shapes_once_and_persists(tmp_path):
+    """The launch-plan cache has a consumer: the tuner times each candidate tile of an unknown shape once, keeps the fastest,
+    answers from the cache afterwards, and reloads its plans from a file (Runtime/GemmPlanCache.cpp)."""
+    from oa_b200.runtime.gemm_tuner import OaGemmTuner
+    cost = {0: 50.0, 128: 70.0, 256: 40.0}
+    launched = []
+
+    def timer(run, reps):
+        run()
+        return cost[launched[-1]]
+
+    path = str(tmp_path / "plans.bin")
+    t = OaGemmTuner(path, tune=True, reps=3, timer=timer)
+    assert t.Plan(4096, 1024, 512, 0, 0, launched.append) == 256
+    assert launched == [0, 128, 256] and t.Tuned == 1
+    assert t.Plan(4096, 1024, 512, 0, 0, launched.append) == 256 and len(launched) == 3       # answered from the cache
+    assert t.Plan(4096, 128, 512, 0, 0, launched.append) == 0                                  # 256 does not fit N = 128
+    assert launched[3:] == [0, 128]
+    med, p95, n = t.Cache.Timing(4096, 1024, 512)
+    assert n >= 1 and med > 0
+    t.Save()
+    again = OaGemmTuner(path, tune=False)
+    assert again.Plan(4096, 1024, 512, 0, 0, launched.append) == 256
+    assert again.Plan(64, 64, 64, 0, 0, launched.append) == 0 and len(launched) == 5           # tuning off: library's choice
