@@ -173,12 +173,24 @@ class OaMultiHeadAttention(OaModule):
             self.RegisterModule(nm, lin)
         self.OutProj = self.RegisterModule("out_proj", OaLinear(d_model, d_model, bias, init_std))
 
+    Plan = None      # OaBlockPlan of the enclosing block (None: every fused engine)
+
     def ProjectQkv(self, x: OaMatrix) -> OaMatrix:
         ws = [self.QProj.Weight.Data, self.KProj.Weight.Data, self.VProj.Weight.Data]
         bs = [l.Bias.Data if l.Bias else None for l in (self.QProj, self.KProj, self.VProj)]
+        if self.Plan is not None and not self.Plan.PackedQkv:          # portable lowering: three products, joined
+            return F.Concat([F.Linear(x, w, b) for w, b in zip(ws, bs)], -1)
         return FF.PackedProjection(x, ws, bs, "PackedLinear3")
 
+    def _flash_capable(self) -> bool:
+        if self.Backend == OaAttentionBackend.Standard:
+            return False
+        w = self.OutProj.Weight.Tensor()
+        return not (w.is_cuda and w.dtype == torch.bfloat16 and self.HeadDim not in (64, 128))
+
     def _use_flash(self) -> bool:
+        if self.Plan is not None and not self.Plan.FlashAttention:
+            return False
         if self.Backend == OaAttentionBackend.Standard:
             return False
         w = self.OutProj.Weight.Tensor()
@@ -236,9 +248,23 @@ class OaFfn(OaModule):
             self.RegisterModule(nm, lin)
         self.Down = self.RegisterModule("down", OaLinear(d_ff, d_model, False, init_std))
 
+    Plan = None      # OaBlockPlan of the enclosing block (None: every fused engine)
+
     def Forward(self, x):
         h = self.Norm.Forward(x)
-        return FF.FfnSwiglu(h, self.Gate.Weight.Data, self.Up.Weight.Data, self.Down.Weight.Data, residual=x)
+        return _ffn_swiglu(self.Plan, h, self.Gate.Weight.Data, self.Up.Weight.Data, self.Down.Weight.Data, x)
+
+
+def _ffn_swiglu(plan, h, gate, up, down, residual=None):
+    if plan is not None and not plan.GatedFfn:                         # portable lowering
+        return F.Linear(F.Mul(F.Silu(F.Linear(h, gate)), F.Linear(h, up)), down, None, residual=residual)
+    return FF.FfnSwiglu(h, gate, up, down, residual=residual)
+
+
+def _ffn_gelu(plan, h, w1, b1, w2, b2, residual=None):
+    if plan is not None and not plan.GemmEpilogue:                     # portable lowering: activation as its own operation
+        return F.Linear(F.Gelu(F.Linear(h, w1, b1)), w2, b2, residual=residual)
+    return FF.FfnGelu(h, w1, b1, w2, b2, residual=residual)
 
 
 class OaTransformerBlock(OaModule):
@@ -291,14 +317,27 @@ class OaTransformerBlock(OaModule):
     def ForwardMasked(self, x: OaMatrix, additive_mask: OaMatrix, batch: Optional[int] = None, seq: Optional[int] = None) -> OaMatrix:
         return self.Forward(x, batch, seq, 0, additive_mask)
 
+    def BlockPlan(self):
+        """The engines this block runs with, from the native fusion planner (planned once per block description)."""
+        from .block_plan import PlanTransformerBlock
+        kind = "moe" if self.Moe is not None else ("gelu" if self.FfnKind == "gelu" else "swiglu")
+        d_ff = self.Ffn1.OutFeatures if kind == "gelu" else (self.Ffn.Down.InFeatures if kind == "swiglu" else 0)
+        plan = PlanTransformerBlock(self.DModel, d_ff, kind, self.Attention.OutProj.Bias is not None, self.Attention._flash_capable(),
+                                    training=self.IsTraining() if hasattr(self, "IsTraining") else True)
+        self.Attention.Plan = plan
+        if self.Moe is None and kind == "swiglu":
+            self.Ffn.Plan = plan
+        return plan
+
     def _ffn_delta(self, h: OaMatrix) -> OaMatrix:
         if self.Moe is not None:
             return self.Moe.Forward(h)
+        plan = self.BlockPlan()
         if self.FfnKind == "gelu":
-            return FF.FfnGelu(h, self.Ffn1.Weight.Data, self.Ffn1.Bias.Data if self.Ffn1.Bias else None, self.Ffn2.Weight.Data,
-                              self.Ffn2.Bias.Data if self.Ffn2.Bias else None)
+            return _ffn_gelu(plan, h, self.Ffn1.Weight.Data, self.Ffn1.Bias.Data if self.Ffn1.Bias else None, self.Ffn2.Weight.Data,
+                             self.Ffn2.Bias.Data if self.Ffn2.Bias else None)
         f = self.Ffn
-        return FF.FfnSwiglu(h, f.Gate.Weight.Data, f.Up.Weight.Data, f.Down.Weight.Data)
+        return _ffn_swiglu(plan, h, f.Gate.Weight.Data, f.Up.Weight.Data, f.Down.Weight.Data)
 
     def ForwardConditioned(self, x: OaMatrix, condition: OaMatrix, additive_mask: Optional[OaMatrix] = None) -> OaMatrix:
         """x [B*S, D], condition [B, C]: x + gate_a * Attn(norm(x) * (1 + scale_a) + shift_a), then the same for the FFN."""
@@ -325,13 +364,14 @@ class OaTransformerBlock(OaModule):
         if batch is None:
             seq = self.SeqLen
             batch = x.Size(0) // seq
+        plan = self.BlockPlan()
         x = self.Attention.Forward(self.LnAttn.Forward(x), batch, seq, residual=x, pos_offset=pos_offset, mask=mask)
         if self.Moe is not None:
             x = self.Moe.Forward(x)
         elif self.FfnKind == "gelu":
             h = self.LnFfn.Forward(x)
-            x = FF.FfnGelu(h, self.Ffn1.Weight.Data, self.Ffn1.Bias.Data if self.Ffn1.Bias else None, self.Ffn2.Weight.Data,
-                           self.Ffn2.Bias.Data if self.Ffn2.Bias else None, residual=x)
+            x = _ffn_gelu(plan, h, self.Ffn1.Weight.Data, self.Ffn1.Bias.Data if self.Ffn1.Bias else None, self.Ffn2.Weight.Data,
+                          self.Ffn2.Bias.Data if self.Ffn2.Bias else None, residual=x)
         else:
             x = self.Ffn.Forward(x)
         return x.Reshape([batch, seq, self.DModel]) if shape3 else x

@@ -108,7 +108,9 @@ class OaRankMonitor:
         for s in self.Peers():
             if s.Rank == self.Rank or s.State == LEFT:
                 continue
-            silent = (now - s.Stamp) if s.Seen else (now - self._start)
+            # silence counts from the later of the peer's last beat and the end of this rank's own rendezvous: a beat that
+            # aged while this rank was still waiting for a slower third rank is start-up skew, not a failure
+            silent = (now - max(s.Stamp, self._start)) if s.Seen else (now - self._start)
             if s.State == FAILED or silent > self.TimeoutS:
                 bad.append(s.Rank)
         self.LastBad = bad                       # the ranks this pass found gone (Guard reports exactly these)
