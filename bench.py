@@ -255,6 +255,11 @@ class OaJob:
         self.h2d = self.batches.bytes_per_copy * self.accum
         self.Tape = OaGradientTape
         self.explicit = self.accum > 1 or len(self.opts) > 1 or (k == 5 and world > 1)
+        if self.explicit:
+            from oa_b200.ml.training import OaAccumulatedStep
+            # expert parallelism reads the routing counts on the host in every layer (exact buffer sizing): not capturable
+            capturable = not args.no_graph and not (k == 3 and world > 1)
+            self.acc_step = OaAccumulatedStep(self.opts, self._micro, self.accum, lambda: self.after_backward(), program=capturable)
         if not self.explicit:
             tcfg = OaItTrainingConfig(TotalSteps=10 ** 9, BatchSize=B * world, SequenceLength=self.seq, Program=not args.no_graph)
             self.training = OaItTraining(self.opts[0], tcfg)
@@ -269,28 +274,23 @@ class OaJob:
             tape.Backward(loss)
         return loss
 
+    def _micro(self):
+        with self.Tape() as tape:
+            loss = self.model.Loss(self.ids, self.tgt)
+            tape.Backward(loss)
+        return loss
+
     def _explicit_step(self, feed):
-        for o in self.opts:
-            o.ZeroGrad()
-        loss = None
-        for m in range(self.accum):
-            if feed is not None:
-                feed()
-            with self.Tape() as tape:
-                loss = self.model.Loss(self.ids, self.tgt)
-                tape.Backward(loss)
-        self.after_backward()
-        for o in self.opts:
-            o.Step()
-        self.loss = loss
+        self.loss = self.acc_step.Run(feed)
 
     def warm(self, n):
         if self.explicit:
             self.batches.feed()
-            n0 = self.native.launches()
-            for _ in range(n):
+            for i in range(n):
+                n0 = self.native.launches()
                 self._explicit_step(None)
-            self.launches_per_step = (self.native.launches() - n0) // n
+                if i == 0:                       # the first step runs eagerly: its launches are what a replayed step issues
+                    self.launches_per_step = self.native.launches() - n0
             return
         for w in range(n):
             self.training.IsDone()
@@ -321,9 +321,12 @@ class OaJob:
 
     def info(self) -> dict:
         prog = self.training.Program() if self.training is not None else None
-        return {"executor": "cuda graph replay" if (prog is not None and prog.IsCaptured()) else "eager stream",
+        micro = self.explicit and self.acc_step.IsReplaying()
+        return {"executor": "cuda graph replay" if (prog is not None and prog.IsCaptured()) else
+                ("cuda graph replay of the micro-step, eager optimizer step" if micro else "eager stream"),
                 "optimizer": "AdamW fp32 master" if self.k != 1 else "Adam fp32", "dp": self.dp_mode, "layers": self.cfg.NLayers,
-                "status": "ok" if self.ctx.Sync() else "error"}
+                "status": "ok" if self.ctx.Sync() else "error",
+                **({"capture": self.acc_step.LastStatus.message} if (self.explicit and not self.acc_step.LastStatus.IsOk()) else {})}
 
     def flops_per_token(self) -> float:
         return self.model.FlopsPerToken() if hasattr(self.model, "FlopsPerToken") else 0.0

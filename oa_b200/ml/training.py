@@ -170,6 +170,71 @@ class OaTrainingProgram:
                 "rng_counters_per_step": self.RngCountersPerStep}
 
 
+class OaAccumulatedStep:
+    """A training step made of `accum` micro-steps (forward + backward of one micro-batch into the gradient arenas) and
+    one optimizer step, with the MICRO-step captured as a CUDA graph and replayed: the form a tensor-parallel or large
+    model trains in, where one step is tens of thousands of launches.
+
+    The first call runs eagerly.  The capture is taken on a micro-step that is not the first of its step: by then every
+    gradient buffer has been written once, so each weight-gradient kernel is recorded in its accumulating form, and a
+    replay right after ZeroGrad adds to zeros.  `after_backward` (gradient synchronisation of replicated parameters) and
+    the optimizers stay outside the graph: they run once per step.  A micro-step that cannot be captured (an operation
+    that reads a device value on the host, a host-stepped optimizer inside it) keeps running eagerly and `LastStatus`
+    says why.  Fused multi-GPU kernels replay like any other: their epochs and counters live in device memory."""
+
+    def __init__(self, optimizers, micro_step: Callable[[], object], accum: int, after_backward: Optional[Callable[[], None]] = None,
+                 program: bool = True):
+        self.Optimizers = list(optimizers)
+        self.MicroStep = micro_step
+        self.Accum = int(accum)
+        self.AfterBackward = after_backward or (lambda: None)
+        self.UseProgram = bool(program) and RT.get_engine().IsCuda()
+        self._program: Optional[OaTrainingProgram] = None
+        self._steps = 0
+        self.LastStatus = OaStatus.Ok()
+        self.Loss = None
+
+    def Program(self) -> Optional[OaTrainingProgram]:
+        return self._program
+
+    def IsReplaying(self) -> bool:
+        return self._program is not None and self._program.IsCaptured()
+
+    def _capture(self):
+        prog = OaTrainingProgram()
+        st = prog.Capture(self.MicroStep)
+        self.LastStatus = st
+        if st.IsOk():
+            self._program = prog
+            prog.Replay()                    # the capture recorded the micro-step without running it
+            return prog.Outputs()
+        self.UseProgram = False
+        return self.MicroStep()
+
+    def Run(self, feed: Optional[Callable[[], None]] = None):
+        """One step: ZeroGrad, `accum` micro-steps (each after `feed()`, which loads the next micro-batch into the static
+        input buffers), `after_backward`, every optimizer's Step.  Returns the loss matrix of the last micro-step."""
+        for o in self.Optimizers:
+            o.ZeroGrad()
+        loss = None
+        for m in range(self.Accum):
+            if feed is not None:
+                feed()
+            if self.IsReplaying():
+                self._program.Replay()
+                loss = self._program.Outputs()
+            elif self.UseProgram and self._steps >= 1 and (m >= 1 or self.Accum == 1):
+                loss = self._capture()
+            else:
+                loss = self.MicroStep()
+        self.AfterBackward()
+        for o in self.Optimizers:
+            o.Step()
+        self._steps += 1
+        self.Loss = loss
+        return loss
+
+
 class OaCallback:
     """Hooks fired by OaItTraining (Source/Public/Oa/Ml/Callbacks.h:49-236). Return an OaStatus or None."""
 

@@ -96,3 +96,46 @@ def test_changed_step_is_not_replayed():
     assert "changed" in tr.LastVerify.message
     assert tr.Program().IsCaptured() and tr.Program().Replays >= 1
     assert all(l == l for l in losses)
+
+
+def test_accumulated_step_replays_the_micro_step():
+    """Four micro-steps per optimizer step, the micro-step captured once and replayed: losses and weights equal the eager
+    run (gradient accumulation into the arenas is recorded in its accumulating form; ZeroGrad and the optimizer stay outside)."""
+    from oa_b200.ml import fn_loss as L
+    from oa_b200.ml.autograd import OaGradientTape
+    from oa_b200.ml.optim import OaAdamW
+    from oa_b200.ml.training import OaAccumulatedStep
+
+    def run(program: bool):
+        F, net = _setup(seed=23)
+        opt = OaAdamW(net.AllParameterPtrs(), 1e-2)
+        opt.SetGradScale(0.25)
+        g = torch.Generator().manual_seed(5)
+        xs = [torch.randn(16, 32, generator=g) for _ in range(20)]
+        ys = [torch.randn(16, 8, generator=g) for _ in range(20)]
+        x = F.FromTensor(torch.zeros(16, 32, device="cuda"))
+        y = F.FromTensor(torch.zeros(16, 8, device="cuda"))
+        k = {"i": 0}
+
+        def feed():
+            x.Tensor().copy_(xs[k["i"]])
+            y.Tensor().copy_(ys[k["i"]])
+            k["i"] += 1
+
+        def micro():
+            with OaGradientTape() as tape:
+                loss = L.Mse(net.Forward(x), y)
+                tape.Backward(loss)
+            return loss
+
+        step = OaAccumulatedStep([opt], micro, accum=4, program=program)
+        losses = [step.Run(feed).Item() for _ in range(5)]
+        w = torch.cat([p.Tensor().float().reshape(-1) for p in net.AllParameterPtrs()]).cpu()
+        return losses, w, step
+
+    eager_l, eager_w, _ = run(False)
+    prog_l, prog_w, step = run(True)
+    assert step.IsReplaying() and step.Program().Replays >= 4 * 3, step.LastStatus.message
+    for a, b in zip(eager_l, prog_l):
+        assert abs(a - b) <= 1e-6 * max(1.0, abs(a)), (eager_l, prog_l)
+    assert (eager_w - prog_w).abs().max().item() <= 1e-6
