@@ -60,6 +60,10 @@ OaModule, OaParameter = _MOD.OaModule, _MOD.OaParameter
 OaOptimizer, OaOptimizerNoOp, OaOptimizerComposite = _O.OaOptimizer, _O.OaOptimizerNoOp, _O.OaOptimizerComposite
 OaAdam, OaAdamW, OaSGD, OaMuon, OaMuonAdamWConfig = _O.OaAdam, _O.OaAdamW, _O.OaSGD, _O.OaMuon, _O.OaMuonAdamWConfig
 OaItTraining, OaItTrainingConfig, OaGpuTimingStats = _TR.OaItTraining, _TR.OaItTrainingConfig, _TR.OaGpuTimingStats
+OaAccumulatedStep = _TR.OaAccumulatedStep
+from oa_b200.core.validation import OA_VALIDATE, OaValidation, OaValidationSeverity  # noqa: E402
+from oa_b200.utils.cli import OaCli  # noqa: E402
+from oa_b200.runtime.gemm_tuner import OaGemmTuner  # noqa: E402
 OaCallback, OaCbTraining = _TR.OaCallback, _TR.OaCbTraining
 OaCbProgressBar, OaCbSummary, OaCbValidation, OaCbCheckpoint = _CB.OaCbProgressBar, _CB.OaCbSummary, _CB.OaCbValidation, _CB.OaCbCheckpoint
 OaCbEarlyStop, OaCbLrScheduler, OaCbCsvLogger, OaCbPhase = _CB.OaCbEarlyStop, _CB.OaCbLrScheduler, _CB.OaCbCsvLogger, _CB.OaCbPhase

@@ -63,12 +63,15 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
             if rc != 0:
                 raise RuntimeError(f"nvcc failed: {' '.join(cmd)}")
     if jobs or not out.exists():
-        cmd = [_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
+        # link beside the target and rename: a reader (or a copy of the tree) never sees a half-written library
+        tmp = out.with_suffix(".so.tmp")
+        cmd = [_nvcc(), "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a",
                "-Xcompiler", "-fPIC", "-lcudart"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link of liboa_kernels.so failed")
+        os.replace(tmp, out)
     return out
 
 
@@ -80,12 +83,14 @@ def build_runtime(force: bool = False) -> Path | None:
     out = LIB_DIR / "liboa_runtime.so"
     newest = max([s.stat().st_mtime for s in srcs] + [_newest_header(RUNTIME_DIR)])
     if force or not out.exists() or out.stat().st_mtime < newest:
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", str(RUNTIME_DIR), "-o", str(out),
+        tmp = out.with_suffix(".so.tmp")
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", str(RUNTIME_DIR), "-o", str(tmp),
                *map(str, srcs)]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("build of liboa_runtime.so failed")
+        os.replace(tmp, out)
     return out
 
 
