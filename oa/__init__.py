@@ -63,6 +63,9 @@ OaItTraining, OaItTrainingConfig, OaGpuTimingStats = _TR.OaItTraining, _TR.OaItT
 OaAccumulatedStep = _TR.OaAccumulatedStep
 from oa_b200.core.validation import OA_VALIDATE, OaValidation, OaValidationSeverity  # noqa: E402
 from oa_b200.utils.cli import OaCli  # noqa: E402
+from oa_b200.extensions.rig import (OaHumanIkCharacterization, OaHumanIkSlot, OaJoint, OaRefJoint, OaRefPose, OaRefPoseFor, OaSkelJoint,  # noqa: E402
+                                    OaSkeleton, OaSkHumanIk, OaSkHumanMl3d, OaSkMetaHuman, OaTransform)
+from oa_b200.extensions.anim import OaFbxWriter, OaPoseClip, OaPosePack, OaRetarget, OaUsd, OaUsdNamedClip, OaUsdSkelClip  # noqa: E402
 from oa_b200.runtime.gemm_tuner import OaGemmTuner  # noqa: E402
 OaCallback, OaCbTraining = _TR.OaCallback, _TR.OaCbTraining
 OaCbProgressBar, OaCbSummary, OaCbValidation, OaCbCheckpoint = _CB.OaCbProgressBar, _CB.OaCbSummary, _CB.OaCbValidation, _CB.OaCbCheckpoint

@@ -669,7 +669,8 @@ struct PairCfg {
 
 template <int A_MN, int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
-gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
   using Cfg = PairCfg;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -690,10 +691,22 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const int m_tiles = (p.M + 255) / 256, n_tiles = (p.N + 255) / 256;
   const int total_tiles = m_tiles * n_tiles;
   const int kb_total = (p.K + BK - 1) / BK;
+  // Tail wave: when the tiles left after the last full wave occupy at most half of the pairs, each of them is split into
+  // two 256 x 128 units (an MMA of N = 128, 64 B rows per CTA), so the tail costs half a wave instead of a whole one.
+  const int full_tiles = (total_tiles / n_pairs) * n_pairs;
+  const int rem_tiles = total_tiles - full_tiles;
+  const bool split_tail = rem_tiles > 0 && 2 * rem_tiles <= n_pairs;
+  const int total_units = split_tail ? full_tiles + 2 * rem_tiles : total_tiles;
+  auto unit_tile = [&](int u, int& half) -> int {
+    if (!split_tail || u < full_tiles) { half = -1; return u; }
+    half = (u - full_tiles) & 1;
+    return full_tiles + ((u - full_tiles) >> 1);
+  };
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    tma_prefetch_desc(&tmB2);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
     mbar_fence_init();
@@ -711,13 +724,16 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
-        int mi, ni;
+      for (int u = pair; u < total_units && ok; u += n_pairs) {
+        int mi, ni, half;
+        const int t = unit_tile(u, half);
         tile_coords(t, m_tiles, n_tiles, 8, mi, ni);
-        const int row0 = mi * 256 + (int)rank * 128, n0 = ni * 256 + (int)rank * 128;
+        const int row0 = mi * 256 + (int)rank * 128;
+        const int n0 = half < 0 ? ni * 256 + (int)rank * 128 : ni * 256 + half * 128 + (int)rank * 64;
+        const uint32_t stage_bytes = half < 0 ? 2 * Cfg::STAGE_BYTES : 2 * (Cfg::A_BYTES + Cfg::B_BYTES / 2);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
-          if (leader) mbar_expect_tx(&full[stage], 2 * Cfg::STAGE_BYTES);
+          if (leader) mbar_expect_tx(&full[stage], stage_bytes);
           uint8_t* a = sA + stage * Cfg::A_BYTES;
           uint8_t* b = sB + stage * Cfg::B_BYTES;
           if (A_MN) {
@@ -727,10 +743,12 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tma_load_3d_pair(a, &tmA, &full[stage], kb * BK, row0, 0);
           }
           if (B_MN) {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) tma_load_3d_pair(b + j * (64 * BK * 2), &tmB, &full[stage], n0 + j * 64, kb * BK, 0);
-          } else {
+            tma_load_3d_pair(b, &tmB, &full[stage], n0, kb * BK, 0);
+            if (half < 0) tma_load_3d_pair(b + 64 * BK * 2, &tmB, &full[stage], n0 + 64, kb * BK, 0);
+          } else if (half < 0) {
             tma_load_3d_pair(b, &tmB, &full[stage], kb * BK, n0, 0);
+          } else {
+            tma_load_3d_pair(b, &tmB2, &full[stage], kb * BK, n0, 0);      // 64 rows of B
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -739,13 +757,17 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0 && leader) {
       // ---------------- MMA issuer of the pair
-      constexpr uint32_t idesc = umma_idesc_bf16(256, 256, A_MN, B_MN);
+      constexpr uint32_t idesc_full = umma_idesc_bf16(256, 256, A_MN, B_MN);
+      constexpr uint32_t idesc_half = umma_idesc_bf16(256, 128, A_MN, B_MN);
       constexpr uint32_t a_lbo = A_MN ? BK * 128 : 16, a_kstep = A_MN ? UMMA_K * 128 : UMMA_K * 2;
       constexpr uint32_t b_lbo = B_MN ? BK * 128 : 16, b_kstep = B_MN ? UMMA_K * 128 : UMMA_K * 2;
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+      for (int u = pair; u < total_units && ok; u += n_pairs) {
+        int half;
+        unit_tile(u, half);
+        const uint32_t idesc = half < 0 ? idesc_full : idesc_half;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
@@ -778,8 +800,9 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int quad = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int t = pair; t < total_tiles; t += n_pairs) {
-      int mi, ni;
+    for (int u = pair; u < total_units; u += n_pairs) {
+      int mi, ni, half;
+      const int t = unit_tile(u, half);
       tile_coords(t, m_tiles, n_tiles, 8, mi, ni);
       bool ok = mbar_wait(&tfull[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
@@ -787,17 +810,19 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = mi * 256 + (int)rank * 128 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256;
+      const int chunks = half < 0 ? 8 : 4;
+      const int col_base = ni * 256 + (half < 0 ? 0 : half * 128);
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < chunks; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
         tmem_ld_wait();
-        if (c == 7) {
+        if (c == chunks - 1) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[acc]) & kPeerBitMask);    // the even CTA's barrier
         }
-        epilogue_chunk<256>(p, r, row, ni * 256 + c * 32, 0, 0);
+        epilogue_chunk<256>(p, r, row, col_base + c * 32, 0, 0);
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
@@ -810,14 +835,15 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 template <int A_MN, int B_MN>
-static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t st) {
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p, int grid,
+                            cudaStream_t st) {
   auto kfn = gemm_pair_bf16_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
     attr_set = true;
   }
-  kfn<<<grid, 192, PairCfg::SMEM_BYTES, st>>>(ta, tb, p);
+  kfn<<<grid, 192, PairCfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
@@ -1007,13 +1033,15 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
     if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb, 0, 64, BK);
     else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 128);
     if (rc) return rc;
+    CUtensorMap tb2 = tb;                                    // 64-row boxes of K-major B for the half-width tail units
+    if (!b_mn) { rc = make_tmap_3d_bf16(&tb2, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 64); if (rc) return rc; }
     cudaStream_t pst = (cudaStream_t)stream;
     const int pgrid = (int)(tiles2 * 2 < sms ? tiles2 * 2 : sms);
     switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
-      case 0: return launch_gemm_pair<0, 0>(ta, tb, p, pgrid, pst);
-      case 1: return launch_gemm_pair<0, 1>(ta, tb, p, pgrid, pst);
-      case 2: return launch_gemm_pair<1, 0>(ta, tb, p, pgrid, pst);
-      default: return launch_gemm_pair<1, 1>(ta, tb, p, pgrid, pst);
+      case 0: return launch_gemm_pair<0, 0>(ta, tb, tb2, p, pgrid, pst);
+      case 1: return launch_gemm_pair<0, 1>(ta, tb, tb2, p, pgrid, pst);
+      case 2: return launch_gemm_pair<1, 0>(ta, tb, tb2, p, pgrid, pst);
+      default: return launch_gemm_pair<1, 1>(ta, tb, tb2, p, pgrid, pst);
     }
   }
   if (a_mn) rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, batch, (uint64_t)lda, sa_batch, 64, BK);
