@@ -63,6 +63,8 @@ OaItTraining, OaItTrainingConfig, OaGpuTimingStats = _TR.OaItTraining, _TR.OaItT
 OaAccumulatedStep = _TR.OaAccumulatedStep
 from oa_b200.core.validation import OA_VALIDATE, OaValidation, OaValidationSeverity  # noqa: E402
 from oa_b200.utils.cli import OaCli  # noqa: E402
+from oa_b200.crypto.sign import (OA_SIGN_PUBKEY_SIZE, OA_SIGN_SECRET_SIZE, OA_SIGN_SIG_SIZE, OaGenerateKeypair, OaKeypair, OaPublicKey,  # noqa: E402
+                                 OaSecretKey, OaSign, OaSignature, OaVerify)
 from oa_b200.extensions.rig import (OaHumanIkCharacterization, OaHumanIkSlot, OaJoint, OaRefJoint, OaRefPose, OaRefPoseFor, OaSkelJoint,  # noqa: E402
                                     OaSkeleton, OaSkHumanIk, OaSkHumanMl3d, OaSkMetaHuman, OaTransform)
 from oa_b200.extensions.anim import OaFbxWriter, OaPoseClip, OaPosePack, OaRetarget, OaUsd, OaUsdNamedClip, OaUsdSkelClip  # noqa: E402
@@ -231,9 +233,7 @@ UNAVAILABLE = ("OaPlot", "OaViewer", "OaVideo", "OaRenderer",
                "OaScreenCaptureCursor", "OaScreenCaptureTarget", "OaVideoCodec", "OaVideoConfig", "OaVideoDecodeCapabilities",
                "OaVideoEncodeCapabilities", "OaVideoEncodeProfile", "OaVideoFrame", "OaVideoFrameResource", "OaVideoPacket",
                "OaVideoRateControl", "OaVideoRecorder", "OaVideoRecorderConfig", "OaVideoStream", "OaVideoStreamOptions",
-               "OaVideoStreamStats", "OaYCbCrModel",
-               # ML-DSA signatures: the reference links liboqs, which is not part of this build
-               "OaKeypair", "OaPublicKey", "OaSecretKey", "OaSignature", "OaGenerateKeypair", "OaSign", "OaVerify")
+               "OaVideoStreamStats", "OaYCbCrModel")
 
 
 def __getattr__(name: str):

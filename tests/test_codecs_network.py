@@ -168,6 +168,6 @@ def test_reference_codec_surface_and_hash_types(tmp_path):
     hs = oa.OaHasher(); hs.Update(b"x"); hs.Reset()
     assert hs.Finalize() == oa.OaHash.Of(b"")
     assert oa.OaLinearWeightBiasBwdResult is not None
-    for name in ("OaVideoStream", "OaSign", "OaScreenCapture"):
+    for name in ("OaVideoStream", "OaVideoRecorder", "OaScreenCapture"):
         with pytest.raises(AttributeError):
             getattr(oa, name)
