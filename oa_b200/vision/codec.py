@@ -1,10 +1,10 @@
-"""Still-image codecs: PNG, BMP, TGA and PPM / PGM, decode and encode, to and from uint8 HWC tensors.
+"""Still-image codecs: PNG, BMP, TGA, PPM / PGM and baseline JPEG, decode and encode, to and from uint8 HWC tensors.
 
 The reference's image codec layer (Source/Private/Oa/Vision: JPEG / PNG / BMP / TGA / WebP through bundled decoders)
 feeds `OaImage`; here the lossless formats are implemented directly (PNG inflate / deflate through zlib, all five scanline
-filters, 8-bit grey / grey-alpha / RGB / RGBA / palette, 16-bit reduced to 8).  JPEG and WebP need entropy decoders that
-are not part of this build and are rejected with Unimplemented; video codecs need the vendor's decode engine through a
-graphics API and are unavailable here.
+filters, 8-bit grey / grey-alpha / RGB / RGBA / palette, 16-bit reduced to 8) and baseline JPEG is written out from the
+standard in `jpeg.py` (progressive streams are refused).  WebP is not part of this build and is rejected with
+Unimplemented; video codecs need the vendor's decode engine through a graphics API and are unavailable here.
 """
 from __future__ import annotations
 
@@ -236,9 +236,10 @@ class OaImageIo:
     @staticmethod
     def DecodeMemory(data: bytes) -> Tuple[Optional[OaImage], OaStatus]:
         kind = OaImageIo.Detect(data)
-        if kind in ("jpeg", "webp"):
-            return None, OaStatus(OaStatusCode.Unimplemented, f"{kind} decoding is not part of this build")
-        fn = {"png": DecodePng, "bmp": DecodeBmp, "tga": DecodeTga, "pnm": DecodePnm}.get(kind)
+        if kind == "webp":
+            return None, OaStatus(OaStatusCode.Unimplemented, "webp decoding is not part of this build")
+        from .jpeg import DecodeJpeg
+        fn = {"png": DecodePng, "bmp": DecodeBmp, "tga": DecodeTga, "pnm": DecodePnm, "jpeg": DecodeJpeg}.get(kind)
         if fn is None:
             return None, OaStatus(OaStatusCode.InvalidArgument, "unrecognised image stream")
         try:
@@ -281,7 +282,9 @@ class OaImageIo:
 
     @staticmethod
     def EncodeMemory(image, kind: str = "png") -> Tuple[Optional[bytes], OaStatus]:
-        fn = {"png": EncodePng, "bmp": EncodeBmp, "tga": EncodeTga, "pnm": EncodePnm, "ppm": EncodePnm, "pgm": EncodePnm}.get(kind.lower())
+        from .jpeg import EncodeJpeg
+        fn = {"png": EncodePng, "bmp": EncodeBmp, "tga": EncodeTga, "pnm": EncodePnm, "ppm": EncodePnm, "pgm": EncodePnm, "jpg": EncodeJpeg,
+              "jpeg": EncodeJpeg}.get(kind.lower())
         if fn is None:
             return None, OaStatus(OaStatusCode.Unimplemented, f"no encoder for '{kind}'")
         try:

@@ -66,7 +66,8 @@ def test_png_filters_palette_and_depths():
     bad = bytearray(good); bad[-20] ^= 0xFF
     img, st = OaImageCodec.DecodeMemory(bytes(bad))
     assert img is None and st.code == OaStatusCode.DataLoss
-    assert OaImageCodec.DecodeMemory(b"\xff\xd8\xff\xe0rest")[1].code == OaStatusCode.Unimplemented
+    assert OaImageCodec.DecodeMemory(b"\xff\xd8\xff\xe0rest")[1].code == OaStatusCode.DataLoss          # JPEG signature, no image behind it
+    assert OaImageCodec.DecodeMemory(b"RIFF\0\0\0\0WEBPVP8 ")[1].code == OaStatusCode.Unimplemented
     assert OaImageCodec.DecodeMemory(b"garbage")[1].code == OaStatusCode.InvalidArgument
 
 
