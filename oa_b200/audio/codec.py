@@ -1,7 +1,7 @@
 """WAV decoding and encoding (Source/Public/Oa/Audio/AudioDecoder.h: LoadFile / LoadMemory; AudioEncoder.h: EncodeWavF32 /
 SaveWavF32).  Decodes RIFF/WAVE PCM 8 / 16 / 24 / 32-bit integer and 32 / 64-bit IEEE float (plain and EXTENSIBLE headers)
-into planar float32 [channels, samples]; encodes 32-bit float.  FLAC and MP3 of the reference's decoder are not part of
-this build and are rejected with Unimplemented.
+into planar float32 [channels, samples]; encodes 32-bit float.  FLAC streams go through `flac.py` (written from the format
+description, bit exact); MP3 is not part of this build and is rejected with Unimplemented.
 """
 from __future__ import annotations
 
@@ -19,8 +19,16 @@ from .fn_audio import OaAudio, OaLayoutForChannels
 class OaAudioDecoder:
     @staticmethod
     def LoadMemory(data: bytes) -> Tuple[Optional[OaAudio], OaStatus]:
-        if data[:4] == b"fLaC" or data[:3] == b"ID3" or (len(data) > 1 and data[0] == 0xFF and (data[1] & 0xE0) == 0xE0):
-            return None, OaStatus(OaStatusCode.Unimplemented, "FLAC / MP3 decoding is not part of this build")
+        if data[:4] == b"fLaC":
+            from .flac import DecodeFlac
+            try:
+                pcm_i, rate, bits = DecodeFlac(data)
+            except (ValueError, KeyError, IndexError, struct.error) as e:
+                return None, OaStatus(OaStatusCode.DataLoss, f"corrupt FLAC stream: {e}")
+            x = torch.from_numpy((pcm_i.astype(np.float64) / float(1 << (bits - 1))).astype(np.float32))
+            return OaAudio(OaMatrix(x.contiguous()), int(rate), OaLayoutForChannels(x.shape[0])), OaStatus.Ok()
+        if data[:3] == b"ID3" or (len(data) > 1 and data[0] == 0xFF and (data[1] & 0xE0) == 0xE0):
+            return None, OaStatus(OaStatusCode.Unimplemented, "MP3 decoding is not part of this build")
         if len(data) < 12 or data[:4] != b"RIFF" or data[8:12] != b"WAVE":
             return None, OaStatus(OaStatusCode.InvalidArgument, "not a RIFF/WAVE stream")
         pos, fmt, pcm = 12, None, None

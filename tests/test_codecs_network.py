@@ -97,7 +97,8 @@ def test_wav_round_trip_and_integer_formats(tmp_path):
     assert a8.AsMatrix().Tensor()[0].tolist() == [0.0, 127 / 128, -1.0]
     a24, _ = OaAudioDecoder.LoadMemory(wav(1, 24, bytes([0, 0, 0x40, 0, 0, 0x80]), 2))
     assert a24.Channels() == 2 and a24.AsMatrix().Tensor()[:, 0].tolist() == [0.5, -1.0]
-    assert OaAudioDecoder.LoadMemory(b"fLaC....")[1].code == OaStatusCode.Unimplemented
+    assert OaAudioDecoder.LoadMemory(b"fLaC....")[1].code == OaStatusCode.DataLoss                  # FLAC marker, nothing behind it
+    assert OaAudioDecoder.LoadMemory(b"ID3\x04rest")[1].code == OaStatusCode.Unimplemented
     assert OaAudioDecoder.LoadMemory(b"nope")[1].code == OaStatusCode.InvalidArgument
     assert OaAudioDecoder.LoadMemory(wav(7, 8, b"\0"))[1].code == OaStatusCode.Unimplemented
     assert OaAudioEncoder.EncodeWavF32(OaAudio())[0] is None
