@@ -70,6 +70,8 @@ int oa_unary(int op, int dtype, const void* x, void* y, long long n, float s0, f
 int oa_binary(int op, int dtype, const void* a, const void* b, void* y, long long n, long long inner_b, int bcast_mode,
               void* stream);
 int oa_cast(int src_dtype, int dst_dtype, const void* x, void* y, long long n, void* stream);
+// parts: bf16[terms][n], successive roundings of x (x ~ sum of the parts); terms 1..3
+int oa_split_bf16(const float* x, void* parts, long long n, int terms, void* stream);
 int oa_fill(int dtype, void* y, long long n, float value, void* stream);
 int oa_swiglu_fwd(int dtype, const void* gate_up, void* out, long long rows, int F, void* stream);
 int oa_swiglu_bwd(int dtype, const void* gate_up, const void* dout, void* dgate_up, long long rows, int F, void* stream);

@@ -566,6 +566,27 @@ extern "C" int oa_binary(int op, int dtype, const void* a, const void* b, void* 
                                                                          inner_b > 0 ? inner_b : 1, bcast_mode, s0));
   return CHECK_LAUNCH();
 }
+// parts[t][i] (t < terms) = successive bf16 roundings of x[i]: x ~ sum_t parts[t], each term carrying the next 8 mantissa bits.
+// Feeds the tensor-core fp32 GEMM, which multiplies the parts pairwise and accumulates in fp32.
+__global__ void split_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ parts, long long n, int terms) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float r = x[i];
+    for (int t = 0; t < terms; ++t) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(r);
+      parts[(long long)t * n + i] = h;
+      r -= __bfloat162float(h);
+    }
+  }
+}
+
+extern "C" int oa_split_bf16(const float* x, void* parts, long long n, int terms, void* stream) {
+  if (n <= 0) return OA_OK;
+  if (terms < 1 || terms > 3) return OA_ERR_ARG;
+  split_bf16_kernel<<<grid_for(n, 256), 256, 0, ST>>>(x, (__nv_bfloat16*)parts, n, terms);
+  return CHECK_LAUNCH();
+}
+
 extern "C" int oa_cast(int sd, int dd, const void* x, void* y, long long n, void* stream) {
   if (n <= 0) return OA_OK;
   int g = grid_for(n, 256);

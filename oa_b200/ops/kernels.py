@@ -116,6 +116,43 @@ def _gelu_grad_ref(x: torch.Tensor) -> torch.Tensor:
 
 # ---------------------------------------------------------------- GEMM
 _gemm_planner = None      # (M, N, K, layout, epilogue, run(bn)) -> N tile; installed by runtime/gemm_tuner.py
+# fp32 GEMMs on the tensor cores: 0 = off (exact fp32 FMA kernel), 2 = two bf16 parts per operand (3 products, ~2^-16 relative),
+# 3 = three parts (6 products, fp32-grade).  OA_GEMM_F32_TENSOR sets the default; problems below _F32_TENSOR_MIN_FLOPS stay on
+# the FMA kernel, where the launch latency of several tensor-core GEMMs would dominate.
+_f32_tensor_terms = int(os.environ.get("OA_GEMM_F32_TENSOR", "0") or 0)
+_F32_TENSOR_MIN_FLOPS = 1 << 28
+
+
+def set_f32_tensor_terms(terms: int) -> None:
+    global _f32_tensor_terms
+    if terms not in (0, 2, 3):
+        raise ValueError("fp32 tensor-core GEMM: 0 (off), 2 or 3 bf16 parts per operand")
+    _f32_tensor_terms = int(terms)
+
+
+def split_bf16(x: torch.Tensor, terms: int) -> torch.Tensor:
+    """[terms, *x.shape] bf16 with x ~ sum of the parts (successive roundings of the remainder)."""
+    x = x.contiguous()
+    if not x.is_cuda:
+        parts, r = [], x.float().clone()
+        for _ in range(terms):
+            h = r.bfloat16()
+            parts.append(h)
+            r = r - h.float()
+        return torch.stack(parts)
+    out = torch.empty((terms, *x.shape), dtype=torch.bfloat16, device=x.device)
+    _launch(N.require().oa_split_bf16(x.data_ptr(), out.data_ptr(), x.numel(), terms, N.stream()), "oa_split_bf16")
+    return out
+
+
+def _gemm_f32_tensor(a, b, a_mn, b_mn, out, accumulate, alpha, terms) -> torch.Tensor:
+    """out = alpha * A B^T in fp32 from bf16 products on the tensor cores: every pair of parts whose combined order is below
+    `terms`, smallest contributions first, accumulated in the fp32 output."""
+    pa, pb = split_bf16(a, terms), split_bf16(b, terms)
+    pairs = sorted(((i, j) for i in range(terms) for j in range(terms) if i + j < terms), key=lambda p: -(p[0] + p[1]))
+    for n, (i, j) in enumerate(pairs):
+        gemm(pa[i], pb[j], a_mn=a_mn, b_mn=b_mn, out=out, accumulate=accumulate or n > 0, alpha=alpha)
+    return out
 
 
 def set_gemm_planner(fn) -> None:
@@ -204,6 +241,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         return out
     if a.dtype == torch.float32:
         assert b.dtype == torch.float32 and out.dtype == torch.float32
+        if (_f32_tensor_terms and 2.0 * M * Nn * K >= _F32_TENSOR_MIN_FLOPS and a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
+                and M % 8 == 0 and Nn % 8 == 0 and K % 8 == 0 and act == ACT_NONE and bias is None and residual is None and aux_out is None
+                and aux_in is None):
+            return _gemm_f32_tensor(a, b, a_mn, b_mn, out, accumulate, alpha, _f32_tensor_terms)
         if act in (ACT_GELU_BWD, ACT_RELU_BWD) or residual is not None or aux_out is not None:
             # composed from the plain product for the exact-fp32 path
             v = gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, alpha=alpha)

@@ -346,3 +346,33 @@ def test_xent_rows_not_16_byte_aligned(dtype):
     lossr, dlr = K.xent_fwd_bwd(x.cpu().float(), tg.cpu(), grad_scale=1.0 / 96)
     _close(loss, lossr, 1e-2 if dtype == torch.bfloat16 else 1e-5, what="xent loss, vocab 27")
     _close(dl, dlr, 2e-2 if dtype == torch.bfloat16 else 1e-6, what="xent grad, vocab 27")
+
+
+@pytest.mark.parametrize("terms,tol", [(2, 4e-5), (3, 2e-6)])
+@pytest.mark.parametrize("layout", [(False, False), (True, True)])
+def test_gemm_f32_on_the_tensor_cores(terms, tol, layout):
+    """fp32 GEMM as bf16 part products on tcgen05 (2 parts: 3 products, 3 parts: 6 products) against an fp64 statement of the
+    product; the FMA kernel is the control.  Error is measured against |A| |B|^T, the scale rounding errors live on."""
+    from oa_b200.ops import kernels as K
+    a_mn, b_mn = layout
+    M, N, Kd = 1024, 512, 768
+    torch.manual_seed(4)
+    a = torch.randn((Kd, M) if a_mn else (M, Kd), device="cuda")
+    b = torch.randn((Kd, N) if b_mn else (N, Kd), device="cuda")
+    A = (a.t() if a_mn else a).double()
+    B = (b.t() if b_mn else b).double()
+    want = A @ B.t()
+    scale = A.abs() @ B.abs().t()
+    exact = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    K.set_f32_tensor_terms(terms)
+    try:
+        got = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+        acc = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=exact.clone(), accumulate=True, alpha=0.5)
+    finally:
+        K.set_f32_tensor_terms(0)
+    assert got.dtype == torch.float32
+    err = ((got.double() - want).abs() / scale).max().item()
+    assert err <= tol, err
+    assert ((exact.double() - want).abs() / scale).max().item() <= 1e-6
+    assert ((acc.double() - 1.5 * want).abs() / scale).max().item() <= 2 * tol + 1e-6
+    K.check_status()
