@@ -48,6 +48,7 @@ struct GemmParams {
   int splits;                      // split-K factor; >1 => write fp32 partials to workspace
   float* workspace;                // [splits, M, N] fp32
   int group_m;
+  int pair_group_m;                // m tiles per raster group of the CTA-pair kernel
   int* status;
   int batch;                       // independent problems of the same shape (tensor maps are rank 3)
   long long sc_batch, sr_batch, saux_batch, sbias_batch;   // element strides between problems
@@ -689,13 +690,15 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int m_tiles = (p.M + 255) / 256, n_tiles = (p.N + 255) / 256;
-  const int total_tiles = m_tiles * n_tiles;
+  const int mn_tiles = m_tiles * n_tiles;
+  const int total_tiles = mn_tiles * p.splits;           // split-K: unit = (split, tile), partials go to the fp32 workspace
   const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_per_split = (kb_total + p.splits - 1) / p.splits;
   // Tail wave: when the tiles left after the last full wave occupy at most half of the pairs, each of them is split into
   // two 256 x 128 units (an MMA of N = 128, 64 B rows per CTA), so the tail costs half a wave instead of a whole one.
   const int full_tiles = (total_tiles / n_pairs) * n_pairs;
   const int rem_tiles = total_tiles - full_tiles;
-  const bool split_tail = rem_tiles > 0 && 2 * rem_tiles <= n_pairs;
+  const bool split_tail = p.splits == 1 && rem_tiles > 0 && 2 * rem_tiles <= n_pairs;
   const int total_units = split_tail ? full_tiles + 2 * rem_tiles : total_tiles;
   auto unit_tile = [&](int u, int& half) -> int {
     if (!split_tail || u < full_tiles) { half = -1; return u; }
@@ -727,11 +730,13 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int u = pair; u < total_units && ok; u += n_pairs) {
         int mi, ni, half;
         const int t = unit_tile(u, half);
-        tile_coords(t, m_tiles, n_tiles, 8, mi, ni);
+        const int split = t / mn_tiles;
+        tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.pair_group_m, mi, ni);
         const int row0 = mi * 256 + (int)rank * 128;
         const int n0 = half < 0 ? ni * 256 + (int)rank * 128 : ni * 256 + half * 128 + (int)rank * 64;
         const uint32_t stage_bytes = half < 0 ? 2 * Cfg::STAGE_BYTES : 2 * (Cfg::A_BYTES + Cfg::B_BYTES / 2);
-        for (int kb = 0; kb < kb_total; ++kb) {
+        const int kb0 = split * kb_per_split, kb1 = min(kb_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
           if (leader) mbar_expect_tx(&full[stage], stage_bytes);
           uint8_t* a = sA + stage * Cfg::A_BYTES;
@@ -766,12 +771,14 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       bool ok = true;
       for (int u = pair; u < total_units && ok; u += n_pairs) {
         int half;
-        unit_tile(u, half);
+        const int t = unit_tile(u, half);
+        const int split = t / mn_tiles;
+        const int kb0 = split * kb_per_split, kb1 = min(kb_total, kb0 + kb_per_split);
         const uint32_t idesc = half < 0 ? idesc_full : idesc_half;
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
-        for (int kb = 0; kb < kb_total; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase)) { report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(sA + stage * Cfg::A_BYTES);
@@ -780,7 +787,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t da = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
             const uint64_t db = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
-            umma_f16_pair(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_f16_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           const uint32_t e = smem_u32(&empty[stage]);
           umma_commit_pair(e);                         // this CTA's stage is free ...
@@ -803,7 +810,8 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int u = pair; u < total_units; u += n_pairs) {
       int mi, ni, half;
       const int t = unit_tile(u, half);
-      tile_coords(t, m_tiles, n_tiles, 8, mi, ni);
+      const int split = t / mn_tiles;
+      tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.pair_group_m, mi, ni);
       bool ok = mbar_wait(&tfull[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
@@ -822,7 +830,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[acc]) & kPeerBitMask);    // the even CTA's barrier
         }
-        epilogue_chunk<256>(p, r, row, col_base + c * 32, 0, 0);
+        epilogue_chunk<256>(p, r, row, col_base + c * 32, split, 0);
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
@@ -1012,37 +1020,73 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
   p.act = act; p.accumulate = accumulate; p.alpha = alpha;
   p.status = status;
   p.group_m = 16;
+  static const int pair_group = []() { const char* e = std::getenv("OA_GEMM_PAIR_GROUP"); int v = e ? atoi(e) : 8; return v > 0 ? v : 8; }();
+  p.pair_group_m = pair_group;
   p.splits = 1;
   p.workspace = (float*)workspace;
   p.batch = batch; p.sc_batch = sc_batch; p.sr_batch = sr_batch; p.saux_batch = saux_batch; p.sbias_batch = sbias_batch;
   p.group_mode = 0; p.group_offsets = nullptr; p.tp_mode = 0; p.tp_comm = 0;
   bool plain = !bias && !residual && !aux_out && !aux_in && act == OA_ACT_NONE;
-  if (workspace && plain && (N % 4 == 0)) {
-    int s = oa_gemm_plan_splits(M * batch, N, K, bn, sms);
-    if (s > 1 && (size_t)s * batch * M * N * sizeof(float) <= workspace_bytes) p.splits = s;
-  }
+  const bool can_split = workspace && plain && (N % 4 == 0);
   CUtensorMap ta, tb;
   int rc;
-  // CTA-pair kernel: plain 2-D problems with at least one 256 x 256 tile per CTA pair (OA_GEMM_PAIR=0 switches it off)
+  cudaStream_t st = (cudaStream_t)stream;
+  // CTA-pair kernel: 2-D problems of at least one 256 x 256 tile (OA_GEMM_PAIR=0 switches it off).  With fewer tiles than CTA
+  // pairs the reduction is split (fp32 partials in the workspace, fixed-order reduce) so that the pairs are filled: the
+  // weight-gradient shapes (small M x N, K = tokens) run here.
   static const bool pair_enabled = []() { const char* e = std::getenv("OA_GEMM_PAIR"); return !(e && e[0] == '0'); }();
   const long long tiles2 = (long long)((M + 255) / 256) * ((N + 255) / 256);
-  if (pair_enabled && !force_bn && batch == 1 && p.splits == 1 && M >= 256 && N >= 256 && tiles2 >= sms / 2 && (sms & 1) == 0) {
-    if (a_mn) rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, 1, (uint64_t)lda, 0, 64, BK);
-    else      rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, 1, (uint64_t)lda, 0, BK, BM);
-    if (rc) return rc;
-    if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb, 0, 64, BK);
-    else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 128);
-    if (rc) return rc;
-    CUtensorMap tb2 = tb;                                    // 64-row boxes of K-major B for the half-width tail units
-    if (!b_mn) { rc = make_tmap_3d_bf16(&tb2, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 64); if (rc) return rc; }
-    cudaStream_t pst = (cudaStream_t)stream;
-    const int pgrid = (int)(tiles2 * 2 < sms ? tiles2 * 2 : sms);
-    switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
-      case 0: return launch_gemm_pair<0, 0>(ta, tb, tb2, p, pgrid, pst);
-      case 1: return launch_gemm_pair<0, 1>(ta, tb, tb2, p, pgrid, pst);
-      case 2: return launch_gemm_pair<1, 0>(ta, tb, tb2, p, pgrid, pst);
-      default: return launch_gemm_pair<1, 1>(ta, tb, tb2, p, pgrid, pst);
+  if (pair_enabled && !force_bn && batch == 1 && M >= 256 && N >= 256 && (sms & 1) == 0) {
+    const int P = sms / 2;
+    const int kb_total = (K + BK - 1) / BK;
+    int ps = 0;                                             // 0: do not use the pair kernel
+    if (tiles2 >= P) ps = 1;
+    else {
+      double best_eff = (double)tiles2 / P;
+      int best = 1;
+      if (can_split) {
+        for (int s2 = 2; s2 <= 16 && kb_total / s2 >= 16; ++s2) {
+          const int per = (kb_total + s2 - 1) / s2;
+          if ((long long)(s2 - 1) * per >= kb_total) continue;                    // an empty split
+          if ((size_t)s2 * M * N * sizeof(float) > workspace_bytes) break;
+          const long long u = tiles2 * s2;
+          const double eff = (double)u / (double)(((u + P - 1) / P) * P);
+          if (eff > best_eff + 0.04) { best_eff = eff; best = s2; }
+        }
+      }
+      if (best_eff >= 0.6) ps = best;
     }
+    if (ps > 0) {
+      p.splits = ps;
+      if (a_mn) rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, 1, (uint64_t)lda, 0, 64, BK);
+      else      rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, 1, (uint64_t)lda, 0, BK, BM);
+      if (rc) return rc;
+      if (b_mn) rc = make_tmap_3d_bf16(&tb, B, (uint64_t)N, (uint64_t)K, 1, (uint64_t)ldb, 0, 64, BK);
+      else      rc = make_tmap_3d_bf16(&tb, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 128);
+      if (rc) return rc;
+      CUtensorMap tb2 = tb;                                  // 64-row boxes of K-major B for the half-width tail units
+      if (!b_mn) { rc = make_tmap_3d_bf16(&tb2, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 64); if (rc) return rc; }
+      const long long units = tiles2 * ps;
+      const int pgrid = (int)(units * 2 < sms ? units * 2 : sms);
+      switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
+        case 0: rc = launch_gemm_pair<0, 0>(ta, tb, tb2, p, pgrid, st); break;
+        case 1: rc = launch_gemm_pair<0, 1>(ta, tb, tb2, p, pgrid, st); break;
+        case 2: rc = launch_gemm_pair<1, 0>(ta, tb, tb2, p, pgrid, st); break;
+        default: rc = launch_gemm_pair<1, 1>(ta, tb, tb2, p, pgrid, st); break;
+      }
+      if (rc) return rc;
+      if (p.splits > 1) {
+        size_t total4 = (size_t)M * N / 4;
+        unsigned blocks = (unsigned)((total4 + 255) / 256);
+        splitk_reduce_kernel<<<blocks, 256, 0, st>>>(p.workspace, p.splits, M, N, out, ldc, out_f32, accumulate, 1, 0);
+        if (cudaGetLastError() != cudaSuccess) return OA_ERR_LAUNCH;
+      }
+      return OA_OK;
+    }
+  }
+  if (can_split) {
+    int s = oa_gemm_plan_splits(M * batch, N, K, bn, sms);
+    if (s > 1 && (size_t)s * batch * M * N * sizeof(float) <= workspace_bytes) p.splits = s;
   }
   if (a_mn) rc = make_tmap_3d_bf16(&ta, A, (uint64_t)M, (uint64_t)K, batch, (uint64_t)lda, sa_batch, 64, BK);
   else      rc = make_tmap_3d_bf16(&ta, A, (uint64_t)K, (uint64_t)M, batch, (uint64_t)lda, sa_batch, BK, BM);
@@ -1052,7 +1096,6 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
   if (rc) return rc;
   long long tiles = (long long)batch * ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * p.splits;
   int grid = tiles < sms ? (int)tiles : sms;
-  cudaStream_t st = (cudaStream_t)stream;
   int sel = (bn == 256 ? 4 : 0) | (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   switch (sel) {
     case 0: rc = launch_gemm<128, 0, 0>(ta, tb, p, grid, st); break;
@@ -1098,7 +1141,7 @@ extern "C" int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void
   p.N = N; p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = (const __nv_bfloat16*)bias; p.residual = nullptr; p.ldr = 0;
   p.aux_out = (__nv_bfloat16*)aux_out; p.aux_in = (const __nv_bfloat16*)aux_in; p.ldaux = ldaux;
-  p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.splits = 1; p.workspace = nullptr;
+  p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.splits = 1; p.workspace = nullptr;
   p.batch = groups; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = sbias_batch;
   p.group_mode = mode; p.group_offsets = offsets; p.tp_mode = 0; p.tp_comm = 0;
   CUtensorMap ta, tb;
@@ -1153,7 +1196,7 @@ extern "C" int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out
   p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = nullptr; p.residual = (const __nv_bfloat16*)residual; p.ldr = ldr;
   p.aux_out = nullptr; p.aux_in = nullptr; p.ldaux = 0;
-  p.act = OA_ACT_NONE; p.accumulate = 0; p.alpha = alpha; p.status = status; p.group_m = 16; p.splits = 1; p.workspace = nullptr;
+  p.act = OA_ACT_NONE; p.accumulate = 0; p.alpha = alpha; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.splits = 1; p.workspace = nullptr;
   p.batch = 1; p.sc_batch = 0; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = 0;
   p.group_mode = 0; p.group_offsets = nullptr;
   p.tp_mode = mode; p.tp_world = world; p.tp_rank = rank; p.tp_comm = comm_ctas;
