@@ -36,10 +36,20 @@ class _Arena:
         self.params = list(params)
         self.dtype = params[0].Tensor().dtype
         self.device = params[0].Tensor().device
-        self.offsets, off = [], 0
-        for p in params:
-            self.offsets.append(off)
-            off += (p.NumElements() + _ALIGN_ELEMS - 1) // _ALIGN_ELEMS * _ALIGN_ELEMS
+        # Placement: parameters that are views of one storage (the row slices of a packed QKV / gate-up tensor) are laid
+        # out next to each other, in their order inside that storage, at the place of the group's first member, so that the
+        # packed view survives the move into the arena even when other parameters (biases) were registered in between.
+        # `params` / `offsets` stay in registration order: checkpoints and shards do not depend on the placement.
+        first, keys = {}, []
+        for i, p in enumerate(params):
+            t = p.Tensor()
+            sp = t.untyped_storage().data_ptr()
+            first.setdefault(sp, i)
+            keys.append((first[sp], t.storage_offset(), i))
+        self.offsets, off = [0] * len(params), 0
+        for _, _, i in sorted(keys):
+            self.offsets[i] = off
+            off += (params[i].NumElements() + _ALIGN_ELEMS - 1) // _ALIGN_ELEMS * _ALIGN_ELEMS
         self.numel = max(off, _ALIGN_ELEMS)
         alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
         self.flat = alloc(self.numel, self.dtype)
