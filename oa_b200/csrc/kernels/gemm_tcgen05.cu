@@ -1042,19 +1042,28 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
     int ps = 0;                                             // 0: do not use the pair kernel
     if (tiles2 >= P) ps = 1;
     else {
-      double best_eff = (double)tiles2 / P;
+      // Fewer tiles than CTA pairs: choose the split count by a cost model in microseconds.  A k-block of a 256 x 256 tile
+      // takes about 0.36 us in steady state, draining a tile about 2.5 us; the partials cost (splits + 1) passes over the
+      // fp32 output at the rate of the reduce kernel (about 4 TB/s).
+      auto cost = [&](int s2) {
+        const int per = (kb_total + s2 - 1) / s2;
+        const long long u = tiles2 * s2;
+        const double waves = (double)((u + P - 1) / P);
+        return waves * (per * 0.36 + 2.5) + (s2 > 1 ? (s2 + 1.0) * (double)M * N * 4.0 / 4.0e6 : 0.0);
+      };
       int best = 1;
+      double best_cost = cost(1);
       if (can_split) {
         for (int s2 = 2; s2 <= 16 && kb_total / s2 >= 16; ++s2) {
           const int per = (kb_total + s2 - 1) / s2;
           if ((long long)(s2 - 1) * per >= kb_total) continue;                    // an empty split
           if ((size_t)s2 * M * N * sizeof(float) > workspace_bytes) break;
-          const long long u = tiles2 * s2;
-          const double eff = (double)u / (double)(((u + P - 1) / P) * P);
-          if (eff > best_eff + 0.04) { best_eff = eff; best = s2; }
+          const double c = cost(s2);
+          if (c < best_cost * 0.97) { best_cost = c; best = s2; }
         }
       }
-      if (best_eff >= 0.6) ps = best;
+      // worth a CTA-pair launch when the pairs are reasonably filled for most of the run
+      if ((double)(tiles2 * best) / P >= 0.5) ps = best;
     }
     if (ps > 0) {
       p.splits = ps;
