@@ -52,6 +52,10 @@ __version__ = _impl.__version__
 # ---- root values
 OaScalarType, OaMatMulPrecision, OaMatrixShape, OaPrecision = _T.OaScalarType, _T.OaMatMulPrecision, _T.OaMatrixShape, _T.OaPrecision
 OaStatus, OaStatusCode, OaError = _T.OaStatus, _T.OaStatusCode, _T.OaError
+OaEnumToString, OaEnumFromString = _T.OaEnumToString, _T.OaEnumFromString
+OaScalarTypeToString, OaScalarTypeFromString = _T.OaScalarTypeToString, _T.OaScalarTypeFromString
+OaPrecisionToString, OaPrecisionFromString = _T.OaPrecisionToString, _T.OaPrecisionFromString
+OaMatMulPrecisionToString, OaMatMulPrecisionFromString = _T.OaMatMulPrecisionToString, _T.OaMatMulPrecisionFromString
 OaContext, OaContextGetDefault = _RT.OaContext, _RT.OaContextGetDefault
 OaInitComputeEngine, OaShutdownComputeEngine = _RT.OaInitComputeEngine, _RT.OaShutdownComputeEngine
 OaEngine, OaEngineConfig = _RT.OaEngine, _RT.OaEngineConfig

@@ -151,3 +151,29 @@ class OaMatrixShape(tuple):
             s.append(acc)
             acc *= d
         return tuple(reversed(s))
+
+
+# ---- string forms of every enumeration of this module (Source/Public/Oa/Core/Type.gen.h: <Type>ToString / <Type>FromString,
+# which the reference generates from its type schemas; here they are derived from the IntEnum classes themselves)
+def OaEnumToString(value) -> str:
+    return value.name if isinstance(value, enum.Enum) else str(value)
+
+
+def OaEnumFromString(cls, text: str, default=None):
+    """Case-insensitive member lookup; `default` (or the first member) for an unknown string, as the reference does."""
+    want = str(text).strip().lower()
+    for m in cls:
+        if m.name.lower() == want:
+            return m
+    return default if default is not None else list(cls)[0]
+
+
+def _make_string_functions() -> None:
+    g = globals()
+    for name, obj in list(g.items()):
+        if isinstance(obj, type) and issubclass(obj, enum.IntEnum) and obj is not enum.IntEnum and name.startswith("Oa"):
+            g[name + "ToString"] = (lambda v, _c=obj: OaEnumToString(_c(v)))
+            g[name + "FromString"] = (lambda text, _c=obj: OaEnumFromString(_c, text))
+
+
+_make_string_functions()

@@ -52,3 +52,13 @@ def test_errors_do_not_raise(tmp_path, capsys):
     assert "YAML load failed" in c.Error
     assert "--lr" in Cli().Usage() and "--help-all" in Cli().Usage()
     capsys.readouterr()
+
+
+def test_enum_string_forms():
+    """<Type>ToString / <Type>FromString of the generated type header (Source/Public/Oa/Core/Type.gen.h:15-66)."""
+    import oa
+    assert oa.OaScalarTypeToString(oa.OaScalarType.BFloat16) == "BFloat16" and oa.OaScalarTypeFromString("bfloat16") == oa.OaScalarType.BFloat16
+    assert oa.OaPrecisionFromString("BF16") == oa.OaPrecision.BF16 and oa.OaPrecisionToString(0) == "FP32"
+    assert oa.OaPrecisionFromString("no such precision") == oa.OaPrecision.FP32            # unknown text: the first member
+    assert oa.OaMatMulPrecisionFromString(" fp32 ") == oa.OaMatMulPrecision.Fp32
+    assert oa.OaEnumFromString(oa.OaStatusCode, "notfound") == oa.OaStatusCode.NotFound and oa.OaEnumToString(oa.OaStatusCode.Ok) == "Ok"
