@@ -63,6 +63,36 @@ def bench_gemm():
     K.check_status()
 
 
+def bench_gemm_epilogue():
+    """The fused epilogues of the flagship's FFN GEMMs against the plain product of the same shape (the epilogue should hide
+    under the next tile's main loop) and against the library sequence that a framework without fusion runs."""
+    import torch.nn.functional as Fn
+    M, D, Ff = 16384, 1024, 4096
+    x = torch.randn(M, D, device="cuda").bfloat16()
+    w1 = torch.randn(Ff, D, device="cuda").bfloat16() * 0.03
+    g = torch.randn(M, D, device="cuda").bfloat16()
+    w2 = torch.randn(D, Ff, device="cuda").bfloat16() * 0.03
+    z = torch.empty(M, Ff, device="cuda", dtype=torch.bfloat16)
+    h = torch.empty(M, Ff, device="cuda", dtype=torch.bfloat16)
+    res = torch.randn(M, D, device="cuda").bfloat16()
+    o = torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
+    t_plain = timeit(lambda: K.gemm(x, w1, out=h))
+    t_gelu = timeit(lambda: K.gemm(x, w1, act=K.ACT_GELU, aux_out=z, out=h))
+    t_bwd = timeit(lambda: K.gemm(g, w2, b_mn=True, act=K.ACT_GELU_BWD, aux_in=z, out=h))
+    t_bwd_plain = timeit(lambda: K.gemm(g, w2, b_mn=True, out=h))
+    t_res = timeit(lambda: K.gemm(h, w2, residual=res, out=o))
+    t_res_plain = timeit(lambda: K.gemm(h, w2, out=o))
+
+    def lib_fwd():
+        torch.matmul(x, w1.t(), out=z)
+        return Fn.gelu(z, approximate="tanh")
+
+    t_lib = timeit(lib_fwd)
+    emit(op="gemm_epilogue", M=M, N=Ff, K=D, plain_ms=t_plain, gelu_aux_out_ms=t_gelu, gelu_bwd_aux_in_ms=t_bwd, gelu_bwd_plain_ms=t_bwd_plain,
+         residual_ms=t_res, residual_plain_ms=t_res_plain, cublas_plus_gelu_kernel_ms=t_lib)
+    K.check_status()
+
+
 def bench_gemm_small_m():
     """Weight-streaming GEMMs of a decode step (32 rows): time against weight bytes, own kernel and cuBLAS."""
     for (M, N, Kk) in [(32, 12288, 4096), (32, 4096, 4096), (32, 22016, 4096), (32, 4096, 11008), (32, 32000, 4096)]:
@@ -378,7 +408,7 @@ def main() -> int:
     ap.add_argument("--only", default="gemm,flash,bw")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image, "decode_attn": bench_decode_attn, "gemm_small_m": bench_gemm_small_m, "misc": bench_misc}
+    table = {"gemm": bench_gemm, "flash": bench_flash, "bw": bench_bw, "mamba": bench_mamba, "mamba1": bench_mamba_once, "tp": bench_tp, "decode": bench_decode, "prof": bench_prof, "image": bench_image, "decode_attn": bench_decode_attn, "gemm_small_m": bench_gemm_small_m, "gemm_epi": bench_gemm_epilogue, "misc": bench_misc}
     for name in args.only.split(","):
         table[name.strip()]()
     if args.out and int(os.environ.get("RANK", "0")) == 0:

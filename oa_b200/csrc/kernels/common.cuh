@@ -378,6 +378,30 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   float du = k0 * (1.f + 3.f * k1 * x * x);
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * du;
 }
+// tanh on the special-function unit (one MUFU operation, relative error about 2^-11): for epilogues whose result is rounded
+// to bf16 anyway.  The exact tanhf above costs 20+ instructions per element, which made a fused GELU epilogue three times
+// longer than the main loop of its tile.
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float x2 = x * x;
+  const float t = tanh_approx(x * fmaf(k0 * k1, x2, k0));
+  const float hx = 0.5f * x;
+  return fmaf(hx, t, hx);
+}
+__device__ __forceinline__ float gelu_tanh_grad_fast(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float x2 = x * x;
+  const float t = tanh_approx(x * fmaf(k0 * k1, x2, k0));
+  const float du = fmaf(3.f * k0 * k1, x2, k0);
+  const float hx = 0.5f * x;
+  // 0.5 (1 + t) + 0.5 x (1 - t^2) du
+  return fmaf(hx * du, fmaf(-t, t, 1.f), fmaf(0.5f, t, 0.5f));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

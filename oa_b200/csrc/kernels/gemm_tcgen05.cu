@@ -49,6 +49,7 @@ struct GemmParams {
   float* workspace;                // [splits, M, N] fp32
   int group_m;
   int pair_group_m;                // m tiles per raster group of the CTA-pair kernel
+  int epi_prefetch;                // CTA-pair kernel: fetch aux_in / residual one chunk ahead
   int* status;
   int batch;                       // independent problems of the same shape (tensor maps are rank 3)
   long long sc_batch, sr_batch, saux_batch, sbias_batch;   // element strides between problems
@@ -146,8 +147,11 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t, cons
   return ti;
 }
 
+// `pre` (may be null): the four 16-byte pieces of this row's saved pre-activation (aux_in) or, when there is no aux_in, of its
+// residual, loaded by the caller ahead of time so that the load latency is not paid between tcgen05.ld and the store.
 template <int BN>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int split, int bi) {
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int split, int bi,
+                                               const uint4* pre = nullptr) {
   if (row >= p.M || col0 >= p.N) return;
   // N is a multiple of 8, so every 8-column group is either fully inside or fully outside.
   int ncols = min(32, p.N - col0);
@@ -184,7 +188,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
   if (p.act == OA_ACT_GELU) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = gelu_tanh(v[i]);
+    for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
   } else if (p.act == OA_ACT_RELU) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
@@ -197,14 +201,14 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       if (g * 8 < ncols) {
-        uint4 b = *reinterpret_cast<const uint4*>(a + g * 8);
+        uint4 b = pre ? pre[g] : *reinterpret_cast<const uint4*>(a + g * 8);
         uint32_t w[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 z = unpack_bf16x2(w[j]);
           if (p.act == OA_ACT_GELU_BWD) {
-            v[g * 8 + 2 * j] *= gelu_tanh_grad(z.x);
-            v[g * 8 + 2 * j + 1] *= gelu_tanh_grad(z.y);
+            v[g * 8 + 2 * j] *= gelu_tanh_grad_fast(z.x);
+            v[g * 8 + 2 * j + 1] *= gelu_tanh_grad_fast(z.y);
           } else {  // OA_ACT_RELU_BWD
             v[g * 8 + 2 * j] = z.x > 0.f ? v[g * 8 + 2 * j] : 0.f;
             v[g * 8 + 2 * j + 1] = z.y > 0.f ? v[g * 8 + 2 * j + 1] : 0.f;
@@ -215,10 +219,11 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
   }
   if (p.residual) {
     const __nv_bfloat16* a = p.residual + bi * p.sr_batch + (size_t)row * p.ldr + col0;
+    const uint4* rpre = p.aux_in ? nullptr : pre;
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       if (g * 8 < ncols) {
-        uint4 b = *reinterpret_cast<const uint4*>(a + g * 8);
+        uint4 b = rpre ? rpre[g] : *reinterpret_cast<const uint4*>(a + g * 8);
         float2 f0 = unpack_bf16x2(b.x), f1 = unpack_bf16x2(b.y), f2 = unpack_bf16x2(b.z), f3 = unpack_bf16x2(b.w);
         v[g * 8 + 0] += f0.x; v[g * 8 + 1] += f0.y; v[g * 8 + 2] += f1.x; v[g * 8 + 3] += f1.y;
         v[g * 8 + 4] += f2.x; v[g * 8 + 5] += f2.y; v[g * 8 + 6] += f3.x; v[g * 8 + 7] += f3.y;
@@ -820,17 +825,29 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256;
       const int chunks = half < 0 ? 8 : 4;
       const int col_base = ni * 256 + (half < 0 ? 0 : half * 128);
+      // the saved pre-activation (or the residual) of chunk c + 1 is fetched while chunk c is worked on
+      const __nv_bfloat16* pre_base = (p.splits > 1 || !p.epi_prefetch) ? nullptr : (p.aux_in ? p.aux_in + (size_t)row * p.ldaux : (p.residual ? p.residual + (size_t)row * p.ldr : nullptr));
+      uint4 nxt[4];
+      auto prefetch = [&](int c) {
+        const int col = col_base + c * 32;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          nxt[g] = (pre_base && row < p.M && col + g * 8 < p.N) ? __ldg(reinterpret_cast<const uint4*>(pre_base + col + g * 8)) : make_uint4(0, 0, 0, 0);
+      };
+      prefetch(0);
 #pragma unroll 1
       for (int c = 0; c < chunks; ++c) {
         uint32_t r[32];
+        uint4 cur[4] = {nxt[0], nxt[1], nxt[2], nxt[3]};
         tmem_ld32(taddr + c * 32, r);
+        if (c + 1 < chunks) prefetch(c + 1);
         tmem_ld_wait();
         if (c == chunks - 1) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[acc]) & kPeerBitMask);    // the even CTA's barrier
         }
-        epilogue_chunk<256>(p, r, row, col_base + c * 32, split, 0);
+        epilogue_chunk<256>(p, r, row, col_base + c * 32, split, 0, pre_base ? cur : nullptr);
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
@@ -1022,6 +1039,8 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
   p.group_m = 16;
   static const int pair_group = []() { const char* e = std::getenv("OA_GEMM_PAIR_GROUP"); int v = e ? atoi(e) : 8; return v > 0 ? v : 8; }();
   p.pair_group_m = pair_group;
+  static const int epi_pf = []() { const char* e = std::getenv("OA_GEMM_EPI_PREFETCH"); return (e && e[0] == '0') ? 0 : 1; }();
+  p.epi_prefetch = epi_pf;
   p.splits = 1;
   p.workspace = (float*)workspace;
   p.batch = batch; p.sc_batch = sc_batch; p.sr_batch = sr_batch; p.saux_batch = saux_batch; p.sbias_batch = sbias_batch;
@@ -1150,7 +1169,7 @@ extern "C" int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void
   p.N = N; p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = (const __nv_bfloat16*)bias; p.residual = nullptr; p.ldr = 0;
   p.aux_out = (__nv_bfloat16*)aux_out; p.aux_in = (const __nv_bfloat16*)aux_in; p.ldaux = ldaux;
-  p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.splits = 1; p.workspace = nullptr;
+  p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.epi_prefetch = 0; p.splits = 1; p.workspace = nullptr;
   p.batch = groups; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = sbias_batch;
   p.group_mode = mode; p.group_offsets = offsets; p.tp_mode = 0; p.tp_comm = 0;
   CUtensorMap ta, tb;
@@ -1205,7 +1224,7 @@ extern "C" int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out
   p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = nullptr; p.residual = (const __nv_bfloat16*)residual; p.ldr = ldr;
   p.aux_out = nullptr; p.aux_in = nullptr; p.ldaux = 0;
-  p.act = OA_ACT_NONE; p.accumulate = 0; p.alpha = alpha; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.splits = 1; p.workspace = nullptr;
+  p.act = OA_ACT_NONE; p.accumulate = 0; p.alpha = alpha; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.epi_prefetch = 0; p.splits = 1; p.workspace = nullptr;
   p.batch = 1; p.sc_batch = 0; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = 0;
   p.group_mode = 0; p.group_offsets = nullptr;
   p.tp_mode = mode; p.tp_world = world; p.tp_rank = rank; p.tp_comm = comm_ctas;

@@ -85,6 +85,20 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
     ref32 = 2 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn)
     _close(out32, ref32, 1e-2, what="pair gemm fp32 accumulate")
     _close_gemm_bf16(out32, ref32, K_, what="pair gemm fp32 accumulate (per element)", out_bf16=False)
+    # the coalesced (shared-memory staged) epilogue: pre-activation copy out, saved pre-activation in, bf16 output
+    aux = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=K.ACT_GELU, aux_out=aux)
+    aux_ref = torch.empty(M, N)
+    ref = K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn, bias=bias.cpu().float(), act=K.ACT_GELU, aux_out=aux_ref)
+    _close(out, ref, 1e-2, what="pair gemm bias+gelu with pre-activation copy")
+    _close(aux, aux_ref, 1e-2, what="pair gemm pre-activation copy")
+    z = _rand(M, N)
+    for act in (K.ACT_GELU_BWD, K.ACT_RELU_BWD):
+        got = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, act=act, aux_in=z)
+        want = K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn, act=act, aux_in=z.cpu().float())
+        _close(got, want, 1e-2, what=f"pair gemm activation backward {act}")
+    plain = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, alpha=0.5)
+    _close(plain, 0.5 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn), 1e-2, what="pair gemm plain bf16 store")
 
 
 @pytest.mark.parametrize("bn", [128, 256])
