@@ -671,10 +671,14 @@ struct PairCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 512;                  // two 256-column accumulators
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  // Warps 0 and 1 load and issue; 4 or 8 epilogue warps follow.  A warp reads the TMEM lanes of its index modulo 4, so with
+  // eight warps two of them share a lane quarter and take half of the accumulator's columns each: one warp per scheduler
+  // leaves every dependency stall of the epilogue arithmetic exposed, two hide most of them.
+  static constexpr int MAX_THREADS = 64 + 8 * 32;
 };
 
 template <int A_MN, int B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::MAX_THREADS, 1)
 gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
   using Cfg = PairCfg;
@@ -687,10 +691,11 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint64_t* full = bars;                 // used in the even CTA: bytes of both CTAs' loads
   uint64_t* empty = bars + STAGES;       // per CTA: the pair's MMA has consumed this CTA's stage
   uint64_t* tfull = bars + 2 * STAGES;   // per CTA: accumulator ready
-  uint64_t* tempty = bars + 2 * STAGES + 2;   // even CTA: 8 epilogue warps (4 per CTA) have drained the accumulator
+  uint64_t* tempty = bars + 2 * STAGES + 2;   // even CTA: the epilogue warps of both CTAs have drained the accumulator
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int epi_warps = (int)(blockDim.x >> 5) - 2;      // 4 or 8
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
@@ -716,7 +721,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmB2);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 2 * epi_warps); }
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc_pair<Cfg::TMEM_COLS>(tmem_slot); tmem_relinquish_pair(); }
@@ -774,6 +779,13 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      // The issuing thread is a single dependent instruction stream, so everything that does not change per k-block is
+      // computed once: the descriptors of stage 0 (a later stage or k-step only adds to the 14-bit address field, which
+      // cannot carry because shared memory ends below 256 KB) and the distance to the odd CTA's copy of a barrier.
+      const uint64_t da0 = umma_smem_desc_sw128(smem_u32(sA), a_lbo, 1024);
+      const uint64_t db0 = umma_smem_desc_sw128(smem_u32(sB), b_lbo, 1024);
+      const uint32_t empty0 = smem_u32(&empty[0]), tfull0 = smem_u32(&tfull[0]);
+      const uint32_t peer_delta = map_to_cta(empty0, 1) - empty0;
       for (int u = pair; u < total_units && ok; u += n_pairs) {
         int half;
         const int t = unit_tile(u, half);
@@ -783,26 +795,26 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
+        uint32_t accumulate = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase)) { report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * Cfg::A_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * Cfg::B_BYTES);
+          const uint64_t da = da0 + (uint64_t)((stage * Cfg::A_BYTES) >> 4);
+          const uint64_t db = db0 + (uint64_t)((stage * Cfg::B_BYTES) >> 4);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t da = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, 1024);
-            const uint64_t db = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, 1024);
-            umma_f16_pair(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            umma_f16_pair(d_tmem, da + (uint64_t)((k * a_kstep) >> 4), db + (uint64_t)((k * b_kstep) >> 4), idesc, k > 0 ? 1u : accumulate);
           }
-          const uint32_t e = smem_u32(&empty[stage]);
+          accumulate = 1;
+          const uint32_t e = empty0 + stage * 8;
           umma_commit_pair(e);                         // this CTA's stage is free ...
-          umma_commit_pair(map_to_cta(e, 1));          // ... and so is the odd CTA's
+          umma_commit_pair(e + peer_delta);            // ... and so is the odd CTA's
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        const uint32_t f = smem_u32(&tfull[acc]);
+        const uint32_t f = tfull0 + acc * 8;
         umma_commit_pair(f);
-        umma_commit_pair(map_to_cta(f, 1));
+        umma_commit_pair(f + peer_delta);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
@@ -810,6 +822,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   } else {
     // ---------------- epilogue warps of both CTAs: each drains its own 128 accumulator rows
     const int quad = warp & 3;
+    const int part = (warp - 2) >> 2, parts = epi_warps >> 2;      // which share of the unit's columns this warp drains
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int u = pair; u < total_units; u += n_pairs) {
@@ -822,9 +835,9 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
       tc_fence_after();
       const int row = mi * 256 + (int)rank * 128 + quad * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256;
-      const int chunks = half < 0 ? 8 : 4;
-      const int col_base = ni * 256 + (half < 0 ? 0 : half * 128);
+      const int chunks = (half < 0 ? 8 : 4) / parts;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + part * chunks * 32;
+      const int col_base = ni * 256 + (half < 0 ? 0 : half * 128) + part * chunks * 32;
       // the saved pre-activation (or the residual) of chunk c + 1 is fetched while chunk c is worked on
       const __nv_bfloat16* pre_base = (p.splits > 1 || !p.epi_prefetch) ? nullptr : (p.aux_in ? p.aux_in + (size_t)row * p.ldaux : (p.residual ? p.residual + (size_t)row * p.ldr : nullptr));
       uint4 nxt[4];
@@ -868,7 +881,8 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
     attr_set = true;
   }
-  kfn<<<grid, 192, PairCfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
+  static const int epi_warps = [] { const char* e = getenv("OA_GEMM_PAIR_EPI_WARPS"); return (e && atoi(e) == 4) ? 4 : 8; }();
+  kfn<<<grid, 64 + 32 * epi_warps, PairCfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
