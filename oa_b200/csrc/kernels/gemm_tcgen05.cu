@@ -50,6 +50,7 @@ struct GemmParams {
   int group_m;
   int pair_group_m;                // m tiles per raster group of the CTA-pair kernel
   int epi_prefetch;                // CTA-pair kernel: fetch aux_in / residual one chunk ahead
+  int tma_store;                   // CTA-pair kernel: bf16 output (and aux_out) leave through TMA stores
   int* status;
   int batch;                       // independent problems of the same shape (tensor maps are rank 3)
   long long sc_batch, sr_batch, saux_batch, sbias_batch;   // element strides between problems
@@ -149,12 +150,42 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t, cons
 
 // `pre` (may be null): the four 16-byte pieces of this row's saved pre-activation (aux_in) or, when there is no aux_in, of its
 // residual, loaded by the caller ahead of time so that the load latency is not paid between tcgen05.ld and the store.
+// Output through TMA stores (CTA-pair kernel, bf16 output without accumulation): a warp's [32 rows x 32 columns] piece is
+// written to a 2 KB shared-memory buffer in the 64-byte swizzle of the tensor map (conflict-free 16-byte stores) and one lane
+// issues the bulk store, which writes whole 64-byte row segments and clips what lies outside the matrix.  Per-lane 16-byte
+// global stores of 32 different rows cost one L1 pass per row and kept the epilogue of a K = 1024 product longer than its
+// main loop.  Two buffers per warp: a buffer is rewritten once the store issued two stores ago has read it.
+struct TmaStoreCtx {
+  const CUtensorMap* out;
+  const CUtensorMap* aux;
+  uint8_t* buf;          // this warp's 2 x 2 KB
+  uint32_t n;            // stores issued by this warp
+  int row0;              // first row of the warp's 32
+};
+__device__ __forceinline__ void tma_store_piece(TmaStoreCtx* ts, const CUtensorMap* m, const float* v, int col0) {
+  const int lane = threadIdx.x & 31;
+  uint8_t* b = ts->buf + (ts->n & 1) * 2048;
+  if (lane == 0) tma_store_wait_read1();
+  __syncwarp();
+  const uint32_t base = smem_u32(b) + lane * 64;
+  const int sw = (lane >> 1) & 3;                       // 64-byte swizzle: 16-byte piece index ^= address bits 7..8
+#pragma unroll
+  for (int g = 0; g < 4; ++g)
+    st_shared_v4(base + ((g ^ sw) << 4), make_uint4(pack_bf16x2(v[g * 8], v[g * 8 + 1]), pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
+                                                    pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7])));
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) { tma_store_2d(m, b, col0, ts->row0); tma_store_commit(); }
+  ++ts->n;
+}
+
 template <int BN>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t* r, int row, int col0, int split, int bi,
-                                               const uint4* pre = nullptr) {
-  if (row >= p.M || col0 >= p.N) return;
+                                               const uint4* pre = nullptr, TmaStoreCtx* ts = nullptr) {
+  if (col0 >= p.N) return;                              // uniform over the warp
+  if (ts ? ts->row0 >= p.M : row >= p.M) return;        // with TMA stores the whole warp stays (rows past M are clipped)
   // N is a multiple of 8, so every 8-column group is either fully inside or fully outside.
-  int ncols = min(32, p.N - col0);
+  int ncols = row < p.M ? min(32, p.N - col0) : 0;
   float v[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -177,7 +208,9 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       }
     }
   }
-  if (p.aux_out) {
+  if (p.aux_out && ts) {
+    tma_store_piece(ts, ts->aux, v, col0);
+  } else if (p.aux_out) {
     __nv_bfloat16* a = p.aux_out + bi * p.saux_batch + (size_t)row * p.ldaux + col0;
 #pragma unroll
     for (int g = 0; g < 4; ++g)
@@ -230,7 +263,9 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       }
     }
   }
-  if (p.out_f32) {
+  if (ts) {
+    tma_store_piece(ts, ts->out, v, col0);
+  } else if (p.out_f32) {
     float* o = reinterpret_cast<float*>(p.out) + bi * p.sc_batch + (size_t)row * p.ldc + col0;
 #pragma unroll
     for (int g = 0; g < 8; ++g) {
@@ -670,24 +705,33 @@ struct PairCfg {
   static constexpr int B_BYTES = 128 * BK * 2;           // this CTA's 128 of the tile's 256 rows of B
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 512;                  // two 256-column accumulators
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int STORE_BYTES = 8 * 2 * 2048;       // TMA-store staging: two 2 KB buffers per epilogue warp
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STORE_BYTES + 1024 + 256;
   // Warps 0 and 1 load and issue; 4 or 8 epilogue warps follow.  A warp reads the TMEM lanes of its index modulo 4, so with
   // eight warps two of them share a lane quarter and take half of the accumulator's columns each: one warp per scheduler
   // leaves every dependency stall of the epilogue arithmetic exposed, two hide most of them.
   static constexpr int MAX_THREADS = 64 + 8 * 32;
 };
 
+#ifdef OA_GEMM_PROBE
+// Diagnostic build only (-DOA_GEMM_PROBE): per CTA pair, clocks that the MMA issuer spent in total / waiting for loads /
+// waiting for a drained accumulator, and clocks that the even CTA's producer spent waiting for a free stage.
+__device__ long long g_pair_probe[128 * 4];
+#endif
+
 template <int A_MN, int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::MAX_THREADS, 1)
 gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+                      const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC,
+                      const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using Cfg = PairCfg;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * Cfg::A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint8_t* sC = smem + STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sC + Cfg::STORE_BYTES);
   uint64_t* full = bars;                 // used in the even CTA: bytes of both CTAs' loads
   uint64_t* empty = bars + STAGES;       // per CTA: the pair's MMA has consumed this CTA's stage
   uint64_t* tfull = bars + 2 * STAGES;   // per CTA: accumulator ready
@@ -720,6 +764,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     tma_prefetch_desc(&tmB2);
+    if (p.tma_store) { tma_prefetch_desc(&tmC); tma_prefetch_desc(&tmAux); }
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 2 * epi_warps); }
     mbar_fence_init();
@@ -737,6 +782,9 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+#ifdef OA_GEMM_PROBE
+      long long w_empty = 0;
+#endif
       for (int u = pair; u < total_units && ok; u += n_pairs) {
         int mi, ni, half;
         const int t = unit_tile(u, half);
@@ -747,7 +795,13 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t stage_bytes = half < 0 ? 2 * Cfg::STAGE_BYTES : 2 * (Cfg::A_BYTES + Cfg::B_BYTES / 2);
         const int kb0 = split * kb_per_split, kb1 = min(kb_total, kb0 + kb_per_split);
         for (int kb = kb0; kb < kb1; ++kb) {
+#ifdef OA_GEMM_PROBE
+          const long long c0 = clock64();
+#endif
           if (!mbar_wait(&empty[stage], phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_EMPTY); ok = false; break; }
+#ifdef OA_GEMM_PROBE
+          w_empty += clock64() - c0;
+#endif
           if (leader) mbar_expect_tx(&full[stage], stage_bytes);
           uint8_t* a = sA + stage * Cfg::A_BYTES;
           uint8_t* b = sB + stage * Cfg::B_BYTES;
@@ -768,6 +822,9 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+#ifdef OA_GEMM_PROBE
+      if (leader && pair < 128) g_pair_probe[pair * 4 + 3] = w_empty;
+#endif
     }
   } else if (warp == 1) {
     if (lane == 0 && leader) {
@@ -786,18 +843,34 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const uint64_t db0 = umma_smem_desc_sw128(smem_u32(sB), b_lbo, 1024);
       const uint32_t empty0 = smem_u32(&empty[0]), tfull0 = smem_u32(&tfull[0]);
       const uint32_t peer_delta = map_to_cta(empty0, 1) - empty0;
+#ifdef OA_GEMM_PROBE
+      long long w_full = 0, w_acc = 0;
+      const long long t_begin = clock64();
+#endif
       for (int u = pair; u < total_units && ok; u += n_pairs) {
         int half;
         const int t = unit_tile(u, half);
         const int split = t / mn_tiles;
         const int kb0 = split * kb_per_split, kb1 = min(kb_total, kb0 + kb_per_split);
         const uint32_t idesc = half < 0 ? idesc_full : idesc_half;
+#ifdef OA_GEMM_PROBE
+        const long long c0 = clock64();
+#endif
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1)) { report_error(p.status, OA_KERR_WAIT_TMEM_EMPTY); break; }
+#ifdef OA_GEMM_PROBE
+        w_acc += clock64() - c0;
+#endif
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
         uint32_t accumulate = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
+#ifdef OA_GEMM_PROBE
+          const long long c1 = clock64();
+#endif
           if (!mbar_wait(&full[stage], phase)) { report_error(p.status, OA_KERR_WAIT_FULL); ok = false; break; }
+#ifdef OA_GEMM_PROBE
+          w_full += clock64() - c1;
+#endif
           tc_fence_after();
           const uint64_t da = da0 + (uint64_t)((stage * Cfg::A_BYTES) >> 4);
           const uint64_t db = db0 + (uint64_t)((stage * Cfg::B_BYTES) >> 4);
@@ -818,6 +891,13 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
+#ifdef OA_GEMM_PROBE
+      if (pair < 128) {
+        g_pair_probe[pair * 4 + 0] = clock64() - t_begin;
+        g_pair_probe[pair * 4 + 1] = w_full;
+        g_pair_probe[pair * 4 + 2] = w_acc;
+      }
+#endif
     }
   } else {
     // ---------------- epilogue warps of both CTAs: each drains its own 128 accumulator rows
@@ -825,11 +905,14 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int part = (warp - 2) >> 2, parts = epi_warps >> 2;      // which share of the unit's columns this warp drains
     int acc = 0;
     uint32_t acc_phase = 0;
+    TmaStoreCtx tsc{&tmC, &tmAux, sC + (warp - 2) * 4096, 0u, 0};
+    TmaStoreCtx* ts = p.tma_store ? &tsc : nullptr;
     for (int u = pair; u < total_units; u += n_pairs) {
       int mi, ni, half;
       const int t = unit_tile(u, half);
       const int split = t / mn_tiles;
       tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.pair_group_m, mi, ni);
+      tsc.row0 = mi * 256 + (int)rank * 128 + quad * 32;
       bool ok = mbar_wait(&tfull[acc], acc_phase);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { if (lane == 0) report_error(p.status, OA_KERR_WAIT_TMEM_FULL); break; }
@@ -860,11 +943,12 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[acc]) & kPeerBitMask);    // the even CTA's barrier
         }
-        epilogue_chunk<256>(p, r, row, col_base + c * 32, split, 0, pre_base ? cur : nullptr);
+        epilogue_chunk<256>(p, r, row, col_base + c * 32, split, 0, pre_base ? cur : nullptr, ts);
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (ts && lane == 0) tma_store_wait_read0();         // the staging buffers stay valid until the last store has read them
   }
   tc_fence_before();
   __syncthreads();
@@ -873,8 +957,8 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 }
 
 template <int A_MN, int B_MN>
-static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p, int grid,
-                            cudaStream_t st) {
+static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tc,
+                            const CUtensorMap& taux, const GemmParams& p, int grid, cudaStream_t st) {
   auto kfn = gemm_pair_bf16_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -882,7 +966,7 @@ static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const 
     attr_set = true;
   }
   static const int epi_warps = [] { const char* e = getenv("OA_GEMM_PAIR_EPI_WARPS"); return (e && atoi(e) == 4) ? 4 : 8; }();
-  kfn<<<grid, 64 + 32 * epi_warps, PairCfg::SMEM_BYTES, st>>>(ta, tb, tb2, p);
+  kfn<<<grid, 64 + 32 * epi_warps, PairCfg::SMEM_BYTES, st>>>(ta, tb, tb2, tc, taux, p);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
@@ -940,7 +1024,7 @@ static PFN_encodeTiled get_encode() {
 
 // 2-D bf16 tensor map: inner (contiguous) extent `inner`, outer extent `outer`, row pitch `ld` elements.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
-                      uint32_t box_inner, uint32_t box_outer) {
+                      uint32_t box_inner, uint32_t box_outer, int swizzle_bytes) {
   PFN_encodeTiled enc = get_encode();
   if (!enc) return OA_ERR_DRIVER;
   if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15)) return OA_ERR_ALIGN;
@@ -949,9 +1033,15 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OA_OK : OA_ERR_DRIVER;
+}
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t ld,
+                      uint32_t box_inner, uint32_t box_outer) {
+  return make_tmap_2d_bf16(out, ptr, inner, outer, ld, box_inner, box_outer, 128);
 }
 
 // 3-D bf16 tensor map: [batch][outer][inner], box = one [box_outer x box_inner] tile of one problem.
@@ -970,6 +1060,12 @@ int make_tmap_3d_bf16(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? OA_OK : OA_ERR_DRIVER;
 }
+
+#ifdef OA_GEMM_PROBE
+extern "C" int oa_gemm_pair_probe_read(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_pair_probe, sizeof(long long) * (n < 512 ? n : 512)) == cudaSuccess ? OA_OK : OA_ERR_DRIVER;
+}
+#endif
 
 int num_sms() {
   static int n = 0;
@@ -1055,6 +1151,7 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
   p.pair_group_m = pair_group;
   static const int epi_pf = []() { const char* e = std::getenv("OA_GEMM_EPI_PREFETCH"); return (e && e[0] == '0') ? 0 : 1; }();
   p.epi_prefetch = epi_pf;
+  p.tma_store = 0;
   p.splits = 1;
   p.workspace = (float*)workspace;
   p.batch = batch; p.sc_batch = sc_batch; p.sr_batch = sr_batch; p.saux_batch = saux_batch; p.sbias_batch = sbias_batch;
@@ -1108,13 +1205,22 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
       if (rc) return rc;
       CUtensorMap tb2 = tb;                                  // 64-row boxes of K-major B for the half-width tail units
       if (!b_mn) { rc = make_tmap_3d_bf16(&tb2, B, (uint64_t)K, (uint64_t)N, 1, (uint64_t)ldb, 0, BK, 64); if (rc) return rc; }
+      // bf16 output without accumulation leaves through TMA stores ([32 x 32] boxes, 64-byte swizzle); OA_GEMM_TMA_STORE=0
+      // keeps the per-lane stores
+      static const bool ts_enabled = []() { const char* e = std::getenv("OA_GEMM_TMA_STORE"); return !(e && e[0] == '0'); }();
+      CUtensorMap tc = ta, taux = ta;
+      p.tma_store = 0;
+      if (ts_enabled && ps == 1 && !out_f32 && !accumulate &&
+          make_tmap_2d_bf16(&tc, out, (uint64_t)N, (uint64_t)M, (uint64_t)ldc, 32, 32, 64) == OA_OK &&
+          (!aux_out || make_tmap_2d_bf16(&taux, aux_out, (uint64_t)N, (uint64_t)M, (uint64_t)ldaux, 32, 32, 64) == OA_OK))
+        p.tma_store = 1;
       const long long units = tiles2 * ps;
       const int pgrid = (int)(units * 2 < sms ? units * 2 : sms);
       switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
-        case 0: rc = launch_gemm_pair<0, 0>(ta, tb, tb2, p, pgrid, st); break;
-        case 1: rc = launch_gemm_pair<0, 1>(ta, tb, tb2, p, pgrid, st); break;
-        case 2: rc = launch_gemm_pair<1, 0>(ta, tb, tb2, p, pgrid, st); break;
-        default: rc = launch_gemm_pair<1, 1>(ta, tb, tb2, p, pgrid, st); break;
+        case 0: rc = launch_gemm_pair<0, 0>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
+        case 1: rc = launch_gemm_pair<0, 1>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
+        case 2: rc = launch_gemm_pair<1, 0>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
+        default: rc = launch_gemm_pair<1, 1>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
       }
       if (rc) return rc;
       if (p.splits > 1) {
@@ -1183,7 +1289,7 @@ extern "C" int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void
   p.N = N; p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = (const __nv_bfloat16*)bias; p.residual = nullptr; p.ldr = 0;
   p.aux_out = (__nv_bfloat16*)aux_out; p.aux_in = (const __nv_bfloat16*)aux_in; p.ldaux = ldaux;
-  p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.epi_prefetch = 0; p.splits = 1; p.workspace = nullptr;
+  p.act = act; p.accumulate = accumulate; p.alpha = 1.f; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.epi_prefetch = 0; p.tma_store = 0; p.splits = 1; p.workspace = nullptr;
   p.batch = groups; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = sbias_batch;
   p.group_mode = mode; p.group_offsets = offsets; p.tp_mode = 0; p.tp_comm = 0;
   CUtensorMap ta, tb;
@@ -1238,7 +1344,7 @@ extern "C" int oa_gemm_bf16_tp(int mode, const void* A, const void* B, void* out
   p.out = out; p.ldc = ldc; p.out_f32 = out_f32;
   p.bias = nullptr; p.residual = (const __nv_bfloat16*)residual; p.ldr = ldr;
   p.aux_out = nullptr; p.aux_in = nullptr; p.ldaux = 0;
-  p.act = OA_ACT_NONE; p.accumulate = 0; p.alpha = alpha; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.epi_prefetch = 0; p.splits = 1; p.workspace = nullptr;
+  p.act = OA_ACT_NONE; p.accumulate = 0; p.alpha = alpha; p.status = status; p.group_m = 16; p.pair_group_m = 8; p.epi_prefetch = 0; p.tma_store = 0; p.splits = 1; p.workspace = nullptr;
   p.batch = 1; p.sc_batch = 0; p.sr_batch = 0; p.saux_batch = 0; p.sbias_batch = 0;
   p.group_mode = 0; p.group_offsets = nullptr;
   p.tp_mode = mode; p.tp_world = world; p.tp_rank = rank; p.tp_comm = comm_ctas;

@@ -85,7 +85,7 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
     ref32 = 2 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn)
     _close(out32, ref32, 1e-2, what="pair gemm fp32 accumulate")
     _close_gemm_bf16(out32, ref32, K_, what="pair gemm fp32 accumulate (per element)", out_bf16=False)
-    # the coalesced (shared-memory staged) epilogue: pre-activation copy out, saved pre-activation in, bf16 output
+    # bf16 outputs (they leave through TMA stores): pre-activation copy out, saved pre-activation in, plain store
     aux = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
     out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=K.ACT_GELU, aux_out=aux)
     aux_ref = torch.empty(M, N)
@@ -99,6 +99,14 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
         _close(got, want, 1e-2, what=f"pair gemm activation backward {act}")
     plain = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, alpha=0.5)
     _close(plain, 0.5 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn), 1e-2, what="pair gemm plain bf16 store")
+    # N a multiple of 8 but not of the 32-column store box, output a column slice of a wider matrix (row pitch != N):
+    # the boxes at the right and bottom edges are clipped, the columns beside the slice stay untouched
+    N2 = 2632
+    b2 = _rand(K_, N2, scale=0.05) if b_mn else _rand(N2, K_, scale=0.05)
+    wide = torch.full((M, N2 + 64), 3.0, dtype=torch.bfloat16, device=DEV)
+    K.gemm(a, b2, a_mn=a_mn, b_mn=b_mn, out=wide[:, 32:32 + N2])
+    _close(wide[:, 32:32 + N2], K.gemm(a.cpu().float(), b2.cpu().float(), a_mn=a_mn, b_mn=b_mn), 1e-2, what="pair gemm into a column slice")
+    assert bool((wide[:, :32] == 3.0).all()) and bool((wide[:, 32 + N2:] == 3.0).all())
 
 
 @pytest.mark.parametrize("bn", [128, 256])
