@@ -832,12 +832,17 @@ def RmsNorm(x: OaMatrix, w: OaMatrix, eps: float = 1e-6) -> OaMatrix:
     y, rstd, _ = K.rmsnorm_fwd(x2, tw, eps)
     out = _w(y.reshape(tx.shape))
 
-    def back(g):
+    def back(g, pending=None):
+        # `pending`: what x has already collected through the residual stream; the kernel adds it while it writes dx
         sink = w.GradSink() if (w.IsLeaf() and w.RequiresGrad()) else None
-        dx, dw = K.rmsnorm_bwd(x2, tw, _rows(g), rstd, dw_out=sink[0] if sink else None, accumulate_dw=bool(sink and sink[1]))
-        return (dx.reshape(tx.shape), None if sink else dw)
+        dres = _rows(pending) if (pending is not None and pending.is_contiguous()) else None
+        dx, dw = K.rmsnorm_bwd(x2, tw, _rows(g), rstd, dres=dres, dw_out=sink[0] if sink else None, accumulate_dw=bool(sink and sink[1]))
+        dx = dx.reshape(tx.shape)
+        if pending is not None and dres is None:
+            dx = K.binary("add", pending, dx)
+        return (dx, None if sink else dw)
 
-    return AG.attach("RmsNorm", out, [x, w], back)
+    return AG.attach("RmsNorm", out, [x, w], back, fold=0)
 
 
 def ResidualRmsNorm(x: OaMatrix, residual: OaMatrix, w: OaMatrix, eps: float = 1e-6):

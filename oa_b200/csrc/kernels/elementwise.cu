@@ -254,20 +254,32 @@ rope_bf16_vec_kernel(__nv_bfloat16* x, long long rows, int row_stride, int n_hea
       if (backward) s[k] = -s[k];
     }
     __nv_bfloat16* row = x + r * row_stride + v * 8;
-    for (int h = 0; h < n_heads; ++h) {
-      uint4* pa = reinterpret_cast<uint4*>(row + h * hd);
-      uint4* pb = reinterpret_cast<uint4*>(row + h * hd + half);
-      const uint4 ua = *pa, ub = *pb;
-      const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
-      uint32_t oa[4], ob[4];
+    // four heads per round: their eight 16-byte loads are issued before the first use, so one thread keeps 128 bytes in flight
+    constexpr int HB = 4;
+    for (int h0 = 0; h0 < n_heads; h0 += HB) {
+      uint4 ua[HB], ub[HB];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 a = unpack_bf16x2(wa[k]), b = unpack_bf16x2(wb[k]);
-        oa[k] = pack_bf16x2(a.x * c[2 * k] - b.x * s[2 * k], a.y * c[2 * k + 1] - b.y * s[2 * k + 1]);
-        ob[k] = pack_bf16x2(b.x * c[2 * k] + a.x * s[2 * k], b.y * c[2 * k + 1] + a.y * s[2 * k + 1]);
+      for (int u = 0; u < HB; ++u) {
+        if (h0 + u < n_heads) {
+          ua[u] = *reinterpret_cast<const uint4*>(row + (h0 + u) * hd);
+          ub[u] = *reinterpret_cast<const uint4*>(row + (h0 + u) * hd + half);
+        }
       }
-      *pa = make_uint4(oa[0], oa[1], oa[2], oa[3]);
-      *pb = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+#pragma unroll
+      for (int u = 0; u < HB; ++u) {
+        if (h0 + u < n_heads) {
+          const uint32_t wa[4] = {ua[u].x, ua[u].y, ua[u].z, ua[u].w}, wb[4] = {ub[u].x, ub[u].y, ub[u].z, ub[u].w};
+          uint32_t oa[4], ob[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 a = unpack_bf16x2(wa[k]), b = unpack_bf16x2(wb[k]);
+            oa[k] = pack_bf16x2(a.x * c[2 * k] - b.x * s[2 * k], a.y * c[2 * k + 1] - b.y * s[2 * k + 1]);
+            ob[k] = pack_bf16x2(b.x * c[2 * k] + a.x * s[2 * k], b.y * c[2 * k + 1] + a.y * s[2 * k + 1]);
+          }
+          *reinterpret_cast<uint4*>(row + (h0 + u) * hd) = make_uint4(oa[0], oa[1], oa[2], oa[3]);
+          *reinterpret_cast<uint4*>(row + (h0 + u) * hd + half) = make_uint4(ob[0], ob[1], ob[2], ob[3]);
+        }
+      }
     }
   }
 }

@@ -421,7 +421,7 @@ __device__ __forceinline__ void tp_reduce_rows(const GemmParams& p, int n_tiles,
 }
 
 template <int BN, int A_MN, int B_MN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmA2, const GemmParams p) {
   using Cfg = GemmCfg<BN>;
@@ -439,6 +439,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // 4 epilogue warps (the tensor-parallel modes, whose staging and counters are laid out for four) or 8: two warps per
+  // scheduler, the two of a TMEM lane quarter taking half of the accumulator's columns each
+  const int epi_warps = (int)(blockDim.x >> 5) - 2;
 
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
@@ -469,7 +472,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 4);  // one arrive per epilogue warp
+      mbar_init(&tempty[a], epi_warps);  // one arrive per epilogue warp
     }
     mbar_fence_init();
   }
@@ -552,6 +555,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // descriptors of stage 0, computed once: a later stage or k-step only adds to the 14-bit address field (no carry,
+      // shared memory ends below 256 KB), which keeps the single issuing thread's instruction stream short
+      const uint64_t da0 = umma_smem_desc_sw128(smem_u32(sA), a_lbo, a_sbo);
+      const uint64_t db0 = umma_smem_desc_sw128(smem_u32(sB), b_lbo, b_sbo);
       for (int t = blockIdx.x; t < total_tiles && ok; t += n_compute) {
         const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
         const int kb0 = ti.kb0, kb1 = ti.kb1;
@@ -561,6 +568,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t accumulate = 0;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase)) {
             report_error(p.status, OA_KERR_WAIT_FULL);
@@ -568,14 +576,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * Cfg::A_BYTES);
-          const uint32_t b_addr = smem_u32(sB + stage * Cfg::B_BYTES);
+          const uint64_t da = da0 + (uint64_t)((stage * Cfg::A_BYTES) >> 4);
+          const uint64_t db = db0 + (uint64_t)((stage * Cfg::B_BYTES) >> 4);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            uint64_t da = umma_smem_desc_sw128(a_addr + k * a_kstep, a_lbo, a_sbo);
-            uint64_t db = umma_smem_desc_sw128(b_addr + k * b_kstep, b_lbo, b_sbo);
-            umma_f16(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16(d_tmem, da + (uint64_t)((k * a_kstep) >> 4), db + (uint64_t)((k * b_kstep) >> 4), idesc, k > 0 ? 1u : accumulate);
+          accumulate = 1;
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -588,6 +594,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ---------------- epilogue warps (2..5); TMEM lane quadrant = warp % 4
     const int quad = warp & 3;
+    const int c_per = (BN / 32) / (epi_warps >> 2);
+    const int c_begin = ((warp - 2) >> 2) * c_per, c_end = c_begin + c_per;
     int acc = 0;
     uint32_t acc_phase = 0;
     int n_pend = 0;
@@ -606,11 +614,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
       const bool empty_split = (kb1 <= kb0);  // nothing accumulated: treat as zeros
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
         tmem_ld_wait();
-        if (c == BN / 32 - 1) {
+        if (c == c_end - 1) {
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -788,7 +796,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int u = pair; u < total_units && ok; u += n_pairs) {
         int mi, ni, half;
         const int t = unit_tile(u, half);
-        const int split = t / mn_tiles;
+        const int split = p.splits > 1 ? t / mn_tiles : 0;
         tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.pair_group_m, mi, ni);
         const int row0 = mi * 256 + (int)rank * 128;
         const int n0 = half < 0 ? ni * 256 + (int)rank * 128 : ni * 256 + half * 128 + (int)rank * 64;
@@ -850,7 +858,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int u = pair; u < total_units && ok; u += n_pairs) {
         int half;
         const int t = unit_tile(u, half);
-        const int split = t / mn_tiles;
+        const int split = p.splits > 1 ? t / mn_tiles : 0;
         const int kb0 = split * kb_per_split, kb1 = min(kb_total, kb0 + kb_per_split);
         const uint32_t idesc = half < 0 ? idesc_full : idesc_half;
 #ifdef OA_GEMM_PROBE
@@ -910,7 +918,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     for (int u = pair; u < total_units; u += n_pairs) {
       int mi, ni, half;
       const int t = unit_tile(u, half);
-      const int split = t / mn_tiles;
+      const int split = p.splits > 1 ? t / mn_tiles : 0;
       tile_coords(t - split * mn_tiles, m_tiles, n_tiles, p.pair_group_m, mi, ni);
       tsc.row0 = mi * 256 + (int)rank * 128 + quad * 32;
       bool ok = mbar_wait(&tfull[acc], acc_phase);
@@ -1088,7 +1096,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       return OA_ERR_LAUNCH;
     attr_set = true;
   }
-  kfn<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, ta2 ? *ta2 : ta, p);
+  kfn<<<grid, p.tp_mode ? 192 : 320, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, ta2 ? *ta2 : ta, p);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 

@@ -47,17 +47,22 @@ class OaGradNode:
     """One recorded differentiable operation.
 
     `backward(upstream: Tensor) -> sequence of (Tensor | None)` returns one gradient per graph input.
+    With `fold = i` the node takes `backward(upstream, pending)`: `pending` is the gradient that input i has already
+    collected from its other consumers (or None) and the returned gradient of input i then CONTAINS it, so the pass
+    replaces the pending gradient instead of launching an add (a norm under a residual stream folds the stream's
+    gradient into its own backward kernel).
     """
 
-    __slots__ = ("name", "inputs", "backward", "seq", "out_shape", "saved")
+    __slots__ = ("name", "inputs", "backward", "seq", "out_shape", "saved", "fold")
 
-    def __init__(self, name: str, inputs: Sequence, backward: Callable, out_shape):
+    def __init__(self, name: str, inputs: Sequence, backward: Callable, out_shape, fold: Optional[int] = None):
         self.name = name
         self.inputs = list(inputs)
         self.backward = backward
         self.seq = NextSeq()
         self.out_shape = tuple(out_shape)
         self.saved = None
+        self.fold = fold
 
     def GraphInputs(self):
         return self.inputs
@@ -148,8 +153,19 @@ class OaGradientTape:
                     continue
                 if tuple(up.shape) != fn.out_shape and up.numel() == _numel(fn.out_shape):
                     up = up.reshape(fn.out_shape)
-                in_grads = fn.backward(up)
-                for inp, d in zip(fn.inputs, in_grads):
+                folded = None
+                if fn.fold is None:
+                    in_grads = fn.backward(up)
+                else:
+                    fi = fn.inputs[fn.fold]
+                    fchild = fi.GetGradFn() if (fi is not None and not fi.IsLeaf() and fi.RequiresGrad()) else None
+                    if fchild is not None:
+                        prev = grad_map.get(id(fchild))
+                        ft = fi.Tensor()
+                        if prev is not None and tuple(prev.shape) == tuple(ft.shape) and prev.dtype == ft.dtype:
+                            folded = prev
+                    in_grads = fn.backward(up, folded)
+                for idx, (inp, d) in enumerate(zip(fn.inputs, in_grads)):
                     if inp is None or d is None or not inp.RequiresGrad():
                         continue
                     if tuple(d.shape) != tuple(inp.Tensor().shape) and d.numel() == inp.NumElements():
@@ -161,8 +177,8 @@ class OaGradientTape:
                     if child is None:
                         continue
                     prev = grad_map.get(id(child))
-                    if prev is None:
-                        grad_map[id(child)] = d
+                    if prev is None or (folded is not None and idx == fn.fold):
+                        grad_map[id(child)] = d            # first contribution, or one that already contains the pending gradient
                     else:
                         if tuple(d.shape) != tuple(prev.shape):
                             d = d.reshape(prev.shape)
@@ -193,8 +209,8 @@ def _numel(shape) -> int:
     return n
 
 
-def attach(name: str, out, inputs: Sequence, backward: Callable):
-    """Attaches a grad node to `out` when recording is on and some input needs a gradient."""
+def attach(name: str, out, inputs: Sequence, backward: Callable, fold: Optional[int] = None):
+    """Attaches a grad node to `out` when recording is on and some input needs a gradient (`fold`: see OaGradNode)."""
     if not IsEnabled():
         return out
     need = False
@@ -204,6 +220,6 @@ def attach(name: str, out, inputs: Sequence, backward: Callable):
             break
     if not need:
         return out
-    node = OaGradNode(name, inputs, backward, out.Tensor().shape)
+    node = OaGradNode(name, inputs, backward, out.Tensor().shape, fold)
     out._set_grad_fn(node)
     return out

@@ -137,6 +137,30 @@ def test_norms_and_gates():
     _check(lambda a, b: F.SiluMul(a, b), lambda a, b: torch.nn.functional.silu(a) * b, [(5, 4), (5, 4)])
 
 
+def test_norm_backward_folds_the_residual_stream_gradient(monkeypatch):
+    """x feeds a residual add and an RmsNorm (and through a second block again): the gradient that x has collected through
+    the residual stream is handed to the norm's backward, which returns the sum, and no separate add is launched."""
+    from oa_b200.ops import kernels as K
+    rms = lambda x, w, eps: x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
+    adds = []
+    real = K.binary
+    monkeypatch.setattr(K, "binary", lambda op, *a, **k: (adds.append(op), real(op, *a, **k))[1])
+
+    def block(h, c, w0, w1):                   # two pre-norm residual blocks on an intermediate (non-leaf) stream
+        h = F.Mul(h, c)
+        h = F.Add(h, F.Mul(F.RmsNorm(h, w0, 1e-6), F.RmsNorm(h, w0, 1e-6)))
+        return F.Add(h, F.RmsNorm(h, w1, 1e-6))
+
+    def ref(h, c, w0, w1):
+        h = h * c
+        h = h + rms(h, w0, 1e-6) * rms(h, w0, 1e-6)
+        return h + rms(h, w1, 1e-6)
+
+    _check(block, ref, [(5, 8), (5, 8), (8,), (8,)])
+    # "add" appears for the two forward Adds only, none for the gradient fan-in of the stream
+    assert adds.count("add") == 2, adds
+
+
 def _rope_ref(x, heads, hd, seq, theta=10000.0):
     rows = x.shape[0]
     xv = x.reshape(rows // seq, seq, heads, hd)
