@@ -137,6 +137,11 @@ def bench_bw():
     _, rstd, _ = K.rmsnorm_fwd(x, w, 1e-5)
     t = timeit(lambda: K.rmsnorm_bwd(x, w, x, rstd))
     emit(op="rmsnorm_bwd", rows=16384, cols=1024, us=t * 1e3, gbs=3 * x.numel() * 2 / t / 1e6)
+    t = timeit(lambda: K.rmsnorm_bwd(x, w, x, rstd, dres=x))
+    emit(op="rmsnorm_bwd_with_residual_gradient", rows=16384, cols=1024, us=t * 1e3, gbs=4 * x.numel() * 2 / t / 1e6)
+    qkv = torch.randn(16384, 3072, device="cuda").bfloat16()
+    t = timeit(lambda: K.rope_(qkv[:, :2048], 32, 64, 2048))          # q and k of a packed projection, in place
+    emit(op="rope_inplace_packed_qk", rows=16384, heads=32, head_dim=64, us=t * 1e3, gbs=2 * 16384 * 2048 * 2 / t / 1e6)
     lg = torch.randn(16384, 32000, device="cuda").bfloat16()
     tg = torch.randint(0, 32000, (16384,), device="cuda")
     t = timeit(lambda: K.xent_fwd_bwd(lg, tg, grad_scale=1.0, dlogits=lg))

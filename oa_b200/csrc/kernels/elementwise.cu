@@ -340,6 +340,15 @@ col_sum_partial_kernel(const T* __restrict__ x, float* __restrict__ partial, lon
   float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   if (c < cols) {
     long long r = r0 + lane;
+    // a lane's 64 rows of a full block as 16 independent loads: small matrices give few blocks, so the time of this kernel is
+    // the latency of its dependent rounds, not bandwidth
+    for (; r + 60 < r1; r += 64) {
+      float v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) v[u] = IO<T>::ld1(x + (r + 4 * u) * cols + c);
+#pragma unroll
+      for (int u = 0; u < 16; u += 4) { s0 += v[u]; s1 += v[u + 1]; s2 += v[u + 2]; s3 += v[u + 3]; }
+    }
     for (; r + 12 < r1; r += 16) {
       s0 += IO<T>::ld1(x + r * cols + c);
       s1 += IO<T>::ld1(x + (r + 4) * cols + c);
