@@ -16,10 +16,7 @@ extern "C" {
 enum { OA_OK = 0, OA_ERR_ARG = 1, OA_ERR_ALIGN = 2, OA_ERR_DRIVER = 3, OA_ERR_LAUNCH = 4, OA_ERR_UNSUPPORTED = 5,
        OA_ERR_TOO_LARGE = 6 };
 enum { OA_F32 = 0, OA_BF16 = 1 };
-// OA_ACT_GELU_DZ: GELU whose aux_out receives the derivative gelu'(value) instead of the value; OA_ACT_MUL_AUX multiplies by
-// aux_in as it is (the pair saves the backward GEMM of a Linear + GELU the evaluation of the derivative).
-enum { OA_ACT_NONE = 0, OA_ACT_GELU = 1, OA_ACT_RELU = 2, OA_ACT_SILU = 3, OA_ACT_GELU_BWD = 4, OA_ACT_RELU_BWD = 5,
-       OA_ACT_GELU_DZ = 6, OA_ACT_MUL_AUX = 7 };
+enum { OA_ACT_NONE = 0, OA_ACT_GELU = 1, OA_ACT_RELU = 2, OA_ACT_SILU = 3, OA_ACT_GELU_BWD = 4, OA_ACT_RELU_BWD = 5 };
 
 // unary ops: y = f(x; s0, s1)
 enum { OA_U_COPY = 0, OA_U_NEG, OA_U_ABS, OA_U_LOG, OA_U_EXP, OA_U_SQRT, OA_U_SIN, OA_U_COS, OA_U_RECIP, OA_U_SCALE,

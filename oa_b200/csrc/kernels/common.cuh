@@ -406,16 +406,6 @@ __device__ __forceinline__ float gelu_tanh_grad_fast(float x) {
   // 0.5 (1 + t) + 0.5 x (1 - t^2) du
   return fmaf(hx * du, fmaf(-t, t, 1.f), fmaf(0.5f, t, 0.5f));
 }
-// GELU and its derivative from one tanh (5 instructions more than the value alone).
-__device__ __forceinline__ void gelu_tanh_value_grad_fast(float x, float& g, float& d) {
-  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  const float x2 = x * x;
-  const float t = tanh_approx(x * fmaf(k0 * k1, x2, k0));
-  const float du = fmaf(3.f * k0 * k1, x2, k0);
-  const float hx = 0.5f * x;
-  g = fmaf(hx, t, hx);
-  d = fmaf(hx * du, fmaf(-t, t, 1.f), fmaf(0.5f, t, 0.5f));
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -3,11 +3,10 @@
 // precision) and the finite-difference gradient checks, where TF32/bf16 rounding is not acceptable.
 // The bf16 path uses gemm_tcgen05.cu instead.
 //   C[b][m,n] = act(alpha * sum_k A[b][m*sam + k*sak] * B[b][n*sbn + k*sbk] + bias[n]) (+ C)
-// 64x64x16 tiles (32x64x16 when the larger tile would leave SMs idle), 256 threads, 4x4 (2x4) outputs per thread with
-// 16-byte shared-memory reads and the next K tile prefetched into registers (the reference's GemmTiled,
+// 64x64x16 tiles, 256 threads, 4x4 outputs per thread with 16-byte shared-memory reads and the next
+// K tile prefetched into registers (the reference's GemmTiled,
 // Source/Private/Oa/Core/Shader/Compute/Blas/Gemm/GemmTiled.slang:1-110, is the same tiling class), here
 // with runtime strides so that NT / NN / TN products and Bmm need no transposed copies.
-#include <cstdlib>
 #include "common.cuh"
 #include "api.h"
 
@@ -15,14 +14,12 @@ namespace oa {
 
 constexpr int FT = 64, FK = 16;
 
-template <int TM>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                 long long sam, long long sak, long long sbn, long long sbk, int ldc, long long batch_a,
                 long long batch_b, long long batch_c, const float* __restrict__ bias, int act, int accumulate,
                 float alpha, int k_chunk) {
-  constexpr int RM = TM / 16;                 // output rows per thread (4 or 2); also the A elements a thread loads per k-tile
-  __shared__ __align__(16) float sA[FK][TM + 4];
+  __shared__ __align__(16) float sA[FK][FT + 4];
   __shared__ __align__(16) float sB[FK][FT + 4];
   const int b = blockIdx.z;
   // k_chunk > 0: split-K mode - blockIdx.z is the K slice (batch 1) and C is the slice's own [M, ldc] partial buffer
@@ -35,40 +32,30 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
     B += (long long)b * batch_b;
     C += (long long)b * batch_c;
   }
-  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * FT;
+  const int m0 = blockIdx.y * FT, n0 = blockIdx.x * FT;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-  // TM x 16 and 64 x 16 elements per operand, 256 threads; the faster-varying index follows the contiguous dimension
-  int ar[RM], ak[RM], br[4], bk[4];
-#pragma unroll
-  for (int i = 0; i < RM; ++i) {
-    const int idx = threadIdx.x + i * 256;
-    if (sak == 1) { ak[i] = idx & 15; ar[i] = idx >> 4; } else { ar[i] = idx & (TM - 1); ak[i] = idx / TM; }
-  }
+  // 64x16 elements per operand, 256 threads -> 4 loads each; the faster-varying index follows the contiguous dimension
+  int ar[4], ak[4], br[4], bk[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int idx = threadIdx.x + i * 256;
+    if (sak == 1) { ak[i] = idx & 15; ar[i] = idx >> 4; } else { ar[i] = idx & 63; ak[i] = idx >> 6; }
     if (sbk == 1) { bk[i] = idx & 15; br[i] = idx >> 4; } else { br[i] = idx & 63; bk[i] = idx >> 6; }
   }
-  float ra[RM], rb[4];
+  float ra[4], rb[4];
   auto fetch = [&](int k0) {       // global -> registers (the next tile is in flight while this one is multiplied)
 #pragma unroll
-    for (int i = 0; i < RM; ++i) {
-      const int gm = m0 + ar[i], gka = k0 + ak[i];
-      ra[i] = (gm < M && gka < k_hi) ? A[gm * sam + gka * sak] : 0.f;
-    }
-#pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int gn = n0 + br[i], gkb = k0 + bk[i];
+      const int gm = m0 + ar[i], gka = k0 + ak[i], gn = n0 + br[i], gkb = k0 + bk[i];
+      ra[i] = (gm < M && gka < k_hi) ? A[gm * sam + gka * sak] : 0.f;
       rb[i] = (gn < N && gkb < k_hi) ? B[gn * sbn + gkb * sbk] : 0.f;
     }
   };
   auto stash = [&]() {
 #pragma unroll
-    for (int i = 0; i < RM; ++i) sA[ak[i]][ar[i]] = ra[i];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) sB[bk[i]][br[i]] = rb[i];
+    for (int i = 0; i < 4; ++i) { sA[ak[i]][ar[i]] = ra[i]; sB[bk[i]][br[i]] = rb[i]; }
   };
-  float acc[RM][4] = {};
+  float acc[4][4] = {};
   if (k_lo < k_hi) fetch(k_lo);
   for (int k0 = k_lo; k0 < k_hi; k0 += FK) {
     stash();
@@ -76,26 +63,19 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
     if (k0 + FK < k_hi) fetch(k0 + FK);
 #pragma unroll
     for (int kk = 0; kk < FK; ++kk) {
-      float a[RM];
-      if constexpr (RM == 4) {
-        const float4 a4 = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
-        a[0] = a4.x; a[1] = a4.y; a[2] = a4.z; a[3] = a4.w;
-      } else {
-        const float2 a2 = *reinterpret_cast<const float2*>(&sA[kk][ty * 2]);
-        a[0] = a2.x; a[1] = a2.y;
-      }
+      const float4 a4 = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]);
       const float4 b4 = *reinterpret_cast<const float4*>(&sB[kk][tx * 4]);
-      const float bb[4] = {b4.x, b4.y, b4.z, b4.w};
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w}, bb[4] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-      for (int i = 0; i < RM; ++i)
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], bb[j], acc[i][j]);
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < RM; ++i) {
-    int gm = m0 + ty * RM + i;
+  for (int i = 0; i < 4; ++i) {
+    int gm = m0 + ty * 4 + i;
     if (gm >= M) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -164,23 +144,15 @@ extern "C" int oa_gemm_f32(const float* A, const float* B, float* C, int M, int 
       float* part = oa::splitk_scratch((size_t)splits * M * N * sizeof(float), st);
       if (part && splits >= 2) {
         grid.z = splits;
-        oa::gemm_f32_kernel<64><<<grid, 256, 0, st>>>(A, B, part, M, N, K, sam, sak, sbn, sbk, N, 0, 0, (long long)M * N, nullptr,
-                                                      OA_ACT_NONE, 0, 1.0f, k_chunk);
+        oa::gemm_f32_kernel<<<grid, 256, 0, st>>>(A, B, part, M, N, K, sam, sak, sbn, sbk, N, 0, 0, (long long)M * N, nullptr,
+                                                  OA_ACT_NONE, 0, 1.0f, k_chunk);
         const long long n = (long long)M * N;
         oa::gemm_f32_splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(part, C, M, N, ldc, splits, accumulate, alpha);
         return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
       }
     }
   }
-  // fewer 64 x 64 tiles than two per SM: halve the tile height so that the grid covers the machine (OA_GEMM_F32_TM=64 keeps 64)
-  static const bool allow32 = [] { const char* e = getenv("OA_GEMM_F32_TM"); return !(e && atoi(e) == 64); }();
-  if (allow32 && (long long)tiles * batch < 296 && M > 32) {
-    grid.y = (M + 31) / 32;
-    oa::gemm_f32_kernel<32><<<grid, 256, 0, st>>>(A, B, C, M, N, K, sam, sak, sbn, sbk, ldc, batch_a, batch_b, batch_c, bias, act,
-                                                  accumulate, alpha, 0);
-    return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
-  }
-  oa::gemm_f32_kernel<64><<<grid, 256, 0, st>>>(A, B, C, M, N, K, sam, sak, sbn, sbk, ldc, batch_a, batch_b, batch_c, bias, act,
-                                                accumulate, alpha, 0);
+  oa::gemm_f32_kernel<<<grid, 256, 0, st>>>(A, B, C, M, N, K, sam, sak, sbn, sbk, ldc, batch_a, batch_b, batch_c, bias, act,
+                                            accumulate, alpha, 0);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }

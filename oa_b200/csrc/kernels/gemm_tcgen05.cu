@@ -162,8 +162,7 @@ struct TmaStoreCtx {
   uint32_t n;            // stores issued by this warp
   int row0;              // first row of the warp's 32
 };
-// `w`: the lane's 32 columns as 16 packed bf16 pairs
-__device__ __forceinline__ void tma_store_packed(TmaStoreCtx* ts, const CUtensorMap* m, const uint32_t* w, int col0) {
+__device__ __forceinline__ void tma_store_piece(TmaStoreCtx* ts, const CUtensorMap* m, const float* v, int col0) {
   const int lane = threadIdx.x & 31;
   uint8_t* b = ts->buf + (ts->n & 1) * 2048;
   if (lane == 0) tma_store_wait_read1();
@@ -171,17 +170,13 @@ __device__ __forceinline__ void tma_store_packed(TmaStoreCtx* ts, const CUtensor
   const uint32_t base = smem_u32(b) + lane * 64;
   const int sw = (lane >> 1) & 3;                       // 64-byte swizzle: 16-byte piece index ^= address bits 7..8
 #pragma unroll
-  for (int g = 0; g < 4; ++g) st_shared_v4(base + ((g ^ sw) << 4), make_uint4(w[g * 4], w[g * 4 + 1], w[g * 4 + 2], w[g * 4 + 3]));
+  for (int g = 0; g < 4; ++g)
+    st_shared_v4(base + ((g ^ sw) << 4), make_uint4(pack_bf16x2(v[g * 8], v[g * 8 + 1]), pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
+                                                    pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7])));
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0) { tma_store_2d(m, b, col0, ts->row0); tma_store_commit(); }
   ++ts->n;
-}
-__device__ __forceinline__ void tma_store_piece(TmaStoreCtx* ts, const CUtensorMap* m, const float* v, int col0) {
-  uint32_t w[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
-  tma_store_packed(ts, m, w, col0);
 }
 
 template <int BN>
@@ -213,24 +208,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
       }
     }
   }
-  if (p.act == OA_ACT_GELU_DZ) {               // value and derivative from one tanh; the derivative goes to aux_out
-    uint32_t dw[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      float d0, d1;
-      gelu_tanh_value_grad_fast(v[2 * i], v[2 * i], d0);
-      gelu_tanh_value_grad_fast(v[2 * i + 1], v[2 * i + 1], d1);
-      dw[i] = pack_bf16x2(d0, d1);
-    }
-    if (p.aux_out && ts) {
-      tma_store_packed(ts, ts->aux, dw, col0);
-    } else if (p.aux_out) {
-      __nv_bfloat16* a = p.aux_out + bi * p.saux_batch + (size_t)row * p.ldaux + col0;
-#pragma unroll
-      for (int g = 0; g < 4; ++g)
-        if (g * 8 < ncols) *reinterpret_cast<uint4*>(a + g * 8) = make_uint4(dw[g * 4], dw[g * 4 + 1], dw[g * 4 + 2], dw[g * 4 + 3]);
-    }
-  } else if (p.aux_out && ts) {
+  if (p.aux_out && ts) {
     tma_store_piece(ts, ts->aux, v, col0);
   } else if (p.aux_out) {
     __nv_bfloat16* a = p.aux_out + bi * p.saux_batch + (size_t)row * p.ldaux + col0;
@@ -261,10 +239,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           float2 z = unpack_bf16x2(w[j]);
-          if (p.act == OA_ACT_MUL_AUX) {
-            v[g * 8 + 2 * j] *= z.x;
-            v[g * 8 + 2 * j + 1] *= z.y;
-          } else if (p.act == OA_ACT_GELU_BWD) {
+          if (p.act == OA_ACT_GELU_BWD) {
             v[g * 8 + 2 * j] *= gelu_tanh_grad_fast(z.x);
             v[g * 8 + 2 * j + 1] *= gelu_tanh_grad_fast(z.y);
           } else {  // OA_ACT_RELU_BWD

@@ -7,8 +7,6 @@ GEMM epilogues (bias, GELU, residual add, GELU-backward) so that no separate ele
 """
 from __future__ import annotations
 
-import os
-
 from typing import Optional, Sequence
 
 import torch
@@ -99,9 +97,6 @@ def PackedProjection(x: OaMatrix, weights: Sequence[OaMatrix], biases: Sequence[
     return AG.attach(name, out, ins, back)
 
 
-_SAVE_GELU_DERIVATIVE = os.environ.get("OA_FFN_GELU_DZ", "1") != "0"      # 0: save the pre-activation and evaluate gelu' in the backward epilogue
-
-
 def FfnGelu(x: OaMatrix, w1: OaMatrix, b1: Optional[OaMatrix], w2: OaMatrix, b2: Optional[OaMatrix],
             residual: Optional[OaMatrix] = None, act: int = K.ACT_GELU) -> OaMatrix:
     """y = act(x W1^T + b1) W2^T + b2 (+ residual).  Backward computes dz = (dy W2) * act'(z) inside the GEMM epilogue."""
@@ -111,15 +106,11 @@ def FfnGelu(x: OaMatrix, w1: OaMatrix, b1: Optional[OaMatrix], w2: OaMatrix, b2:
     x2 = F._rows(tx)
     tw1, tw2 = F._c(w1.Tensor()), F._c(w2.Tensor())
     z = torch.empty((x2.shape[0], tw1.shape[0]), dtype=tx.dtype, device=tx.device)
-    # bf16 GELU: the forward epilogue has the fp32 pre-activation and one tanh in registers, so it saves gelu'(z) instead of z
-    # and the backward epilogue only multiplies
-    fwd_act, bwd_act = act, (K.ACT_GELU_BWD if act == K.ACT_GELU else K.ACT_RELU_BWD)
-    if act == K.ACT_GELU and tx.dtype == torch.bfloat16 and _SAVE_GELU_DERIVATIVE:
-        fwd_act, bwd_act = K.ACT_GELU_DZ, K.ACT_MUL_AUX
-    h = K.gemm(x2, tw1, bias=b1.Tensor() if b1 is not None else None, act=fwd_act, aux_out=z)
+    h = K.gemm(x2, tw1, bias=b1.Tensor() if b1 is not None else None, act=act, aux_out=z)
     res2 = F._rows(residual.Tensor()) if residual is not None else None
     y = K.gemm(h, tw2, bias=b2.Tensor() if b2 is not None else None, residual=res2)
     out = OaMatrix(y.reshape(*tx.shape[:-1], tw2.shape[0]))
+    bwd_act = K.ACT_GELU_BWD if act == K.ACT_GELU else K.ACT_RELU_BWD
 
     def back(g):
         g2 = F._rows(g)

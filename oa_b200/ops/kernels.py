@@ -19,7 +19,6 @@ from ..core import validation as V
 C = N.CONST
 ACT_NONE, ACT_GELU, ACT_RELU, ACT_SILU = C["OA_ACT_NONE"], C["OA_ACT_GELU"], C["OA_ACT_RELU"], C["OA_ACT_SILU"]
 ACT_GELU_BWD, ACT_RELU_BWD = C["OA_ACT_GELU_BWD"], C["OA_ACT_RELU_BWD"]
-ACT_GELU_DZ, ACT_MUL_AUX = C["OA_ACT_GELU_DZ"], C["OA_ACT_MUL_AUX"]
 
 _DT = {torch.float32: 0, torch.bfloat16: 1}
 
@@ -169,9 +168,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     """out[M,N] = epilogue(alpha * A @ B^T) with A = a ([M,K]) or a^T (a is [K,M] when a_mn), B likewise.
 
     Epilogue order: + bias[N]; aux_out := value (pre-activation copy); act; * act'(aux_in) for the
-    *_BWD modes; + residual[M,N]; + out when `accumulate`.  ACT_GELU_DZ is GELU whose aux_out receives gelu'(value)
-    instead of the value, ACT_MUL_AUX multiplies by aux_in as it is (bf16 only): the forward product of a Linear + GELU
-    then saves the derivative and the backward product needs two instructions per element instead of fifteen.
+    *_BWD modes; + residual[M,N]; + out when `accumulate`.
     """
     assert a.dim() == 2 and b.dim() == 2
     M, K = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
@@ -188,11 +185,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         if bias is not None:
             v = v + bias.float()
         if aux_out is not None:
-            aux_out.copy_(_gelu_grad_ref(v) if act == ACT_GELU_DZ else v)
-        if act in (ACT_GELU, ACT_GELU_DZ):
+            aux_out.copy_(v)
+        if act == ACT_GELU:
             v = _gelu_ref(v)
-        elif act == ACT_MUL_AUX:
-            v = v * aux_in.float()
         elif act == ACT_RELU:
             v = torch.relu(v)
         elif act == ACT_SILU:
@@ -246,8 +241,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         return out
     if a.dtype == torch.float32:
         assert b.dtype == torch.float32 and out.dtype == torch.float32
-        if act in (ACT_GELU_DZ, ACT_MUL_AUX):
-            raise ValueError("gemm: ACT_GELU_DZ / ACT_MUL_AUX are epilogues of the bf16 kernel")
         if (_f32_tensor_terms and 2.0 * M * Nn * K >= _F32_TENSOR_MIN_FLOPS and a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
                 and M % 8 == 0 and Nn % 8 == 0 and K % 8 == 0 and act == ACT_NONE and bias is None and residual is None and aux_out is None
                 and aux_in is None):

@@ -99,14 +99,6 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
         _close(got, want, 1e-2, what=f"pair gemm activation backward {act}")
     plain = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, alpha=0.5)
     _close(plain, 0.5 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn), 1e-2, what="pair gemm plain bf16 store")
-    # GELU that saves its derivative, and the backward product that multiplies by it: together they equal GELU / GELU_BWD
-    dz = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    out = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, act=K.ACT_GELU_DZ, aux_out=dz)
-    pre = K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn, bias=bias.cpu().float())
-    _close(out, K._gelu_ref(pre), 1e-2, what="pair gemm GELU (derivative saved)")
-    _close(dz, K._gelu_grad_ref(pre), 1e-2, what="pair gemm saved GELU derivative")
-    got = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, act=K.ACT_MUL_AUX, aux_in=dz)
-    _close(got, K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn) * dz.cpu().float(), 1e-2, what="pair gemm multiply by aux")
     # N a multiple of 8 but not of the 32-column store box, output a column slice of a wider matrix (row pitch != N):
     # the boxes at the right and bottom edges are clipped, the columns beside the slice stay untouched
     N2 = 2632
@@ -137,13 +129,6 @@ def test_gemm_bf16_epilogues(bn):
     K.gemm(a, b, act=K.ACT_GELU_BWD, aux_in=z, out=acc, accumulate=True, force_bn=bn)
     K.gemm(a.cpu().float(), b.cpu().float(), act=K.ACT_GELU_BWD, aux_in=z.cpu().float(), out=acc_ref, accumulate=True)
     _close(acc, acc_ref, 1e-2, what="gelu_bwd+accumulate fp32")
-    dz = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    out = K.gemm(a, b, bias=bias, act=K.ACT_GELU_DZ, aux_out=dz, force_bn=bn)
-    pre = K.gemm(a.cpu().float(), b.cpu().float(), bias=bias.cpu().float())
-    _close(out, K._gelu_ref(pre), 1e-2, what="GELU (derivative saved)")
-    _close(dz, K._gelu_grad_ref(pre), 1e-2, what="saved GELU derivative")
-    got = K.gemm(a, b, act=K.ACT_MUL_AUX, aux_in=dz, force_bn=bn)
-    _close(got, K.gemm(a.cpu().float(), b.cpu().float()) * dz.cpu().float(), 1e-2, what="multiply by aux")
 
 
 def test_gemm_bf16_split_k():
