@@ -239,6 +239,8 @@ __global__ void rope_kernel(T* x, long long rows, int row_stride, int n_heads, i
 __global__ void __launch_bounds__(256)
 rope_bf16_vec_kernel(__nv_bfloat16* x, long long rows, int row_stride, int n_heads, int hd, int seq_len, int pos_offset, float theta,
                      int backward, const int* __restrict__ pos_dev) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (pos_dev) pos_offset += *pos_dev;
   const int half = hd >> 1, jv = half >> 3;                 // 8-wide vectors per half head
   const long long total = rows * jv;
@@ -637,8 +639,8 @@ extern "C" int oa_rope(int dtype, void* x, long long rows, int row_stride, int n
                        int pos_offset, float theta, int backward, const int* pos_dev, void* stream) {
   if (head_dim % 2) return OA_ERR_ARG;
   if (dtype == OA_BF16 && head_dim % 16 == 0 && row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-    rope_bf16_vec_kernel<<<grid_for(rows * (head_dim / 16), 256), 256, 0, ST>>>((__nv_bfloat16*)x, rows, row_stride, n_heads, head_dim,
-                                                                                 seq_len, pos_offset, theta, backward, pos_dev);
+    launch_pdl(rope_bf16_vec_kernel, dim3(grid_for(rows * (head_dim / 16), 256)), dim3(256), 0, ST, (__nv_bfloat16*)x, rows, row_stride, n_heads,
+               head_dim, seq_len, pos_offset, theta, backward, pos_dev);
     return CHECK_LAUNCH();
   }
   DISPATCH_T(dtype, rope_kernel<T><<<grid_for(rows * n_heads * head_dim / 2, 256), 256, 0, ST>>>(

@@ -123,6 +123,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                            // the prologue above ran under the previous kernel's tail; global memory from here on
 
   if (warp == 9) {
     // ------------- producer: the whole warp walks the loop and waits together; one lane issues the copies.  K block i is
@@ -315,6 +316,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (p.lse && half == 0 && qi < p.seq) p.lse[((long long)b * p.heads + h) * p.seq + qi] = (m_run + log2f(l_run)) / LOG2E;
     }
   }
+  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
@@ -398,6 +400,7 @@ flash_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                            // the prologue above ran under the previous kernel's tail; global memory from here on
 
   // item -> (pair, head, batch) and the block counts of its two tiles (tile 1 absent: 0)
   auto decode = [&](int item, int& pr, int& h, int& b, int& nkv0, int& nkv1) {
@@ -633,6 +636,7 @@ flash_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       tc_fence_before();   // the O reads above complete before this warp's next p_full arrival lets the next item's first P V overwrite O
     }
   }
+  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
@@ -645,7 +649,7 @@ static int launch_fwd2(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
     if (cudaFuncSetAttribute(flash_fwd2_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, Fwd2Cfg<HD>::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
     set = true;
   }
-  flash_fwd2_kernel<HD><<<grid, FA_THREADS, Fwd2Cfg<HD>::SMEM_BYTES, st>>>(tq, tk, tv, p);
+  launch_pdl(flash_fwd2_kernel<HD>, grid, dim3(FA_THREADS), Fwd2Cfg<HD>::SMEM_BYTES, st, tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }
 
@@ -665,6 +669,8 @@ struct FlashBwdParams {
 __global__ void __launch_bounds__(256)
 flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, float* __restrict__ delta, int batch,
                    int heads, int seq, int hd, long long o_stride, long long do_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lpi = hd >> 3;                                   // lanes per item: 8 (hd 64) or 16 (hd 128)
   const long long total = (long long)batch * seq * heads;
   const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -779,6 +785,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                            // the prologue above ran under the previous kernel's tail; global memory from here on
 
   if (warp == 11) {
     // ------------- TMA producer (also stages the per-query statistics of each block)
@@ -1019,6 +1026,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tc_fence_before();   // dV / dK are read before this warp's next pds_full arrival lets the next item's products overwrite them
     }
   }
+  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
@@ -1096,6 +1104,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                            // the prologue above ran under the previous kernel's tail; global memory from here on
 
   if (warp == 10) {
     uint32_t itc = 0, kc = 0;
@@ -1288,6 +1297,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_before();   // dQ is read before this warp's next ds_full arrival lets the next item's products overwrite it
     }
   }
+  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if (warp == 8) { tc_fence_after(); tmem_dealloc<Cfg::TMEM_COLS>(tmem_base); }
@@ -1327,7 +1337,7 @@ extern "C" int oa_flash_fwd(const void* q, const void* k, const void* v, void* o
     const int nblk = (seq + FA_BM - 1) / FA_BM;
     const long long items = (long long)((nblk + 1) / 2) * heads * batch;
     const int ctas = (int)(items < sms ? items : sms);
-    flash_fwd_pair_kernel<<<ctas, FwdPairCfg::THREADS, FwdPairCfg::SMEM_BYTES, st>>>(tq, tk, tv, p);
+    launch_pdl(flash_fwd_pair_kernel, dim3(ctas), dim3(FwdPairCfg::THREADS), FwdPairCfg::SMEM_BYTES, st, tq, tk, tv, p);
     return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
   }
   return launch_fwd2<128>(tq, tk, tv, p, dim3((seq + FA_BM - 1) / FA_BM, heads, batch), st);
@@ -1365,8 +1375,8 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
   {
     long long threads = (long long)batch * seq * heads * (head_dim / 8);
     unsigned blocks = (unsigned)((threads + 255) / 256);
-    flash_delta_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, scratch, batch, heads, seq,
-                                               head_dim, o_row_stride, o_row_stride);
+    launch_pdl(flash_delta_kernel, dim3(blocks), dim3(256), 0, st, (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, scratch, batch, heads,
+               seq, head_dim, o_row_stride, o_row_stride);
   }
   FlashBwdParams p;
   p.batch = batch; p.heads = heads; p.seq = seq; p.head_dim = head_dim; p.scale = scale; p.causal = causal;
@@ -1388,8 +1398,8 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
       if ((rc = set_max_smem(flash_bwd_q_kernel<64>, BwdQCfg<64>::SMEM_BYTES))) return rc;
       set = true;
     }
-    flash_bwd_kv_kernel<64><<<grid, FA_BWD_THREADS, BwdKvCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    flash_bwd_q_kernel<64><<<grid, FA_BWD_THREADS, BwdQCfg<64>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    launch_pdl(flash_bwd_kv_kernel<64>, dim3(grid), dim3(FA_BWD_THREADS), BwdKvCfg<64>::SMEM_BYTES, st, tq, tk, tv, tdo, p);
+    launch_pdl(flash_bwd_q_kernel<64>, dim3(grid), dim3(FA_BWD_THREADS), BwdQCfg<64>::SMEM_BYTES, st, tq, tk, tv, tdo, p);
   } else {
     static bool set = false;
     if (!set) {
@@ -1397,8 +1407,8 @@ extern "C" int oa_flash_bwd(const void* q, const void* k, const void* v, const v
       if ((rc = set_max_smem(flash_bwd_q_kernel<128>, BwdQCfg<128>::SMEM_BYTES))) return rc;
       set = true;
     }
-    flash_bwd_kv_kernel<128><<<grid, FA_BWD_THREADS, BwdKvCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
-    flash_bwd_q_kernel<128><<<grid, FA_BWD_THREADS, BwdQCfg<128>::SMEM_BYTES, st>>>(tq, tk, tv, tdo, p);
+    launch_pdl(flash_bwd_kv_kernel<128>, dim3(grid), dim3(FA_BWD_THREADS), BwdKvCfg<128>::SMEM_BYTES, st, tq, tk, tv, tdo, p);
+    launch_pdl(flash_bwd_q_kernel<128>, dim3(grid), dim3(FA_BWD_THREADS), BwdQCfg<128>::SMEM_BYTES, st, tq, tk, tv, tdo, p);
   }
   return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
 }

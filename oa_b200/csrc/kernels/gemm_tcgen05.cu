@@ -162,7 +162,8 @@ struct TmaStoreCtx {
   uint32_t n;            // stores issued by this warp
   int row0;              // first row of the warp's 32
 };
-__device__ __forceinline__ void tma_store_piece(TmaStoreCtx* ts, const CUtensorMap* m, const float* v, int col0) {
+// `w`: the lane's 32 columns as 16 packed bf16 pairs
+__device__ __forceinline__ void tma_store_packed(TmaStoreCtx* ts, const CUtensorMap* m, const uint32_t* w, int col0) {
   const int lane = threadIdx.x & 31;
   uint8_t* b = ts->buf + (ts->n & 1) * 2048;
   if (lane == 0) tma_store_wait_read1();
@@ -170,13 +171,17 @@ __device__ __forceinline__ void tma_store_piece(TmaStoreCtx* ts, const CUtensorM
   const uint32_t base = smem_u32(b) + lane * 64;
   const int sw = (lane >> 1) & 3;                       // 64-byte swizzle: 16-byte piece index ^= address bits 7..8
 #pragma unroll
-  for (int g = 0; g < 4; ++g)
-    st_shared_v4(base + ((g ^ sw) << 4), make_uint4(pack_bf16x2(v[g * 8], v[g * 8 + 1]), pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]),
-                                                    pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7])));
+  for (int g = 0; g < 4; ++g) st_shared_v4(base + ((g ^ sw) << 4), make_uint4(w[g * 4], w[g * 4 + 1], w[g * 4 + 2], w[g * 4 + 3]));
   fence_proxy_async_smem();
   __syncwarp();
   if (lane == 0) { tma_store_2d(m, b, col0, ts->row0); tma_store_commit(); }
   ++ts->n;
+}
+__device__ __forceinline__ void tma_store_piece(TmaStoreCtx* ts, const CUtensorMap* m, const float* v, int col0) {
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+  tma_store_packed(ts, m, w, col0);
 }
 
 template <int BN>
@@ -437,6 +442,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty = bars + 2 * STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
 
+  if (p.group_mode == 1) pdl_wait();     // the prologue below reads the group offsets, which the previous kernel may have written
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // 4 epilogue warps (the tensor-parallel modes, whose staging and counters are laid out for four) or 8: two warps per
@@ -485,6 +491,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = p.group_mode == 1 ? s_prefix[p.batch] : tiles_per_batch * p.batch;
+  pdl_wait();                            // global memory (operands, flags, outputs) only from here on
   const int n_compute = (int)gridDim.x;
   unsigned long long tp_epoch = 0;
   if (p.tp_mode) tp_epoch = *reinterpret_cast<volatile unsigned long long*>(p.tp_sync) + 1;
@@ -683,6 +690,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __syncthreads();
     tp_reduce_rows(p, n_tiles, tp_epoch, &s_tp_ok);
   }
+  pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -727,7 +735,10 @@ struct PairCfg {
 __device__ long long g_pair_probe[128 * 4];
 #endif
 
-template <int A_MN, int B_MN>
+// LEAN: the instantiation for a plain bf16 product (scale, round, TMA store). Its epilogue is a few dozen instructions
+// instead of the generic one's thousands, which the epilogue warps would otherwise keep fetching through the instruction
+// caches that the MMA-issuing and the loading warp share with them.
+template <int A_MN, int B_MN, int LEAN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::MAX_THREADS, 1)
 gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC,
@@ -783,6 +794,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   cluster_sync_all();                    // both CTAs' barriers exist before anything arrives on them from the other side
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                            // everything above ran under the previous kernel's tail; global memory from here on
 
   if (warp == 0) {
     if (lane == 0) {
@@ -929,6 +941,68 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int chunks = (half < 0 ? 8 : 4) / parts;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + part * chunks * 32;
       const int col_base = ni * 256 + (half < 0 ? 0 : half * 128) + part * chunks * 32;
+      if constexpr (LEAN != 0) {
+        // LEAN 1: scale, round, store.  2: + residual.  3: GELU with the pre-activation copy (two stores).  4: multiply by
+        // gelu'(saved pre-activation).  The row of the residual / saved pre-activation is fetched one chunk ahead.
+        const bool live = tsc.row0 < p.M;
+        const __nv_bfloat16* pre_base = LEAN == 2 ? p.residual + (size_t)row * p.ldr : (LEAN == 4 ? p.aux_in + (size_t)row * p.ldaux : nullptr);
+        uint4 nxt[4];
+        auto prefetch = [&](int c) {
+          const int col = col_base + c * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            nxt[g] = (row < p.M && col + g * 8 < p.N) ? __ldg(reinterpret_cast<const uint4*>(pre_base + col + g * 8)) : make_uint4(0, 0, 0, 0);
+        };
+        if constexpr (LEAN == 2 || LEAN == 4) prefetch(0);
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          uint32_t r[32];
+          uint4 cur[4];
+          if constexpr (LEAN == 2 || LEAN == 4) { cur[0] = nxt[0]; cur[1] = nxt[1]; cur[2] = nxt[2]; cur[3] = nxt[3]; }
+          tmem_ld32(taddr + c * 32, r);
+          if constexpr (LEAN == 2 || LEAN == 4) { if (c + 1 < chunks) prefetch(c + 1); }
+          tmem_ld_wait();
+          if (c == chunks - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[acc]) & kPeerBitMask);
+          }
+          const int col0 = col_base + c * 32;
+          if (live && col0 < p.N) {
+            uint32_t w[16];
+            if constexpr (LEAN == 1) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * p.alpha, __uint_as_float(r[2 * i + 1]) * p.alpha);
+            } else if constexpr (LEAN == 2) {
+              const uint32_t* cw = reinterpret_cast<const uint32_t*>(cur);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float2 q = unpack_bf16x2(cw[i]);
+                w[i] = pack_bf16x2(fmaf(__uint_as_float(r[2 * i]), p.alpha, q.x), fmaf(__uint_as_float(r[2 * i + 1]), p.alpha, q.y));
+              }
+            } else if constexpr (LEAN == 3) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * p.alpha, __uint_as_float(r[2 * i + 1]) * p.alpha);
+              tma_store_packed(&tsc, &tmAux, w, col0);
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                w[i] = pack_bf16x2(gelu_tanh_fast(__uint_as_float(r[2 * i]) * p.alpha), gelu_tanh_fast(__uint_as_float(r[2 * i + 1]) * p.alpha));
+            } else {
+              const uint32_t* cw = reinterpret_cast<const uint32_t*>(cur);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const float2 z = unpack_bf16x2(cw[i]);
+                w[i] = pack_bf16x2(__uint_as_float(r[2 * i]) * p.alpha * gelu_tanh_grad_fast(z.x),
+                                   __uint_as_float(r[2 * i + 1]) * p.alpha * gelu_tanh_grad_fast(z.y));
+              }
+            }
+            tma_store_packed(&tsc, &tmC, w, col0);
+          }
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
+      }
       // the saved pre-activation (or the residual) of chunk c + 1 is fetched while chunk c is worked on
       const __nv_bfloat16* pre_base = (p.splits > 1 || !p.epi_prefetch) ? nullptr : (p.aux_in ? p.aux_in + (size_t)row * p.ldaux : (p.residual ? p.residual + (size_t)row * p.ldr : nullptr));
       uint4 nxt[4];
@@ -958,29 +1032,32 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     }
     if (ts && lane == 0) tma_store_wait_read0();         // the staging buffers stay valid until the last store has read them
   }
+  pdl_launch_dependents();               // this CTA's work is issued: the next kernel's CTAs may take the SM as it drains
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();                    // neither CTA leaves (or frees TMEM) while the other may still touch it
   if (warp == 1) { tc_fence_after(); tmem_dealloc_pair<Cfg::TMEM_COLS>(tmem_base); }
 }
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, int LEAN>
 static int launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tc,
                             const CUtensorMap& taux, const GemmParams& p, int grid, cudaStream_t st) {
-  auto kfn = gemm_pair_bf16_kernel<A_MN, B_MN>;
+  auto kfn = gemm_pair_bf16_kernel<A_MN, B_MN, LEAN>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess) return OA_ERR_LAUNCH;
     attr_set = true;
   }
   static const int epi_warps = [] { const char* e = getenv("OA_GEMM_PAIR_EPI_WARPS"); return (e && atoi(e) == 4) ? 4 : 8; }();
-  kfn<<<grid, 64 + 32 * epi_warps, PairCfg::SMEM_BYTES, st>>>(ta, tb, tb2, tc, taux, p);
-  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+  const cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(64 + 32 * epi_warps), PairCfg::SMEM_BYTES, st, ta, tb, tb2, tc, taux, p);
+  return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? OA_OK : OA_ERR_LAUNCH;
 }
 
 // Fixed-order reduction of split-K partials (deterministic), then the plain store / accumulate epilogue.
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int M, int N, void* out, int ldc,
                                      int out_f32, int accumulate, int batch, long long sc_batch) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   size_t total4 = (size_t)batch * M * N / 4;
   if (i4 >= total4) return;
@@ -1096,8 +1173,12 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       return OA_ERR_LAUNCH;
     attr_set = true;
   }
-  kfn<<<grid, p.tp_mode ? 192 : 320, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, ta2 ? *ta2 : ta, p);
-  return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+  if (p.tp_mode) {   // kernels that wait on other ranks start the ordinary way
+    kfn<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, ta2 ? *ta2 : ta, p);
+    return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
+  }
+  const cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(320), GemmCfg<BN>::SMEM_BYTES, st, ta, tb, ta2 ? *ta2 : ta, p);
+  return (e == cudaSuccess && cudaGetLastError() == cudaSuccess) ? OA_OK : OA_ERR_LAUNCH;
 }
 
 }  // namespace oa
@@ -1224,18 +1305,37 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
         p.tma_store = 1;
       const long long units = tiles2 * ps;
       const int pgrid = (int)(units * 2 < sms ? units * 2 : sms);
-      switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {
-        case 0: rc = launch_gemm_pair<0, 0>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
-        case 1: rc = launch_gemm_pair<0, 1>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
-        case 2: rc = launch_gemm_pair<1, 0>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
-        default: rc = launch_gemm_pair<1, 1>(ta, tb, tb2, tc, taux, p, pgrid, st); break;
+      // specialised epilogues (small code): plain, + residual, GELU with pre-activation copy, GELU backward; anything else
+      // (bias, other activations, fp32 output, accumulation, split-K) takes the generic instantiation
+      static const bool lean_enabled = []() { const char* e = std::getenv("OA_GEMM_LEAN"); return !(e && e[0] == '0'); }();
+      int lean = 0;
+      if (lean_enabled && p.tma_store && !bias) {
+        if (plain) lean = 1;
+        else if (residual && !aux_out && !aux_in && act == OA_ACT_NONE) lean = 2;
+        else if (!residual && aux_out && !aux_in && act == OA_ACT_GELU) lean = 3;
+        else if (!residual && !aux_out && aux_in && act == OA_ACT_GELU_BWD) lean = 4;
       }
+#define OA_PAIR_CASE(L)                                                                                    \
+      switch ((a_mn ? 2 : 0) | (b_mn ? 1 : 0)) {                                                          \
+        case 0: rc = launch_gemm_pair<0, 0, L>(ta, tb, tb2, tc, taux, p, pgrid, st); break;               \
+        case 1: rc = launch_gemm_pair<0, 1, L>(ta, tb, tb2, tc, taux, p, pgrid, st); break;               \
+        case 2: rc = launch_gemm_pair<1, 0, L>(ta, tb, tb2, tc, taux, p, pgrid, st); break;               \
+        default: rc = launch_gemm_pair<1, 1, L>(ta, tb, tb2, tc, taux, p, pgrid, st); break;              \
+      }
+      switch (lean) {
+        case 1: OA_PAIR_CASE(1); break;
+        case 2: OA_PAIR_CASE(2); break;
+        case 3: OA_PAIR_CASE(3); break;
+        case 4: OA_PAIR_CASE(4); break;
+        default: OA_PAIR_CASE(0); break;
+      }
+#undef OA_PAIR_CASE
       if (rc) return rc;
       if (p.splits > 1) {
         size_t total4 = (size_t)M * N / 4;
         unsigned blocks = (unsigned)((total4 + 255) / 256);
-        splitk_reduce_kernel<<<blocks, 256, 0, st>>>(p.workspace, p.splits, M, N, out, ldc, out_f32, accumulate, 1, 0);
-        if (cudaGetLastError() != cudaSuccess) return OA_ERR_LAUNCH;
+        if (launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, st, (const float*)p.workspace, p.splits, M, N, out, ldc, out_f32,
+                       accumulate, 1, 0LL) != cudaSuccess || cudaGetLastError() != cudaSuccess) return OA_ERR_LAUNCH;
       }
       return OA_OK;
     }

@@ -41,6 +41,8 @@ template <typename T>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, float* __restrict__ rstd_out,
                    long long rows, int cols, float eps, const T* __restrict__ res_in, T* __restrict__ res_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int V = NIO<T>::VEC;
   const int lane = threadIdx.x & 31;
   const long long warp_global = (long long)blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
@@ -83,6 +85,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy,
                    const float* __restrict__ rstd_in, T* __restrict__ dx, long long rows, int cols,
                    const T* __restrict__ dres, float* __restrict__ partial, int warps_used) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float s_dw[];  // [warps_used][cols]
   constexpr int V = NIO<T>::VEC;
   const int lane = threadIdx.x & 31;
@@ -140,6 +144,8 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_reg_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ dy,
                        const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx, long long rows, const __nv_bfloat16* __restrict__ dres,
                        float* __restrict__ partial) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float s_dw[];  // [NORM_WARPS][cols]
   constexpr int cols = ITER * 256;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -315,6 +321,8 @@ layernorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* 
 template <typename D>
 __global__ void __launch_bounds__(256)
 partial_rows_sum_kernel(const float* __restrict__ partial, D* __restrict__ out, int nparts, int cols, int accumulate) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[8][33];
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
@@ -364,7 +372,7 @@ extern "C" int oa_rmsnorm_fwd(int dtype, const void* x, const void* w, void* y, 
   if (dtype == OA_F32)
     rmsnorm_fwd_kernel<float><<<(int)b, NORM_THREADS, 0, ST>>>((const float*)x, (const float*)w, (float*)y, rstd, rows, cols, eps, (const float*)residual_in, (float*)residual_out);
   else if (dtype == OA_BF16)
-    rmsnorm_fwd_kernel<__nv_bfloat16><<<(int)b, NORM_THREADS, 0, ST>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, cols, eps, (const __nv_bfloat16*)residual_in, (__nv_bfloat16*)residual_out);
+    launch_pdl(rmsnorm_fwd_kernel<__nv_bfloat16>, dim3((unsigned)b), dim3(NORM_THREADS), 0, ST, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, rstd, rows, cols, eps, (const __nv_bfloat16*)residual_in, (__nv_bfloat16*)residual_out);
   else return OA_ERR_UNSUPPORTED;
   return CHECK_LAUNCH();
 }
@@ -398,7 +406,7 @@ extern "C" int oa_rmsnorm_bwd(int dtype, const void* x, const void* w, const voi
     __nv_bfloat16* bo = (__nv_bfloat16*)dx;
 #define OA_RMS_BWD_REG(IT)                                                                          \
     if ((rc = set_smem(rmsnorm_bwd_reg_kernel<IT>, smem))) return rc;                                \
-    rmsnorm_bwd_reg_kernel<IT><<<blocks, NORM_THREADS, smem, ST>>>(bx, bw, bd, rstd, bo, rows, br, scratch)
+    launch_pdl(rmsnorm_bwd_reg_kernel<IT>, dim3(blocks), dim3(NORM_THREADS), smem, ST, bx, bw, bd, rstd, bo, rows, br, scratch)
     switch (cols / 256) {
       case 1: OA_RMS_BWD_REG(1); break;
       case 2: OA_RMS_BWD_REG(2); break;
@@ -411,8 +419,8 @@ extern "C" int oa_rmsnorm_bwd(int dtype, const void* x, const void* w, const voi
     rmsnorm_bwd_kernel<__nv_bfloat16><<<blocks, NORM_THREADS, smem, ST>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy, rstd, (__nv_bfloat16*)dx, rows, cols, (const __nv_bfloat16*)dres, scratch, warps);
   } else return OA_ERR_UNSUPPORTED;
   if (dw) {
-    if (dw_dtype == OA_F32) partial_rows_sum_kernel<float><<<(cols + 31) / 32, 256, 0, ST>>>(scratch, (float*)dw, blocks, cols, accumulate_dw);
-    else partial_rows_sum_kernel<__nv_bfloat16><<<(cols + 31) / 32, 256, 0, ST>>>(scratch, (__nv_bfloat16*)dw, blocks, cols, accumulate_dw);
+    if (dw_dtype == OA_F32) launch_pdl(partial_rows_sum_kernel<float>, dim3((cols + 31) / 32), dim3(256), 0, ST, scratch, (float*)dw, blocks, cols, accumulate_dw);
+    else launch_pdl(partial_rows_sum_kernel<__nv_bfloat16>, dim3((cols + 31) / 32), dim3(256), 0, ST, scratch, (__nv_bfloat16*)dw, blocks, cols, accumulate_dw);
   }
   return CHECK_LAUNCH();
 }
