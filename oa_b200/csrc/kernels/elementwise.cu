@@ -4,6 +4,7 @@
 // (Source/Private/Oa/Ml/Shader/Compute/Nn/Activation/*.slang), Swiglu, RopeApply, Embedding /
 // Gather and the Philox generators (Source/Private/Oa/Core/Shader/Compute/Math/Philox.slang:18-84).
 // All are bandwidth-bound: 16-byte vector accesses, grid-stride loops sized to the SM count.
+#include <cstring>
 #include "common.cuh"
 #include "api.h"
 
@@ -161,6 +162,12 @@ template <typename T>
 __global__ void fill_kernel(T* y, long long n, float value) {
   long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) IO<T>::st1(y + i, value);
+}
+
+// 16 bytes per store for the bulk of an aligned fill (the element-wise kernel above writes 2 or 4 bytes per thread)
+__global__ void fill_vec_kernel(uint4* y, long long n16, uint4 pattern) {
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) y[i] = pattern;
 }
 
 // Swiglu on a packed [rows, 2F] tensor: out = silu(A[:, :F]) * A[:, F:]
@@ -622,6 +629,22 @@ extern "C" int oa_cast(int sd, int dd, const void* x, void* y, long long n, void
 }
 extern "C" int oa_fill(int dtype, void* y, long long n, float value, void* stream) {
   if (n <= 0) return OA_OK;
+  const int esz = dtype == OA_BF16 ? 2 : (dtype == OA_F32 ? 4 : 0);
+  if (esz && n * esz >= (1 << 16) && (reinterpret_cast<uintptr_t>(y) & 15) == 0) {
+    uint32_t word;
+    if (dtype == OA_BF16) {
+      const __nv_bfloat16 b = __float2bfloat16(value);
+      unsigned short h;
+      memcpy(&h, &b, 2);
+      word = (uint32_t)h | ((uint32_t)h << 16);
+    } else {
+      memcpy(&word, &value, 4);
+    }
+    const long long n16 = n * esz / 16, done = n16 * 16 / esz;
+    fill_vec_kernel<<<grid_for(n16, 256), 256, 0, ST>>>((uint4*)y, n16, make_uint4(word, word, word, word));
+    if (done < n) { DISPATCH_T(dtype, fill_kernel<T><<<1, 32, 0, ST>>>((T*)y + done, n - done, value)); }
+    return CHECK_LAUNCH();
+  }
   DISPATCH_T(dtype, fill_kernel<T><<<grid_for(n, 256), 256, 0, ST>>>((T*)y, n, value));
   return CHECK_LAUNCH();
 }

@@ -941,7 +941,41 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int chunks = (half < 0 ? 8 : 4) / parts;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * 256 + part * chunks * 32;
       const int col_base = ni * 256 + (half < 0 ? 0 : half * 128) + part * chunks * 32;
-      if constexpr (LEAN != 0) {
+      if constexpr (LEAN == 5 || LEAN == 6) {
+        // 5: split-K partial, the scaled fp32 accumulator goes to this split's slice of the workspace
+        // 6: fp32 output, optionally added to what is there (weight gradients accumulated in place)
+        float* wrow = LEAN == 5 ? p.workspace + ((size_t)split * p.M + row) * p.N : reinterpret_cast<float*>(p.out) + (size_t)row * p.ldc;
+        const bool add = LEAN == 6 && p.accumulate;
+#pragma unroll 1
+        for (int c = 0; c < chunks; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (c == chunks - 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(smem_u32(&tempty[acc]) & kPeerBitMask);
+          }
+          const int col0 = col_base + c * 32;
+          if (row < p.M) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (col0 + g * 4 < p.N) {
+                float4 x = make_float4(__uint_as_float(r[g * 4]) * p.alpha, __uint_as_float(r[g * 4 + 1]) * p.alpha,
+                                       __uint_as_float(r[g * 4 + 2]) * p.alpha, __uint_as_float(r[g * 4 + 3]) * p.alpha);
+                if (add) {
+                  const float4 o = *reinterpret_cast<const float4*>(wrow + col0 + g * 4);
+                  x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+                }
+                *reinterpret_cast<float4*>(wrow + col0 + g * 4) = x;
+              }
+            }
+          }
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
+      } else if constexpr (LEAN != 0) {
         // LEAN 1: scale, round, store.  2: + residual.  3: GELU with the pre-activation copy (two stores).  4: multiply by
         // gelu'(saved pre-activation).  The row of the residual / saved pre-activation is fetched one chunk ahead.
         const bool live = tsc.row0 < p.M;
@@ -1309,7 +1343,9 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
       // (bias, other activations, fp32 output, accumulation, split-K) takes the generic instantiation
       static const bool lean_enabled = []() { const char* e = std::getenv("OA_GEMM_LEAN"); return !(e && e[0] == '0'); }();
       int lean = 0;
-      if (lean_enabled && p.tma_store && !bias) {
+      if (lean_enabled && ps > 1) lean = 5;         // split-K runs only for plain products (N a multiple of 4)
+      else if (lean_enabled && plain && out_f32) lean = 6;
+      else if (lean_enabled && p.tma_store && !bias) {
         if (plain) lean = 1;
         else if (residual && !aux_out && !aux_in && act == OA_ACT_NONE) lean = 2;
         else if (!residual && aux_out && !aux_in && act == OA_ACT_GELU) lean = 3;
@@ -1327,6 +1363,8 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
         case 2: OA_PAIR_CASE(2); break;
         case 3: OA_PAIR_CASE(3); break;
         case 4: OA_PAIR_CASE(4); break;
+        case 5: OA_PAIR_CASE(5); break;
+        case 6: OA_PAIR_CASE(6); break;
         default: OA_PAIR_CASE(0); break;
       }
 #undef OA_PAIR_CASE

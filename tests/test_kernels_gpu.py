@@ -109,6 +109,20 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
     assert bool((wide[:, :32] == 3.0).all()) and bool((wide[:, 32 + N2:] == 3.0).all())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fill_large_and_unaligned(dtype):
+    """Large aligned fills use 16-byte stores for the bulk and the element kernel for the remainder; a view that does not start
+    on a 16-byte boundary takes the element kernel; the guard elements around the filled range stay untouched."""
+    n = (1 << 20) + 3
+    buf = torch.full((n + 16,), 7.0, dtype=dtype, device=DEV)
+    for off in (8, 9):                                   # 8 elements: 16-byte aligned for both types; 9: not aligned
+        buf.fill_(7.0)
+        K.fill_(buf[off:off + n], -1.5)
+        torch.cuda.synchronize()
+        assert bool((buf[off:off + n] == -1.5).all()), off
+        assert bool((buf[:off] == 7.0).all()) and bool((buf[off + n:] == 7.0).all()), off
+
+
 @pytest.mark.parametrize("bn", [128, 256])
 def test_gemm_bf16_epilogues(bn):
     torch.manual_seed(1)
