@@ -8,6 +8,7 @@ CPU-only machine `lib()` returns None and callers use the fp32 reference math in
 from __future__ import annotations
 
 import ctypes
+import os
 import re
 from pathlib import Path
 from typing import Optional
@@ -16,7 +17,8 @@ import torch
 
 _ROOT = Path(__file__).resolve().parent
 _API_H = _ROOT / "csrc" / "kernels" / "api.h"
-_LIB_PATH = _ROOT / "_lib" / "liboa_kernels.so"
+# OA_KERNELS_LIB: another build of the same sources (an experiment compiled with different macros) to load instead
+_LIB_PATH = Path(os.environ["OA_KERNELS_LIB"]) if os.environ.get("OA_KERNELS_LIB") else _ROOT / "_lib" / "liboa_kernels.so"
 
 _CTYPES = {
     "int": ctypes.c_int, "float": ctypes.c_float, "size_t": ctypes.c_size_t, "long long": ctypes.c_longlong,
