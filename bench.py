@@ -227,7 +227,9 @@ class OaJob:
             from oa_b200.parallel.mesh import OaDeviceMesh
             self.mesh = OaDeviceMesh()
             self.model = OaGptModel(cfg)
-            self.ep = OaExpertParallel(self.model, self.mesh, tokens_per_rank=B * self.seq)
+            # first size of the dispatch buffers: twice the mean rows per rank (they grow on demand, but a growth is a collective
+            # reallocation that would land in the timed steps while the router is still drifting)
+            self.ep = OaExpertParallel(self.model, self.mesh, tokens_per_rank=B * self.seq, capacity_factor=2.0)
             ex = self.ep.ExpertParameters()
             ex_ids = {id(p) for p in ex}
             dense = [p for p in self.model.AllParameterPtrs() if id(p) not in ex_ids]
@@ -326,6 +328,7 @@ class OaJob:
                 ("cuda graph replay of the micro-step, eager optimizer step" if micro else "eager stream"),
                 "optimizer": "AdamW fp32 master" if self.k != 1 else "Adam fp32", "dp": self.dp_mode, "layers": self.cfg.NLayers,
                 "status": "ok" if self.ctx.Sync() else "error",
+                **({"ep_buffer_growths": self.ep.Growths()} if getattr(self, "ep", None) is not None else {}),
                 **({"capture": self.acc_step.LastStatus.message} if (self.explicit and not self.acc_step.LastStatus.IsOk()) else {})}
 
     def flops_per_token(self) -> float:

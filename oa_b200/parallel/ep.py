@@ -218,6 +218,10 @@ class OaExpertParallel:
         for _, c in module.Children():
             self._walk(c, cls)
 
+    def Growths(self) -> int:
+        """How often any layer's row buffers had to be replaced by larger ones so far (each time is a collective reallocation)."""
+        return sum(layer.Dispatcher.Grown for layer in self.layers)
+
     def ExpertParameters(self):
         out = []
         for layer in self.layers:

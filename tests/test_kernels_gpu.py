@@ -99,6 +99,15 @@ def test_gemm_bf16_cta_pair_kernel(a_mn, b_mn):
         _close(got, want, 1e-2, what=f"pair gemm activation backward {act}")
     plain = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, alpha=0.5)
     _close(plain, 0.5 * K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn), 1e-2, what="pair gemm plain bf16 store")
+    # the specialised epilogue forms (no bias): + residual; GELU with the pre-activation copy
+    got = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, residual=res)
+    _close(got, K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn, residual=res.cpu().float()), 1e-2, what="pair gemm + residual")
+    aux2 = torch.full((M, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    got = K.gemm(a, b, a_mn=a_mn, b_mn=b_mn, act=K.ACT_GELU, aux_out=aux2)
+    aux2_ref = torch.empty(M, N)
+    want = K.gemm(a.cpu().float(), b.cpu().float(), a_mn=a_mn, b_mn=b_mn, act=K.ACT_GELU, aux_out=aux2_ref)
+    _close(got, want, 1e-2, what="pair gemm gelu with pre-activation copy, no bias")
+    _close(aux2, aux2_ref, 1e-2, what="pair gemm pre-activation copy, no bias")
     # N a multiple of 8 but not of the 32-column store box, output a column slice of a wider matrix (row pitch != N):
     # the boxes at the right and bottom edges are clipped, the columns beside the slice stay untouched
     N2 = 2632
@@ -239,7 +248,7 @@ def test_swiglu_rope_embedding(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,cols", [(33, 128), (1000, 1024)])
+@pytest.mark.parametrize("rows,cols", [(33, 128), (300, 512), (1000, 1024)])
 def test_norms(dtype, rows, cols):
     torch.manual_seed(6)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
