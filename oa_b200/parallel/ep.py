@@ -62,13 +62,14 @@ class _GradStaging:
 
 class OaEpDispatcher:
     def __init__(self, mesh: OaDeviceMesh, num_experts: int, d_model: int, d_ff: int, tokens: int, k: int,
-                 capacity_factor: float = 1.25, shared_bwd: Optional[_GradStaging] = None):
+                 capacity_factor: float = 2.0, shared_bwd: Optional[_GradStaging] = None):
         self.mesh, self.E, self.D, self.F, self.T, self.k = mesh, num_experts, d_model, d_ff, tokens, k
         W = mesh.world
         assert num_experts % W == 0 and num_experts % 4 == 0
         self.E_loc = num_experts // W
         avg = tokens * k                                   # rows an owner receives when the load is uniform
-        # `capacity_factor` only sets the FIRST size of the row buffers; they grow to what the routing asks for
+        # `capacity_factor` only sets the FIRST size of the row buffers; they grow to what the routing asks for.  Twice the
+        # mean by default: a growth is a collective reallocation (measured: a step that grows costs about twice a step that does not)
         self.cap = _round_up(int(avg * capacity_factor) + self.E_loc * M.SEG, M.SEG)
         self.Grown = 0                                     # how many times the buffers had to grow
         dev = mesh.device
@@ -192,7 +193,7 @@ class OaEpDispatcher:
 class OaExpertParallel:
     """Shards the routed experts of every OaMoE layer of `model` over the mesh and installs the dispatchers."""
 
-    def __init__(self, model, mesh: Optional[OaDeviceMesh] = None, tokens_per_rank: int = 0, capacity_factor: float = 1.25):
+    def __init__(self, model, mesh: Optional[OaDeviceMesh] = None, tokens_per_rank: int = 0, capacity_factor: float = 2.0):
         from ..ml.nn.moe import OaMoE
         self.mesh = mesh or OaDeviceMesh()
         self.layers = []
