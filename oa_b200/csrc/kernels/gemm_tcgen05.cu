@@ -445,7 +445,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (p.group_mode == 1) pdl_wait();     // the prologue below reads the group offsets, which the previous kernel may have written
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // 4 epilogue warps (the tensor-parallel modes, whose staging and counters are laid out for four) or 8: two warps per
+  // 4 epilogue warps (the GEMM -> reduce-scatter mode, whose staging and counters are laid out for four) or 8: two warps per
   // scheduler, the two of a TMEM lane quarter taking half of the accumulator's columns each
   const int epi_warps = (int)(blockDim.x >> 5) - 2;
 
@@ -606,7 +606,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     int n_pend = 0;
-    if (p.tp_mode == 1) tp_push_shard(p, tp_epoch);
+    if (p.tp_mode == 1 && warp < 6) tp_push_shard(p, tp_epoch);   // warps 2..5: its work split and its named barrier count 128 threads
     for (int t = blockIdx.x; t < total_tiles; t += n_compute) {
       const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
       const int bi = ti.bi, ni = ti.ni, split = ti.split, kb0 = ti.kb0, kb1 = ti.kb1;
@@ -1207,8 +1207,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       return OA_ERR_LAUNCH;
     attr_set = true;
   }
-  if (p.tp_mode) {   // kernels that wait on other ranks start the ordinary way
-    kfn<<<grid, 192, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, ta2 ? *ta2 : ta, p);
+  if (p.tp_mode) {   // kernels that wait on other ranks start the ordinary way; the reduce-scatter mode's staging is laid out for 4 warps
+    kfn<<<grid, p.tp_mode == 2 ? 192 : 320, GemmCfg<BN>::SMEM_BYTES, st>>>(ta, tb, ta2 ? *ta2 : ta, p);
     return cudaGetLastError() == cudaSuccess ? OA_OK : OA_ERR_LAUNCH;
   }
   const cudaError_t e = launch_pdl(kfn, dim3(grid), dim3(320), GemmCfg<BN>::SMEM_BYTES, st, ta, tb, ta2 ? *ta2 : ta, p);
