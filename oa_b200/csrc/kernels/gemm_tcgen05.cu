@@ -9,11 +9,12 @@
 // (dX = dY * W) and weight-gradient (dW = dY^T * X) products need, so no
 // transposed copies are ever made.
 //
-// Structure: persistent kernel, one CTA per SM, 192 threads.
+// Structure: persistent kernel, one CTA per SM (or one CTA pair per two SMs), 320 threads.
 //   warp 0 (one lane)  TMA producer: cp.async.bulk.tensor tiles into a 4/6 stage smem ring (128B swizzle)
-//   warp 1 (one lane)  tcgen05.mma issuer: 128 x BN x 16 MMAs into one of two TMEM accumulators
-//   warps 2..5         epilogue: tcgen05.ld the finished accumulator, fuse bias / GELU / residual /
-//                      GELU-backward / accumulate, store bf16 or fp32
+//   warp 1 (one lane)  tcgen05.mma issuer: 128 x BN x 16 MMAs (256 x 256 x 16 for a pair) into one of two TMEM accumulators
+//   warps 2..9         epilogue, two warps per scheduler (warps 2..5 only in the GEMM -> reduce-scatter mode): tcgen05.ld the
+//                      finished accumulator, fuse bias / GELU / residual / GELU-backward / accumulate, store bf16 (through
+//                      TMA stores in the pair kernel) or fp32
 // The two TMEM accumulators let the epilogue of tile i overlap the main loop of tile i+1.
 // Split-K (for weight gradients whose output has too few tiles to fill 148 SMs) writes fp32
 // partials to a workspace that a small second kernel reduces in a fixed order (deterministic).
