@@ -195,6 +195,19 @@ def test_gemm_f32():
     _close(out, a.cpu() @ b.cpu().t(), 1e-5, what="f32 gemm mn")
     x, y = torch.randn(5, 40, 24, device=DEV), torch.randn(5, 24, 36, device=DEV)
     _close(K.bmm_f32(x, y, b_mn=True), torch.bmm(x.cpu(), y.cpu()), 1e-5, what="bmm")
+    # whole 64 x 64 tiles next to edge tiles, both layouts, epilogues, accumulation
+    for (M, N, Kk) in [(256, 192, 128), (200, 136, 64), (128, 64, 1024)]:      # the last one takes the split-K path
+        a, b = torch.randn(M, Kk, device=DEV), torch.randn(N, Kk, device=DEV)
+        bias = torch.randn(N, device=DEV)
+        ref = a.cpu().double() @ b.cpu().double().t()
+        _close(K.gemm(a, b), ref.float(), 2e-5, what=f"f32 gemm {M}x{N}x{Kk} K-major")
+        _close(K.gemm(a.t().contiguous(), b.t().contiguous(), a_mn=True, b_mn=True), ref.float(), 2e-5, what=f"f32 gemm {M}x{N}x{Kk} MN-major")
+        _close(K.gemm(a, b.t().contiguous(), b_mn=True, bias=bias, act=K.ACT_RELU), torch.relu(ref + bias.cpu().double()).float(), 2e-5,
+               what=f"f32 gemm {M}x{N}x{Kk} mixed layouts, bias + relu")
+        acc = torch.randn(M, N, device=DEV)
+        want = acc.cpu().double() + 0.5 * ref
+        K.gemm(a, b, out=acc, accumulate=True, alpha=0.5)
+        _close(acc, want.float(), 2e-5, what=f"f32 gemm {M}x{N}x{Kk} accumulate")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
