@@ -3,8 +3,8 @@
 The reference's image codec layer (Source/Private/Oa/Vision: JPEG / PNG / BMP / TGA / WebP through bundled decoders)
 feeds `OaImage`; here the lossless formats are implemented directly (PNG inflate / deflate through zlib, all five scanline
 filters, 8-bit grey / grey-alpha / RGB / RGBA / palette, 16-bit reduced to 8) and baseline JPEG is written out from the
-standard in `jpeg.py` (progressive streams are refused).  WebP is not part of this build and is rejected with
-Unimplemented; video codecs need the vendor's decode engine through a graphics API and are unavailable here.
+standard in `jpeg.py` (progressive streams are refused).  Lossless WebP (VP8L) is decoded and encoded by `webp.py`; lossy WebP
+(VP8) is rejected with Unimplemented; video codecs need the vendor's decode engine through a graphics API and are unavailable here.
 """
 from __future__ import annotations
 
@@ -236,10 +236,9 @@ class OaImageIo:
     @staticmethod
     def DecodeMemory(data: bytes) -> Tuple[Optional[OaImage], OaStatus]:
         kind = OaImageIo.Detect(data)
-        if kind == "webp":
-            return None, OaStatus(OaStatusCode.Unimplemented, "webp decoding is not part of this build")
         from .jpeg import DecodeJpeg
-        fn = {"png": DecodePng, "bmp": DecodeBmp, "tga": DecodeTga, "pnm": DecodePnm, "jpeg": DecodeJpeg}.get(kind)
+        from .webp import DecodeWebp
+        fn = {"png": DecodePng, "bmp": DecodeBmp, "tga": DecodeTga, "pnm": DecodePnm, "jpeg": DecodeJpeg, "webp": DecodeWebp}.get(kind)
         if fn is None:
             return None, OaStatus(OaStatusCode.InvalidArgument, "unrecognised image stream")
         try:
@@ -283,8 +282,9 @@ class OaImageIo:
     @staticmethod
     def EncodeMemory(image, kind: str = "png") -> Tuple[Optional[bytes], OaStatus]:
         from .jpeg import EncodeJpeg
+        from .webp import EncodeWebp
         fn = {"png": EncodePng, "bmp": EncodeBmp, "tga": EncodeTga, "pnm": EncodePnm, "ppm": EncodePnm, "pgm": EncodePnm, "jpg": EncodeJpeg,
-              "jpeg": EncodeJpeg}.get(kind.lower())
+              "jpeg": EncodeJpeg, "webp": EncodeWebp}.get(kind.lower())
         if fn is None:
             return None, OaStatus(OaStatusCode.Unimplemented, f"no encoder for '{kind}'")
         try:
@@ -332,7 +332,7 @@ class OaFilter(enum.IntEnum):
     Linear = 1
 
 
-_KIND = {OaImageCodec.Png: "png", OaImageCodec.Bmp: "bmp", OaImageCodec.Tga: "tga"}
+_KIND = {OaImageCodec.Png: "png", OaImageCodec.Bmp: "bmp", OaImageCodec.Tga: "tga", OaImageCodec.Jpeg: "jpeg", OaImageCodec.Webp: "webp"}
 
 
 def _convert(image: OaImage, fmt: OaImageFormat) -> OaImage:
@@ -358,7 +358,7 @@ def _convert(image: OaImage, fmt: OaImageFormat) -> OaImage:
 class OaImageDecoder:
     @staticmethod
     def Supports(codec: OaImageCodec) -> bool:
-        return OaImageCodec(codec) in (OaImageCodec.Auto, OaImageCodec.Png, OaImageCodec.Bmp, OaImageCodec.Tga)
+        return OaImageCodec(codec) in (OaImageCodec.Auto, OaImageCodec.Png, OaImageCodec.Bmp, OaImageCodec.Tga, OaImageCodec.Jpeg, OaImageCodec.Webp)
 
     @staticmethod
     def LoadMemory(Data: bytes, Format: OaImageFormat = OaImageFormat.Rgb) -> OaImage:
@@ -382,7 +382,7 @@ class OaImageEncoder:
 
     @staticmethod
     def Encode(Image: OaImage, Codec: OaImageCodec, Quality: int = 90) -> bytes:
-        """`Quality` applies to lossy codecs only; the codecs built here are lossless."""
+        """`Quality` applies to lossy codecs only (baseline JPEG here; WebP is written lossless)."""
         if not OaImageEncoder.Supports(Codec):
             raise RuntimeError(f"no encoder for {OaImageCodec(Codec).name} in this build")
         blob, st = OaImageIo.EncodeMemory(Image, _KIND[OaImageCodec(Codec)])
