@@ -3,7 +3,7 @@
 The reference's image codec layer (Source/Private/Oa/Vision: JPEG / PNG / BMP / TGA / WebP through bundled decoders)
 feeds `OaImage`; here the lossless formats are implemented directly (PNG inflate / deflate through zlib, all five scanline
 filters, 8-bit grey / grey-alpha / RGB / RGBA / palette, 16-bit reduced to 8) and baseline JPEG is written out from the
-standard in `jpeg.py` (progressive streams are refused).  Lossless WebP (VP8L) is decoded and encoded by `webp.py`; lossy WebP
+standard in `jpeg.py` (sequential and progressive frames).  Lossless WebP (VP8L) is decoded and encoded by `webp.py`; lossy WebP
 (VP8) is rejected with Unimplemented; video codecs need the vendor's decode engine through a graphics API and are unavailable here.
 """
 from __future__ import annotations

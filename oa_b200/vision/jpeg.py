@@ -3,7 +3,8 @@
 The reference decodes JPEG through a bundled decoder (Source/Private/Oa/Vision/Image); this is a from-the-standard
 implementation.  Decoder: SOF0 / SOF1 frames with 8-bit samples, 1 or 3 components, any sampling factors up to 2 x 2 (4:4:4,
 4:2:2, 4:2:0, 4:4:0), DQT with 8- or 16-bit entries, DHT, DRI / RSTn restart intervals, JFIF and Adobe APP14 colour hints
-(YCbCr by default, RGB when Adobe says transform 0), stuffed bytes and fill bytes.  Progressive (SOF2), lossless and
+(YCbCr by default, RGB when Adobe says transform 0), stuffed bytes and fill bytes, and progressive frames (SOF2: spectral
+selection and successive approximation, interleaved DC and per-component AC scans, end-of-band runs).  Lossless, hierarchical and
 arithmetic-coded streams are refused with NotImplementedError.  The entropy decode walks the bit stream on the host; the
 inverse DCT, chroma up-sampling (the centred triangular filter that libjpeg applies by default for a factor of 2, pixel
 replication otherwise) and colour conversion run as batched array operations over all blocks.  Encoder: baseline, quality-scaled Annex K tables, 4:4:4 or 4:2:0, optional restart interval.
@@ -185,7 +186,7 @@ def DecodeJpeg(data: bytes) -> np.ndarray:
                     raise ValueError("short Huffman table")
                 huff[(tc, th)] = _Huff(counts, values)
                 i += 17 + n
-        elif m in (0xC0, 0xC1):
+        elif m in (0xC0, 0xC1, 0xC2):
             prec, h, w, nc = seg[0], struct.unpack(">H", seg[1:3])[0], struct.unpack(">H", seg[3:5])[0], seg[5]
             if prec != 8:
                 raise NotImplementedError("JPEG with samples other than 8 bits")
@@ -194,9 +195,14 @@ def DecodeJpeg(data: bytes) -> np.ndarray:
             comps = [{"id": seg[6 + 3 * c], "h": seg[7 + 3 * c] >> 4, "v": seg[7 + 3 * c] & 15, "tq": seg[8 + 3 * c]} for c in range(nc)]
             if any(not (1 <= c["h"] <= 2 and 1 <= c["v"] <= 2) for c in comps):
                 raise NotImplementedError("JPEG sampling factors above 2")
-            frame = {"h": h, "w": w, "comps": comps}
-        elif m in (0xC2, 0xC3, 0xC5, 0xC6, 0xC7, 0xC9, 0xCA, 0xCB, 0xCD, 0xCE, 0xCF):
-            raise NotImplementedError("progressive, lossless or arithmetic-coded JPEG")
+            if nc == 1:
+                comps[0]["h"] = comps[0]["v"] = 1      # a single component is never interleaved: its sampling factors do not order anything
+            frame = {"h": h, "w": w, "comps": comps, "progressive": m == 0xC2}
+            if m == 0xC2:
+                _geometry(frame)
+                coeffs = [np.zeros((frame["mcuy"] * c["v"], frame["mcux"] * c["h"], 64), np.int32) for c in comps]
+        elif m in (0xC3, 0xC5, 0xC6, 0xC7, 0xC9, 0xCA, 0xCB, 0xCD, 0xCE, 0xCF):
+            raise NotImplementedError("lossless, hierarchical or arithmetic-coded JPEG")
         elif m == 0xDD:
             restart_interval = struct.unpack(">H", seg[:2])[0]
         elif m == 0xEE and seg[:5] == b"Adobe" and len(seg) >= 12:
@@ -205,6 +211,15 @@ def DecodeJpeg(data: bytes) -> np.ndarray:
             if frame is None:
                 raise ValueError("scan before frame header")
             ns = seg[0]
+            if frame["progressive"]:
+                scan = []
+                for k in range(ns):
+                    cid, tbl = seg[1 + 2 * k], seg[2 + 2 * k]
+                    ci = next(i for i, c in enumerate(frame["comps"]) if c["id"] == cid)
+                    scan.append((ci, tbl >> 4, tbl & 15))
+                ss, se, ah, al = seg[1 + 2 * ns], seg[2 + 2 * ns], seg[3 + 2 * ns] >> 4, seg[3 + 2 * ns] & 15
+                pos = _decode_progressive_scan(data, pos, frame, huff, restart_interval, scan, ss, se, ah, al, coeffs)
+                continue
             if ns != len(frame["comps"]):
                 raise NotImplementedError("non-interleaved baseline scans")
             for k in range(ns):
@@ -217,11 +232,123 @@ def DecodeJpeg(data: bytes) -> np.ndarray:
     return _reconstruct(frame, coeffs, qt, adobe_transform)
 
 
-def _decode_scan(data, pos, frame, huff, restart_interval):
+def _geometry(frame) -> None:
     comps = frame["comps"]
     hmax, vmax = max(c["h"] for c in comps), max(c["v"] for c in comps)
     mcux, mcuy = -(-frame["w"] // (8 * hmax)), -(-frame["h"] // (8 * vmax))
     frame.update(hmax=hmax, vmax=vmax, mcux=mcux, mcuy=mcuy)
+
+
+def _next_marker(data, end: int) -> int:
+    while end + 1 < len(data) and not (data[end] == 0xFF and data[end + 1] not in (0, 0xFF) and not (0xD0 <= data[end + 1] <= 0xD7)):
+        end += 1
+    return end
+
+
+def _decode_progressive_scan(data, pos, frame, huff, restart_interval, scan, ss, se, ah, al, coeffs) -> int:
+    """One scan of a progressive frame (ITU T.81 Annex G): a band [ss, se] of the zig-zag order at bit position al, either its first
+    pass (ah = 0) or a refinement of one more bit.  DC scans may interleave components; AC scans carry one component and use
+    end-of-band runs.  The coefficients accumulate in `coeffs` (natural order) and are dequantised after the last scan."""
+    comps = frame["comps"]
+    if ss > se or se > 63 or (ss == 0 and se != 0) or (ss > 0 and len(scan) != 1):
+        raise ValueError("bad spectral selection")
+    br = _Bits(data, pos)
+    p1, m1 = 1 << al, -(1 << al)
+    if len(scan) == 1:                          # non-interleaved: the component's own blocks in raster order
+        ci = scan[0][0]
+        c = comps[ci]
+        bw = -(-(-(-frame["w"] * c["h"] // frame["hmax"])) // 8)
+        bh = -(-(-(-frame["h"] * c["v"] // frame["vmax"])) // 8)
+        units = [[(ci, y, x)] for y in range(bh) for x in range(bw)]
+    else:
+        units = []
+        for my in range(frame["mcuy"]):
+            for mx in range(frame["mcux"]):
+                units.append([(ci, my * comps[ci]["v"] + by, mx * comps[ci]["h"] + bx)
+                              for ci, _, _ in scan for by in range(comps[ci]["v"]) for bx in range(comps[ci]["h"])])
+    tables = {ci: (huff.get((0, td)), huff.get((1, ta))) for ci, td, ta in scan}
+    pred = {ci: 0 for ci, _, _ in scan}
+    eobrun = 0
+    for n, unit in enumerate(units):
+        if restart_interval and n and n % restart_interval == 0:
+            br.restart()
+            pred = {ci: 0 for ci in pred}
+            eobrun = 0
+        for ci, by, bx in unit:
+            blk = coeffs[ci][by, bx]
+            dc_t, ac_t = tables[ci]
+            if ss == 0:
+                if ah == 0:
+                    if dc_t is None:
+                        raise ValueError("missing DC table")
+                    pred[ci] += br.receive_extend(br.decode(dc_t))
+                    blk[0] = pred[ci] * p1
+                elif br.bits(1):
+                    blk[0] |= p1
+                continue
+            if ac_t is None:
+                raise ValueError("missing AC table")
+            if ah == 0:                         # first pass of an AC band
+                if eobrun:
+                    eobrun -= 1
+                    continue
+                k = ss
+                while k <= se:
+                    rs = br.decode(ac_t)
+                    r, s_ = rs >> 4, rs & 15
+                    if s_ == 0:
+                        if r < 15:
+                            eobrun = (1 << r) - 1 + (br.bits(r) if r else 0)
+                            break
+                        k += 16
+                        continue
+                    k += r
+                    if k > se:
+                        raise ValueError("AC coefficient index beyond the band")
+                    blk[ZIGZAG[k]] = br.receive_extend(s_) * p1
+                    k += 1
+                continue
+            # refinement of an AC band: new coefficients of magnitude 1 << al, one correction bit for every known non-zero one
+            k = ss
+            if eobrun == 0:
+                while k <= se:
+                    rs = br.decode(ac_t)
+                    r, s_ = rs >> 4, rs & 15
+                    value = 0
+                    if s_ == 0:
+                        if r < 15:
+                            eobrun = (1 << r) + (br.bits(r) if r else 0)     # this block counts as the first of the run
+                            break
+                    elif s_ == 1:
+                        value = p1 if br.bits(1) else m1
+                    else:
+                        raise ValueError("refinement coefficient larger than one bit")
+                    while k <= se:
+                        z = ZIGZAG[k]
+                        k += 1
+                        if blk[z] != 0:
+                            if br.bits(1) and (blk[z] & p1) == 0:
+                                blk[z] += p1 if blk[z] > 0 else m1
+                        else:
+                            if r == 0:
+                                if value:
+                                    blk[z] = value
+                                break
+                            r -= 1
+            if eobrun:
+                while k <= se:                  # the rest of the band only receives correction bits
+                    z = ZIGZAG[k]
+                    k += 1
+                    if blk[z] != 0 and br.bits(1) and (blk[z] & p1) == 0:
+                        blk[z] += p1 if blk[z] > 0 else m1
+                eobrun -= 1
+    return _next_marker(data, br.p)
+
+
+def _decode_scan(data, pos, frame, huff, restart_interval):
+    comps = frame["comps"]
+    _geometry(frame)
+    hmax, vmax, mcux, mcuy = frame["hmax"], frame["vmax"], frame["mcux"], frame["mcuy"]
     out = [np.zeros((mcuy * c["v"], mcux * c["h"], 64), np.int32) for c in comps]
     br = _Bits(data, pos)
     pred = [0] * len(comps)
