@@ -4,7 +4,7 @@ wrap a workload, request validation and attach graph / benchmark artifacts under
 
     python -m oa_b200.devtools.evidence --output var/report/snapshot
     python -m oa_b200.devtools.evidence --validation sync --output var/report/flagship -- python bench.py --steps 3 --warmup 3
-    python -m oa_b200.devtools.evidence --attach gpurun_out/flagship.json --attach profiles/flagship_step_launch_shares.md
+    python -m oa_b200.devtools.evidence --attach var/report/flagship.json --attach profiles/flagship_step_launch_shares.md
 
 The manifest records: git commit, branch and dirty state; platform, Python, torch and CUDA versions; the devices as
 `nvidia-smi --query-gpu` reports them (read only; absent on a CPU box); an allowlist of environment variables
