@@ -74,6 +74,8 @@ struct GemmParams {
   PeerTable tp_bufs;                  // mode 1: staging [M, K] of every rank; mode 2: staging [world, M / world, N] of every rank
   PeerTable tp_flags;                 // u64 per 128-row block (mode 1: [world * blocks]; mode 2: [blocks]) on every rank
   unsigned long long* tp_sync;        // [0] epoch of this call site, [1] CTAs finished (device resident: graph replay safe)
+  // single-CTA kernel: rank-3 map {N, rows, problems} of a bf16 output that leaves through TMA stores (tma_store set)
+  alignas(64) CUtensorMap tm_out;
 };
 
 constexpr int BM = 128;
@@ -88,7 +90,8 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int EPI_ROW_BYTES = 144;      // 64 bf16 columns + 16 B pad
-  static constexpr int EPI_BYTES = 4 * 32 * EPI_ROW_BYTES;   // per epilogue warp: 32 rows (reduce-scatter mode only)
+  // staging behind the ring: 4 warps x 32 rows of the reduce-scatter mode, or 8 warps x two 2 KB TMA-store buffers
+  static constexpr int EPI_BYTES = (4 * 32 * EPI_ROW_BYTES > 8 * 4096) ? 4 * 32 * EPI_ROW_BYTES : 8 * 4096;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/ + 1280 /*group tile prefix*/ + EPI_BYTES;
 };
 
@@ -162,6 +165,7 @@ struct TmaStoreCtx {
   uint8_t* buf;          // this warp's 2 x 2 KB
   uint32_t n;            // stores issued by this warp
   int row0;              // first row of the warp's 32
+  int z;                 // problem index for a rank-3 map, -1 for a rank-2 map
 };
 // `w`: the lane's 32 columns as 16 packed bf16 pairs
 __device__ __forceinline__ void tma_store_packed(TmaStoreCtx* ts, const CUtensorMap* m, const uint32_t* w, int col0) {
@@ -175,7 +179,11 @@ __device__ __forceinline__ void tma_store_packed(TmaStoreCtx* ts, const CUtensor
   for (int g = 0; g < 4; ++g) st_shared_v4(base + ((g ^ sw) << 4), make_uint4(w[g * 4], w[g * 4 + 1], w[g * 4 + 2], w[g * 4 + 3]));
   fence_proxy_async_smem();
   __syncwarp();
-  if (lane == 0) { tma_store_2d(m, b, col0, ts->row0); tma_store_commit(); }
+  if (lane == 0) {
+    if (ts->z < 0) tma_store_2d(m, b, col0, ts->row0);
+    else tma_store_3d(m, b, col0, ts->row0, ts->z);
+    tma_store_commit();
+  }
   ++ts->n;
 }
 __device__ __forceinline__ void tma_store_piece(TmaStoreCtx* ts, const CUtensorMap* m, const float* v, int col0) {
@@ -429,7 +437,7 @@ __device__ __forceinline__ void tp_reduce_rows(const GemmParams& p, int n_tiles,
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(320, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmA2, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -456,8 +464,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_per_batch = mn_tiles * p.splits;
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
   uint8_t* s_epi = smem + STAGES * Cfg::STAGE_BYTES + 256 + 1280;     // reduce-scatter epilogue staging (4 warps)
-  __shared__ int s_tp_ok;
-  __shared__ unsigned long long* s_pend[4][16];   // reduce-scatter: counters of stored tiles not yet published, per epilogue warp
+  // reduce-scatter mode only, behind its 18 KB of staging (the TMA-store buffers that share this region are off in that mode);
+  // kept out of static shared memory: ring + staging already fill the 227 KB of a CTA to within 512 bytes
+  unsigned long long* (*s_pend)[16] = reinterpret_cast<unsigned long long* (*)[16]>(s_epi + 4 * 32 * Cfg::EPI_ROW_BYTES);   // [4][16]: counters of stored tiles not yet published, per epilogue warp
+  int& s_tp_ok = *reinterpret_cast<int*>(s_epi + 4 * 32 * Cfg::EPI_ROW_BYTES + 512);
   if (p.group_mode == 1 && threadIdx.x == 32) {
     int run = 0;
     for (int g = 0; g < p.batch; ++g) {
@@ -473,6 +483,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     if (p.tp_mode == 1) tma_prefetch_desc(&tmA2);
+    if (p.tma_store) tma_prefetch_desc(&p.tm_out);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -607,6 +618,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int acc = 0;
     uint32_t acc_phase = 0;
     int n_pend = 0;
+    TmaStoreCtx tsc{&p.tm_out, nullptr, s_epi + (warp - 2) * 4096, 0u, 0, 0};
+    TmaStoreCtx* ts = p.tma_store ? &tsc : nullptr;
     if (p.tp_mode == 1 && warp < 6) tp_push_shard(p, tp_epoch);   // warps 2..5: its work split and its named barrier count 128 threads
     for (int t = blockIdx.x; t < total_tiles; t += n_compute) {
       const TileInfo ti = decode_tile(p, t, s_prefix, m_tiles, n_tiles, mn_tiles, tiles_per_batch, kb_total, kb_per_split);
@@ -675,12 +688,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         } else {
-          epilogue_chunk<BN>(p, r, row, ni * BN + c * 32, split, bi);
+          tsc.row0 = ti.row0 + quad * 32;
+          tsc.z = p.group_mode == 1 ? 0 : bi;      // rows-grouped output is one flat matrix; batched / reduction-grouped: one per problem
+          epilogue_chunk<BN>(p, r, row, ni * BN + c * 32, split, bi, nullptr, ts);
         }
       }
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (ts && lane == 0) tma_store_wait_read0();       // the staging buffers stay valid until the last store has read them
     if (n_pend > 0) {
       __threadfence_system();
       __syncwarp();
@@ -926,7 +942,7 @@ gemm_pair_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int part = (warp - 2) >> 2, parts = epi_warps >> 2;      // which share of the unit's columns this warp drains
     int acc = 0;
     uint32_t acc_phase = 0;
-    TmaStoreCtx tsc{&tmC, &tmAux, sC + (warp - 2) * 4096, 0u, 0};
+    TmaStoreCtx tsc{&tmC, &tmAux, sC + (warp - 2) * 4096, 0u, 0, -1};
     TmaStoreCtx* ts = p.tma_store ? &tsc : nullptr;
     for (int u = pair; u < total_units; u += n_pairs) {
       int mi, ni, half;
@@ -1187,6 +1203,26 @@ extern "C" int gemm_pair_probe_read(long long* host, int n) {
 }
 #endif
 
+// Rank-3 store map {cols, rows, problems} with [32 x 32] boxes in the 64-byte swizzle, for the TMA-store epilogue of the
+// single-CTA kernel.  Sets p.tma_store when the output qualifies: bf16, written (not accumulated, not split), no second
+// output, pointer and pitches on 16-byte boundaries.  OA_GEMM_TMA_STORE=0 keeps the per-lane stores.
+static void try_store_map(GemmParams& p, void* out, uint64_t cols, uint64_t rows, uint64_t problems, uint64_t ld, uint64_t problem_stride) {
+  static const bool enabled = []() { const char* e = std::getenv("OA_GEMM_TMA_STORE"); return !(e && (e[0] == '0' || e[0] == 'p')); }();   // "pair": CTA-pair kernel only
+  p.tma_store = 0;
+  if (!enabled || p.out_f32 || p.accumulate || p.splits != 1 || p.aux_out || p.tp_mode) return;
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) return;
+  if (problems <= 1) { problems = 1; problem_stride = ld * rows; }
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || ((ld * 2) & 15) || ((problem_stride * 2) & 15)) return;
+  cuuint64_t dims[3] = {cols, rows, problems};
+  cuuint64_t strides[2] = {ld * 2, problem_stride * 2};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (enc(&p.tm_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+    p.tma_store = 1;
+}
+
 int num_sms() {
   static int n = 0;
   if (!n) {
@@ -1391,6 +1427,7 @@ extern "C" int oa_gemm_bf16_batched(const void* A, const void* B, void* out, int
   if (rc) return rc;
   long long tiles = (long long)batch * ((M + BM - 1) / BM) * ((N + bn - 1) / bn) * p.splits;
   int grid = tiles < sms ? (int)tiles : sms;
+  try_store_map(p, out, (uint64_t)N, (uint64_t)M, (uint64_t)batch, (uint64_t)ldc, (uint64_t)sc_batch);
   int sel = (bn == 256 ? 4 : 0) | (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   switch (sel) {
     case 0: rc = launch_gemm<128, 0, 0>(ta, tb, p, grid, st); break;
@@ -1460,6 +1497,8 @@ extern "C" int oa_gemm_bf16_grouped(int mode, const void* A, const void* B, void
     grid = tiles < sms ? (int)tiles : sms;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  if (mode == 1) try_store_map(p, out, (uint64_t)N, (uint64_t)max_rows, 1, (uint64_t)ldc, 0);
+  else try_store_map(p, out, (uint64_t)N, (uint64_t)M, (uint64_t)groups, (uint64_t)ldc, (uint64_t)sc_batch);
   if (mode == 1) {
     if (bn == 256) rc = b_mn ? launch_gemm<256, 0, 1>(ta, tb, p, grid, st) : launch_gemm<256, 0, 0>(ta, tb, p, grid, st);
     else           rc = b_mn ? launch_gemm<128, 0, 1>(ta, tb, p, grid, st) : launch_gemm<128, 0, 0>(ta, tb, p, grid, st);
