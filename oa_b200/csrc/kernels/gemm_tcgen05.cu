@@ -463,7 +463,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int mn_tiles = m_tiles * n_tiles;
   const int tiles_per_batch = mn_tiles * p.splits;
   int* s_prefix = reinterpret_cast<int*>(smem + STAGES * Cfg::STAGE_BYTES + 256);
-  uint8_t* s_epi = smem + STAGES * Cfg::STAGE_BYTES + 256 + 1280;     // reduce-scatter epilogue staging (4 warps)
+  uint8_t* s_epi = smem + STAGES * Cfg::STAGE_BYTES + 256 + 1280;     // staging: reduce-scatter tiles (4 warps) or TMA-store buffers (8 warps x 2 x 2 KB)
   // reduce-scatter mode only, behind its 18 KB of staging (the TMA-store buffers that share this region are off in that mode);
   // kept out of static shared memory: ring + staging already fill the 227 KB of a CTA to within 512 bytes
   unsigned long long* (*s_pend)[16] = reinterpret_cast<unsigned long long* (*)[16]>(s_epi + 4 * 32 * Cfg::EPI_ROW_BYTES);   // [4][16]: counters of stored tiles not yet published, per epilogue warp
